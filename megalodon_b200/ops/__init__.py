@@ -1,0 +1,144 @@
+"""Operator layer: one functional entry point per operator.
+
+Each function runs the hand-written sm_100a kernel (`ops/cuda_ops.py` over the
+`_C` extension) for CUDA tensors and the plain-PyTorch statement in
+`ops/reference.py` for CPU tensors.  The names follow the reference's
+`megalodon.modules.fused_ops` (fused_ops/__init__.py:1-14) plus the operators
+the reference takes from apex / ATen (norms, linear, cross-entropy, AdamW).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from . import reference
+from ._ext import have_ext, native_for, require as require_ext
+from .dropout import (
+    memory_efficient_dropout,
+    memory_efficient_dropout_fwd,
+    memory_efficient_dropout_bwd,
+)
+
+Tensor = torch.Tensor
+
+
+def _cuda():
+    from . import cuda_ops
+    return cuda_ops
+
+
+# ------------------------------------------------------------------ GEMM-shaped
+def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: Optional[str] = None) -> Tensor:
+    """y = act(x @ w^T + b); `act` is None or "silu"."""
+    if native_for(x):
+        return _cuda().linear(x, w, b, act)
+    return reference.linear(x, w, b, act)
+
+
+def swiglu(a: Tensor, b: Tensor) -> Tensor:
+    if native_for(a):
+        return _cuda().swiglu(a, b)
+    return reference.swiglu(a, b)
+
+
+# ------------------------------------------------------------------ norms
+def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
+    if native_for(x):
+        return _cuda().rms_norm(x, weight, eps)
+    return reference.rms_norm(x, weight, eps)
+
+
+def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float) -> Tensor:
+    if native_for(x):
+        return _cuda().layer_norm(x, weight, bias, eps)
+    return reference.layer_norm(x, weight, bias, eps)
+
+
+def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=None,
+                  num_groups=None, eps: float = 1e-5):
+    """Returns (y, count, mean, var); see `reference.timestep_norm`."""
+    if native_for(x):
+        return _cuda().timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
+                                     padding_mask, num_groups, eps)
+    return reference.timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
+                                   padding_mask, num_groups, eps)
+
+
+def sequence_norm(x, gamma, beta, padding_mask=None, num_groups=None, eps: float = 1e-5,
+                  length_last: bool = False):
+    if native_for(x):
+        return _cuda().sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
+    return reference.sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
+
+
+# ------------------------------------------------------------------ CEMA
+def ema_parameters(p, q, gamma, hx, length: int):
+    if native_for(p):
+        return _cuda().ema_parameters(p, q, gamma, hx, length)
+    return reference.ema_parameters(p, q, gamma, hx, length)
+
+
+def ema_hidden(x, p, q, hx):
+    if native_for(x):
+        return _cuda().ema_hidden(x, p, q, hx)
+    return reference.ema_hidden(x, p, q, hx)
+
+
+def fftconv(x, k):
+    if native_for(x):
+        return _cuda().fftconv(x, k)
+    return reference.fftconv(x, k)
+
+
+def rfft(x, flip: bool = False):
+    if native_for(x):
+        return _cuda().rfft(x, flip)
+    return reference.rfft(x, flip)
+
+
+def cema(x, p, q, gamma, omega, hx, compute_last_state: bool):
+    """Fused complex-EMA layer on channels-last x [B, L, D] -> (y, h_last)."""
+    if native_for(x):
+        return _cuda().cema(x, p, q, gamma, omega, hx, compute_last_state)
+    return reference.cema(x, p, q, gamma, omega, hx, compute_last_state)
+
+
+# ------------------------------------------------------------------ attention
+def attention(q, k, v, scale: float = 1.0, dropout: float = 0.0, use_causal_mask: bool = True,
+              training: bool = True):
+    if native_for(q):
+        return _cuda().attention(q, k, v, scale, dropout, use_causal_mask, training)
+    return reference.attention(q, k, v, scale, dropout, use_causal_mask, training)
+
+
+swift_efficient_attention = attention
+
+
+def attention_softmax(x, dropout: float = 0.0, use_causal_mask: bool = True, training: bool = True):
+    if native_for(x):
+        return _cuda().attention_softmax(x, dropout, use_causal_mask, training)
+    return reference.attention_softmax(x, dropout, use_causal_mask, training)
+
+
+def rotary(x, freqs_cis, conj: bool = False):
+    if native_for(x):
+        return _cuda().rotary(x, freqs_cis, conj)
+    return reference.rotary(x, freqs_cis, conj)
+
+
+# ------------------------------------------------------------------ loss / optimiser
+def cross_entropy(logits, target, weight=None, ignore_index: int = -100, label_smoothing: float = 0.0):
+    """Per-token negative log-likelihood [N]; logits [N, V] in any float dtype."""
+    if native_for(logits) and weight is None and label_smoothing == 0.0:
+        return _cuda().cross_entropy(logits, target, ignore_index)
+    return reference.cross_entropy(logits, target, weight, ignore_index, label_smoothing)
+
+
+def adamw_step(param, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
+               low=None):
+    if native_for(param):
+        return _cuda().adamw_step(param, grad, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                                  weight_decay=weight_decay, step=step, grad_scale=grad_scale, low=low)
+    return reference.adamw_step(param, grad, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
+                                weight_decay=weight_decay, step=step, grad_scale=grad_scale, low=low)

@@ -1,0 +1,633 @@
+"""In-house fully-sharded data parallelism (ZeRO-3) - no fairscale.
+
+Public surface follows the reference's subclass of fairscale's FSDP
+(megalodon/distributed/fairscale_fsdp.py:15-219) and the way the model uses it
+(megalodon/model/mega.py:245-269): nested wrapping (one unit per block plus a
+root unit), `parameters()` yielding the fp32 flat shards that the optimiser
+updates, `clip_grad_norm_`, `grad_all_reduce`, and full / local state dicts.
+
+Design of one unit
+------------------
+* All parameters of the unit live in ONE flat buffer.  Each parameter starts
+  at a multiple of 64 elements (128 B in bf16) so TMA tiles and vector loads
+  of any parameter are aligned; the buffer is padded to a multiple of
+  `world * 64` and cut into `world` equal shards.
+* The fp32 shard is an `nn.Parameter` (`flat_param`): the master weights.
+  A compute-dtype copy of the shard (`flat_param._lowp_shard`) feeds the
+  all-gather; the fused AdamW kernel refreshes it in the same pass that
+  updates the master weights.
+* Forward: all-gather the compute-dtype shards into the full buffer, hand the
+  wrapped module *views* of it, run, optionally free the full buffer
+  (`reshard_after_forward`).  The storage is resized in place so views and
+  tensors saved for backward stay valid once it is re-gathered.
+* Backward: a hook on the unit's outputs re-gathers the parameters if needed;
+  a hook on the flat leaf fires once every parameter gradient of the unit is
+  known and launches the reduce-scatter (on a side stream on GPUs).
+* The gradient shard stays in the reduction dtype (`_grad_shard`).  The fused
+  optimiser reads it directly; for generic optimisers an fp32 `.grad` is
+  materialised (`materialize_fp32_grads`).
+
+Sharding group
+--------------
+`process_group` is the group the parameters are sharded over.  The reference
+shards over the data-parallel group only and replicates across the chunk
+group, summing gradients there in a separate `grad_all_reduce()` call.  Chunk
+ranks process different tokens with the same weights, exactly like
+data-parallel ranks, so this implementation can also shard over the combined
+data x chunk group (`gradient_divide_factor` = data-parallel size keeps the
+reference's scaling: mean over data ranks, sum over chunk ranks); then
+`grad_all_reduce()` has nothing left to do.
+"""
+from __future__ import annotations
+
+import math
+from collections import OrderedDict
+from enum import Enum, auto
+from typing import Any, Dict, Iterator, List, Optional, Tuple, Union
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .utils import all_gather_flat, reduce_scatter_flat
+
+ALIGN = 64
+
+
+class TrainingState(Enum):
+    IDLE = auto()
+    FORWARD = auto()
+    BACKWARD_PRE = auto()
+    BACKWARD_POST = auto()
+
+
+class _ParamInfo:
+    __slots__ = ("name", "shape", "numel", "offset", "owners")
+
+    def __init__(self, name, shape, numel, offset, owners):
+        self.name, self.shape, self.numel, self.offset, self.owners = name, shape, numel, offset, owners
+
+
+def _group_size(group) -> int:
+    if group is None or not (dist.is_available() and dist.is_initialized()):
+        return 1
+    return dist.get_world_size(group)
+
+
+def _group_rank(group) -> int:
+    if group is None or not (dist.is_available() and dist.is_initialized()):
+        return 0
+    return dist.get_rank(group)
+
+
+def calc_grad_norm(grads: List[torch.Tensor], norm_type: float) -> torch.Tensor:
+    """Norm of a list of gradient tensors viewed as one vector (fp32 accumulate)."""
+    grads = [g for g in grads if g is not None]
+    if not grads:
+        return torch.tensor(0.0)
+    if norm_type == math.inf:
+        return torch.stack([g.detach().abs().max().float() for g in grads]).max()
+    parts = torch.stack([torch.linalg.vector_norm(g.detach().float(), norm_type) for g in grads])
+    return torch.linalg.vector_norm(parts, norm_type)
+
+
+class FullyShardedDataParallel(nn.Module):
+    _is_wrapper = True
+
+    def __init__(
+        self,
+        module: nn.Module,
+        process_group: Optional[dist.ProcessGroup] = None,
+        process_group_reduce_scatter: Any = None,
+        model_parallel_process_group: Optional[dist.ProcessGroup] = None,
+        chunk_parallel_process_group: Optional[dist.ProcessGroup] = None,
+        *,
+        compute_dtype: Optional[torch.dtype] = None,
+        mixed_precision: bool = False,
+        flatten_parameters: bool = True,
+        fp32_reduce_scatter: bool = False,
+        reshard_after_forward: bool = True,
+        state_dict_device: Optional[torch.device] = None,
+        bucket_cap_mb: int = 25,
+        buffer_dtype: Optional[torch.dtype] = None,
+        compute_device: Optional[torch.device] = None,
+        move_params_to_cpu: bool = False,
+        move_grads_to_cpu: bool = False,
+        clear_autocast_cache: bool = False,
+        force_input_to_fp32: bool = False,
+        verbose: bool = False,
+        gradient_divide_factor: Optional[float] = None,
+        chunk_group_is_sharded: bool = False,
+        materialize_fp32_grads: bool = True,
+    ):
+        super().__init__()
+        assert flatten_parameters, "only flattened parameters are supported"
+        assert not move_params_to_cpu and not move_grads_to_cpu, "CPU offload is not supported"
+        self.process_group = process_group
+        self.process_group_reduce_scatter = process_group_reduce_scatter or process_group
+        self.model_parallel_process_group = model_parallel_process_group
+        self.model_parallel_world_size = _group_size(model_parallel_process_group)
+        self.chunk_parallel_process_group = chunk_parallel_process_group
+        self.chunk_parallel_world_size = _group_size(chunk_parallel_process_group)
+        self.chunk_group_is_sharded = chunk_group_is_sharded
+        self.world_size = _group_size(process_group)
+        self.rank = _group_rank(process_group)
+        self.mixed_precision = mixed_precision
+        self.compute_dtype = (compute_dtype or torch.float32) if mixed_precision else torch.float32
+        self.buffer_dtype = buffer_dtype or self.compute_dtype
+        self.fp32_reduce_scatter = fp32_reduce_scatter
+        self.reshard_after_forward = reshard_after_forward and self.world_size > 1
+        self.flatten_parameters = True
+        self.state_dict_device = state_dict_device
+        self.bucket_cap_mb = bucket_cap_mb
+        self.move_params_to_cpu = False
+        self.move_grads_to_cpu = False
+        self.clear_autocast_cache = clear_autocast_cache
+        self.force_input_to_fp32 = force_input_to_fp32
+        self.verbose = verbose
+        self.materialize_fp32_grads = materialize_fp32_grads
+        self.gradient_divide_factor = float(gradient_divide_factor if gradient_divide_factor is not None
+                                            else self.world_size)
+        self.training_state = TrainingState.IDLE
+        self._is_root: Optional[bool] = None
+        self._wrapped = module
+        self._comm_stream = None
+        self._pending: List[Any] = []
+
+        self._flatten(module, compute_device)
+        self.compute_device = self.flat_param.device
+        self._full: Optional[torch.Tensor] = None          # gathered compute-dtype buffer
+        self._full_leaf: Optional[torch.Tensor] = None
+        self._full_version = -1
+        self._bwd_hook_armed = False
+
+    # ------------------------------------------------------------------ construction
+    def _flatten(self, module: nn.Module, device: Optional[torch.device]) -> None:
+        infos: List[_ParamInfo] = []
+        by_id: Dict[int, _ParamInfo] = {}
+        offset = 0
+        datas: List[torch.Tensor] = []
+        for mod_name, mod in module.named_modules():
+            if isinstance(mod, FullyShardedDataParallel):
+                continue
+            if self._inside_child_unit(module, mod_name):
+                continue
+            for pname, p in list(mod._parameters.items()):
+                if p is None:
+                    continue
+                full_name = _clean_name(f"{mod_name}.{pname}" if mod_name else pname)
+                if id(p) in by_id:
+                    by_id[id(p)].owners.append((mod, pname, full_name))
+                    continue
+                info = _ParamInfo(full_name, tuple(p.shape), p.numel(), offset, [(mod, pname, full_name)])
+                by_id[id(p)] = info
+                infos.append(info)
+                datas.append(p.detach())
+                offset += -(-p.numel() // ALIGN) * ALIGN
+        self._infos = infos
+        world = self.world_size
+        quantum = world * ALIGN
+        self._numel_padded = max(quantum, -(-offset // quantum) * quantum)
+        self._shard_numel = self._numel_padded // world
+        if device is None:
+            device = datas[0].device if datas else torch.device("cpu")
+        lo = self.rank * self._shard_numel
+        hi = lo + self._shard_numel
+        shard = torch.zeros(self._shard_numel, dtype=torch.float32, device=device)
+        for info, d in zip(infos, datas):
+            a, b = max(info.offset, lo), min(info.offset + info.numel, hi)
+            if a < b:
+                shard[a - lo:b - lo].copy_(d.reshape(-1)[a - info.offset:b - info.offset])
+        self.flat_param = nn.Parameter(shard)
+        self.flat_param._fsdp_unit = self
+        self.flat_param._grad_shard = None
+        self.flat_param._lowp_shard = None
+        self.flat_param._lowp_version = -1
+        # the wrapped modules give up their Parameters; they get views each forward
+        for info in infos:
+            for mod, pname, _ in info.owners:
+                del mod._parameters[pname]
+                setattr(mod, pname, None)
+        if self.mixed_precision:
+            # buffers follow the compute dtype like the reference's `model.to(dtype)` path
+            for b_name, buf in list(module.named_buffers()):
+                if buf.is_floating_point() and not self._inside_child_unit(module, b_name.rpartition(".")[0]):
+                    buf.data = buf.data.to(self.buffer_dtype)
+
+    @staticmethod
+    def _inside_child_unit(root: nn.Module, mod_name: str) -> bool:
+        if not mod_name:
+            return False
+        cur = root
+        for part in mod_name.split("."):
+            cur = cur._modules[part]
+            if isinstance(cur, FullyShardedDataParallel):
+                return True
+        return False
+
+    def __getattr__(self, name: str) -> Any:
+        try:
+            return super().__getattr__(name)
+        except AttributeError:
+            return getattr(self._modules["_wrapped"], name)
+
+    @property
+    def module(self) -> nn.Module:
+        return self._wrapped
+
+    # ------------------------------------------------------------------ unit tree
+    def _units(self) -> List["FullyShardedDataParallel"]:
+        return [m for m in self.modules() if isinstance(m, FullyShardedDataParallel)]
+
+    def _lazy_init(self) -> None:
+        if self._is_root is not None:
+            return
+        self._is_root = True
+        for u in self._units():
+            if u is not self:
+                u._is_root = False
+                u._root = self
+        self._root = self
+        if self.compute_device.type == "cuda" and self.world_size > 1:
+            self._comm_stream = torch.cuda.Stream(self.compute_device)
+
+    @property
+    def children_share_process_group(self) -> bool:
+        return all(u.process_group is self.process_group for u in self._units())
+
+    def assert_state(self, state: TrainingState) -> None:
+        if self.training_state != state:
+            raise AssertionError(f"expected FSDP state {state}, got {self.training_state}")
+
+    @property
+    def params_with_grad(self) -> List[nn.Parameter]:
+        out = []
+        for u in self._units():
+            p = u.flat_param
+            if p.grad is not None or p._grad_shard is not None:
+                out.append(p)
+        return out
+
+    # ------------------------------------------------------------------ gather / free
+    def _lowp_shard(self) -> torch.Tensor:
+        p = self.flat_param
+        if not self.mixed_precision:
+            return p.data
+        if p._lowp_shard is None:
+            p._lowp_shard = torch.empty(self._shard_numel, dtype=self.compute_dtype, device=p.device)
+            p._lowp_version = -1
+        if p._lowp_version != _ver(p):
+            p._lowp_shard.copy_(p.data)
+            p._lowp_version = _ver(p)
+        return p._lowp_shard
+
+    def _full_is_valid(self) -> bool:
+        return (self._full is not None and self._full.untyped_storage().size() > 0
+                and self._full_version == _ver(self.flat_param))
+
+    def _gather_full(self) -> None:
+        """Make `self._full` hold every parameter of the unit in compute dtype."""
+        shard = self._lowp_shard()
+        if self.world_size == 1:
+            if self._full is None or self._full.data_ptr() != shard.data_ptr():
+                self._full = shard
+            self._full_version = _ver(self.flat_param)
+            return
+        if self._full is None:
+            self._full = torch.empty(self._numel_padded, dtype=shard.dtype, device=shard.device)
+        elif self._full.untyped_storage().size() == 0:
+            self._full.untyped_storage().resize_(self._numel_padded * self._full.element_size())
+        # write through `.data`: the re-gather before backward must not bump the
+        # autograd version counter shared with the views handed to the module
+        all_gather_flat(self._full.data, shard, self.process_group)
+        self._full_version = _ver(self.flat_param)
+
+    def _free_full(self) -> None:
+        if self.world_size > 1 and self._full is not None:
+            self._full.untyped_storage().resize_(0)
+
+    def _set_views(self, leaf: torch.Tensor) -> None:
+        sizes = []
+        for i, info in enumerate(self._infos):
+            nxt = self._infos[i + 1].offset if i + 1 < len(self._infos) else self._numel_padded
+            sizes.append(nxt - info.offset)
+        chunks = torch.split(leaf, sizes)
+        for info, c in zip(self._infos, chunks):
+            v = c[:info.numel].view(info.shape)
+            for mod, pname, _ in info.owners:
+                mod.__dict__[pname] = v
+
+    # ------------------------------------------------------------------ forward / backward
+    def forward(self, *args, **kwargs):
+        self._lazy_init()
+        p = self.flat_param
+        if not self._full_is_valid():
+            self._gather_full()
+        want_grad = torch.is_grad_enabled() and p.requires_grad
+        if want_grad:
+            leaf = self._full.detach().requires_grad_(True)
+            leaf.register_post_accumulate_grad_hook(self._post_backward)
+            self._full_leaf = leaf
+        else:
+            leaf = self._full
+        self._set_views(leaf)
+        self.training_state = TrainingState.FORWARD
+        out = self._wrapped(*args, **kwargs)
+        self.training_state = TrainingState.IDLE
+        if self.reshard_after_forward and not self._is_root:
+            self._free_full()
+            if want_grad:
+                out = self._arm_pre_backward(out)
+        return out
+
+    def _arm_pre_backward(self, out):
+        self._bwd_hook_armed = True
+
+        def pre_backward(grad):
+            if self._bwd_hook_armed:
+                self._bwd_hook_armed = False
+                if not self._full_is_valid():
+                    self._gather_full()
+            return grad
+
+        def visit(o):
+            if isinstance(o, torch.Tensor) and o.requires_grad:
+                o.register_hook(pre_backward)
+            elif isinstance(o, (tuple, list)):
+                for x in o:
+                    visit(x)
+        visit(out)
+        return out
+
+    def _post_backward(self, leaf: torch.Tensor):
+        """Runs once the gradient of the unit's whole flat buffer is known."""
+        flat_grad = leaf.grad
+        leaf.grad = None
+        p = self.flat_param
+        red_dtype = torch.float32 if (self.fp32_reduce_scatter or not self.mixed_precision) else self.compute_dtype
+        g = flat_grad if flat_grad.dtype == red_dtype else flat_grad.to(red_dtype)
+        if self.world_size > 1:
+            if self.gradient_divide_factor != 1.0:
+                g = g / self.gradient_divide_factor
+            shard = torch.empty(self._shard_numel, dtype=red_dtype, device=g.device)
+            root = self._root
+            if root._comm_stream is not None:
+                root._comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(root._comm_stream):
+                    reduce_scatter_flat(shard, g, self.process_group_reduce_scatter)
+                g.record_stream(root._comm_stream)
+                shard.record_stream(root._comm_stream)
+                root._pending.append(True)
+            else:
+                reduce_scatter_flat(shard, g, self.process_group_reduce_scatter)
+        else:
+            shard = g
+            if self.gradient_divide_factor != 1.0:
+                shard = shard / self.gradient_divide_factor
+        if p._grad_shard is None:
+            p._grad_shard = shard
+        else:
+            self._sync_comm()
+            p._grad_shard = p._grad_shard + shard
+        if self.reshard_after_forward and not self._is_root:
+            self._free_full()
+        self._full_leaf = None
+        return None
+
+    def _sync_comm(self) -> None:
+        root = getattr(self, "_root", self)
+        if root._comm_stream is not None and root._pending:
+            torch.cuda.current_stream().wait_stream(root._comm_stream)
+            root._pending.clear()
+
+    def finish_backward(self) -> None:
+        """Wait for outstanding reduce-scatters and (optionally) expose fp32
+        `.grad` on the flat parameters.  Called by every public method that
+        reads gradients; safe to call more than once."""
+        self._lazy_init()
+        self._sync_comm()
+        if self.materialize_fp32_grads:
+            for u in self._units():
+                p = u.flat_param
+                if p._grad_shard is not None:
+                    g32 = p._grad_shard.float()
+                    p.grad = g32 if p.grad is None else p.grad + g32
+                    p._grad_shard = None
+
+    def _grad_tensors(self) -> List[torch.Tensor]:
+        out = []
+        for u in self._units():
+            p = u.flat_param
+            if p._grad_shard is not None:
+                out.append(p._grad_shard)
+            if p.grad is not None:
+                out.append(p.grad)
+        return out
+
+    # ------------------------------------------------------------------ public gradient API
+    @torch.no_grad()
+    def grad_all_reduce(self) -> None:
+        """Sum gradients over the chunk-parallel group.  Must be called after
+        backward when the chunk group holds replicas (reference semantics).  A
+        no-op when the chunk group is part of the sharding group."""
+        self._lazy_init()
+        assert self._is_root, "grad_all_reduce should only be called on the root (parent) instance"
+        self.assert_state(TrainingState.IDLE)
+        self.finish_backward()
+        if self.chunk_parallel_world_size == 1 or self.chunk_group_is_sharded:
+            return
+        for g in self._grad_tensors():
+            dist.all_reduce(g, group=self.chunk_parallel_process_group)
+
+    @torch.no_grad()
+    def clip_grad_norm_(self, max_norm: Union[float, int], norm_type: Union[float, int] = 2.0) -> torch.Tensor:
+        """Clip the global gradient norm (over the sharding group and the
+        model-parallel group) to `max_norm`; returns the norm before clipping."""
+        self._lazy_init()
+        assert self._is_root, "clip_grad_norm should only be called on the root (parent) instance"
+        self.assert_state(TrainingState.IDLE)
+        self.finish_backward()
+        max_norm, norm_type = float(max_norm), float(norm_type)
+        grads = self._grad_tensors()
+        dev = self.compute_device
+        local = calc_grad_norm(grads, norm_type).to(dev)
+        if norm_type == math.inf:
+            total = local
+            if self.world_size > 1:
+                dist.all_reduce(total, op=dist.ReduceOp.MAX, group=self.process_group)
+            if self.model_parallel_world_size > 1:
+                dist.all_reduce(total, op=dist.ReduceOp.MAX, group=self.model_parallel_process_group)
+        else:
+            total = local ** norm_type
+            if self.world_size > 1:
+                dist.all_reduce(total, group=self.process_group)
+            if self.model_parallel_world_size > 1:
+                dist.all_reduce(total, group=self.model_parallel_process_group)
+            total = total ** (1.0 / norm_type)
+        coef = max_norm / (total + 1e-6)
+        if coef < 1:
+            for g in grads:
+                g.mul_(coef.to(g.dtype))
+        return total
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for u in self._units():
+            u.flat_param.grad = None
+            u.flat_param._grad_shard = None
+
+    # ------------------------------------------------------------------ state dicts
+    def _unit_prefixes(self) -> List[Tuple[str, "FullyShardedDataParallel"]]:
+        out = []
+        for name, m in self.named_modules():
+            if isinstance(m, FullyShardedDataParallel):
+                out.append((_clean_name(name), m))
+        return out
+
+    @torch.no_grad()
+    def _full_fp32(self) -> torch.Tensor:
+        shard = self.flat_param.data
+        if self.world_size == 1:
+            return shard
+        full = torch.empty(self._numel_padded, dtype=shard.dtype, device=shard.device)
+        all_gather_flat(full, shard.contiguous(), self.process_group)
+        return full
+
+    @torch.no_grad()
+    def state_dict(self, *args, **kwargs) -> "OrderedDict[str, torch.Tensor]":
+        """Full (unsharded, unflattened) fp32 state dict under the wrapped
+        model's own parameter names; every rank of the sharding group must call
+        it.  Tensors are moved to `state_dict_device` when that is set."""
+        self._lazy_init()
+        sd: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+        dev = self.state_dict_device
+        for prefix, unit in self._unit_prefixes():
+            full = unit._full_fp32()
+            for info in unit._infos:
+                t = full[info.offset:info.offset + info.numel].view(info.shape).clone()
+                t = t.to(dev) if dev is not None else t
+                for _, _, name in info.owners:
+                    sd[f"{prefix}.{name}" if prefix else name] = t
+        for name, buf in self._wrapped.named_buffers():
+            owner = self._wrapped
+            parts = name.split(".")
+            for part in parts[:-1]:
+                owner = owner._modules[part]
+            if parts[-1] in owner._non_persistent_buffers_set:
+                continue
+            sd[_clean_name(name)] = buf.detach().clone().to(dev) if dev is not None else buf.detach().clone()
+        return sd
+
+    @torch.no_grad()
+    def load_state_dict(self, state_dict: Dict[str, torch.Tensor], strict: bool = True):
+        """Load a full state dict (every rank passes the same dict)."""
+        self._lazy_init()
+        missing, used = [], set()
+        for prefix, unit in self._unit_prefixes():
+            lo = unit.rank * unit._shard_numel
+            hi = lo + unit._shard_numel
+            for info in unit._infos:
+                src = None
+                for _, _, name in info.owners:
+                    key = f"{prefix}.{name}" if prefix else name
+                    if key in state_dict:
+                        src = state_dict[key]
+                        used.add(key)
+                if src is None:
+                    missing.append(f"{prefix}.{info.name}" if prefix else info.name)
+                    continue
+                assert tuple(src.shape) == info.shape, (info.name, tuple(src.shape), info.shape)
+                a, b = max(info.offset, lo), min(info.offset + info.numel, hi)
+                if a < b:
+                    unit.flat_param.data[a - lo:b - lo].copy_(
+                        src.reshape(-1)[a - info.offset:b - info.offset].to(unit.flat_param.device))
+            unit.flat_param._master_version = getattr(unit.flat_param, "_master_version", 0) + 1
+        bufs = dict(self._wrapped.named_buffers())
+        for name, buf in bufs.items():
+            key = _clean_name(name)
+            if key in state_dict:
+                buf.copy_(state_dict[key].to(buf.device))
+                used.add(key)
+        unexpected = [k for k in state_dict if k not in used]
+        if strict and (missing or unexpected):
+            raise RuntimeError(f"load_state_dict: missing={missing} unexpected={unexpected}")
+        return nn.modules.module._IncompatibleKeys(missing, unexpected)
+
+    @torch.no_grad()
+    def local_state_dict(self) -> Dict[str, Any]:
+        """This rank's shards only (no communication): the sharded-checkpoint payload."""
+        self._lazy_init()
+        out: Dict[str, Any] = {"shards": OrderedDict(), "meta": OrderedDict(), "buffers": OrderedDict()}
+        for prefix, unit in self._unit_prefixes():
+            key = prefix or "_root"
+            out["shards"][key] = unit.flat_param.detach().cpu().clone()
+            out["meta"][key] = {
+                "world_size": unit.world_size, "rank": unit.rank, "numel_padded": unit._numel_padded,
+                "params": [(i.name, list(i.shape), i.offset) for i in unit._infos],
+            }
+        for name, buf in self._wrapped.named_buffers():
+            out["buffers"][_clean_name(name)] = buf.detach().cpu().clone()
+        return out
+
+    @torch.no_grad()
+    def load_local_state_dict(self, payload: Dict[str, Any]) -> None:
+        self._lazy_init()
+        for prefix, unit in self._unit_prefixes():
+            key = prefix or "_root"
+            meta = payload["meta"][key]
+            assert meta["world_size"] == unit.world_size and meta["rank"] == unit.rank, \
+                "sharded checkpoint was written with a different sharding layout"
+            unit.flat_param.data.copy_(payload["shards"][key].to(unit.flat_param.device))
+            unit.flat_param._master_version = getattr(unit.flat_param, "_master_version", 0) + 1
+        bufs = dict(self._wrapped.named_buffers())
+        for name, buf in bufs.items():
+            key = _clean_name(name)
+            if key in payload["buffers"]:
+                buf.copy_(payload["buffers"][key].to(buf.device))
+
+    def extra_repr(self) -> str:
+        return (f"world_size=({self.world_size}, {self.chunk_parallel_world_size}, "
+                f"{self.model_parallel_world_size}), flatten_parameters={self.flatten_parameters}, "
+                f"mixed_precision={self.mixed_precision}, compute_dtype={self.compute_dtype}, "
+                f"fp32_reduce_scatter={self.fp32_reduce_scatter}, "
+                f"reshard_after_forward={self.reshard_after_forward}")
+
+
+def _ver(p: torch.Tensor):
+    """Version of the master shard: autograd's counter (in-place updates by
+    ordinary optimisers) plus a counter bumped by writers that go through
+    `.data` (the fused optimiser, checkpoint loading)."""
+    return (p._version, getattr(p, "_master_version", 0))
+
+
+def _clean_name(name: str) -> str:
+    """Drop wrapper path segments so names match the unwrapped model's."""
+    return ".".join(p for p in name.split(".") if p not in ("_wrapped",))
+
+
+# ---------------------------------------------------------------------- auto-wrap context
+_WRAP_STATE: Dict[str, Any] = {"cls": None, "kwargs": None}
+
+
+class enable_wrap:
+    """Inside this context `wrap(module)` wraps with the given class/kwargs;
+    outside it `wrap` is the identity (same contract as fairscale's)."""
+
+    def __init__(self, wrapper_cls=FullyShardedDataParallel, **kwargs):
+        self.cls, self.kwargs = wrapper_cls, kwargs
+
+    def __enter__(self):
+        self.prev = dict(_WRAP_STATE)
+        _WRAP_STATE["cls"], _WRAP_STATE["kwargs"] = self.cls, self.kwargs
+        return self
+
+    def __exit__(self, *exc):
+        _WRAP_STATE.update(self.prev)
+        return False
+
+
+def wrap(module: nn.Module, **overrides) -> nn.Module:
+    if _WRAP_STATE["cls"] is None:
+        return module
+    kwargs = dict(_WRAP_STATE["kwargs"])
+    kwargs.update(overrides)
+    return _WRAP_STATE["cls"](module, **kwargs)

@@ -1,0 +1,115 @@
+"""N-rank result == 1-rank result for forward, loss, gradient norm and one
+AdamW step, over data / chunk / model parallel layouts on CPU (gloo)."""
+import pytest
+import torch
+
+from dist_utils import run_ranks
+
+
+def _tiny_cfg(**kw):
+    from megalodon_b200.config import ModelConf
+    base = dict(num_layers=2, model_dim=64, num_heads=2, z_dim=32, value_dim=128, ffn_hidden_dim=128,
+                cema_ndim=4, chunk_size=16, vocab_size=96, swiglu=True, norm_num_groups=8)
+    base.update(kw)
+    return ModelConf(**base)
+
+
+def _train_steps(rank, world, mp, cp, cfg_kw, shard_cp, steps, dtype):
+    import torch.distributed as dist
+    from megalodon_b200.parallel import initialize_model_parallel, get_data_parallel_rank, \
+        get_data_parallel_world_size
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.optim import build_optimizer
+    from megalodon_b200.config import OptimConf
+    from megalodon_b200.modules.losses import cross_entropy
+    from megalodon_b200.utils import clip_grad_norm_, set_random_seed
+    if world > 1 or mp * cp > 1:
+        initialize_model_parallel(mp, cp)
+    set_random_seed(1234)
+    cfg = _tiny_cfg(**cfg_kw)
+    model = build_model(cfg, dtype, False, True, shard_over_chunk_group=shard_cp)
+    opt, sched = build_optimizer(model, OptimConf(lr=1e-2, warmup=1, weight_decay=0.1), 10, dtype)
+    g = torch.Generator().manual_seed(7)
+    dp = get_data_parallel_world_size()
+    all_toks = torch.randint(0, cfg.vocab_size, (4, 65), generator=g)
+    per = 4 // dp
+    toks = all_toks[get_data_parallel_rank() * per:(get_data_parallel_rank() + 1) * per]
+    x, y = toks[:, :-1], toks[:, 1:]
+    out = []
+    for _ in range(steps):
+        pred, _ = model(x)
+        loss = cross_entropy(pred, y).mean()
+        loss.backward()
+        model.grad_all_reduce()
+        norm = clip_grad_norm_(model, 1.0)
+        opt.step(); sched.step(); opt.zero_grad()
+        lsum = loss.detach().clone()
+        if dp > 1:
+            from megalodon_b200.parallel import get_data_parallel_group
+            dist.all_reduce(lsum, group=get_data_parallel_group())
+            lsum /= dp
+        out.append((lsum.item(), float(norm)))
+    sd = model.state_dict()
+    return out, {k: v.float() for k, v in sd.items()}
+
+
+def _gather_mp(states, key, mp):
+    """Concatenate model-parallel slices of `key` (first mp ranks = one replica)."""
+    parts = [states[r][key] for r in range(mp)]
+    if parts[0].dim() == 0 or ".rmsnorm." in key or ".nffn.norm." in key:
+        return parts[0]
+    col = ("wv.weight", "wz.weight", "wr.weight", "wh1.weight", "fc1.weight", "fc3.weight")
+    row = ("wh2.weight", "fc2.weight", "embed.weight", "output.output.weight")
+    if key.endswith(col):
+        return torch.cat(parts, 0)
+    if key.endswith(row):
+        return torch.cat(parts, 1)
+    if key.endswith(("gamma", "beta")) and parts[0].dim() == 2 and ".mega." in key and "cema" not in key:
+        return torch.cat(parts, 1)
+    return torch.cat(parts, 0)
+
+
+LAYOUTS = [
+    # world, mp, cp, shard_over_cp
+    (2, 1, 1, False),     # dp = 2
+    (2, 1, 2, False),     # cp = 2, replicated + grad_all_reduce
+    (2, 1, 2, True),      # cp = 2, sharded over the chunk group
+    (2, 2, 1, False),     # mp = 2
+    (4, 1, 4, False),     # cp = 4
+    (4, 2, 2, False),     # mp = 2 x cp = 2
+    (4, 1, 2, True),      # dp = 2 x cp = 2 sharded over both
+]
+
+
+@pytest.fixture(scope="module")
+def baseline():
+    res = run_ranks(_train_steps, 1, 1, 1, {}, False, 2, "fp32")
+    return res[0]
+
+
+@pytest.mark.parametrize("world,mp,cp,shard_cp", LAYOUTS)
+def test_layout_matches_single_rank(baseline, world, mp, cp, shard_cp):
+    base_curve, base_state = baseline
+    res = run_ranks(_train_steps, world, mp, cp, {}, shard_cp, 2, "fp32")
+    curve = res[0][0]
+    for (l0, n0), (l1, n1) in zip(base_curve, curve):
+        assert abs(l0 - l1) < 2e-4 * max(1.0, abs(l0)), (base_curve, curve)
+        assert abs(n0 - n1) < 2e-3 * max(1.0, abs(n0)), (base_curve, curve)
+    states = [r[1] for r in res]
+    for key, ref in base_state.items():
+        if key == "rope.freqs":
+            continue
+        got = _gather_mp(states, key, mp) if mp > 1 else states[0][key]
+        assert got.shape == ref.shape, (key, got.shape, ref.shape)
+        assert torch.allclose(got, ref, atol=2e-4, rtol=2e-3), (key, (got - ref).abs().max())
+
+
+def test_checkpointing_and_bf16_run():
+    res = run_ranks(_train_steps, 2, 1, 2, {"layerwise_ckpt": True}, False, 2, "fp32")
+    base = run_ranks(_train_steps, 1, 1, 1, {}, False, 2, "fp32")
+    for (l0, n0), (l1, n1) in zip(base[0][0], res[0][0]):
+        assert abs(l0 - l1) < 2e-4 * max(1.0, abs(l0))
+        assert abs(n0 - n1) < 2e-3 * max(1.0, abs(n0))
+    res16 = run_ranks(_train_steps, 2, 1, 1, {}, False, 2, "bf16")
+    assert all(torch.isfinite(torch.tensor(l)) for l, _ in res16[0][0])
+    assert abs(res16[0][0][0][0] - base[0][0][0][0]) < 0.1
