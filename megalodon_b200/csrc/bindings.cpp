@@ -1,0 +1,382 @@
+// Python bindings: tensor checks, output allocation and stream selection around
+// the raw-pointer launchers in kernels.h.  The extension module is
+// `megalodon_b200._C`.
+#include <ATen/cuda/CUDAContext.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <torch/extension.h>
+
+#include <optional>
+#include <tuple>
+#include <vector>
+
+#include "kernels.h"
+
+namespace {
+
+using torch::Tensor;
+using OptTensor = std::optional<Tensor>;
+
+int dtype_code(const Tensor& t) {
+  switch (t.scalar_type()) {
+    case at::kFloat: return 0;
+    case at::kBFloat16: return 1;
+    case at::kHalf: return 2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t.scalar_type());
+  }
+  return -1;
+}
+
+void check_cuda_contig(const Tensor& t, const char* name) {
+  TORCH_CHECK(t.is_cuda(), name, " must be a CUDA tensor");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
+int weight_code(const Tensor& x, const Tensor& w) {
+  TORCH_CHECK(w.scalar_type() == at::kFloat || w.scalar_type() == x.scalar_type(),
+              "weight dtype must be fp32 or the activation dtype");
+  return dtype_code(w);
+}
+
+cudaStream_t stream() { return at::cuda::getCurrentCUDAStream().stream(); }
+
+const void* opt_ptr(const OptTensor& t) { return t.has_value() ? t->data_ptr() : nullptr; }
+
+// ------------------------------------------------------------------ norms
+std::tuple<Tensor, Tensor> rms_norm_fwd(const Tensor& x, const OptTensor& w, double w_off, double eps) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1);
+  const long long M = x.numel() / D;
+  TORCH_CHECK(D <= 8192, "rms_norm: last dim > 8192 is not supported");
+  Tensor y = torch::empty_like(x);
+  Tensor rstd = torch::empty({M}, x.options().dtype(at::kFloat));
+  int wc = 0;
+  if (w.has_value()) { check_cuda_contig(*w, "weight"); wc = weight_code(x, *w); }
+  mb::rms_norm_fwd(x.data_ptr(), opt_ptr(w), (float)w_off, y.data_ptr(), rstd.data_ptr<float>(), M, D,
+                   (float)eps, dtype_code(x), wc, stream());
+  return {y, rstd};
+}
+
+std::tuple<Tensor, OptTensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, const OptTensor& w, double w_off,
+                                           const Tensor& rstd) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1);
+  const long long M = x.numel() / D;
+  Tensor dx = torch::empty_like(x);
+  OptTensor dw;
+  int wc = 0;
+  if (w.has_value()) {
+    dw = torch::zeros({D}, x.options().dtype(at::kFloat));
+    wc = weight_code(x, *w);
+  }
+  mb::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), opt_ptr(w), (float)w_off, rstd.data_ptr<float>(), dx.data_ptr(),
+                   dw.has_value() ? dw->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream());
+  return {dx, dw};
+}
+
+std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const OptTensor& w, const OptTensor& b,
+                                                  double w_off, double eps) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1);
+  const long long M = x.numel() / D;
+  TORCH_CHECK(D <= 8192, "layer_norm: last dim > 8192 is not supported");
+  Tensor y = torch::empty_like(x);
+  Tensor mean = torch::empty({M}, x.options().dtype(at::kFloat));
+  Tensor rstd = torch::empty({M}, x.options().dtype(at::kFloat));
+  int wc = 0;
+  if (w.has_value()) { wc = weight_code(x, *w); }
+  if (b.has_value()) { TORCH_CHECK(w.has_value() && b->scalar_type() == w->scalar_type(), "bias/weight dtype"); }
+  mb::layer_norm_fwd(x.data_ptr(), opt_ptr(w), opt_ptr(b), (float)w_off, y.data_ptr(), mean.data_ptr<float>(),
+                     rstd.data_ptr<float>(), M, D, (float)eps, dtype_code(x), wc, stream());
+  return {y, mean, rstd};
+}
+
+std::tuple<Tensor, OptTensor, OptTensor> layer_norm_bwd(const Tensor& dy, const Tensor& x, const OptTensor& w,
+                                                        double w_off, const Tensor& mean, const Tensor& rstd) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int D = x.size(-1);
+  const long long M = x.numel() / D;
+  Tensor dx = torch::empty_like(x);
+  OptTensor dw, db;
+  int wc = 0;
+  if (w.has_value()) {
+    dw = torch::zeros({D}, x.options().dtype(at::kFloat));
+    db = torch::zeros({D}, x.options().dtype(at::kFloat));
+    wc = weight_code(x, *w);
+  }
+  mb::layer_norm_bwd(dy.data_ptr(), x.data_ptr(), opt_ptr(w), (float)w_off, mean.data_ptr<float>(),
+                     rstd.data_ptr<float>(), dx.data_ptr(), dw.has_value() ? dw->data_ptr<float>() : nullptr,
+                     db.has_value() ? db->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream());
+  return {dx, dw, db};
+}
+
+// ------------------------------------------------------------------ TimestepNorm
+// returns y, count, mean, var, cummean, cumrstd
+std::vector<Tensor> timestep_norm_fwd(const Tensor& x, const Tensor& prev_count, const Tensor& prev_mean,
+                                      const Tensor& prev_var, const Tensor& gamma, double gamma_off,
+                                      const Tensor& beta, const OptTensor& mask, int64_t G, double eps) {
+  check_cuda_contig(x, "x");
+  check_cuda_contig(prev_mean, "prev_mean");
+  check_cuda_contig(prev_var, "prev_var");
+  check_cuda_contig(gamma, "gamma");
+  check_cuda_contig(beta, "beta");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(x.dim() == 3, "x must be [B, L, H]");
+  const int B = x.size(0), L = x.size(1), H = x.size(2);
+  TORCH_CHECK(H % G == 0 && H <= 8192, "bad feature/group sizes");
+  TORCH_CHECK(prev_count.scalar_type() == at::kLong && prev_count.is_contiguous());
+  TORCH_CHECK(prev_mean.scalar_type() == x.scalar_type() && prev_var.scalar_type() == x.scalar_type());
+  TORCH_CHECK(gamma.scalar_type() == beta.scalar_type());
+  if (mask.has_value()) TORCH_CHECK(mask->scalar_type() == at::kBool && mask->is_contiguous());
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor y = torch::empty_like(x);
+  Tensor count = torch::empty_like(prev_count);
+  Tensor mean = torch::empty_like(prev_mean);
+  Tensor var = torch::empty_like(prev_var);
+  Tensor cummean = torch::empty({B, L, G}, f32);
+  Tensor cumrstd = torch::empty({B, L, G}, f32);
+  Tensor gu = torch::empty({B, L, G}, f32);
+  Tensor gv = torch::empty({B, L, G}, f32);
+  mb::timestep_norm_fwd(x.data_ptr(), (const long long*)prev_count.data_ptr<int64_t>(), prev_mean.data_ptr(),
+                        prev_var.data_ptr(), gamma.data_ptr(), (float)gamma_off, beta.data_ptr(),
+                        mask.has_value() ? mask->data_ptr<bool>() : nullptr, y.data_ptr(),
+                        (long long*)count.data_ptr<int64_t>(), mean.data_ptr(), var.data_ptr(),
+                        cummean.data_ptr<float>(), cumrstd.data_ptr<float>(), gu.data_ptr<float>(),
+                        gv.data_ptr<float>(), B, L, H, (int)G, (float)eps, dtype_code(x), weight_code(x, gamma),
+                        stream());
+  return {y, count, mean, var, cummean, cumrstd};
+}
+
+// returns dx, dprev_mean, dprev_var, dgamma(fp32), dbeta(fp32)
+std::vector<Tensor> timestep_norm_bwd(const Tensor& dy, const Tensor& dmean, const Tensor& dvar, const Tensor& x,
+                                      const Tensor& prev_mean, const Tensor& count, const Tensor& cummean,
+                                      const Tensor& cumrstd, const Tensor& gamma, double gamma_off,
+                                      const OptTensor& mask, int64_t G) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(x, "x");
+  check_cuda_contig(dmean, "dmean");
+  check_cuda_contig(dvar, "dvar");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int B = x.size(0), L = x.size(1), H = x.size(2);
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dx = torch::empty_like(x);
+  Tensor dpm = torch::empty_like(prev_mean);
+  Tensor dpv = torch::empty_like(prev_mean);
+  Tensor dgamma = torch::zeros({H}, f32);
+  Tensor dbeta = torch::zeros({H}, f32);
+  Tensor scratch = torch::empty({5, B, L, G}, f32);
+  float* sp = scratch.data_ptr<float>();
+  const long long n = (long long)B * L * G;
+  mb::timestep_norm_bwd(dy.data_ptr(), dmean.data_ptr(), dvar.data_ptr(), x.data_ptr(), prev_mean.data_ptr(),
+                        (const long long*)count.data_ptr<int64_t>(), cummean.data_ptr<float>(),
+                        cumrstd.data_ptr<float>(), gamma.data_ptr(), (float)gamma_off,
+                        mask.has_value() ? mask->data_ptr<bool>() : nullptr, dx.data_ptr(), dpm.data_ptr(),
+                        dpv.data_ptr(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), sp, sp + n, sp + 2 * n,
+                        sp + 3 * n, sp + 4 * n, B, L, H, (int)G, dtype_code(x), weight_code(x, gamma), stream());
+  return {dx, dpm, dpv, dgamma, dbeta};
+}
+
+// ------------------------------------------------------------------ CEMA
+// p [D,N] f32, q/gamma [D,N,2] f32, omega [D] f32, hx [B,D,N,2] f32 or none
+std::tuple<Tensor, OptTensor> cema_fwd(const Tensor& x, const Tensor& p, const Tensor& q, const Tensor& gamma,
+                                       const Tensor& omega, const OptTensor& hx, bool want_last) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int B = x.size(0), L = x.size(1), D = x.size(2), N = p.size(1);
+  TORCH_CHECK(mb::cema_supported_ndim(N), "cema: ndim must be one of 1,2,4,8,16,32");
+  for (const Tensor* t : {&p, &q, &gamma, &omega}) {
+    TORCH_CHECK(t->is_cuda() && t->is_contiguous() && t->scalar_type() == at::kFloat, "cema coefficients must be contiguous fp32");
+  }
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor y = torch::empty_like(x);
+  OptTensor h_last;
+  if (want_last) h_last = torch::empty({B, D, N, 2}, f32);
+  const int S = mb::cema_num_segments(L);
+  Tensor carry = torch::empty({S > 1 ? (long long)B * S * N * D * 2 : 0}, f32);
+  mb::cema_fwd(x.data_ptr(), p.data_ptr<float>(), q.data_ptr<float>(), gamma.data_ptr<float>(),
+               omega.data_ptr<float>(), hx.has_value() ? hx->data_ptr<float>() : nullptr, y.data_ptr(),
+               h_last.has_value() ? h_last->data_ptr<float>() : nullptr, carry.data_ptr<float>(), B, L, D, N,
+               dtype_code(x), stream());
+  return {y, h_last};
+}
+
+// returns dx, dp, dq, dgamma, domega, dhx
+std::vector<Tensor> cema_bwd(const Tensor& dy, const Tensor& x, const Tensor& p, const Tensor& q,
+                             const Tensor& gamma, const Tensor& omega, const OptTensor& hx,
+                             const OptTensor& dh_last) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int B = x.size(0), L = x.size(1), D = x.size(2), N = p.size(1);
+  auto f32 = x.options().dtype(at::kFloat);
+  Tensor dx = torch::empty_like(x);
+  Tensor dp = torch::zeros({D, N}, f32);
+  Tensor dq = torch::zeros({D, N, 2}, f32);
+  Tensor dgamma = torch::zeros({D, N, 2}, f32);
+  Tensor domega = torch::zeros({D}, f32);
+  Tensor dhx = torch::empty({B, D, N, 2}, f32);
+  const int S = mb::cema_num_segments(L);
+  const long long cn = S > 1 ? (long long)B * S * N * D * 2 : 0;
+  Tensor carry = torch::empty({2 * cn}, f32);
+  if (dh_last.has_value()) TORCH_CHECK(dh_last->is_contiguous() && dh_last->scalar_type() == at::kFloat);
+  mb::cema_bwd(dy.data_ptr(), x.data_ptr(), p.data_ptr<float>(), q.data_ptr<float>(), gamma.data_ptr<float>(),
+               omega.data_ptr<float>(), hx.has_value() ? hx->data_ptr<float>() : nullptr,
+               dh_last.has_value() ? dh_last->data_ptr<float>() : nullptr, dx.data_ptr(), dp.data_ptr<float>(),
+               dq.data_ptr<float>(), dgamma.data_ptr<float>(), domega.data_ptr<float>(), dhx.data_ptr<float>(),
+               carry.data_ptr<float>(), carry.data_ptr<float>() + cn, B, L, D, N, dtype_code(x), stream());
+  return {dx, dp, dq, dgamma, domega, dhx};
+}
+
+// ------------------------------------------------------------------ element-wise
+Tensor swiglu_fwd(const Tensor& a, const Tensor& b) {
+  check_cuda_contig(a, "a");
+  check_cuda_contig(b, "b");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor out = torch::empty_like(a);
+  mb::swiglu_fwd(a.data_ptr(), b.data_ptr(), out.data_ptr(), a.numel(), dtype_code(a), stream());
+  return out;
+}
+
+std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& a, const Tensor& b) {
+  check_cuda_contig(g, "g");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor da = torch::empty_like(a), db = torch::empty_like(b);
+  mb::swiglu_bwd(g.data_ptr(), a.data_ptr(), b.data_ptr(), da.data_ptr(), db.data_ptr(), a.numel(), dtype_code(a),
+                 stream());
+  return {da, db};
+}
+
+// x [rows, H, Dh]; freqs [L, Dh/2, 2] fp32 (cos, sin); position = row % L
+Tensor rotary(const Tensor& x, const Tensor& freqs, bool conj) {
+  check_cuda_contig(x, "x");
+  check_cuda_contig(freqs, "freqs");
+  c10::cuda::CUDAGuard guard(x.device());
+  TORCH_CHECK(freqs.scalar_type() == at::kFloat && x.dim() >= 3);
+  const int Dh = x.size(-1), H = x.size(-2), L = freqs.size(0);
+  TORCH_CHECK(Dh % 2 == 0 && freqs.size(1) == Dh / 2);
+  const long long rows = x.numel() / ((long long)H * Dh);
+  Tensor out = torch::empty_like(x);
+  mb::rotary_apply(x.data_ptr(), freqs.data_ptr<float>(), out.data_ptr(), rows, L, H, Dh, conj, dtype_code(x),
+                   stream());
+  return out;
+}
+
+std::tuple<Tensor, Tensor> cross_entropy_fwd(const Tensor& logits, const Tensor& target, int64_t ignore_index) {
+  check_cuda_contig(logits, "logits");
+  check_cuda_contig(target, "target");
+  c10::cuda::CUDAGuard guard(logits.device());
+  TORCH_CHECK(logits.dim() == 2 && target.scalar_type() == at::kLong);
+  const long long rows = logits.size(0);
+  auto f32 = logits.options().dtype(at::kFloat);
+  Tensor loss = torch::empty({rows}, f32), lse = torch::empty({rows}, f32);
+  mb::cross_entropy_fwd(logits.data_ptr(), (const long long*)target.data_ptr<int64_t>(), loss.data_ptr<float>(),
+                        lse.data_ptr<float>(), rows, (int)logits.size(1), ignore_index, dtype_code(logits), stream());
+  return {loss, lse};
+}
+
+Tensor cross_entropy_bwd(const Tensor& logits, const Tensor& target, const Tensor& lse, const Tensor& dloss,
+                         int64_t ignore_index) {
+  c10::cuda::CUDAGuard guard(logits.device());
+  Tensor dlogits = torch::empty_like(logits);
+  Tensor dl = dloss.to(at::kFloat).contiguous();
+  mb::cross_entropy_bwd(logits.data_ptr(), (const long long*)target.data_ptr<int64_t>(), lse.data_ptr<float>(),
+                        dl.data_ptr<float>(), dlogits.data_ptr(), logits.size(0), (int)logits.size(1), ignore_index,
+                        dtype_code(logits), stream());
+  return dlogits;
+}
+
+void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTensor& low, double lr, double beta1,
+                double beta2, double eps, double wd, int64_t step, double grad_scale, const OptTensor& scale_ptr) {
+  check_cuda_contig(p, "param");
+  check_cuda_contig(g, "grad");
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
+  TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel());
+  if (low.has_value()) TORCH_CHECK(low->numel() == p.numel() && low->is_contiguous());
+  mb::adamw_step(p.data_ptr<float>(), g.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(),
+                 low.has_value() ? low->data_ptr() : nullptr, p.numel(), (float)lr, (float)beta1, (float)beta2,
+                 (float)eps, (float)wd, (int)step, (float)grad_scale,
+                 scale_ptr.has_value() ? scale_ptr->data_ptr<float>() : nullptr, dtype_code(g),
+                 low.has_value() ? dtype_code(*low) : 1, stream());
+}
+
+void sum_squares(const Tensor& g, Tensor& out) {
+  check_cuda_contig(g, "g");
+  c10::cuda::CUDAGuard guard(g.device());
+  TORCH_CHECK(out.scalar_type() == at::kDouble && out.numel() == 1);
+  mb::sum_squares(g.data_ptr(), g.numel(), out.data_ptr<double>(), dtype_code(g), stream());
+}
+
+void scale_by_ptr(Tensor& g, const Tensor& scale) {
+  check_cuda_contig(g, "g");
+  c10::cuda::CUDAGuard guard(g.device());
+  mb::scale_by_ptr(g.data_ptr(), g.numel(), scale.data_ptr<float>(), dtype_code(g), stream());
+}
+
+std::tuple<Tensor, Tensor> clip_coef(const Tensor& sumsq, double max_norm) {
+  c10::cuda::CUDAGuard guard(sumsq.device());
+  auto f32 = sumsq.options().dtype(at::kFloat);
+  Tensor norm = torch::empty({}, f32), coef = torch::empty({}, f32);
+  mb::clip_coef(sumsq.data_ptr<double>(), (float)max_norm, norm.data_ptr<float>(), coef.data_ptr<float>(), stream());
+  return {norm, coef};
+}
+
+// ------------------------------------------------------------------ GEMM
+// C[M,N] = act(A B^T + bias).  a_mn / b_mn: the operand is stored [K, rows] instead of [rows, K].
+// Returns (C, preact or None).  `err` is a persistent int32 device flag set by the kernel on a wait timeout.
+std::tuple<Tensor, OptTensor> gemm(const Tensor& A, const Tensor& B, const OptTensor& bias, int64_t act,
+                                   bool a_mn, bool b_mn, bool want_preact, int64_t out_dtype_code, Tensor& err) {
+  check_cuda_contig(A, "A");
+  check_cuda_contig(B, "B");
+  c10::cuda::CUDAGuard guard(A.device());
+  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.scalar_type() == B.scalar_type());
+  TORCH_CHECK(A.scalar_type() == at::kBFloat16 || A.scalar_type() == at::kHalf, "tcgen05 GEMM takes bf16/fp16");
+  const int M = a_mn ? A.size(1) : A.size(0);
+  const int K = a_mn ? A.size(0) : A.size(1);
+  const int N = b_mn ? B.size(1) : B.size(0);
+  TORCH_CHECK((b_mn ? B.size(0) : B.size(1)) == K, "inner dimensions differ");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(A.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(B.data_ptr()) % 16 == 0,
+              "operands must be 16-byte aligned");
+  at::ScalarType odt = out_dtype_code == 0 ? at::kFloat : (out_dtype_code == 1 ? at::kBFloat16 : at::kHalf);
+  Tensor C = torch::empty({M, N}, A.options().dtype(odt));
+  OptTensor pre;
+  if (want_preact) pre = torch::empty({M, N}, A.options().dtype(odt));
+  TORCH_CHECK(N % 8 == 0, "N must be a multiple of 8");
+  int bias_code = 0;
+  if (bias.has_value()) { check_cuda_contig(*bias, "bias"); bias_code = dtype_code(*bias); TORCH_CHECK(bias->numel() == N); }
+  const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  const int rc = mb::gemm_bf16_tcgen05(A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                       pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
+                                       (int)act, M, N, K, a_mn, b_mn, dtype_code(A), (int)out_dtype_code,
+                                       err.data_ptr<int>(), sms, stream());
+  TORCH_CHECK(rc == 0, "tcgen05 GEMM launch failed with code ", rc);
+  return {C, pre};
+}
+
+}  // namespace
+
+PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  m.def("rms_norm_fwd", &rms_norm_fwd);
+  m.def("rms_norm_bwd", &rms_norm_bwd);
+  m.def("layer_norm_fwd", &layer_norm_fwd);
+  m.def("layer_norm_bwd", &layer_norm_bwd);
+  m.def("timestep_norm_fwd", &timestep_norm_fwd);
+  m.def("timestep_norm_bwd", &timestep_norm_bwd);
+  m.def("cema_fwd", &cema_fwd);
+  m.def("cema_bwd", &cema_bwd);
+  m.def("swiglu_fwd", &swiglu_fwd);
+  m.def("swiglu_bwd", &swiglu_bwd);
+  m.def("rotary", &rotary);
+  m.def("cross_entropy_fwd", &cross_entropy_fwd);
+  m.def("cross_entropy_bwd", &cross_entropy_bwd);
+  m.def("adamw_step", &adamw_step);
+  m.def("sum_squares", &sum_squares);
+  m.def("scale_by_ptr", &scale_by_ptr);
+  m.def("clip_coef", &clip_coef);
+  m.def("gemm", &gemm);
+}

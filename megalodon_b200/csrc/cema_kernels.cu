@@ -1,0 +1,478 @@
+// Complex exponential moving average (CEMA) as a segmented linear scan.
+//
+//   h_t = q h_{t-1} + p x_t          (N complex states per feature)
+//   y_t = Re(sum_n gamma_n h_t,n) + omega x_t
+//
+// The reference evaluates this as an FFT convolution with a kernel built from
+// q^j plus a bias from the carried state plus a separate kernel for the last
+// state (ema_parameters + fftconv + ema_hidden; csrc/ops/ema_parameters_kernel.cu,
+// fftconv_kernel.cu, ema_hidden_kernel.cu).  With N = 16 the recurrence costs
+// O(L N) = about the same arithmetic as two length-2L FFTs, needs no transposed
+// layout (threads own consecutive features of the channels-last activations, so
+// loads are coalesced), never materialises a spectrum, and produces the carried
+// state exactly and for free.  So here the whole layer is three small kernels:
+//
+//   A: per (batch, segment, feature)  end state of the segment from a zero start
+//   B: per (batch, feature, n)        sequential combine over segments -> incoming state
+//   C: per (batch, segment, feature)  rerun the segment from its incoming state, emit y
+//
+// Backward runs the adjoint recurrence (reverse time) for dx, dp, domega, dh_prev
+// and a forward recurrence on (h, u = dh/dq) for dgamma and dq.
+//
+// Work split: a feature's N states are divided over NSPLIT adjacent lanes
+// (NPT = N / NSPLIT states each); the sum over n for y / dx is one shuffle.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb {
+namespace {
+
+constexpr int kCemaThreads = 256;
+
+template <int NPT>
+struct Coef {
+  float p[NPT];
+  cfloat q[NPT];
+  cfloat g[NPT];
+};
+
+template <int NPT, int NSPLIT>
+__device__ __forceinline__ void load_coef(Coef<NPT>& c, const float* p, const cfloat* q, const cfloat* g,
+                                          int d, int split, int N) {
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = split * NPT + i;
+    c.p[i] = p[d * N + n];
+    c.q[i] = q[d * N + n];
+    c.g[i] = g[d * N + n];
+  }
+}
+
+template <int NSPLIT>
+__device__ __forceinline__ float split_sum(float v) {
+#pragma unroll
+  for (int o = NSPLIT / 2; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ cfloat cpow_int(cfloat q, int n) {
+  cfloat r = {1.f, 0.f};
+  cfloat base = q;
+  while (n > 0) {
+    if (n & 1) r = cmul(r, base);
+    base = cmul(base, base);
+    n >>= 1;
+  }
+  return r;
+}
+
+// index into the [B, S, N, D] carry buffers
+__device__ __forceinline__ long long cidx(int b, int s, int n, int d, int S, int N, int D) {
+  return (((long long)b * S + s) * N + n) * D + d;
+}
+
+struct Geo {
+  int B, L, D, N, S, Ts;
+};
+
+#define CEMA_THREAD_SETUP()                                                    \
+  const int tix = blockIdx.x * blockDim.x + threadIdx.x;                       \
+  const int d = tix / NSPLIT;                                                  \
+  const int split = tix % NSPLIT;                                              \
+  const int s = blockIdx.y;                                                    \
+  const int b = blockIdx.z;                                                    \
+  const bool live = d < geo.D;                                                 \
+  const int dd = live ? d : 0;                                                 \
+  const int t0 = s * geo.Ts;                                                   \
+  const int t1 = min(geo.L, t0 + geo.Ts);
+
+// ------------------------------------------------------------------ forward
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_fwd_local(const T* __restrict__ x, const float* __restrict__ p,
+                               const cfloat* __restrict__ q, const cfloat* __restrict__ g,
+                               cfloat* __restrict__ carry, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat h[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) h[i] = {0.f, 0.f};
+  const T* xp = x + (long long)b * geo.L * geo.D + dd;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = to_f(xp[(long long)t * geo.D]);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const cfloat hn = cmul(c.q[i], h[i]);
+      h[i] = {hn.re + c.p[i] * xv, hn.im};
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) carry[cidx(b, s, split * NPT + i, d, geo.S, geo.N, geo.D)] = h[i];
+  }
+}
+
+// One thread per (b, n, d): carry[b, s] (end state from zero) -> incoming state of segment s.
+// `conj_q` runs the adjoint (segments visited from last to first).
+__global__ void cema_combine(cfloat* __restrict__ carry, const cfloat* __restrict__ q,
+                             const cfloat* __restrict__ init /* [B, D, N] or null */,
+                             cfloat* __restrict__ final_out /* [B, D, N] or null */, Geo geo, bool reverse) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long per_b = (long long)geo.N * geo.D;
+  if (i >= per_b * geo.B) return;
+  const int b = (int)(i / per_b);
+  const int n = (int)((i % per_b) / geo.D);
+  const int d = (int)(i % geo.D);
+  cfloat qq = q[d * geo.N + n];
+  if (reverse) qq = cconj(qq);
+  const cfloat q_full = cpow_int(qq, geo.Ts);
+  const int last_len = geo.L - (geo.S - 1) * geo.Ts;
+  const cfloat q_last = cpow_int(qq, last_len);
+  cfloat H = init ? init[((long long)b * geo.D + d) * geo.N + n] : cfloat{0.f, 0.f};
+  for (int k = 0; k < geo.S; ++k) {
+    const int s = reverse ? geo.S - 1 - k : k;
+    const long long idx = cidx(b, s, n, d, geo.S, geo.N, geo.D);
+    const cfloat c = carry[idx];
+    carry[idx] = H;
+    H = cadd(cmul(s == geo.S - 1 ? q_last : q_full, H), c);
+  }
+  if (final_out) final_out[((long long)b * geo.D + d) * geo.N + n] = H;
+}
+
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_fwd_final(const T* __restrict__ x, const float* __restrict__ p,
+                               const cfloat* __restrict__ q, const cfloat* __restrict__ g,
+                               const float* __restrict__ omega, const cfloat* __restrict__ incoming,
+                               const cfloat* __restrict__ hx, T* __restrict__ y,
+                               cfloat* __restrict__ h_last, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat h[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = split * NPT + i;
+    if (incoming != nullptr) h[i] = incoming[cidx(b, s, n, dd, geo.S, geo.N, geo.D)];
+    else if (hx != nullptr) h[i] = hx[((long long)b * geo.D + dd) * geo.N + n];
+    else h[i] = {0.f, 0.f};
+  }
+  const float om = omega[dd];
+  const long long base = (long long)b * geo.L * geo.D + dd;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = to_f(x[base + (long long)t * geo.D]);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const cfloat hn = cmul(c.q[i], h[i]);
+      h[i] = {hn.re + c.p[i] * xv, hn.im};
+      acc += c.g[i].re * h[i].re - c.g[i].im * h[i].im;
+    }
+    acc = split_sum<NSPLIT>(acc);
+    if (live && split == 0) y[base + (long long)t * geo.D] = from_f<T>(acc + om * xv);
+  }
+  if (h_last != nullptr && live && s == geo.S - 1) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) h_last[((long long)b * geo.D + d) * geo.N + split * NPT + i] = h[i];
+  }
+}
+
+// ------------------------------------------------------------------ backward: adjoint (reverse time)
+// state s_n = conj(q_n) * lambda_{t+1,n};  lambda_t = s + conj(gamma) dy_t
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_bwd_rev_local(const T* __restrict__ dy, const float* __restrict__ p,
+                                   const cfloat* __restrict__ q, const cfloat* __restrict__ g,
+                                   cfloat* __restrict__ carry, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat st[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) st[i] = {0.f, 0.f};
+  const long long base = (long long)b * geo.L * geo.D + dd;
+  for (int t = t1 - 1; t >= t0; --t) {
+    const float gy = to_f(dy[base + (long long)t * geo.D]);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
+      st[i] = cmul(cconj(c.q[i]), lam);
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) carry[cidx(b, s, split * NPT + i, d, geo.S, geo.N, geo.D)] = st[i];
+  }
+}
+
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_bwd_rev_final(const T* __restrict__ dy, const T* __restrict__ x,
+                                   const float* __restrict__ p, const cfloat* __restrict__ q,
+                                   const cfloat* __restrict__ g, const float* __restrict__ omega,
+                                   const cfloat* __restrict__ incoming, const cfloat* __restrict__ dh_last,
+                                   T* __restrict__ dx, float* __restrict__ dp, float* __restrict__ domega,
+                                   cfloat* __restrict__ dhx, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat st[NPT];
+  float acc_p[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = split * NPT + i;
+    if (incoming != nullptr) st[i] = incoming[cidx(b, s, n, dd, geo.S, geo.N, geo.D)];
+    else if (dh_last != nullptr) st[i] = dh_last[((long long)b * geo.D + dd) * geo.N + n];
+    else st[i] = {0.f, 0.f};
+    acc_p[i] = 0.f;
+  }
+  const float om = omega[dd];
+  float acc_om = 0.f;
+  const long long base = (long long)b * geo.L * geo.D + dd;
+  for (int t = t1 - 1; t >= t0; --t) {
+    const float gy = to_f(dy[base + (long long)t * geo.D]);
+    const float xv = to_f(x[base + (long long)t * geo.D]);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
+      acc += c.p[i] * lam.re;
+      acc_p[i] += lam.re * xv;
+      st[i] = cmul(cconj(c.q[i]), lam);
+    }
+    acc = split_sum<NSPLIT>(acc);
+    acc_om += gy * xv;
+    if (live && split == 0) dx[base + (long long)t * geo.D] = from_f<T>(acc + om * gy);
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) atomicAdd(dp + d * geo.N + split * NPT + i, acc_p[i]);
+    if (split == 0) atomicAdd(domega + d, acc_om);
+    if (dhx != nullptr && s == 0 && incoming == nullptr) {
+      // single-segment case: the combine kernel did not run, finish here
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) dhx[((long long)b * geo.D + d) * geo.N + split * NPT + i] = st[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ backward: forward-time pass on (h, u = dh/dq)
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_bwd_fwd_local(const T* __restrict__ x, const float* __restrict__ p,
+                                   const cfloat* __restrict__ q, const cfloat* __restrict__ g,
+                                   cfloat* __restrict__ carry_h, cfloat* __restrict__ carry_u, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat h[NPT], u[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) h[i] = u[i] = {0.f, 0.f};
+  const long long base = (long long)b * geo.L * geo.D + dd;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = to_f(x[base + (long long)t * geo.D]);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
+      const cfloat hn = cmul(c.q[i], h[i]);
+      h[i] = {hn.re + c.p[i] * xv, hn.im};
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const long long idx = cidx(b, s, split * NPT + i, d, geo.S, geo.N, geo.D);
+      carry_h[idx] = h[i];
+      carry_u[idx] = u[i];
+    }
+  }
+}
+
+// per (b, n, d): incoming (h, u) of every segment; adds the last-state term of dq
+__global__ void cema_bwd_fwd_combine(cfloat* __restrict__ carry_h, cfloat* __restrict__ carry_u,
+                                     const cfloat* __restrict__ q, const cfloat* __restrict__ hx,
+                                     const cfloat* __restrict__ dh_last, float* __restrict__ dq, Geo geo) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long per_b = (long long)geo.N * geo.D;
+  if (i >= per_b * geo.B) return;
+  const int b = (int)(i / per_b);
+  const int n = (int)((i % per_b) / geo.D);
+  const int d = (int)(i % geo.D);
+  const cfloat qq = q[d * geo.N + n];
+  const int last_len = geo.L - (geo.S - 1) * geo.Ts;
+  const cfloat qT = cpow_int(qq, geo.Ts), qTm1 = cpow_int(qq, geo.Ts - 1);
+  const cfloat qL = cpow_int(qq, last_len), qLm1 = cpow_int(qq, last_len - 1);
+  cfloat H = hx ? hx[((long long)b * geo.D + d) * geo.N + n] : cfloat{0.f, 0.f};
+  cfloat U = {0.f, 0.f};
+  for (int s = 0; s < geo.S; ++s) {
+    const long long idx = cidx(b, s, n, d, geo.S, geo.N, geo.D);
+    const cfloat ch = carry_h[idx], cu = carry_u[idx];
+    carry_h[idx] = H;
+    carry_u[idx] = U;
+    const bool last = s == geo.S - 1;
+    const int len = last ? last_len : geo.Ts;
+    const cfloat a = last ? qL : qT, am1 = last ? qLm1 : qTm1;
+    cfloat lh = cmul(am1, H);
+    lh = {lh.re * len, lh.im * len};
+    U = cadd(cadd(cmul(a, U), lh), cu);
+    H = cadd(cmul(a, H), ch);
+  }
+  if (dh_last != nullptr) {
+    // dL/dq += g_last * conj(u_{L-1})
+    const cfloat gl = dh_last[((long long)b * geo.D + d) * geo.N + n];
+    const cfloat v = cmul(gl, cconj(U));
+    atomicAdd(dq + 2 * (d * geo.N + n), v.re);
+    atomicAdd(dq + 2 * (d * geo.N + n) + 1, v.im);
+  }
+}
+
+template <typename T, int NPT, int NSPLIT>
+__global__ void cema_bwd_fwd_final(const T* __restrict__ dy, const T* __restrict__ x,
+                                   const float* __restrict__ p, const cfloat* __restrict__ q,
+                                   const cfloat* __restrict__ g, const cfloat* __restrict__ inc_h,
+                                   const cfloat* __restrict__ inc_u, const cfloat* __restrict__ hx,
+                                   const cfloat* __restrict__ dh_last, float* __restrict__ dgamma,
+                                   float* __restrict__ dq, Geo geo) {
+  CEMA_THREAD_SETUP();
+  Coef<NPT> c;
+  load_coef<NPT, NSPLIT>(c, p, q, g, dd, split, geo.N);
+  cfloat h[NPT], u[NPT], ag[NPT], aq[NPT];
+#pragma unroll
+  for (int i = 0; i < NPT; ++i) {
+    const int n = split * NPT + i;
+    if (inc_h != nullptr) {
+      const long long idx = cidx(b, s, n, dd, geo.S, geo.N, geo.D);
+      h[i] = inc_h[idx];
+      u[i] = inc_u[idx];
+    } else {
+      h[i] = hx ? hx[((long long)b * geo.D + dd) * geo.N + n] : cfloat{0.f, 0.f};
+      u[i] = {0.f, 0.f};
+    }
+    ag[i] = aq[i] = {0.f, 0.f};
+  }
+  const long long base = (long long)b * geo.L * geo.D + dd;
+  for (int t = t0; t < t1; ++t) {
+    const float xv = to_f(x[base + (long long)t * geo.D]);
+    const float gy = to_f(dy[base + (long long)t * geo.D]);
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
+      const cfloat hn = cmul(c.q[i], h[i]);
+      h[i] = {hn.re + c.p[i] * xv, hn.im};
+      // dgamma += conj(h) dy ; dq += (conj(gamma) dy) conj(u)
+      ag[i].re += h[i].re * gy;
+      ag[i].im -= h[i].im * gy;
+      const cfloat cg = {c.g[i].re * gy, -c.g[i].im * gy};
+      const cfloat v = cmul(cg, cconj(u[i]));
+      aq[i].re += v.re;
+      aq[i].im += v.im;
+    }
+  }
+  if (inc_h == nullptr && dh_last != nullptr) {
+    // single-segment case (the combine kernel did not run): dq += g_last * conj(u_{L-1})
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const cfloat gl = dh_last[((long long)b * geo.D + dd) * geo.N + split * NPT + i];
+      const cfloat v = cmul(gl, cconj(u[i]));
+      aq[i].re += v.re;
+      aq[i].im += v.im;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) {
+      const int o = 2 * (d * geo.N + split * NPT + i);
+      atomicAdd(dgamma + o, ag[i].re);
+      atomicAdd(dgamma + o + 1, ag[i].im);
+      atomicAdd(dq + o, aq[i].re);
+      atomicAdd(dq + o + 1, aq[i].im);
+    }
+  }
+}
+
+void pick_split(int N, int& npt, int& nsplit) {
+  if (N % 8 == 0) { npt = 8; nsplit = N / 8; }
+  else if (N % 4 == 0) { npt = 4; nsplit = N / 4; }
+  else if (N % 2 == 0) { npt = 2; nsplit = N / 2; }
+  else { npt = 1; nsplit = N; }
+}
+
+#define CEMA_SWITCH(N, ...)                                                                  \
+  do {                                                                                       \
+    int npt_, nsplit_;                                                                       \
+    pick_split(N, npt_, nsplit_);                                                            \
+    if (npt_ == 8 && nsplit_ == 1) { constexpr int NPT = 8, NSPLIT = 1; __VA_ARGS__; }       \
+    else if (npt_ == 8 && nsplit_ == 2) { constexpr int NPT = 8, NSPLIT = 2; __VA_ARGS__; }  \
+    else if (npt_ == 8 && nsplit_ == 4) { constexpr int NPT = 8, NSPLIT = 4; __VA_ARGS__; }  \
+    else if (npt_ == 4 && nsplit_ == 1) { constexpr int NPT = 4, NSPLIT = 1; __VA_ARGS__; }  \
+    else if (npt_ == 2 && nsplit_ == 1) { constexpr int NPT = 2, NSPLIT = 1; __VA_ARGS__; }  \
+    else { constexpr int NPT = 1, NSPLIT = 1; __VA_ARGS__; }                                 \
+  } while (0)
+
+}  // namespace
+
+bool cema_supported_ndim(int N) { return N == 1 || N == 2 || N == 4 || N == 8 || N == 16 || N == 32; }
+
+int cema_num_segments(int L) { return (L + kCemaSegLen - 1) / kCemaSegLen; }
+
+void cema_fwd(const void* x, const float* p, const float* q, const float* gamma, const float* omega,
+              const float* hx, void* y, float* h_last, float* carry, int B, int L, int D, int N,
+              int x_dtype, cudaStream_t st) {
+  Geo geo{B, L, D, N, cema_num_segments(L), kCemaSegLen};
+  const cfloat* qc = (const cfloat*)q;
+  const cfloat* gc = (const cfloat*)gamma;
+  MB_DISPATCH_DTYPE(x_dtype, {
+    using T = scalar_t;
+    CEMA_SWITCH(N, {
+      dim3 grid(div_up((long long)D * NSPLIT, kCemaThreads), geo.S, B);
+      const cfloat* incoming = nullptr;
+      if (geo.S > 1) {
+        cema_fwd_local<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>((const T*)x, p, qc, gc, (cfloat*)carry, geo);
+        const long long n = (long long)B * N * D;
+        cema_combine<<<div_up(n, 256), 256, 0, st>>>((cfloat*)carry, qc, (const cfloat*)hx, nullptr, geo, false);
+        incoming = (const cfloat*)carry;
+      }
+      cema_fwd_final<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>(
+          (const T*)x, p, qc, gc, omega, incoming, (const cfloat*)hx, (T*)y, (cfloat*)h_last, geo);
+    });
+  });
+}
+
+void cema_bwd(const void* dy, const void* x, const float* p, const float* q, const float* gamma,
+              const float* omega, const float* hx, const float* dh_last, void* dx, float* dp, float* dq,
+              float* dgamma, float* domega, float* dhx, float* carry_a, float* carry_b, int B, int L,
+              int D, int N, int x_dtype, cudaStream_t st) {
+  Geo geo{B, L, D, N, cema_num_segments(L), kCemaSegLen};
+  const cfloat* qc = (const cfloat*)q;
+  const cfloat* gc = (const cfloat*)gamma;
+  const long long nbd = (long long)B * N * D;
+  MB_DISPATCH_DTYPE(x_dtype, {
+    using T = scalar_t;
+    CEMA_SWITCH(N, {
+      dim3 grid(div_up((long long)D * NSPLIT, kCemaThreads), geo.S, B);
+      // adjoint pass
+      const cfloat* inc = nullptr;
+      if (geo.S > 1) {
+        cema_bwd_rev_local<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>((const T*)dy, p, qc, gc, (cfloat*)carry_a, geo);
+        cema_combine<<<div_up(nbd, 256), 256, 0, st>>>((cfloat*)carry_a, qc, (const cfloat*)dh_last,
+                                                       (cfloat*)dhx, geo, true);
+        inc = (const cfloat*)carry_a;
+      }
+      cema_bwd_rev_final<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>(
+          (const T*)dy, (const T*)x, p, qc, gc, omega, inc, (const cfloat*)dh_last, (T*)dx, dp, domega,
+          (cfloat*)dhx, geo);
+      // forward-time pass for dgamma, dq
+      const cfloat* inc_h = nullptr;
+      const cfloat* inc_u = nullptr;
+      if (geo.S > 1) {
+        cema_bwd_fwd_local<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>((const T*)x, p, qc, gc, (cfloat*)carry_a,
+                                                                        (cfloat*)carry_b, geo);
+        cema_bwd_fwd_combine<<<div_up(nbd, 256), 256, 0, st>>>((cfloat*)carry_a, (cfloat*)carry_b, qc,
+                                                               (const cfloat*)hx, (const cfloat*)dh_last, dq, geo);
+        inc_h = (const cfloat*)carry_a;
+        inc_u = (const cfloat*)carry_b;
+      }
+      cema_bwd_fwd_final<T, NPT, NSPLIT><<<grid, kCemaThreads, 0, st>>>(
+          (const T*)dy, (const T*)x, p, qc, gc, inc_h, inc_u, (const cfloat*)hx, (const cfloat*)dh_last,
+          dgamma, dq, geo);
+    });
+  });
+}
+
+}  // namespace mb

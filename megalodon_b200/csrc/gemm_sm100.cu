@@ -1,0 +1,389 @@
+// Persistent, warp-specialised tcgen05 GEMM for sm_100a.
+//
+//   C[M, N] = epilogue( A * B^T )       fp32 accumulation in tensor memory
+//
+// A supplies M rows, B supplies N rows, both reduced over K.  Each operand is
+// either K-major (stored [rows, K], K contiguous) or MN-major (stored
+// [K, rows], rows contiguous), so the three GEMMs of a linear layer need no
+// transposed copies:
+//   forward  y  = x  w^T      A = x  [M, K]  K-major,   B = w  [N, K]  K-major
+//   dgrad    dx = dy w        A = dy [M, N'] K-major,   B = w  [N', K'] MN-major
+//   wgrad    dw = dy^T x      A = dy [T, N'] MN-major,  B = x  [T, K'] MN-major
+//
+// CTA = 6 warps: warp 0 issues TMA loads (128B-swizzled tiles, no multicast)
+// into a 4-stage shared-memory ring; warp 1 issues tcgen05.mma (128 x BN x 16)
+// into one of two TMEM accumulators; warps 2-5 drain the other accumulator
+// with tcgen05.ld, apply bias / SiLU and store, so the epilogue of tile i
+// overlaps the main loop of tile i+1.  Tiles are walked M-fastest so CTAs that
+// run together share B tiles in L2.
+//
+// All mbarrier waits are bounded; a timeout sets `*err` and the CTA unwinds
+// (releasing its TMEM) instead of hanging.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include <mutex>
+
+#include "common.cuh"
+#include "kernels.h"
+#include "sm100_ptx.cuh"
+
+namespace mb {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;
+constexpr int BK = 64;          // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int kStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 4;
+
+template <int BN>
+struct SmemLayout {
+  static constexpr int a_bytes = BM * BK * 2;       // 16 KiB
+  static constexpr int b_bytes = BN * BK * 2;       // 32 KiB at BN = 256
+  static constexpr int stage_bytes = a_bytes + b_bytes;
+  static constexpr int bar_offset = kStages * stage_bytes;
+  static constexpr int total = bar_offset + 256 + 1024;  // barriers + alignment slack
+};
+
+struct GemmParams {
+  int M, N, K;
+  void* C;             // [M, N]
+  void* preact;        // optional [M, N]: value before the activation
+  const void* bias;    // optional [N]
+  int bias_dtype;      // DType
+  int act;             // 0 none, 1 SiLU
+  int* err;
+};
+
+__device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = globaltimer_ns();
+  uint32_t spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xff) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+    }
+  }
+  return true;
+}
+
+template <typename OutT>
+__device__ __forceinline__ void store_row32(OutT* dst, const float (&v)[32], int ncols_valid);
+
+template <>
+__device__ __forceinline__ void store_row32<__nv_bfloat16>(__nv_bfloat16* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 pk;
+      __nv_bfloat162 t0 = __floats2bfloat162_rn(v[8 * i + 0], v[8 * i + 1]);
+      __nv_bfloat162 t1 = __floats2bfloat162_rn(v[8 * i + 2], v[8 * i + 3]);
+      __nv_bfloat162 t2 = __floats2bfloat162_rn(v[8 * i + 4], v[8 * i + 5]);
+      __nv_bfloat162 t3 = __floats2bfloat162_rn(v[8 * i + 6], v[8 * i + 7]);
+      pk.x = *reinterpret_cast<uint32_t*>(&t0);
+      pk.y = *reinterpret_cast<uint32_t*>(&t1);
+      pk.z = *reinterpret_cast<uint32_t*>(&t2);
+      pk.w = *reinterpret_cast<uint32_t*>(&t3);
+      reinterpret_cast<uint4*>(dst)[i] = pk;
+    }
+  } else {
+    for (int i = 0; i < nvalid; ++i) dst[i] = __float2bfloat16_rn(v[i]);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row32<__half>(__half* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 pk;
+      __half2 t0 = __floats2half2_rn(v[8 * i + 0], v[8 * i + 1]);
+      __half2 t1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+      __half2 t2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
+      __half2 t3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+      pk.x = *reinterpret_cast<uint32_t*>(&t0);
+      pk.y = *reinterpret_cast<uint32_t*>(&t1);
+      pk.z = *reinterpret_cast<uint32_t*>(&t2);
+      pk.w = *reinterpret_cast<uint32_t*>(&t3);
+      reinterpret_cast<uint4*>(dst)[i] = pk;
+    }
+  } else {
+    for (int i = 0; i < nvalid; ++i) dst[i] = __float2half_rn(v[i]);
+  }
+}
+
+template <>
+__device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+  } else {
+    for (int i = 0; i < nvalid; ++i) dst[i] = v[i];
+  }
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    GemmParams p, int in_fmt) {
+  using L = SmemLayout<BN>;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::bar_offset);
+  uint64_t* empty_bar = full_bar + kStages;
+  uint64_t* tmem_full = empty_bar + kStages;
+  uint64_t* tmem_empty = tmem_full + 2;
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (p.M + BM - 1) / BM;
+  const int num_n = (p.N + BN - 1) / BN;
+  const int num_tiles = num_m * num_n;
+  const int num_k = (p.K + BK - 1) / BK;
+  constexpr uint32_t kTmemCols = 2 * BN;     // two accumulators (power of two: 256 or 512)
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kStages; ++i) {
+      mbar_init(full_bar + i, 1);
+      mbar_init(empty_bar + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full + i, 1);
+      mbar_init(tmem_empty + i, kEpiWarps);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_holder, kTmemCols);
+    tmem_relinquish();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (elect_one()) {
+      prefetch_tmap(&tmap_a);
+      prefetch_tmap(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % num_m) * BM;
+        const int n0 = (tile / num_m) * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!wait_or_abort(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::stage_bytes;
+          uint8_t* sb = sa + L::a_bytes;
+          mbar_expect_tx(full_bar + stage, L::stage_bytes);
+          const int k0 = kb * BK;
+          if constexpr (!A_MN) {
+            tma_load_2d(sa, &tmap_a, full_bar + stage, k0, m0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, full_bar + stage, m0 + 64 * j, k0);
+          }
+          if constexpr (!B_MN) {
+            tma_load_2d(sb, &tmap_b, full_bar + stage, k0, n0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, full_bar + stage, n0 + 64 * j, k0);
+          }
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (elect_one()) {
+      const uint32_t idesc = make_idesc_f16(BM, BN, in_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        if (!wait_or_abort(tmem_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!wait_or_abort(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::stage_bytes);
+          const uint32_t sb = sa + L::a_bytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sb + kk * 32, 16, 1024);
+            umma_f16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          umma_commit(empty_bar + stage);      // stage reusable once these MMAs have read it
+          if (++stage == kStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        umma_commit(tmem_full + acc);          // accumulator complete
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;              // TMEM lanes [32 * quarter, +32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    OutT* C = reinterpret_cast<OutT*>(p.C);
+    OutT* P = reinterpret_cast<OutT*>(p.preact);
+    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+      const int m0 = (tile % num_m) * BM;
+      const int n0 = (tile / num_m) * BN;
+      if (!wait_or_abort(tmem_full + acc, acc_phase, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;            // warp-uniform
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        const int nvalid = min(32, p.N - col0);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (i < nvalid) {
+              float bv;
+              if (p.bias_dtype == kF32) bv = reinterpret_cast<const float*>(p.bias)[col0 + i];
+              else if (p.bias_dtype == kBF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col0 + i]);
+              else bv = __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + i]);
+              v[i] += bv;
+            }
+          }
+        }
+        if (row < p.M) {
+          const long long off = (long long)row * p.N + col0;
+          if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
+          if (p.act == 1) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+          }
+          store_row32<OutT>(C + off, v, nvalid);
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(tmem_empty + acc);
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
+  }
+
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ---------------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+}  // namespace
+
+// 2-D bf16/fp16 tensor map: `inner` contiguous elements per row, `outer` rows, 128-byte swizzle.
+bool make_tmap_2d(CUtensorMap* out, const void* base, long long inner, long long outer, int box_inner,
+                  int box_outer, int elem_dtype) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  const cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUtensorMapDataType dt = elem_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  return fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <int BN, bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt, int sms,
+                       cudaStream_t st) {
+  using L = SmemLayout<BN>;
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int grid = tiles < sms ? tiles : sms;
+  kern<<<grid, kGemmThreads, L::total, st>>>(ta, tb, p, in_fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+// Returns 0 on success, negative on a host-side failure.  `err` is a device int
+// that the kernel sets non-zero if one of its bounded waits gives up.
+int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
+                      int act, int M, int N, int K, bool a_mn, bool b_mn, int in_dtype, int out_dtype, int* err,
+                      int num_sms, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  // 16-byte global strides for TMA
+  if ((a_mn ? M : K) % 8 != 0 || (b_mn ? N : K) % 8 != 0) return -1;
+  const int BN = 256;
+  CUtensorMap ta, tb;
+  bool ok = a_mn ? make_tmap_2d(&ta, A, M, K, 64, 64, in_dtype) : make_tmap_2d(&ta, A, K, M, BK, BM, in_dtype);
+  ok = ok && (b_mn ? make_tmap_2d(&tb, B, N, K, 64, 64, in_dtype) : make_tmap_2d(&tb, B, K, N, BK, BN, in_dtype));
+  if (!ok) return -4;
+  GemmParams p{M, N, K, C, preact, bias, bias_dtype, act, err};
+  const int fmt = in_dtype == kBF16 ? 1 : 0;
+#define GEMM_CASE(AMN, BMN)                                                                              \
+  if (a_mn == AMN && b_mn == BMN) {                                                                      \
+    if (out_dtype == kBF16) return launch_gemm<256, AMN, BMN, __nv_bfloat16>(ta, tb, p, fmt, num_sms, st); \
+    if (out_dtype == kF16) return launch_gemm<256, AMN, BMN, __half>(ta, tb, p, fmt, num_sms, st);       \
+    return launch_gemm<256, AMN, BMN, float>(ta, tb, p, fmt, num_sms, st);                               \
+  }
+  GEMM_CASE(false, false)
+  GEMM_CASE(false, true)
+  GEMM_CASE(true, true)
+  GEMM_CASE(true, false)
+#undef GEMM_CASE
+  return -5;
+}
+
+}  // namespace mb

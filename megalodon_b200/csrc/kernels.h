@@ -1,0 +1,70 @@
+// Launchers of the sm_100a kernels.  Plain C++ signatures over raw device
+// pointers so the kernel translation units do not depend on libtorch.
+#pragma once
+
+#include <cuda_runtime.h>
+
+namespace mb {
+
+// ---- row-wise norms (norm_kernels.cu); weight dtype is fp32 or the activation dtype
+void rms_norm_fwd(const void* x, const void* w, float w_off, void* y, float* rstd, long long M, int D,
+                  float eps, int x_dtype, int w_dtype, cudaStream_t st);
+void rms_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* rstd, void* dx,
+                  float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st);
+void layer_norm_fwd(const void* x, const void* w, const void* b, float w_off, void* y, float* mean,
+                    float* rstd, long long M, int D, float eps, int x_dtype, int w_dtype, cudaStream_t st);
+void layer_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* mean,
+                    const float* rstd, void* dx, float* dw, float* db, long long M, int D, int x_dtype,
+                    int w_dtype, cudaStream_t st);
+
+// ---- TimestepNorm (timestep_norm_kernels.cu)
+void timestep_norm_fwd(const void* x, const long long* prev_count, const void* prev_mean,
+                       const void* prev_var, const void* gamma, float gamma_offset, const void* beta,
+                       const bool* mask, void* y, long long* count_out, void* mean_out, void* var_out,
+                       float* cummean, float* cumrstd, float* gu, float* gv, int B, int L, int H, int G,
+                       float eps, int x_dtype, int w_dtype, cudaStream_t st);
+void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_out, const void* x,
+                       const void* prev_mean, const long long* count_final, const float* cummean,
+                       const float* cumrstd, const void* gamma, float gamma_offset, const bool* mask,
+                       void* dx, void* dprev_mean, void* dprev_var, float* dgamma, float* dbeta,
+                       float* ux, float* ds, float* db, float* dux, float* dvx, int B, int L, int H, int G,
+                       int x_dtype, int w_dtype, cudaStream_t st);
+
+// ---- CEMA (cema_kernels.cu); complex tensors are interleaved (re, im) fp32
+constexpr int kCemaSegLen = 128;
+bool cema_supported_ndim(int N);
+int cema_num_segments(int L);
+// carry: scratch of B * S * N * D complex (S = cema_num_segments(L)); unused when S == 1
+void cema_fwd(const void* x, const float* p, const float* q, const float* gamma, const float* omega,
+              const float* hx, void* y, float* h_last, float* carry, int B, int L, int D, int N,
+              int x_dtype, cudaStream_t st);
+// dp [D,N], dq/dgamma [D,N,2], domega [D] must be zero-initialised (accumulated with atomics)
+void cema_bwd(const void* dy, const void* x, const float* p, const float* q, const float* gamma,
+              const float* omega, const float* hx, const float* dh_last, void* dx, float* dp, float* dq,
+              float* dgamma, float* domega, float* dhx, float* carry_a, float* carry_b, int B, int L,
+              int D, int N, int x_dtype, cudaStream_t st);
+
+// ---- element-wise (elementwise_kernels.cu)
+void swiglu_fwd(const void* a, const void* b, void* out, long long n, int dtype, cudaStream_t st);
+void swiglu_bwd(const void* g, const void* a, const void* b, void* da, void* db, long long n, int dtype,
+                cudaStream_t st);
+void rotary_apply(const void* x, const float* freqs, void* out, long long rows, int L, int H, int Dh,
+                  bool conj, int dtype, cudaStream_t st);
+void cross_entropy_fwd(const void* logits, const long long* target, float* loss, float* lse, long long rows,
+                       int V, long long ignore_index, int dtype, cudaStream_t st);
+void cross_entropy_bwd(const void* logits, const long long* target, const float* lse, const float* dloss,
+                       void* dlogits, long long rows, int V, long long ignore_index, int dtype,
+                       cudaStream_t st);
+void adamw_step(float* p, const void* g, float* m, float* v, void* low, long long n, float lr, float beta1,
+                float beta2, float eps, float wd, int step, float grad_scale, const float* scale_ptr,
+                int g_dtype, int low_dtype, cudaStream_t st);
+void sum_squares(const void* g, long long n, double* out, int dtype, cudaStream_t st);
+void scale_by_ptr(void* g, long long n, const float* scale, int dtype, cudaStream_t st);
+void clip_coef(const double* sumsq, float max_norm, float* norm_out, float* coef_out, cudaStream_t st);
+
+// ---- tcgen05 GEMM (gemm_sm100.cu): C[M,N] = act(A B^T + bias)
+int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
+                      int act, int M, int N, int K, bool a_mn, bool b_mn, int in_dtype, int out_dtype, int* err,
+                      int num_sms, cudaStream_t st);
+
+}  // namespace mb

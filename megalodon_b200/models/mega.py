@@ -68,10 +68,11 @@ class MegaBlock(nn.Module):
             dropout=cfg.dropout, hidden_dropout=cfg.hidden_dropout, norm_affine=cfg.norm_affine,
             norm_eps=cfg.norm_eps, rescale=rescale, init_mode=cfg.init_mode)
 
-    def forward(self, x: Tensor, freqs_cis: Tensor, mask: Optional[Tensor] = None, cache=None):
-        y, cache = self.mega(x, freqs_cis, mask, cache)
+    def forward(self, x: Tensor, freqs_cis: Tensor, mask: Optional[Tensor] = None, cache=None,
+                carry=None, piece=None):
+        y, state = self.mega(x, freqs_cis, mask, cache, carry, piece)
         # two-hop residual: the FFN adds the block input, not the attention output
-        return self.nffn(y, x), cache
+        return self.nffn(y, x), state
 
 
 class MegaOutputLayer(nn.Module):
@@ -87,14 +88,22 @@ class MegaOutputLayer(nn.Module):
         if self.share_emb:
             self.output.weight = embed_weight
 
-    def forward(self, x: Tensor, cache: Optional[Tuple[Tensor, Tensor, Tensor]] = None):
+    def normalize(self, x: Tensor, cache=None, carry=None, piece=None):
+        """Final TimestepNorm with the same cache / carry / piece protocol as the
+        MEGA layer.  Returns (normalised x, cache or carry)."""
         prev_count = prev_mean = prev_var = None
+        streaming = piece is not None
+        first_piece = piece is None or piece[0] == 0
+        last_piece = piece is None or piece[0] == piece[1] - 1
         if cache is not None:
             prev_count, prev_mean, prev_var = cache
-        elif should_recv_from_prev():
-            bsz, seq_len, _ = x.shape
+        elif carry is not None:
+            prev_count, prev_mean, prev_var = carry
+        elif first_piece and should_recv_from_prev():
+            bsz = x.size(0)
+            local_len = x.size(1) if piece is None else piece[2]
             g = self.final_norm.groups_per_partition
-            prev_count = torch.full((bsz,), seq_len * get_chunk_parallel_rank(), dtype=torch.int64,
+            prev_count = torch.full((bsz,), local_len * get_chunk_parallel_rank(), dtype=torch.int64,
                                     device=x.device)
             buf = torch.empty((bsz, 2 * g), dtype=x.dtype, device=x.device,
                               requires_grad=self.training and torch.is_grad_enabled())
@@ -104,11 +113,18 @@ class MegaOutputLayer(nn.Module):
         x, prev_count, prev_mean, prev_var = self.final_norm(x, prev_count, prev_mean, prev_var)
 
         if cache is not None:
-            cache = (prev_count.detach(), prev_mean.detach(), prev_var.detach())
-        elif should_send_to_next():
+            return x, (prev_count.detach(), prev_mean.detach(), prev_var.detach())
+        if last_piece and should_send_to_next():
             packed = send_to_next_chunk_parallel_region(torch.cat([prev_mean, prev_var], dim=-1))
             x = attach_to_graph(x, packed)
-        return self.output(x), cache
+        if streaming and not last_piece:
+            return x, (prev_count, prev_mean, prev_var)
+        return x, None
+
+    def forward(self, x: Tensor, cache: Optional[Tuple[Tensor, Tensor, Tensor]] = None, carry=None,
+                piece=None):
+        x, state = self.normalize(x, cache, carry, piece)
+        return self.output(x), state
 
 
 class Mega(nn.Module):
@@ -142,7 +158,18 @@ class Mega(nn.Module):
             self.layers.append(wrap(layer))
         self.output = MegaOutputLayer(cfg, self.embed.weight)
 
-    def forward(self, tokens: Tensor, cache=None):
+    def forward(self, tokens: Tensor, cache=None, targets: Optional[Tensor] = None):
+        """tokens [B, L].  Returns `(logits fp32 [B, L/cp, V], cache)`.
+
+        With `targets` [B, L] (training only) the vocabulary projection and the
+        cross-entropy are evaluated piece by piece and the first return value is
+        the vector of per-token losses gathered over the chunk group (what
+        `modules.losses.cross_entropy(logits, targets)` returns), so the fp32
+        logits of the whole sequence are never materialised.
+
+        `self.seq_microbatch_chunks = k` feeds the local sequence through every
+        layer in pieces of k chunks, carrying the TimestepNorm statistics and
+        CEMA state from piece to piece: same math, bounded activation memory."""
         bsz, seq_len = tokens.shape
         c = self.chunk_size
         if cache is None:
@@ -152,7 +179,10 @@ class Mega(nn.Module):
             seq_len //= self.chunk_parallel_size
             lo = self.chunk_parallel_rank * seq_len
             tokens = tokens[:, lo:lo + seq_len]
+            if targets is not None:
+                targets = targets[:, lo:lo + seq_len]
         else:
+            assert targets is None
             cache_layers, cache_output = cache
             first_kv = cache_layers[0][0]
             cache_len = 0 if first_kv is None else first_kv[-1]
@@ -172,16 +202,51 @@ class Mega(nn.Module):
             m = min(seq_len, c)
             mask = torch.full((1, 1, m, m + cache_len), float("-inf"), device=tokens.device)
             mask = torch.triu(mask, diagonal=cache_len + 1).to(x.dtype)
-
         freqs_cis = self.rope.get_freqs_cis(cache_len, min(cache_len + seq_len, c))
-        for i, layer in enumerate(self.layers):
-            x, layer_cache = layer(x, freqs_cis, mask, cache_layers[i] if cache is not None else None)
+
+        piece_len = None
+        k = getattr(self, "seq_microbatch_chunks", None)
+        if cache is None and k and seq_len > k * c:
+            piece_len = k * c
+        if piece_len is None:
+            for i, layer in enumerate(self.layers):
+                x, layer_cache = layer(x, freqs_cis, mask, cache_layers[i] if cache is not None else None)
+                if cache is not None:
+                    cache_layers[i] = layer_cache
+            if targets is not None:
+                xn, _ = self.output.normalize(x)
+                return self._gather_losses([self._piece_loss(xn, targets)]), None
+            out, cache_output = self.output(x, cache_output)
             if cache is not None:
-                cache_layers[i] = layer_cache
-        out, cache_output = self.output(x, cache_output)
-        if cache is not None:
-            cache = (cache_layers, cache_output)
-        return out.float(), cache
+                cache = (cache_layers, cache_output)
+            return out.float(), cache
+
+        # ---- sequence micro-batching (training / scoring without cache)
+        pieces = list(torch.split(x, piece_len, dim=1))
+        n = len(pieces)
+        for layer in self.layers:
+            carry = None
+            for i in range(n):
+                pieces[i], carry = layer(pieces[i], freqs_cis, mask, None, carry, (i, n, seq_len))
+        outs, carry = [], None
+        tgt = None if targets is None else torch.split(targets, piece_len, dim=1)
+        for i in range(n):
+            xn, carry = self.output.normalize(pieces[i], None, carry, (i, n, seq_len))
+            pieces[i] = None
+            outs.append(self._piece_loss(xn, tgt[i]) if targets is not None else self.output.output(xn).float())
+        if targets is not None:
+            return self._gather_losses(outs), None
+        return torch.cat(outs, dim=1), None
+
+    def _piece_loss(self, xn: Tensor, targets: Tensor) -> Tensor:
+        logits = self.output.output(xn)
+        return ops.cross_entropy(logits.flatten(0, 1), targets.flatten(0, 1)).view(targets.shape)
+
+    @staticmethod
+    def _gather_losses(parts: List[Tensor]) -> Tensor:
+        from ..parallel.chunk_parallel import gather_from_chunk_parallel_region
+        local = parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)
+        return gather_from_chunk_parallel_region(local.flatten())
 
 
 def build_model(model_cfg: ModelConf, dtype: str, fp32_reduce_scatter: bool = False,

@@ -35,8 +35,7 @@ class FusedLayerNorm(nn.Module):
             self.register_parameter("bias", None)
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:
-        w = None if self.weight is None else self.weight + 1.0
-        return ops.layer_norm(input_, w, self.bias, self.eps)
+        return ops.layer_norm(input_, self.weight, self.bias, self.eps, weight_offset=1.0)
 
     def extra_repr(self):
         return f"{tuple(self.normalized_shape)}, eps={self.eps}, elementwise_affine={self.elementwise_affine}"
@@ -54,8 +53,7 @@ class FusedRMSNorm(nn.Module):
             self.register_parameter("weight", None)
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:
-        w = None if self.weight is None else self.weight + 1.0
-        return ops.rms_norm(input_, w, self.eps)
+        return ops.rms_norm(input_, self.weight, self.eps, weight_offset=1.0)
 
     def extra_repr(self):
         return f"{tuple(self.normalized_shape)}, eps={self.eps}, elementwise_affine={self.elementwise_affine}"
@@ -67,8 +65,7 @@ def layernorm_fwd(x: torch.Tensor, weight: Optional[torch.Tensor], bias: Optiona
     xf = x.float()
     mean = xf.mean(-1)
     invvar = torch.rsqrt(xf.var(-1, unbiased=False) + eps)
-    w = None if weight is None else weight + 1.0
-    return ops.layer_norm(x, w, bias, eps), mean, invvar
+    return ops.layer_norm(x, weight, bias, eps, weight_offset=1.0), mean, invvar
 
 
 def layernorm_bwd(y_grad, x, mean, invvar, weight, bias, dim: int, eps: float):
@@ -85,8 +82,7 @@ def layernorm_bwd(y_grad, x, mean, invvar, weight, bias, dim: int, eps: float):
 
 def rmsnorm_fwd(x: torch.Tensor, weight: Optional[torch.Tensor], dim: int, eps: float):
     invvar = torch.rsqrt(x.float().pow(2).mean(-1) + eps)
-    w = None if weight is None else weight + 1.0
-    return ops.rms_norm(x, w, eps), invvar
+    return ops.rms_norm(x, weight, eps, weight_offset=1.0), invvar
 
 
 def rmsnorm_bwd(y_grad, x, invvar, weight, dim: int, eps: float):

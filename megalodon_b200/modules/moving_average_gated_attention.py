@@ -155,11 +155,11 @@ class MovingAverageGatedAttention(nn.Module):
         self.beta = Parameter(torch.zeros(2, self.z_head_dim * self.local_heads))
 
     # ---- chunk-parallel state packing: [mean(G) | var(G) | Re/Im h (2 D N)] fp32 ----
-    def _empty_prev(self, x: Tensor):
-        bsz, seq_len, _ = x.shape
+    def _empty_prev(self, x: Tensor, local_len: int):
+        bsz = x.size(0)
         g = self.timenorm.groups_per_partition
         width = 2 * g + 2 * self.local_mdim * self.cema.ndim
-        prev_count = torch.full((bsz,), seq_len * get_chunk_parallel_rank(), dtype=torch.int64,
+        prev_count = torch.full((bsz,), local_len * get_chunk_parallel_rank(), dtype=torch.int64,
                                 device=x.device)
         buf = torch.empty((bsz, width), dtype=torch.float32, device=x.device,
                           requires_grad=self.training and torch.is_grad_enabled())
@@ -175,29 +175,46 @@ class MovingAverageGatedAttention(nn.Module):
         return mean.to(x.dtype), var.to(x.dtype), _r2c(h.reshape(x.size(0), d, n, 2))
 
     def forward(self, x: Tensor, freqs_cis: Tensor, mask: Optional[Tensor] = None,
-                cache: Optional[Tuple] = None):
+                cache: Optional[Tuple] = None, carry: Optional[Tuple] = None,
+                piece: Optional[Tuple[int, int, int]] = None):
+        """`cache`: inference state (detached).  `carry` / `piece`: sequence
+        micro-batching in training - the local sequence is fed in `piece[1]`
+        consecutive pieces (`piece = (index, count, local_len)`), and `carry =
+        (count, mean, var, hx)` hands the differentiable running state from one
+        piece to the next; only the first piece receives from the previous
+        chunk-parallel rank and only the last one sends to the next."""
         bsz, seq_len, _ = x.shape
         residual = x
+        streaming = piece is not None
+        first_piece = piece is None or piece[0] == 0
+        last_piece = piece is None or piece[0] == piece[1] - 1
+        local_len = seq_len if piece is None else piece[2]
         cache_attn = cache_norm = hx = None
         prev_count = prev_mean = prev_var = None
         if cache is not None:
             cache_attn, cache_norm, hx = cache
             prev_count, prev_mean, prev_var = cache_norm
-        elif should_recv_from_prev():
-            prev_count, buf = self._empty_prev(x)
+        elif carry is not None:
+            prev_count, prev_mean, prev_var, hx = carry
+        elif first_piece and should_recv_from_prev():
+            prev_count, buf = self._empty_prev(x, local_len)
             packed = recv_from_prev_chunk_parallel_region(buf)
             prev_mean, prev_var, hx = self._unpack_prev_tensors(x, packed)
 
         out_tsn, prev_count, prev_mean, prev_var = self.timenorm(x, prev_count, prev_mean, prev_var)
-        need_state = cache_attn is not None or (cache is None and should_send_to_next())
+        send_now = cache is None and last_piece and should_send_to_next()
+        need_state = cache_attn is not None or send_now or (streaming and not last_piece)
         out_cema, hx = self.cema.forward_channels_last(out_tsn, hx, need_state)
 
+        new_carry = None
         if cache is not None:
             cache_norm = (prev_count.detach(), prev_mean.detach(), prev_var.detach())
             hx = None if hx is None else hx.detach()
-        elif should_send_to_next():
+        elif send_now:
             packed = send_to_next_chunk_parallel_region(self._pack_prev_tensors(prev_mean, prev_var, hx))
             out_cema = attach_to_graph(out_cema, packed)
+        elif streaming and not last_piece:
+            new_carry = (prev_count, prev_mean, prev_var, hx)
 
         out_cema = gather_from_model_parallel_region(out_cema)
         mx = self.rmsnorm(out_cema)
@@ -219,8 +236,8 @@ class MovingAverageGatedAttention(nn.Module):
         h = ops.memory_efficient_dropout(h, self.dropout, self.training)
         out = h + residual
         if cache is not None:
-            cache = (cache_attn, cache_norm, hx)
-        return out, cache
+            return out, (cache_attn, cache_norm, hx)
+        return out, new_carry
 
     def extra_repr(self) -> str:
         return (f"edim={self.mdim}, zdim={self.zdim}, hdim={self.hdim}, heads={self.num_heads}, "

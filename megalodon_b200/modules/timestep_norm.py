@@ -71,8 +71,8 @@ class TimestepNorm(nn.Module):
         prev_count = c0 if prev_count is None else prev_count
         prev_mean = m0 if prev_mean is None else prev_mean
         prev_var = v0 if prev_var is None else prev_var
-        return ops.timestep_norm(x, prev_count, prev_mean, prev_var, self.weight + 1.0, self.bias,
-                                 padding_mask, self.groups_per_partition, self.eps)
+        return ops.timestep_norm(x, prev_count, prev_mean, prev_var, self.weight, self.bias,
+                                 padding_mask, self.groups_per_partition, self.eps, gamma_offset=1.0)
 
     def extra_repr(self) -> str:
         return (f"num_features={self.num_features} ({self.features_per_partition}), "

@@ -43,26 +43,28 @@ def swiglu(a: Tensor, b: Tensor) -> Tensor:
 
 
 # ------------------------------------------------------------------ norms
-def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
+def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float, weight_offset: float = 0.0) -> Tensor:
+    """The scale applied is `weight + weight_offset`, formed in fp32."""
     if native_for(x):
-        return _cuda().rms_norm(x, weight, eps)
-    return reference.rms_norm(x, weight, eps)
+        return _cuda().rms_norm(x, weight, eps, weight_offset)
+    return reference.rms_norm(x, weight, eps, weight_offset)
 
 
-def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float) -> Tensor:
+def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float,
+               weight_offset: float = 0.0) -> Tensor:
     if native_for(x):
-        return _cuda().layer_norm(x, weight, bias, eps)
-    return reference.layer_norm(x, weight, bias, eps)
+        return _cuda().layer_norm(x, weight, bias, eps, weight_offset)
+    return reference.layer_norm(x, weight, bias, eps, weight_offset)
 
 
 def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=None,
-                  num_groups=None, eps: float = 1e-5):
+                  num_groups=None, eps: float = 1e-5, gamma_offset: float = 0.0):
     """Returns (y, count, mean, var); see `reference.timestep_norm`."""
     if native_for(x):
         return _cuda().timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
-                                     padding_mask, num_groups, eps)
+                                     padding_mask, num_groups, eps, gamma_offset)
     return reference.timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
-                                   padding_mask, num_groups, eps)
+                                   padding_mask, num_groups, eps, gamma_offset)
 
 
 def sequence_norm(x, gamma, beta, padding_mask=None, num_groups=None, eps: float = 1e-5,
@@ -128,6 +130,13 @@ def rotary(x, freqs_cis, conj: bool = False):
 
 
 # ------------------------------------------------------------------ loss / optimiser
+def sum_squares(g: Tensor, out: Tensor) -> None:
+    """out (fp64 scalar tensor) += sum(g^2)."""
+    if native_for(g):
+        return _cuda().sum_squares(g, out)
+    out.add_(g.double().pow(2).sum())
+
+
 def cross_entropy(logits, target, weight=None, ignore_index: int = -100, label_smoothing: float = 0.0):
     """Per-token negative log-likelihood [N]; logits [N, V] in any float dtype."""
     if native_for(logits) and weight is None and label_smoothing == 0.0:

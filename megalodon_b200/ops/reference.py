@@ -20,19 +20,21 @@ Tensor = torch.Tensor
 
 
 # --------------------------------------------------------------------------- norms
-def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float) -> Tensor:
-    """y = x * rsqrt(mean(x^2) + eps) * weight over the last dim; `weight` is the
-    effective scale (callers pass `param + 1`)."""
+def rms_norm(x: Tensor, weight: Optional[Tensor], eps: float, weight_offset: float = 0.0) -> Tensor:
+    """y = x * rsqrt(mean(x^2) + eps) * (weight + weight_offset) over the last
+    dim; the scale is formed in fp32 (modules keep zero-centred weights and
+    pass offset 1)."""
     xf = x.float()
     y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps)
     if weight is not None:
-        y = y * weight.float()
+        y = y * (weight.float() + weight_offset)
     return y.to(x.dtype)
 
 
-def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float) -> Tensor:
+def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps: float,
+               weight_offset: float = 0.0) -> Tensor:
     y = F.layer_norm(x.float(), (x.shape[-1],),
-                     None if weight is None else weight.float(),
+                     None if weight is None else weight.float() + weight_offset,
                      None if bias is None else bias.float(), eps)
     return y.to(x.dtype)
 
@@ -40,7 +42,7 @@ def layer_norm(x: Tensor, weight: Optional[Tensor], bias: Optional[Tensor], eps:
 def timestep_norm(
     x: Tensor, prev_count: Tensor, prev_mean: Tensor, prev_var: Tensor,
     gamma: Tensor, beta: Tensor, padding_mask: Optional[Tensor],
-    num_groups: Optional[int], eps: float,
+    num_groups: Optional[int], eps: float, gamma_offset: float = 0.0,
 ) -> Tuple[Tensor, Tensor, Tensor, Tensor]:
     """Cumulative (prefix) group normalisation over time.
 
@@ -76,7 +78,7 @@ def timestep_norm(
     var = torch.where(empty, v0.expand_as(var), var)
     rstd = torch.rsqrt(var + eps)
     y = (xd - mean.unsqueeze(-1)) * rstd.unsqueeze(-1)
-    y = y.view(B, L, H) * gamma.double() + beta.double()
+    y = y.view(B, L, H) * (gamma.double() + gamma_offset) + beta.double()
     y = y * valid
     count = prev_count + (valid.squeeze(-1).sum(1)).to(prev_count.dtype)
     return y.to(x.dtype), count, mean[:, -1].to(prev_mean.dtype), var[:, -1].to(prev_var.dtype)

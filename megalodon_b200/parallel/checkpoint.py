@@ -35,17 +35,17 @@ def _rng_restore(device: torch.device, snap) -> None:
 
 class _Checkpoint(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, run_fn, n_tensors, dummy, *args):
-        tensors = args[:n_tensors]
+    def forward(ctx, run_fn, spec, dummy, *tensors):
+        # `spec` rebuilds the original argument list from (tensor slots, constants)
         ctx.run_fn = run_fn
-        ctx.extra = args[n_tensors:]
+        ctx.spec = spec
         device = tensors[0].device
         ctx.device = device
         ctx.rng = _rng_snapshot(device)
         ctx.tape = HandoffTape()
         ctx.save_for_backward(*tensors)
         with torch.no_grad(), use_tape(ctx.tape):
-            out = run_fn(*tensors, *ctx.extra)
+            out = run_fn(*_rebuild(spec, tensors))
         return out
 
     @staticmethod
@@ -55,7 +55,7 @@ class _Checkpoint(torch.autograd.Function):
         _rng_restore(ctx.device, ctx.rng)
         ctx.tape.start_replay()
         with torch.enable_grad(), use_tape(ctx.tape):
-            out = ctx.run_fn(*inputs, *ctx.extra)
+            out = ctx.run_fn(*_rebuild(ctx.spec, inputs))
         _rng_restore(ctx.device, now)
         outs = out if isinstance(out, (tuple, list)) else (out,)
         pairs = [(o, g) for o, g in zip(outs, grads)
@@ -63,25 +63,40 @@ class _Checkpoint(torch.autograd.Function):
         if pairs:
             torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         in_grads = tuple(t.grad if t.requires_grad else None for t in inputs)
-        return (None, None, None) + in_grads + (None,) * len(ctx.extra)
+        return (None, None, None) + in_grads
+
+
+def _rebuild(spec, tensors):
+    return [tensors[v] if is_slot else v for is_slot, v in spec]
 
 
 def checkpoint(fn, *args):
-    """Run `fn(*args)` under activation checkpointing.  Leading tensor arguments
-    are differentiated through; everything from the first non-tensor argument
-    on is passed along untouched (masks, tables, `None`)."""
-    n = 0
-    while n < len(args) and isinstance(args[n], torch.Tensor) and args[n].is_floating_point():
-        n += 1
-    assert n > 0, "checkpoint needs at least one floating-point tensor argument"
-    dummy = torch.empty(0, requires_grad=True, device=args[0].device)
-    return _Checkpoint.apply(fn, n, dummy, *args)
+    """Run `fn(*args)` under activation checkpointing.  Tensor arguments that
+    require grad are differentiated through (real or complex); every other
+    argument (masks, tables, integer tensors, `None`) is passed along as a
+    constant.  `fn` must return a tensor or a flat tuple of tensors / None."""
+    spec, tensors = [], []
+    for a in args:
+        if isinstance(a, torch.Tensor) and a.requires_grad:
+            spec.append((True, len(tensors)))
+            tensors.append(a)
+        else:
+            spec.append((False, a))
+    if not tensors:
+        # nothing upstream needs a gradient: still recompute for the parameters
+        first = next(a for a in args if isinstance(a, torch.Tensor))
+        anchor = first.detach().requires_grad_(True)
+        spec[[i for i, a in enumerate(args) if a is first][0]] = (True, 0)
+        tensors.append(anchor)
+    dummy = torch.empty(0, requires_grad=True, device=tensors[0].device)
+    return _Checkpoint.apply(fn, tuple(spec), dummy, *tensors)
 
 
 class CheckpointWrapper(nn.Module):
-    """Wraps a block whose forward is `block(x, freqs_cis, mask, cache)` and
-    returns `(y, cache)`.  Calls with a cache (inference) or without autograd
-    run the block directly."""
+    """Wraps a block with signature `block(x, freqs_cis, mask, cache, carry, piece)`
+    returning `(y, state)`, where `state` is an inference cache, a tuple of
+    carried tensors (sequence micro-batching) or None.  Calls with a cache
+    (inference) or without autograd run the block directly."""
 
     _is_wrapper = True
 
@@ -95,17 +110,17 @@ class CheckpointWrapper(nn.Module):
         except AttributeError:
             return getattr(self._modules["_wrapped"], name)
 
-    def forward(self, x, *rest):
-        cache = rest[-1] if rest else None
+    def forward(self, x, freqs_cis=None, mask=None, cache=None, carry=None, piece=None):
         if cache is not None or not torch.is_grad_enabled():
-            return self._wrapped(x, *rest)
+            return self._wrapped(x, freqs_cis, mask, cache, carry, piece)
 
-        def run(x_, *extra):
-            y, _ = self._wrapped(x_, *extra)
-            return y
+        def run(x_, freqs_, mask_, piece_, *carry_):
+            y, state = self._wrapped(x_, freqs_, mask_, None, tuple(carry_) if carry_ else None, piece_)
+            return (y,) + (tuple(state) if state is not None else ())
 
-        y = checkpoint(run, x, *rest)
-        return y, None
+        out = checkpoint(run, x, freqs_cis, mask, piece, *(carry or ()))
+        y, state = out[0], out[1:]
+        return y, (tuple(state) if state else None)
 
 
 def checkpoint_wrapper(module: nn.Module) -> CheckpointWrapper:

@@ -160,6 +160,8 @@ class FullyShardedDataParallel(nn.Module):
         self._full_leaf: Optional[torch.Tensor] = None
         self._full_version = -1
         self._bwd_hook_armed = False
+        self._calls = 0
+        self._fires = 0
 
     # ------------------------------------------------------------------ construction
     def _flatten(self, module: nn.Module, device: Optional[torch.device]) -> None:
@@ -325,12 +327,19 @@ class FullyShardedDataParallel(nn.Module):
             self._gather_full()
         want_grad = torch.is_grad_enabled() and p.requires_grad
         if want_grad:
-            leaf = self._full.detach().requires_grad_(True)
-            leaf.register_post_accumulate_grad_hook(self._post_backward)
-            self._full_leaf = leaf
+            # One leaf per iteration: when the unit is called several times before
+            # backward (sequence micro-batching) every call shares it, so the
+            # gradients of all calls accumulate into one flat buffer.
+            if self._full_leaf is None:
+                leaf = self._full.detach().requires_grad_(True)
+                leaf.register_post_accumulate_grad_hook(self._post_backward)
+                self._full_leaf = leaf
+                self._calls = 0
+                self._fires = 0
+                self._set_views(leaf)
+            self._calls += 1
         else:
-            leaf = self._full
-        self._set_views(leaf)
+            self._set_views(self._full)
         self.training_state = TrainingState.FORWARD
         out = self._wrapped(*args, **kwargs)
         self.training_state = TrainingState.IDLE
@@ -360,9 +369,17 @@ class FullyShardedDataParallel(nn.Module):
         return out
 
     def _post_backward(self, leaf: torch.Tensor):
-        """Runs once the gradient of the unit's whole flat buffer is known."""
+        """Runs whenever autograd has accumulated into the flat leaf.  With an
+        activation-checkpointed block that is once per forward call of this
+        iteration (each recomputation runs its own backward); otherwise once."""
+        from .checkpoint import CheckpointWrapper
+        self._fires += 1
+        expected = self._calls if isinstance(self._wrapped, CheckpointWrapper) else 1
+        if self._fires < expected:
+            return None          # keep accumulating in leaf.grad
         flat_grad = leaf.grad
         leaf.grad = None
+        self._full_leaf = None
         p = self.flat_param
         red_dtype = torch.float32 if (self.fp32_reduce_scatter or not self.mixed_precision) else self.compute_dtype
         g = flat_grad if flat_grad.dtype == red_dtype else flat_grad.to(red_dtype)
@@ -391,7 +408,6 @@ class FullyShardedDataParallel(nn.Module):
             p._grad_shard = p._grad_shard + shard
         if self.reshard_after_forward and not self._is_root:
             self._free_full()
-        self._full_leaf = None
         return None
 
     def _sync_comm(self) -> None:
@@ -405,6 +421,16 @@ class FullyShardedDataParallel(nn.Module):
         `.grad` on the flat parameters.  Called by every public method that
         reads gradients; safe to call more than once."""
         self._lazy_init()
+        from .checkpoint import CheckpointWrapper
+        for u in self._units():
+            leaf = u._full_leaf
+            if leaf is None:
+                continue
+            if leaf.grad is not None:      # backward ended before every expected accumulation arrived
+                u._fires = (u._calls if isinstance(u._wrapped, CheckpointWrapper) else 1) - 1
+                u._post_backward(leaf)
+            else:
+                u._full_leaf = None
         self._sync_comm()
         if self.materialize_fp32_grads:
             for u in self._units():
@@ -450,6 +476,8 @@ class FullyShardedDataParallel(nn.Module):
         max_norm, norm_type = float(max_norm), float(norm_type)
         grads = self._grad_tensors()
         dev = self.compute_device
+        if dev.type == "cuda" and norm_type == 2.0:
+            return self._clip_l2_on_device(grads, max_norm)
         local = calc_grad_norm(grads, norm_type).to(dev)
         if norm_type == math.inf:
             total = local
@@ -469,6 +497,24 @@ class FullyShardedDataParallel(nn.Module):
             for g in grads:
                 g.mul_(coef.to(g.dtype))
         return total
+
+    def _clip_l2_on_device(self, grads: List[torch.Tensor], max_norm: float) -> torch.Tensor:
+        """L2 clipping without a host round trip: sum-of-squares kernels into one
+        fp64 scalar, scalar all-reduces, then every gradient is scaled by a
+        coefficient that stays on the device (a no-op kernel when it is 1)."""
+        from .. import ops
+        from ..ops import cuda_ops
+        acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
+        for g in grads:
+            ops.sum_squares(g, acc)
+        if self.world_size > 1:
+            dist.all_reduce(acc, group=self.process_group)
+        if self.model_parallel_world_size > 1:
+            dist.all_reduce(acc, group=self.model_parallel_process_group)
+        norm, coef = cuda_ops.clip_coef(acc, max_norm)
+        for g in grads:
+            cuda_ops.scale_by_ptr(g, coef)
+        return norm
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         for u in self._units():

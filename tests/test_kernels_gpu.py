@@ -1,0 +1,297 @@
+"""CUDA kernels against the plain-PyTorch fp32/fp64 statements of the same
+operators (values and gradients).  Needs a B200; run with `-m gpu`."""
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _dev():
+    return torch.device("cuda", 0)
+
+
+def _close(a, b, atol, rtol, what=""):
+    a, b = a.float(), b.float()
+    err = (a - b).abs().max().item()
+    ref = b.abs().max().item()
+    assert torch.allclose(a, b, atol=atol, rtol=rtol), f"{what}: max err {err:.3e} (ref max {ref:.3e})"
+
+
+def _tol(dtype):
+    return (2e-5, 2e-4) if dtype == torch.float32 else (3e-2, 3e-2)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D", [256, 1000, 4096])
+def test_rms_and_layer_norm(dtype, D):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(0)
+    x = torch.randn(3, 37, D, device=_dev(), dtype=dtype)
+    w = (torch.randn(D, device=_dev()) * 0.1).to(dtype)
+    b = (torch.randn(D, device=_dev()) * 0.1).to(dtype)
+    g = torch.randn_like(x)
+    atol, rtol = _tol(dtype)
+    for kind in ("rms", "rms_noaffine", "layer"):
+        xs = [x.clone().requires_grad_(), x.clone().requires_grad_()]
+        ws = [w.clone().requires_grad_(), w.clone().requires_grad_()]
+        bs = [b.clone().requires_grad_(), b.clone().requires_grad_()]
+        outs = []
+        for i, mod in enumerate((ops, reference)):
+            if kind == "rms":
+                y = mod.rms_norm(xs[i], ws[i], 1e-5, 1.0)
+            elif kind == "rms_noaffine":
+                y = mod.rms_norm(xs[i], None, 1e-5, 0.0)
+            else:
+                y = mod.layer_norm(xs[i], ws[i], bs[i], 1e-5, 1.0)
+            y.backward(g)
+            outs.append(y)
+        _close(outs[0], outs[1], atol, rtol, f"{kind} y")
+        _close(xs[0].grad, xs[1].grad, atol * 4, rtol, f"{kind} dx")
+        if kind != "rms_noaffine":
+            _close(ws[0].grad, ws[1].grad, atol * 40, rtol * 3, f"{kind} dw")
+        if kind == "layer":
+            _close(bs[0].grad, bs[1].grad, atol * 40, rtol * 3, f"{kind} db")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,H,G,masked", [(2, 70, 64, 8, True), (1, 1, 128, 32, False),
+                                            (2, 1030, 256, 4, False), (1, 300, 96, 96, True)])
+def test_timestep_norm(dtype, B, L, H, G, masked):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(1)
+    dev = _dev()
+    x = torch.randn(B, L, H, device=dev, dtype=dtype) * 1.5 + 0.3
+    pc = torch.tensor([5, 0][:B], device=dev, dtype=torch.int64) if G != H else torch.full((B,), 4, device=dev)
+    pm = (torch.randn(B, G, device=dev) * 0.2).to(dtype)
+    pv = (torch.rand(B, G, device=dev) + 0.5).to(dtype)
+    gamma = (torch.randn(H, device=dev) * 0.1).to(dtype)
+    beta = (torch.randn(H, device=dev) * 0.1).to(dtype)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool, device=dev)
+        mask[0, L - L // 4:] = True
+        if L > 4:
+            mask[-1, 3] = True
+    gy = torch.randn_like(x)
+    gm = torch.randn(B, G, device=dev).to(dtype)
+    gv = torch.randn(B, G, device=dev).to(dtype)
+    res = []
+    for mod in (ops, reference):
+        leaves = [t.clone().requires_grad_() for t in (x, pm, pv, gamma, beta)]
+        y, c, m, v = mod.timestep_norm(leaves[0], pc, leaves[1], leaves[2], leaves[3], leaves[4], mask, G,
+                                       1e-5, 1.0)
+        (y.float() * gy.float()).sum().add((m.float() * gm.float()).sum()).add((v.float() * gv.float()).sum()).backward()
+        res.append((y, c, m, v, [t.grad for t in leaves]))
+    atol, rtol = _tol(dtype)
+    (y0, c0, m0, v0, g0), (y1, c1, m1, v1, g1) = res
+    assert torch.equal(c0, c1)
+    _close(y0, y1, atol * 2, rtol, "y")
+    _close(m0, m1, atol, rtol, "mean")
+    _close(v0, v1, atol, rtol, "var")
+    names = ["dx", "dprev_mean", "dprev_var", "dgamma", "dbeta"]
+    scale = [4, 20, 20, 60, 60]
+    for n, s, a, b in zip(names, scale, g0, g1):
+        _close(a, b, atol * s, rtol * 3, n)
+
+
+def _cema_coeffs(D, N, dev):
+    alpha = torch.sigmoid(torch.randn(D, N, 1, device=dev))
+    delta = torch.sigmoid(torch.randn(D, N, 1, device=dev))
+    theta = torch.sigmoid(torch.randn(D, 1, 1, device=dev)) * (2 * math.pi / N) * \
+        torch.arange(1, N + 1, device=dev).view(1, N, 1)
+    p = alpha
+    q = torch.polar(1.0 - alpha * delta, theta)
+    gamma = torch.view_as_complex(torch.randn(D, N, 2, device=dev)) * math.sqrt(1.0 / N)
+    omega = torch.randn(D, 1, device=dev) * 0.3
+    return p, q, gamma, omega
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,L,D,N,with_h", [(2, 37, 24, 16, True), (1, 300, 40, 16, True),
+                                            (2, 260, 16, 4, False), (1, 1, 32, 16, True),
+                                            (2, 513, 8, 8, True)])
+def test_cema(dtype, B, L, D, N, with_h):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(2)
+    dev = _dev()
+    x = (torch.randn(B, L, D, device=dev)).to(dtype)
+    p, q, gamma, omega = _cema_coeffs(D, N, dev)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2, device=dev)) if with_h else None
+    gy = torch.randn_like(x)
+    gh = torch.view_as_complex(torch.randn(B, D, N, 2, device=dev))
+    res = []
+    for mod in (ops, reference):
+        leaves = [t.clone().requires_grad_() for t in (x, p, q, gamma, omega)]
+        h_in = None if hx is None else hx.clone().requires_grad_()
+        y, h = mod.cema(leaves[0], leaves[1], leaves[2], leaves[3], leaves[4], h_in, True)
+        loss = (y.float() * gy.float()).sum() + (torch.view_as_real(h) * torch.view_as_real(gh)).sum()
+        loss.backward()
+        res.append((y, h, [t.grad for t in leaves] + ([h_in.grad] if h_in is not None else [])))
+    atol, rtol = (1e-4, 1e-3) if dtype == torch.float32 else (4e-2, 4e-2)
+    (y0, h0, g0), (y1, h1, g1) = res
+    _close(y0, y1, atol, rtol, "y")
+    _close(torch.view_as_real(h0), torch.view_as_real(h1), 1e-3, 1e-2, "h_last")
+    names = ["dx", "dp", "dq", "dgamma", "domega", "dhx"]
+    for n, a, b in zip(names, g0, g1):
+        if a.is_complex():
+            a, b = torch.view_as_real(a), torch.view_as_real(b)
+        big = b.float().abs().max().item() + 1.0
+        tol = (2e-3 if dtype == torch.float32 else 6e-2) * big
+        _close(a, b, tol, rtol, n)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_elementwise(dtype):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(3)
+    dev = _dev()
+    atol, rtol = _tol(dtype)
+    a = torch.randn(5, 33, 96, device=dev, dtype=dtype)
+    b = torch.randn_like(a)
+    g = torch.randn_like(a)
+    outs = []
+    for mod in (ops, reference):
+        aa, bb = a.clone().requires_grad_(), b.clone().requires_grad_()
+        y = mod.swiglu(aa, bb)
+        y.backward(g)
+        outs.append((y, aa.grad, bb.grad))
+    for u, v in zip(*outs):
+        _close(u, v, atol, rtol, "swiglu")
+    # rotary
+    x = torch.randn(2, 16, 3, 64, device=dev, dtype=dtype)
+    ang = torch.outer(torch.arange(16, device=dev).float(), torch.rand(32, device=dev))
+    fc = torch.polar(torch.ones_like(ang), ang)
+    for conj in (False, True):
+        _close(ops.rotary(x, fc, conj), reference.rotary(x, fc, conj), atol, rtol, "rotary")
+    xr = x.clone().requires_grad_()
+    ops.rotary(xr, fc).backward(g[:2, :16, :3, :64].contiguous())
+    xr2 = x.clone().requires_grad_()
+    reference.rotary(xr2, fc).backward(g[:2, :16, :3, :64].contiguous())
+    _close(xr.grad, xr2.grad, atol, rtol, "rotary grad")
+
+
+def test_cross_entropy_and_adamw():
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(4)
+    dev = _dev()
+    logits = torch.randn(50, 1000, device=dev) * 3
+    tgt = torch.randint(0, 1000, (50,), device=dev)
+    tgt[7] = -100
+    g = torch.rand(50, device=dev)
+    outs = []
+    for mod in (ops, reference):
+        l = logits.clone().requires_grad_()
+        loss = mod.cross_entropy(l, tgt)
+        loss.backward(g)
+        outs.append((loss, l.grad))
+    _close(outs[0][0], outs[1][0], 1e-4, 1e-4, "ce")
+    _close(outs[0][1], outs[1][1], 1e-5, 1e-3, "ce grad")
+
+    n = 4096 + 64
+    state = [torch.randn(n, device=dev) for _ in range(2)]
+    grad = torch.randn(n, device=dev)
+    for gdtype in (torch.float32, torch.bfloat16):
+        ps = [state[0].clone(), state[0].clone()]
+        ms = [torch.zeros(n, device=dev), torch.zeros(n, device=dev)]
+        vs = [torch.zeros(n, device=dev), torch.zeros(n, device=dev)]
+        lows = [torch.empty(n, device=dev, dtype=torch.bfloat16) for _ in range(2)]
+        for step in (1, 2, 3):
+            for i, mod in enumerate((ops, reference)):
+                mod.adamw_step(ps[i], grad.to(gdtype), ms[i], vs[i], lr=1e-2, beta1=0.9, beta2=0.98, eps=1e-8,
+                               weight_decay=0.1, step=step, grad_scale=0.5, low=lows[i])
+        _close(ps[0], ps[1], 1e-5, 1e-4, "adamw p")
+        _close(ms[0], ms[1], 1e-6, 1e-4, "adamw m")
+        _close(vs[0], vs[1], 1e-6, 1e-4, "adamw v")
+        _close(lows[0], lows[1], 1e-2, 1e-2, "adamw low")
+    acc = torch.zeros((), dtype=torch.float64, device=dev)
+    ops.sum_squares(grad.bfloat16(), acc)
+    assert abs(acc.item() - grad.bfloat16().double().pow(2).sum().item()) < 1e-3 * acc.item()
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (300, 264, 136), (4096, 1024, 4096), (512, 11264, 4096)])
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_tcgen05_gemm(M, N, K, layout):
+    """C = A B^T for K-major / MN-major operand layouts against fp32 matmul of the same bf16 inputs."""
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(5)
+    dev = _dev()
+    A = torch.randn(M, K, device=dev).bfloat16()
+    Bm = torch.randn(N, K, device=dev).bfloat16()
+    ref = A.float() @ Bm.float().t()
+    if layout == "nt":
+        out, _ = cuda_ops.gemm(A, Bm)
+    elif layout == "nn":          # B stored [K, N]
+        out, _ = cuda_ops.gemm(A, Bm.t().contiguous(), b_mn=True)
+    else:                          # A stored [K, M], B stored [K, N]
+        out, _ = cuda_ops.gemm(A.t().contiguous(), Bm.t().contiguous(), a_mn=True, b_mn=True)
+    torch.cuda.synchronize()
+    cuda_ops.check_kernel_errors()
+    tol = 2e-2 * math.sqrt(K)
+    _close(out, ref, tol, 2e-2, f"gemm {layout}")
+
+
+def test_tcgen05_gemm_epilogue_and_linear_grad():
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(6)
+    dev = _dev()
+    x = torch.randn(3, 100, 256, device=dev).bfloat16()
+    w = (torch.randn(384, 256, device=dev) * 0.05).bfloat16()
+    b = torch.randn(384, device=dev).bfloat16()
+    g = torch.randn(3, 100, 384, device=dev).bfloat16()
+    for act in (None, "silu"):
+        xs = [x.clone().requires_grad_(), x.float().clone().requires_grad_()]
+        ws = [w.clone().requires_grad_(), w.float().clone().requires_grad_()]
+        bs = [b.clone().requires_grad_(), b.float().clone().requires_grad_()]
+        y0 = ops.linear(xs[0], ws[0], bs[0], act)
+        y0.backward(g)
+        y1 = torch.nn.functional.linear(xs[1], ws[1], bs[1])
+        y1 = torch.nn.functional.silu(y1) if act else y1
+        y1.backward(g.float())
+        cuda_ops.check_kernel_errors()
+        _close(y0, y1, 5e-2, 3e-2, f"linear {act}")
+        _close(xs[0].grad, xs[1].grad, 5e-2, 3e-2, f"linear dx {act}")
+        _close(ws[0].grad, ws[1].grad, 0.3, 3e-2, f"linear dw {act}")
+        _close(bs[0].grad, bs[1].grad, 0.3, 3e-2, f"linear db {act}")
+
+
+def test_tiny_model_trains_on_gpu():
+    from megalodon_b200.config import ModelConf, OptimConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.modules.losses import cross_entropy
+    from megalodon_b200.optim import build_optimizer
+    from megalodon_b200.utils import clip_grad_norm_, set_random_seed
+    from megalodon_b200.ops import cuda_ops
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused", layerwise_ckpt=True)
+    losses = {}
+    for dtype in ("bf16",):
+        set_random_seed(0)
+        model = build_model(cfg, dtype, False, True)
+        opt, sched = build_optimizer(model, OptimConf(lr=3e-3, warmup=2), 20, dtype)
+        g = torch.Generator().manual_seed(0)
+        toks = torch.randint(0, 512, (2, 257), generator=g).cuda()
+        x, y = toks[:, :-1], toks[:, 1:]
+        curve = []
+        for _ in range(8):
+            pred, _ = model(x)
+            loss = cross_entropy(pred, y).mean()
+            loss.backward()
+            model.grad_all_reduce()
+            clip_grad_norm_(model, 1.0)
+            opt.step(); sched.step(); opt.zero_grad()
+            curve.append(loss.item())
+        cuda_ops.check_kernel_errors()
+        losses[dtype] = curve
+    c = losses["bf16"]
+    assert all(math.isfinite(v) for v in c), c
+    assert abs(c[0] - math.log(512)) < 0.5, c
+    assert c[-1] < c[0] - 0.1, c
