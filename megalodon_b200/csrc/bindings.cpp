@@ -328,9 +328,10 @@ std::tuple<Tensor, Tensor> clip_coef(const Tensor& sumsq, double max_norm) {
 
 // ------------------------------------------------------------------ GEMM
 // C[M,N] = act(A B^T + bias).  a_mn / b_mn: the operand is stored [K, rows] instead of [rows, K].
-// Returns (C, preact or None).  `err` is a persistent int32 device flag set by the kernel on a wait timeout.
-std::tuple<Tensor, OptTensor> gemm(const Tensor& A, const Tensor& B, const OptTensor& bias, int64_t act,
-                                   bool a_mn, bool b_mn, bool want_preact, int64_t out_dtype_code, Tensor& err) {
+// Returns (C, preact or None, launch status).  `err` is a persistent int32 device flag set by the kernel on a wait timeout.
+std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, const OptTensor& bias, int64_t act,
+                                            bool a_mn, bool b_mn, bool want_preact, int64_t out_dtype_code,
+                                            Tensor& err) {
   check_cuda_contig(A, "A");
   check_cuda_contig(B, "B");
   c10::cuda::CUDAGuard guard(A.device());
@@ -354,8 +355,8 @@ std::tuple<Tensor, OptTensor> gemm(const Tensor& A, const Tensor& B, const OptTe
                                        pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
                                        (int)act, M, N, K, a_mn, b_mn, dtype_code(A), (int)out_dtype_code,
                                        err.data_ptr<int>(), sms, stream());
-  TORCH_CHECK(rc == 0, "tcgen05 GEMM launch failed with code ", rc);
-  return {C, pre};
+  // the launcher's status goes back to Python, which raises on a non-zero code
+  return {C, pre, (int64_t)rc};
 }
 
 }  // namespace

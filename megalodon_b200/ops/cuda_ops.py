@@ -69,7 +69,9 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
          out_dtype: Optional[torch.dtype] = None):
     """C = act(A B^T + bias).  `a_mn` / `b_mn`: operand is stored [K, rows].  Returns (C, preact | None)."""
     out_dtype = out_dtype or a.dtype
-    if _GEMM_BACKEND[0] == "cublas" or a.dtype == torch.float32:
+    # TMA needs 16-byte row strides: the contiguous dim of each operand and N must be multiples of 8
+    aligned = a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and (b.shape[1] if b_mn else b.shape[0]) % 8 == 0
+    if _GEMM_BACKEND[0] == "cublas" or a.dtype == torch.float32 or not aligned:
         A = a.t() if a_mn else a
         Bm = b if b_mn else b.t()
         pre = torch.matmul(A, Bm)
@@ -78,8 +80,10 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
         out = F.silu(pre) if act == "silu" else pre
         return out.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
     _bump()
-    out, pre = _C().gemm(a.contiguous(), b.contiguous(), bias, 1 if act == "silu" else 0, a_mn, b_mn,
-                         want_preact, _DT[out_dtype], _err_flag(a.device))
+    out, pre, rc = _C().gemm(a.contiguous(), b.contiguous(), bias, 1 if act == "silu" else 0, a_mn, b_mn,
+                             want_preact, _DT[out_dtype], _err_flag(a.device))
+    if rc != 0:
+        raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
     return out, pre
 
 
