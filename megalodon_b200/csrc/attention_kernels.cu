@@ -1,0 +1,140 @@
+// Softmax stages of chunk-local attention, forward and backward, in place on
+// the score matrix produced by the tcgen05 GEMM.
+//
+// Same semantics as the reference's standalone softmax op
+// (csrc/softmax.cuh:86-234): with a causal mask, row r of an L1 x L2 block sees
+// columns 0 .. L2 - L1 + r; a fully masked row gives zeros; DropKey removes
+// keys (sets their logit to -inf with probability p) *before* the softmax.
+// Because dropped keys get probability zero, the backward pass
+// dS = P * (dP - sum(P * dP)) needs no mask.
+//
+// Layout: `rows` rows of length L2 with row stride `ld`; row index modulo L1 is
+// the query position.  The forward pass also writes zeros to the masked columns
+// up to the next multiple of 128, because the causal GEMMs that follow read
+// whole 128-wide diagonal blocks; columns further right are never read by them
+// and are left untouched (they may hold uninitialised scores).
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb {
+namespace {
+
+constexpr int kSmThreads = 256;
+constexpr int kSmMaxPerThread = 32;   // rows up to 8192 columns
+
+// Philox4x32-10 counter-based generator (Salmon et al. 2011): 4 x 32 random bits per counter.
+__device__ __forceinline__ uint4 philox4x32(uint4 ctr, uint2 key) {
+  const unsigned int M0 = 0xD2511F53u, M1 = 0xCD9E8D57u, W0 = 0x9E3779B9u, W1 = 0xBB67AE85u;
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const unsigned int hi0 = __umulhi(M0, ctr.x), lo0 = M0 * ctr.x;
+    const unsigned int hi1 = __umulhi(M1, ctr.z), lo1 = M1 * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += W0;
+    key.y += W1;
+  }
+  return ctr;
+}
+
+__device__ __forceinline__ float uniform01(unsigned long long seed, unsigned long long offset,
+                                           unsigned long long idx) {
+  const unsigned long long c = idx >> 2;
+  const uint4 r = philox4x32(make_uint4((unsigned int)c, (unsigned int)(c >> 32), (unsigned int)offset,
+                                        (unsigned int)(offset >> 32)),
+                             make_uint2((unsigned int)seed, (unsigned int)(seed >> 32)));
+  const unsigned int w = (idx & 3) == 0 ? r.x : (idx & 3) == 1 ? r.y : (idx & 3) == 2 ? r.z : r.w;
+  return (w >> 8) * (1.0f / 16777216.0f);
+}
+
+template <typename T>
+__global__ void attn_softmax_fwd_kernel(T* __restrict__ s, float* __restrict__ lse, int L1, int L2,
+                                        long long ld, bool causal, float drop_p, unsigned long long seed,
+                                        unsigned long long offset) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int pos = (int)(row % L1);
+  const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;      // visible columns
+  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;  // masked columns that must read as 0
+  T* sr = s + row * ld;
+  float v[kSmMaxPerThread];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kSmMaxPerThread; ++i) {
+    const int c = threadIdx.x + i * kSmThreads;
+    float x = -INFINITY;
+    if (c < n) {
+      x = to_f(sr[c]);
+      if (drop_p > 0.f && uniform01(seed, offset, (unsigned long long)row * L2 + c) < drop_p) x = -INFINITY;
+    }
+    v[i] = x;
+    m = fmaxf(m, x);
+  }
+  m = block_max(m, scratch);
+  float sum = 0.f;
+  if (m > -INFINITY) {
+#pragma unroll
+    for (int i = 0; i < kSmMaxPerThread; ++i) {
+      v[i] = __expf(v[i] - m);          // exp(-inf) = 0 for masked / dropped entries
+      sum += v[i];
+    }
+  }
+  sum = block_sum(sum, scratch);
+  const float inv = sum > 0.f ? 1.f / sum : 0.f;
+#pragma unroll
+  for (int i = 0; i < kSmMaxPerThread; ++i) {
+    const int c = threadIdx.x + i * kSmThreads;
+    if (c < n) sr[c] = from_f<T>(m > -INFINITY ? v[i] * inv : 0.f);
+    else if (c < zero_to) sr[c] = from_f<T>(0.f);
+  }
+  if (lse != nullptr && threadIdx.x == 0) lse[row] = sum > 0.f ? m + logf(sum) : -INFINITY;
+}
+
+template <typename T>
+__global__ void attn_softmax_bwd_kernel(const T* __restrict__ p, T* __restrict__ dp, int L1, int L2, long long ld,
+                                        bool causal) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int pos = (int)(row % L1);
+  const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
+  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  const T* pr = p + row * ld;
+  T* dr = dp + row * ld;
+  float pv[kSmMaxPerThread], gv[kSmMaxPerThread];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kSmMaxPerThread; ++i) {
+    const int c = threadIdx.x + i * kSmThreads;
+    pv[i] = gv[i] = 0.f;
+    if (c < n) {
+      pv[i] = to_f(pr[c]);
+      gv[i] = to_f(dr[c]);
+      dot += pv[i] * gv[i];
+    }
+  }
+  dot = block_sum(dot, scratch);
+#pragma unroll
+  for (int i = 0; i < kSmMaxPerThread; ++i) {
+    const int c = threadIdx.x + i * kSmThreads;
+    if (c < n) dr[c] = from_f<T>(pv[i] * (gv[i] - dot));
+    else if (c < zero_to) dr[c] = from_f<T>(0.f);
+  }
+}
+
+}  // namespace
+
+void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2, long long ld, bool causal,
+                      float dropkey_p, unsigned long long seed, unsigned long long offset, int dtype,
+                      cudaStream_t st) {
+  if (rows == 0) return;
+  MB_DISPATCH_DTYPE(dtype, (attn_softmax_fwd_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
+                               (scalar_t*)s_inout, lse, L1, L2, ld, causal, dropkey_p, seed, offset)));
+}
+
+void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
+                      int dtype, cudaStream_t st) {
+  if (rows == 0) return;
+  MB_DISPATCH_DTYPE(dtype, (attn_softmax_bwd_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
+                               (const scalar_t*)p, (scalar_t*)dp_inout, L1, L2, ld, causal)));
+}
+
+}  // namespace mb

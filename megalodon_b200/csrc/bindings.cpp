@@ -327,36 +327,85 @@ std::tuple<Tensor, Tensor> clip_coef(const Tensor& sumsq, double max_norm) {
 }
 
 // ------------------------------------------------------------------ GEMM
-// C[M,N] = act(A B^T + bias).  a_mn / b_mn: the operand is stored [K, rows] instead of [rows, K].
-// Returns (C, preact or None, launch status).  `err` is a persistent int32 device flag set by the kernel on a wait timeout.
-std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, const OptTensor& bias, int64_t act,
-                                            bool a_mn, bool b_mn, bool want_preact, int64_t out_dtype_code,
+// C = act(alpha * A B^T + bias) on the tcgen05 kernel.  A, B (and `out`) are 2-D matrices or 3-D
+// batches of matrices whose last dim is contiguous; row and batch strides are taken from the tensors,
+// so strided views (one head of a [B, L, H, d] tensor, a slice of a flat buffer) need no copy.
+// a_mn / b_mn: the operand is stored [K, rows] instead of [rows, K].  mode: causal tile structure
+// (0 dense; see gemm_sm100.cu).  Returns (C, preact or None, launch status); `err` is a persistent
+// int32 device flag that the kernel sets if one of its bounded waits gives up.
+std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, const OptTensor& out,
+                                            const OptTensor& bias, int64_t act, bool a_mn, bool b_mn,
+                                            bool want_preact, int64_t out_dtype_code, int64_t mode, double alpha,
                                             Tensor& err) {
-  check_cuda_contig(A, "A");
-  check_cuda_contig(B, "B");
+  TORCH_CHECK(A.is_cuda() && B.is_cuda(), "operands must be CUDA tensors");
   c10::cuda::CUDAGuard guard(A.device());
-  TORCH_CHECK(A.dim() == 2 && B.dim() == 2 && A.scalar_type() == B.scalar_type());
+  TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && A.dim() == B.dim(), "operands must both be 2-D or both 3-D");
+  TORCH_CHECK(A.scalar_type() == B.scalar_type());
   TORCH_CHECK(A.scalar_type() == at::kBFloat16 || A.scalar_type() == at::kHalf, "tcgen05 GEMM takes bf16/fp16");
-  const int M = a_mn ? A.size(1) : A.size(0);
-  const int K = a_mn ? A.size(0) : A.size(1);
-  const int N = b_mn ? B.size(1) : B.size(0);
-  TORCH_CHECK((b_mn ? B.size(0) : B.size(1)) == K, "inner dimensions differ");
+  TORCH_CHECK(A.stride(-1) == 1 && B.stride(-1) == 1, "last dim of the operands must be contiguous");
+  const int batch = A.dim() == 3 ? (int)A.size(0) : 1;
+  TORCH_CHECK(A.dim() == 2 || B.size(0) == batch, "batch sizes differ");
+  const int M = a_mn ? A.size(-1) : A.size(-2);
+  const int K = a_mn ? A.size(-2) : A.size(-1);
+  const int N = b_mn ? B.size(-1) : B.size(-2);
+  TORCH_CHECK((b_mn ? B.size(-2) : B.size(-1)) == K, "inner dimensions differ");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(A.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(B.data_ptr()) % 16 == 0,
               "operands must be 16-byte aligned");
   at::ScalarType odt = out_dtype_code == 0 ? at::kFloat : (out_dtype_code == 1 ? at::kBFloat16 : at::kHalf);
-  Tensor C = torch::empty({M, N}, A.options().dtype(odt));
+  Tensor C;
+  if (out.has_value()) {
+    C = *out;
+    TORCH_CHECK(C.is_cuda() && C.scalar_type() == odt && C.dim() == A.dim() && C.stride(-1) == 1);
+    TORCH_CHECK(C.size(-2) == M && C.size(-1) == N && (A.dim() == 2 || C.size(0) == batch), "bad output shape");
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(C.data_ptr()) % 16 == 0, "output must be 16-byte aligned");
+  } else {
+    C = A.dim() == 3 ? torch::empty({batch, M, N}, A.options().dtype(odt)) : torch::empty({M, N}, A.options().dtype(odt));
+  }
   OptTensor pre;
-  if (want_preact) pre = torch::empty({M, N}, A.options().dtype(odt));
-  TORCH_CHECK(N % 8 == 0, "N must be a multiple of 8");
+  if (want_preact) {
+    TORCH_CHECK(batch == 1 && !out.has_value(), "pre-activation output is only available for plain 2-D calls");
+    pre = torch::empty({M, N}, A.options().dtype(odt));
+  }
   int bias_code = 0;
-  if (bias.has_value()) { check_cuda_contig(*bias, "bias"); bias_code = dtype_code(*bias); TORCH_CHECK(bias->numel() == N); }
+  if (bias.has_value()) {
+    check_cuda_contig(*bias, "bias");
+    bias_code = dtype_code(*bias);
+    TORCH_CHECK(bias->numel() == N);
+  }
+  const long long a_bs = A.dim() == 3 ? A.stride(0) : 0, b_bs = B.dim() == 3 ? B.stride(0) : 0;
+  const long long c_bs = C.dim() == 3 ? C.stride(0) : 0;
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
   const int rc = mb::gemm_bf16_tcgen05(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                        pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
-                                       (int)act, M, N, K, a_mn, b_mn, dtype_code(A), (int)out_dtype_code,
-                                       err.data_ptr<int>(), sms, stream());
+                                       (int)act, M, N, K, A.stride(-2), B.stride(-2), C.stride(-2), a_mn, b_mn,
+                                       (int)mode, (float)alpha, batch, a_bs, b_bs, c_bs, dtype_code(A),
+                                       (int)out_dtype_code, err.data_ptr<int>(), sms, stream());
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
+}
+
+// ------------------------------------------------------------------ attention softmax (in place)
+// s [..., L1, L2] with contiguous last dim and uniform row stride; returns lse [rows] (fp32)
+Tensor attn_softmax_fwd(Tensor& s, int64_t L1, int64_t L2, bool causal, double drop_p, int64_t seed,
+                        int64_t offset) {
+  TORCH_CHECK(s.is_cuda() && s.stride(-1) == 1 && L2 <= 8192, "attention softmax: bad input");
+  c10::cuda::CUDAGuard guard(s.device());
+  const long long ld = s.stride(-2);
+  const long long rows = s.numel() / s.size(-1);
+  for (int d = 0; d + 2 < s.dim(); ++d) TORCH_CHECK(s.stride(d) == s.stride(d + 1) * s.size(d + 1), "rows must be evenly strided");
+  Tensor lse = torch::empty({rows}, s.options().dtype(at::kFloat));
+  mb::attn_softmax_fwd(s.data_ptr(), lse.data_ptr<float>(), rows, (int)L1, (int)L2, ld, causal, (float)drop_p,
+                       (unsigned long long)seed, (unsigned long long)offset, dtype_code(s), stream());
+  return lse;
+}
+
+void attn_softmax_bwd(const Tensor& p, Tensor& dp, int64_t L1, int64_t L2, bool causal) {
+  TORCH_CHECK(p.is_cuda() && dp.is_cuda() && p.stride(-1) == 1 && dp.stride(-1) == 1);
+  TORCH_CHECK(p.stride(-2) == dp.stride(-2) && p.scalar_type() == dp.scalar_type() && L2 <= 8192);
+  c10::cuda::CUDAGuard guard(p.device());
+  const long long rows = p.numel() / p.size(-1);
+  mb::attn_softmax_bwd(p.data_ptr(), dp.data_ptr(), rows, (int)L1, (int)L2, p.stride(-2), causal, dtype_code(p),
+                       stream());
 }
 
 }  // namespace
@@ -380,4 +429,6 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("scale_by_ptr", &scale_by_ptr);
   m.def("clip_coef", &clip_coef);
   m.def("gemm", &gemm);
+  m.def("attn_softmax_fwd", &attn_softmax_fwd);
+  m.def("attn_softmax_bwd", &attn_softmax_bwd);
 }

@@ -51,15 +51,48 @@ struct SmemLayout {
   static constexpr int total = bar_offset + 256 + 1024;  // barriers + alignment slack
 };
 
+// Triangular (causal) structure, used when the GEMM is one of the products of
+// chunk-local causal attention (row index and contraction / column index count
+// the same positions):
+//   1  skip output tiles that lie entirely above the diagonal   (S = Q K^T, dP = dO V^T)
+//   2  contract only over k <= last row of the tile             (O = P V, dQ = dS K;  A lower-triangular)
+//   3  contract only over k >= first row of the tile            (dV = P^T dO, dK = dS^T Q; A^T lower-triangular)
 struct GemmParams {
   int M, N, K;
-  void* C;             // [M, N]
+  void* C;             // [M, N] with row stride ldc
   void* preact;        // optional [M, N]: value before the activation
   const void* bias;    // optional [N]
   int bias_dtype;      // DType
   int act;             // 0 none, 1 SiLU
   int* err;
+  long long ldc;       // elements
+  int mode;            // 0 dense, 1..3 see above
+  float alpha;         // C = alpha * acc (+ bias)
+  int batch;           // independent problems sharing shapes (tensor maps carry their strides)
+  long long c_batch_stride;   // elements between consecutive C (and preact) matrices
 };
+
+struct TileCoord {
+  int m0, n0, bz;
+};
+template <int BN>
+__device__ __forceinline__ TileCoord decode_tile(int tile, int num_m, int tiles_per_batch) {
+  const int bz = tile / tiles_per_batch;
+  const int t = tile - bz * tiles_per_batch;
+  return {(t % num_m) * BM, (t / num_m) * BN, bz};
+}
+
+template <int BN>
+__device__ __forceinline__ bool tile_skipped(const GemmParams& p, int m0, int n0) {
+  return p.mode == 1 && n0 > m0 + BM - 1;
+}
+
+__device__ __forceinline__ void k_range(const GemmParams& p, int m0, int num_k, int& kb0, int& kb1) {
+  kb0 = 0;
+  kb1 = num_k;
+  if (p.mode == 2) kb1 = min(num_k, (m0 + BM + BK - 1) / BK);
+  if (p.mode == 3) kb0 = min(num_k - 1, m0 / BK);
+}
 
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   if (mbar_try_wait(bar, parity)) return true;
@@ -148,7 +181,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   const int lane = threadIdx.x & 31;
   const int num_m = (p.M + BM - 1) / BM;
   const int num_n = (p.N + BN - 1) / BN;
-  const int num_tiles = num_m * num_n;
+  const int tiles_per_batch = num_m * num_n;
+  const int num_tiles = tiles_per_batch * p.batch;
   const int num_k = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * BN;     // two accumulators (power of two: 256 or 512)
 
@@ -182,25 +216,28 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int m0 = (tile % num_m) * BM;
-        const int n0 = (tile / num_m) * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        const TileCoord tc = decode_tile<BN>(tile, num_m, tiles_per_batch);
+        const int m0 = tc.m0, n0 = tc.n0, bz = tc.bz;
+        if (tile_skipped<BN>(p, m0, n0)) continue;
+        int kb0, kb1;
+        k_range(p, m0, num_k, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::stage_bytes;
           uint8_t* sb = sa + L::a_bytes;
           mbar_expect_tx(full_bar + stage, L::stage_bytes);
           const int k0 = kb * BK;
           if constexpr (!A_MN) {
-            tma_load_2d(sa, &tmap_a, full_bar + stage, k0, m0);
+            tma_load_3d(sa, &tmap_a, full_bar + stage, k0, m0, bz);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_2d(sa + j * 8192, &tmap_a, full_bar + stage, m0 + 64 * j, k0);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, &tmap_a, full_bar + stage, m0 + 64 * j, k0, bz);
           }
           if constexpr (!B_MN) {
-            tma_load_2d(sb, &tmap_b, full_bar + stage, k0, n0);
+            tma_load_3d(sb, &tmap_b, full_bar + stage, k0, n0, bz);
           } else {
 #pragma unroll
-            for (int j = 0; j < BN / 64; ++j) tma_load_2d(sb + j * 8192, &tmap_b, full_bar + stage, n0 + 64 * j, k0);
+            for (int j = 0; j < BN / 64; ++j) tma_load_3d(sb + j * 8192, &tmap_b, full_bar + stage, n0 + 64 * j, k0, bz);
           }
           if (++stage == kStages) { stage = 0; phase ^= 1; }
         }
@@ -217,10 +254,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const TileCoord tc = decode_tile<BN>(tile, num_m, tiles_per_batch);
+        const int m0 = tc.m0, n0 = tc.n0;
+        if (tile_skipped<BN>(p, m0, n0)) continue;
+        int kb0, kb1;
+        k_range(p, m0, num_k, kb0, kb1);
         if (!wait_or_abort(tmem_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
         tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(full_bar + stage, phase, abort_flag)) { ok = false; break; }
           tcgen05_fence_after();
           const uint32_t sa = smem_u32(smem + stage * L::stage_bytes);
@@ -231,7 +273,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
                                      : make_smem_desc(sa + kk * 32, 16, 1024);
             const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
                                      : make_smem_desc(sb + kk * 32, 16, 1024);
-            umma_f16(d_tmem, da, db, idesc, (kb | kk) != 0 ? 1u : 0u);
+            umma_f16(d_tmem, da, db, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
           }
           umma_commit(empty_bar + stage);      // stage reusable once these MMAs have read it
           if (++stage == kStages) { stage = 0; phase ^= 1; }
@@ -251,8 +293,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
     OutT* C = reinterpret_cast<OutT*>(p.C);
     OutT* P = reinterpret_cast<OutT*>(p.preact);
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      const int m0 = (tile % num_m) * BM;
-      const int n0 = (tile / num_m) * BN;
+      const TileCoord tc = decode_tile<BN>(tile, num_m, tiles_per_batch);
+      const int m0 = tc.m0, n0 = tc.n0;
+      if (tile_skipped<BN>(p, m0, n0)) continue;
       if (!wait_or_abort(tmem_full + acc, acc_phase, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
       const int row = m0 + quarter * 32 + lane;
@@ -266,7 +309,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
         if (col0 >= p.N) continue;            // warp-uniform
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
         const int nvalid = min(32, p.N - col0);
         if (p.bias != nullptr) {
 #pragma unroll
@@ -281,7 +324,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
         if (row < p.M) {
-          const long long off = (long long)row * p.N + col0;
+          const long long off = (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0;
           if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
           if (p.act == 1) {
 #pragma unroll
@@ -327,16 +370,19 @@ EncodeTiledFn get_encode_fn() {
 }  // namespace
 
 // 2-D bf16/fp16 tensor map: `inner` contiguous elements per row, `outer` rows, 128-byte swizzle.
-bool make_tmap_2d(CUtensorMap* out, const void* base, long long inner, long long outer, int box_inner,
-                  int box_outer, int elem_dtype) {
+// 3-D bf16/fp16 tensor map [batch, outer, inner] (inner contiguous) with a {1, box_outer, box_inner} box
+// and 128-byte swizzle.  Strides are in elements and must be multiples of 8 (16 bytes).
+bool make_tmap_3d(CUtensorMap* out, const void* base, long long inner, long long outer, long long batch,
+                  long long row_stride, long long batch_stride, int box_inner, int box_outer, int elem_dtype) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
-  const cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
-  const cuuint64_t strides[1] = {(cuuint64_t)inner * 2};
-  const cuuint32_t box[2] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer};
-  const cuuint32_t estr[2] = {1, 1};
+  if (batch <= 1) batch_stride = row_stride * outer;      // unused, but must be a valid stride
+  const cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(batch < 1 ? 1 : batch)};
+  const cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
+  const cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
+  const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = elem_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  return fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
@@ -351,7 +397,7 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total) != cudaSuccess) return -2;
     configured = true;
   }
-  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN);
+  const int tiles = ((p.M + BM - 1) / BM) * ((p.N + BN - 1) / BN) * p.batch;
   const int grid = tiles < sms ? tiles : sms;
   kern<<<grid, kGemmThreads, L::total, st>>>(ta, tb, p, in_fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
@@ -360,17 +406,21 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 // Returns 0 on success, negative on a host-side failure.  `err` is a device int
 // that the kernel sets non-zero if one of its bounded waits gives up.
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
-                      int act, int M, int N, int K, bool a_mn, bool b_mn, int in_dtype, int out_dtype, int* err,
-                      int num_sms, cudaStream_t st) {
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  // 16-byte global strides for TMA
-  if ((a_mn ? M : K) % 8 != 0 || (b_mn ? N : K) % 8 != 0) return -1;
+                      int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
+                      bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
+                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st) {
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
+  // TMA wants 16-byte strides; the vectorised epilogue wants 16-byte aligned rows of C
+  if (lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return -1;
+  if (batch > 1 && (a_bs % 8 != 0 || b_bs % 8 != 0 || c_bs % 8 != 0)) return -1;
   const int BN = 256;
   CUtensorMap ta, tb;
-  bool ok = a_mn ? make_tmap_2d(&ta, A, M, K, 64, 64, in_dtype) : make_tmap_2d(&ta, A, K, M, BK, BM, in_dtype);
-  ok = ok && (b_mn ? make_tmap_2d(&tb, B, N, K, 64, 64, in_dtype) : make_tmap_2d(&tb, B, K, N, BK, BN, in_dtype));
+  bool ok = a_mn ? make_tmap_3d(&ta, A, M, K, batch, lda, a_bs, 64, 64, in_dtype)
+                 : make_tmap_3d(&ta, A, K, M, batch, lda, a_bs, BK, BM, in_dtype);
+  ok = ok && (b_mn ? make_tmap_3d(&tb, B, N, K, batch, ldb, b_bs, 64, 64, in_dtype)
+                   : make_tmap_3d(&tb, B, K, N, batch, ldb, b_bs, BK, BN, in_dtype));
   if (!ok) return -4;
-  GemmParams p{M, N, K, C, preact, bias, bias_dtype, act, err};
+  GemmParams p{M, N, K, C, preact, bias, bias_dtype, act, err, ldc, mode, alpha, batch, c_bs};
   const int fmt = in_dtype == kBF16 ? 1 : 0;
 #define GEMM_CASE(AMN, BMN)                                                                              \
   if (a_mn == AMN && b_mn == BMN) {                                                                      \

@@ -63,8 +63,19 @@ void scale_by_ptr(void* g, long long n, const float* scale, int dtype, cudaStrea
 void clip_coef(const double* sumsq, float max_norm, float* norm_out, float* coef_out, cudaStream_t st);
 
 // ---- tcgen05 GEMM (gemm_sm100.cu): C[M,N] = act(A B^T + bias)
+// lda / ldb / ldc: row strides in elements (multiples of 8).  mode: 0 dense, 1..3 causal tile structure
+// (see gemm_sm100.cu).  The result is scaled by alpha before bias / activation.  `batch` independent
+// problems of the same shape are addressed through the batch strides a_bs / b_bs / c_bs (elements).
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
-                      int act, int M, int N, int K, bool a_mn, bool b_mn, int in_dtype, int out_dtype, int* err,
-                      int num_sms, cudaStream_t st);
+                      int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
+                      bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
+                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st);
+
+// ---- attention softmax (attention_kernels.cu)
+void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2, long long ld, bool causal,
+                      float dropkey_p, unsigned long long seed, unsigned long long offset, int dtype,
+                      cudaStream_t st);
+void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
+                      int dtype, cudaStream_t st);
 
 }  // namespace mb

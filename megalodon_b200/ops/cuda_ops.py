@@ -64,27 +64,44 @@ def check_kernel_errors(device: Optional[torch.device] = None) -> None:
             raise RuntimeError(f"tcgen05 kernel wait timed out on {key} (role code {code})")
 
 
+def _tma_ok(t: Tensor) -> bool:
+    return (t.stride(-1) == 1 and t.stride(-2) % 8 == 0 and t.data_ptr() % 16 == 0
+            and (t.dim() == 2 or t.stride(0) % 8 == 0))
+
+
 def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str] = None, *,
          a_mn: bool = False, b_mn: bool = False, want_preact: bool = False,
-         out_dtype: Optional[torch.dtype] = None):
-    """C = act(A B^T + bias).  `a_mn` / `b_mn`: operand is stored [K, rows].  Returns (C, preact | None)."""
-    out_dtype = out_dtype or a.dtype
-    # TMA needs 16-byte row strides: the contiguous dim of each operand and N must be multiples of 8
-    aligned = a.shape[-1] % 8 == 0 and b.shape[-1] % 8 == 0 and (b.shape[1] if b_mn else b.shape[0]) % 8 == 0
-    if _GEMM_BACKEND[0] == "cublas" or a.dtype == torch.float32 or not aligned:
-        A = a.t() if a_mn else a
-        Bm = b if b_mn else b.t()
+         out_dtype: Optional[torch.dtype] = None, out: Optional[Tensor] = None, mode: int = 0,
+         alpha: float = 1.0):
+    """C = act(alpha * A B^T + bias).  `a_mn` / `b_mn`: operand is stored [K, rows].
+    Operands may be 2-D or 3-D (batched) strided views with a contiguous last
+    dim.  `mode` 1..3 exploits causal structure (see gemm_sm100.cu).  Returns
+    (C, preact | None)."""
+    out_dtype = out_dtype or (out.dtype if out is not None else a.dtype)
+    native = (_GEMM_BACKEND[0] == "tcgen05" and a.dtype in (torch.bfloat16, torch.float16)
+              and _tma_ok(a) and _tma_ok(b) and (out is None or _tma_ok(out))
+              and (b.shape[-1] if b_mn else b.shape[-2]) % 8 == 0)
+    if not native:
+        A = a.transpose(-1, -2) if a_mn else a
+        Bm = b if b_mn else b.transpose(-1, -2)
         pre = torch.matmul(A, Bm)
+        if alpha != 1.0:
+            pre = pre * alpha
         if bias is not None:
             pre = pre + bias.to(pre.dtype)
-        out = F.silu(pre) if act == "silu" else pre
-        return out.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
+        res = F.silu(pre) if act == "silu" else pre
+        if mode == 1:       # the kernel leaves tiles above the diagonal unwritten; nothing reads them
+            pass
+        if out is not None:
+            out.copy_(res)
+            res = out
+        return res.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
     _bump()
-    out, pre, rc = _C().gemm(a.contiguous(), b.contiguous(), bias, 1 if act == "silu" else 0, a_mn, b_mn,
-                             want_preact, _DT[out_dtype], _err_flag(a.device))
+    res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
+                             _DT[out_dtype], mode, alpha, _err_flag(a.device))
     if rc != 0:
         raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
-    return out, pre
+    return res, pre
 
 
 class _Linear(torch.autograd.Function):
@@ -327,12 +344,106 @@ def rfft(x, flip=False):
 
 
 # ----------------------------------------------------------------------------- attention
+# Chunk-local attention as five tensor-core products around an in-place softmax:
+#   S = scale Q K^T -> P = softmax_causal(S) -> O = P V
+#   dV = P^T dO,  dP = dO V^T,  dS = P (dP - rowsum(P dP)),  dQ = scale dS K,  dK = scale dS^T Q
+# All products run on the tcgen05 GEMM, batched over heads through strided 3-D
+# views of the [B, L, H, d] tensors (no per-head copies) and, for square causal
+# blocks, restricted to the tiles on or below the diagonal.
+def _heads_view(t: Tensor, b: int) -> Tensor:
+    """[B, L, H, d] -> view [H, L, d] of batch element b (strides d, H*d, 1)."""
+    return t[b].permute(1, 0, 2)
+
+
+def _attention_native_ok(q, k, v) -> bool:
+    return (q.dtype in (torch.bfloat16, torch.float16) and q.shape[-1] % 8 == 0 and v.shape[-1] % 8 == 0
+            and k.shape[1] <= 8192 and _GEMM_BACKEND[0] == "tcgen05")
+
+
+class _Attention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, scale, drop_p, causal):
+        q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+        B, L1, H, dk = q.shape
+        L2, dv = k.shape[1], v.shape[-1]
+        square = causal and L1 == L2
+        ld = -(-L2 // 128) * 128                     # padded row length of the score buffer
+        P = torch.empty(B, H, L1, ld, dtype=q.dtype, device=q.device)
+        out = torch.empty(B, L1, H, dv, dtype=q.dtype, device=q.device)
+        seed = offset = 0
+        if drop_p > 0.0:
+            seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+        for b in range(B):
+            Pb = P[b][:, :, :L2]
+            gemm(_heads_view(q, b), _heads_view(k, b), out=Pb, mode=1 if square else 0, alpha=scale)
+            _bump()
+            _C().attn_softmax_fwd(Pb, L1, L2, causal, drop_p, seed, offset + b)
+            gemm(Pb, _heads_view(v, b), b_mn=True, out=_heads_view(out, b), mode=2 if square else 0)
+        ctx.save_for_backward(q, k, v, P)
+        ctx.meta = (scale, causal, square, L2)
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, P = ctx.saved_tensors
+        scale, causal, square, L2 = ctx.meta
+        dout = dout.contiguous()
+        B, L1, H, dk = q.shape
+        dq, dk_, dv_ = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        dP = torch.empty_like(P[0])
+        for b in range(B):
+            Pb = P[b][:, :, :L2]
+            dPb = dP[:, :, :L2]
+            dOb = _heads_view(dout, b)
+            # dV = P^T dO   (A = P stored [q, key] = [K, M]; B = dO stored [q, dv] = [K, N])
+            gemm(Pb, dOb, a_mn=True, b_mn=True, out=_heads_view(dv_, b), mode=3 if square else 0)
+            # dP = dO V^T
+            gemm(dOb, _heads_view(v, b), out=dPb, mode=1 if square else 0)
+            _bump()
+            _C().attn_softmax_bwd(Pb, dPb, L1, L2, causal)      # dP <- dS in place
+            # dQ = scale dS K ; dK = scale dS^T Q
+            gemm(dPb, _heads_view(k, b), b_mn=True, out=_heads_view(dq, b), mode=2 if square else 0, alpha=scale)
+            gemm(dPb, _heads_view(q, b), a_mn=True, b_mn=True, out=_heads_view(dk_, b),
+                 mode=3 if square else 0, alpha=scale)
+        return dq, dk_, dv_, None, None, None
+
+
 def attention(q, k, v, scale, dropout, use_causal_mask, training):
-    return reference.attention(q, k, v, scale, dropout, use_causal_mask, training)
+    if not _attention_native_ok(q, k, v):
+        return reference.attention(q, k, v, scale, dropout, use_causal_mask, training)
+    return _Attention.apply(q, k, v, float(scale), float(dropout) if training else 0.0, bool(use_causal_mask))
+
+
+class _AttentionSoftmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, drop_p, causal):
+        L1, L2 = x.shape[-2:]
+        y = x.contiguous().clone()
+        seed = int(torch.randint(0, 2 ** 62, (1,)).item()) if drop_p > 0.0 else 0
+        _bump()
+        _C().attn_softmax_fwd(y, L1, L2, causal, drop_p, seed, 0)
+        ctx.save_for_backward(y)
+        ctx.causal = causal
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        (y,) = ctx.saved_tensors
+        L1, L2 = y.shape[-2:]
+        dx = g.contiguous().clone()
+        _bump()
+        _C().attn_softmax_bwd(y, dx, L1, L2, ctx.causal)
+        if ctx.causal:       # columns the kernel does not visit carry the incoming gradient: clear them
+            r = torch.arange(L1, device=y.device).unsqueeze(-1)
+            c = torch.arange(L2, device=y.device).unsqueeze(0)
+            dx = dx.masked_fill(c > r + (L2 - L1), 0)
+        return dx, None, None
 
 
 def attention_softmax(x, dropout, use_causal_mask, training):
-    return reference.attention_softmax(x, dropout, use_causal_mask, training)
+    if x.shape[-1] > 8192:
+        return reference.attention_softmax(x, dropout, use_causal_mask, training)
+    return _AttentionSoftmax.apply(x, float(dropout) if training else 0.0, bool(use_causal_mask))
 
 
 class _Rotary(torch.autograd.Function):

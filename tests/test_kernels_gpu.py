@@ -296,3 +296,53 @@ def test_tiny_model_trains_on_gpu():
     assert all(math.isfinite(v) for v in c), c
     assert abs(c[0] - math.log(512)) < 0.5, c
     assert c[-1] < c[0] - 0.1, c
+
+
+@pytest.mark.parametrize("B,L1,L2,H,dk,dv,causal", [
+    (2, 256, 256, 2, 64, 128, True),      # square causal: triangular tile structure
+    (1, 640, 640, 4, 256, 512, True),     # several 128-blocks, 7B head dims scaled down in dv
+    (2, 1, 100, 2, 64, 128, False),       # single-token decode against a cache
+    (1, 24, 152, 1, 32, 64, True),        # prompt remainder against a cache (L1 < L2)
+])
+def test_attention_matches_reference(B, L1, L2, H, dk, dv, causal):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import cuda_ops, reference
+    torch.manual_seed(8)
+    dev = _dev()
+    q = (torch.randn(B, L1, H, dk, device=dev) * 0.3).bfloat16()
+    k = (torch.randn(B, L2, H, dk, device=dev) * 0.3).bfloat16()
+    v = torch.randn(B, L2, H, dv, device=dev).bfloat16()
+    g = torch.randn(B, L1, H, dv, device=dev).bfloat16()
+    res = []
+    for mod, cast in ((ops, lambda t: t), (reference, lambda t: t.float())):
+        qq, kk, vv = (cast(t).clone().requires_grad_() for t in (q, k, v))
+        o = mod.attention(qq, kk, vv, 0.7, 0.0, causal, True)
+        o.backward(cast(g))
+        res.append((o, qq.grad, kk.grad, vv.grad))
+    cuda_ops.check_kernel_errors()
+    for name, a, b in zip(("o", "dq", "dk", "dv"), *res):
+        scale = b.float().abs().max().item() + 1e-3
+        _close(a, b, 3e-2 * scale, 5e-2, f"attention {name}")
+
+
+def test_attention_softmax_op():
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(9)
+    dev = _dev()
+    x = torch.randn(2, 3, 40, 72, device=dev)
+    g = torch.randn_like(x)
+    for causal in (True, False):
+        outs = []
+        for mod in (ops, reference):
+            xx = x.clone().requires_grad_()
+            y = mod.attention_softmax(xx, 0.0, causal, True)
+            y.backward(g)
+            outs.append((y, xx.grad))
+        _close(outs[0][0], outs[1][0], 1e-5, 1e-4, "softmax")
+        _close(outs[0][1], outs[1][1], 1e-5, 1e-3, "softmax grad")
+    # DropKey: rows still sum to one, roughly p of the visible keys are removed
+    y = ops.attention_softmax(x, 0.5, False, True)
+    assert torch.allclose(y.sum(-1), torch.ones_like(y.sum(-1)), atol=1e-4)
+    frac = (y == 0).float().mean().item()
+    assert 0.4 < frac < 0.6, frac
