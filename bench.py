@@ -153,6 +153,7 @@ def main():
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)
     model._wrapped.seq_microbatch_chunks = 1
+    model.defer_grad_clip = True      # clipping coefficient is applied inside the fused AdamW kernel
     opt, sched = build_optimizer(model, OptimConf(lr=1e-4, warmup=10, clip=1.0), 1000, "bf16")
     data = SyntheticTokens(cfg.vocab_size, 1, args.seq_len, seed=0)
     n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)

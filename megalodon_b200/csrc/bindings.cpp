@@ -142,13 +142,14 @@ std::vector<Tensor> timestep_norm_fwd(const Tensor& x, const Tensor& prev_count,
   Tensor cumrstd = torch::empty({B, L, G}, f32);
   Tensor gu = torch::empty({B, L, G}, f32);
   Tensor gv = torch::empty({B, L, G}, f32);
+  Tensor seg = torch::empty({3LL * B * mb::tsn_num_segments(L) * G}, x.options().dtype(at::kDouble));
   mb::timestep_norm_fwd(x.data_ptr(), (const long long*)prev_count.data_ptr<int64_t>(), prev_mean.data_ptr(),
                         prev_var.data_ptr(), gamma.data_ptr(), (float)gamma_off, beta.data_ptr(),
                         mask.has_value() ? mask->data_ptr<bool>() : nullptr, y.data_ptr(),
                         (long long*)count.data_ptr<int64_t>(), mean.data_ptr(), var.data_ptr(),
                         cummean.data_ptr<float>(), cumrstd.data_ptr<float>(), gu.data_ptr<float>(),
-                        gv.data_ptr<float>(), B, L, H, (int)G, (float)eps, dtype_code(x), weight_code(x, gamma),
-                        stream());
+                        gv.data_ptr<float>(), seg.data_ptr<double>(), B, L, H, (int)G, (float)eps, dtype_code(x),
+                        weight_code(x, gamma), stream());
   return {y, count, mean, var, cummean, cumrstd};
 }
 
@@ -172,12 +173,15 @@ std::vector<Tensor> timestep_norm_bwd(const Tensor& dy, const Tensor& dmean, con
   Tensor scratch = torch::empty({5, B, L, G}, f32);
   float* sp = scratch.data_ptr<float>();
   const long long n = (long long)B * L * G;
+  Tensor seg = torch::empty({4LL * B * mb::tsn_num_segments(L) * G}, x.options().dtype(at::kDouble));
+  Tensor cumvalid = torch::empty({mask.has_value() ? (long long)B * L : 0}, x.options().dtype(at::kInt));
   mb::timestep_norm_bwd(dy.data_ptr(), dmean.data_ptr(), dvar.data_ptr(), x.data_ptr(), prev_mean.data_ptr(),
                         (const long long*)count.data_ptr<int64_t>(), cummean.data_ptr<float>(),
                         cumrstd.data_ptr<float>(), gamma.data_ptr(), (float)gamma_off,
                         mask.has_value() ? mask->data_ptr<bool>() : nullptr, dx.data_ptr(), dpm.data_ptr(),
                         dpv.data_ptr(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), sp, sp + n, sp + 2 * n,
-                        sp + 3 * n, sp + 4 * n, B, L, H, (int)G, dtype_code(x), weight_code(x, gamma), stream());
+                        sp + 3 * n, sp + 4 * n, seg.data_ptr<double>(), cumvalid.data_ptr<int>(), B, L, H, (int)G,
+                        dtype_code(x), weight_code(x, gamma), stream());
   return {dx, dpm, dpv, dgamma, dbeta};
 }
 
@@ -298,6 +302,10 @@ void adamw_step(Tensor& p, const Tensor& g, Tensor& m, Tensor& v, const OptTenso
   TORCH_CHECK(p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat && v.scalar_type() == at::kFloat);
   TORCH_CHECK(g.numel() == p.numel() && m.numel() == p.numel() && v.numel() == p.numel());
   if (low.has_value()) TORCH_CHECK(low->numel() == p.numel() && low->is_contiguous());
+  for (const void* ptr : {(const void*)p.data_ptr(), (const void*)g.data_ptr(), (const void*)m.data_ptr(),
+                          (const void*)v.data_ptr()})
+    TORCH_CHECK(reinterpret_cast<uintptr_t>(ptr) % 16 == 0, "adamw_step: tensors must be 16-byte aligned");
+  if (low.has_value()) TORCH_CHECK(reinterpret_cast<uintptr_t>(low->data_ptr()) % 8 == 0);
   mb::adamw_step(p.data_ptr<float>(), g.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(),
                  low.has_value() ? low->data_ptr() : nullptr, p.numel(), (float)lr, (float)beta1, (float)beta2,
                  (float)eps, (float)wd, (int)step, (float)grad_scale,

@@ -28,6 +28,7 @@ namespace mb {
 namespace {
 
 constexpr int kCemaThreads = 256;
+constexpr int kPf = 1;   // time steps whose inputs are fetched together (larger values cost registers and ran slower)
 
 template <int NPT>
 struct Coef {
@@ -98,12 +99,19 @@ __global__ void cema_fwd_local(const T* __restrict__ x, const float* __restrict_
 #pragma unroll
   for (int i = 0; i < NPT; ++i) h[i] = {0.f, 0.f};
   const T* xp = x + (long long)b * geo.L * geo.D + dd;
-  for (int t = t0; t < t1; ++t) {
-    const float xv = to_f(xp[(long long)t * geo.D]);
+  for (int tb = t0; tb < t1; tb += kPf) {
+    float xs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const cfloat hn = cmul(c.q[i], h[i]);
-      h[i] = {hn.re + c.p[i] * xv, hn.im};
+    for (int j = 0; j < kPf; ++j) xs[j] = tb + j < t1 ? to_f(xp[(long long)(tb + j) * geo.D]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      if (tb + j >= t1) break;
+      const float xv = xs[j];
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const cfloat hn = cmul(c.q[i], h[i]);
+        h[i] = {hn.re + c.p[i] * xv, hn.im};
+      }
     }
   }
   if (live) {
@@ -158,17 +166,25 @@ __global__ void cema_fwd_final(const T* __restrict__ x, const float* __restrict_
   }
   const float om = omega[dd];
   const long long base = (long long)b * geo.L * geo.D + dd;
-  for (int t = t0; t < t1; ++t) {
-    const float xv = to_f(x[base + (long long)t * geo.D]);
-    float acc = 0.f;
+  for (int tb = t0; tb < t1; tb += kPf) {
+    float xs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const cfloat hn = cmul(c.q[i], h[i]);
-      h[i] = {hn.re + c.p[i] * xv, hn.im};
-      acc += c.g[i].re * h[i].re - c.g[i].im * h[i].im;
+    for (int j = 0; j < kPf; ++j) xs[j] = tb + j < t1 ? to_f(x[base + (long long)(tb + j) * geo.D]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      const int t = tb + j;
+      if (t >= t1) break;
+      const float xv = xs[j];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const cfloat hn = cmul(c.q[i], h[i]);
+        h[i] = {hn.re + c.p[i] * xv, hn.im};
+        acc += c.g[i].re * h[i].re - c.g[i].im * h[i].im;
+      }
+      acc = split_sum<NSPLIT>(acc);
+      if (live && split == 0) y[base + (long long)t * geo.D] = from_f<T>(acc + om * xv);
     }
-    acc = split_sum<NSPLIT>(acc);
-    if (live && split == 0) y[base + (long long)t * geo.D] = from_f<T>(acc + om * xv);
   }
   if (h_last != nullptr && live && s == geo.S - 1) {
 #pragma unroll
@@ -189,12 +205,19 @@ __global__ void cema_bwd_rev_local(const T* __restrict__ dy, const float* __rest
 #pragma unroll
   for (int i = 0; i < NPT; ++i) st[i] = {0.f, 0.f};
   const long long base = (long long)b * geo.L * geo.D + dd;
-  for (int t = t1 - 1; t >= t0; --t) {
-    const float gy = to_f(dy[base + (long long)t * geo.D]);
+  for (int tb = t1 - 1; tb >= t0; tb -= kPf) {
+    float gs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
-      st[i] = cmul(cconj(c.q[i]), lam);
+    for (int j = 0; j < kPf; ++j) gs[j] = tb - j >= t0 ? to_f(dy[base + (long long)(tb - j) * geo.D]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      if (tb - j < t0) break;
+      const float gy = gs[j];
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
+        st[i] = cmul(cconj(c.q[i]), lam);
+      }
     }
   }
   if (live) {
@@ -226,20 +249,31 @@ __global__ void cema_bwd_rev_final(const T* __restrict__ dy, const T* __restrict
   const float om = omega[dd];
   float acc_om = 0.f;
   const long long base = (long long)b * geo.L * geo.D + dd;
-  for (int t = t1 - 1; t >= t0; --t) {
-    const float gy = to_f(dy[base + (long long)t * geo.D]);
-    const float xv = to_f(x[base + (long long)t * geo.D]);
-    float acc = 0.f;
+  for (int tb = t1 - 1; tb >= t0; tb -= kPf) {
+    float gs[kPf], xs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
-      acc += c.p[i] * lam.re;
-      acc_p[i] += lam.re * xv;
-      st[i] = cmul(cconj(c.q[i]), lam);
+    for (int j = 0; j < kPf; ++j) {
+      const bool in = tb - j >= t0;
+      gs[j] = in ? to_f(dy[base + (long long)(tb - j) * geo.D]) : 0.f;
+      xs[j] = in ? to_f(x[base + (long long)(tb - j) * geo.D]) : 0.f;
     }
-    acc = split_sum<NSPLIT>(acc);
-    acc_om += gy * xv;
-    if (live && split == 0) dx[base + (long long)t * geo.D] = from_f<T>(acc + om * gy);
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      const int t = tb - j;
+      if (t < t0) break;
+      const float gy = gs[j], xv = xs[j];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        const cfloat lam = {st[i].re + c.g[i].re * gy, st[i].im - c.g[i].im * gy};
+        acc += c.p[i] * lam.re;
+        acc_p[i] += lam.re * xv;
+        st[i] = cmul(cconj(c.q[i]), lam);
+      }
+      acc = split_sum<NSPLIT>(acc);
+      acc_om += gy * xv;
+      if (live && split == 0) dx[base + (long long)t * geo.D] = from_f<T>(acc + om * gy);
+    }
   }
   if (live) {
 #pragma unroll
@@ -265,13 +299,20 @@ __global__ void cema_bwd_fwd_local(const T* __restrict__ x, const float* __restr
 #pragma unroll
   for (int i = 0; i < NPT; ++i) h[i] = u[i] = {0.f, 0.f};
   const long long base = (long long)b * geo.L * geo.D + dd;
-  for (int t = t0; t < t1; ++t) {
-    const float xv = to_f(x[base + (long long)t * geo.D]);
+  for (int tb = t0; tb < t1; tb += kPf) {
+    float xs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
-      const cfloat hn = cmul(c.q[i], h[i]);
-      h[i] = {hn.re + c.p[i] * xv, hn.im};
+    for (int j = 0; j < kPf; ++j) xs[j] = tb + j < t1 ? to_f(x[base + (long long)(tb + j) * geo.D]) : 0.f;
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      if (tb + j >= t1) break;
+      const float xv = xs[j];
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
+        const cfloat hn = cmul(c.q[i], h[i]);
+        h[i] = {hn.re + c.p[i] * xv, hn.im};
+      }
     }
   }
   if (live) {
@@ -347,21 +388,31 @@ __global__ void cema_bwd_fwd_final(const T* __restrict__ dy, const T* __restrict
     ag[i] = aq[i] = {0.f, 0.f};
   }
   const long long base = (long long)b * geo.L * geo.D + dd;
-  for (int t = t0; t < t1; ++t) {
-    const float xv = to_f(x[base + (long long)t * geo.D]);
-    const float gy = to_f(dy[base + (long long)t * geo.D]);
+  for (int tb = t0; tb < t1; tb += kPf) {
+    float xs[kPf], gs[kPf];
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) {
-      u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
-      const cfloat hn = cmul(c.q[i], h[i]);
-      h[i] = {hn.re + c.p[i] * xv, hn.im};
-      // dgamma += conj(h) dy ; dq += (conj(gamma) dy) conj(u)
-      ag[i].re += h[i].re * gy;
-      ag[i].im -= h[i].im * gy;
-      const cfloat cg = {c.g[i].re * gy, -c.g[i].im * gy};
-      const cfloat v = cmul(cg, cconj(u[i]));
-      aq[i].re += v.re;
-      aq[i].im += v.im;
+    for (int j = 0; j < kPf; ++j) {
+      const bool in = tb + j < t1;
+      xs[j] = in ? to_f(x[base + (long long)(tb + j) * geo.D]) : 0.f;
+      gs[j] = in ? to_f(dy[base + (long long)(tb + j) * geo.D]) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kPf; ++j) {
+      if (tb + j >= t1) break;
+      const float xv = xs[j], gy = gs[j];
+#pragma unroll
+      for (int i = 0; i < NPT; ++i) {
+        u[i] = cadd(cmul(c.q[i], u[i]), h[i]);
+        const cfloat hn = cmul(c.q[i], h[i]);
+        h[i] = {hn.re + c.p[i] * xv, hn.im};
+        // dgamma += conj(h) dy ; dq += (conj(gamma) dy) conj(u)
+        ag[i].re += h[i].re * gy;
+        ag[i].im -= h[i].im * gy;
+        const cfloat cg = {c.g[i].re * gy, -c.g[i].im * gy};
+        const cfloat v = cmul(cg, cconj(u[i]));
+        aq[i].re += v.re;
+        aq[i].im += v.im;
+      }
     }
   }
   if (inc_h == nullptr && dh_last != nullptr) {

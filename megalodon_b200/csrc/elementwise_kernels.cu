@@ -85,6 +85,41 @@ __global__ void ce_bwd_kernel(const T* __restrict__ logits, const long long* __r
   }
 }
 
+__device__ __forceinline__ void load4(const float* p, float (&o)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  o[0] = t.x; o[1] = t.y; o[2] = t.z; o[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&o)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&t.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&t.y);
+  o[0] = __low2float(a); o[1] = __high2float(a); o[2] = __low2float(b); o[3] = __high2float(b);
+}
+__device__ __forceinline__ void load4(const __half* p, float (&o)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const __half2 a = *reinterpret_cast<const __half2*>(&t.x);
+  const __half2 b = *reinterpret_cast<const __half2*>(&t.y);
+  o[0] = __low2float(a); o[1] = __high2float(a); o[2] = __low2float(b); o[3] = __high2float(b);
+}
+__device__ __forceinline__ void store4(float* p, const float (&v)[4]) {
+  *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+__device__ __forceinline__ void store4(__half* p, const float (&v)[4]) {
+  __half2 a = __floats2half2_rn(v[0], v[1]), b = __floats2half2_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<uint32_t*>(&a);
+  t.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
+// Four elements per thread per iteration (16-byte accesses to the fp32 state).
 template <typename G, typename Lo>
 __global__ void adamw_kernel(float* __restrict__ p, const G* __restrict__ g, float* __restrict__ m,
                              float* __restrict__ v, Lo* __restrict__ low, long long n, float lr, float beta1,
@@ -93,17 +128,37 @@ __global__ void adamw_kernel(float* __restrict__ p, const G* __restrict__ g, flo
   const float gs = grad_scale * (scale_ptr ? *scale_ptr : 1.f);
   const float step = lr / bc1;
   const float decay = 1.f - lr * wd;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+  const long long n4 = n / 4;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4;
        i += (long long)gridDim.x * blockDim.x) {
-    const float gv = to_f(g[i]) * gs;
-    const float mv = beta1 * m[i] + (1.f - beta1) * gv;
-    const float vv = beta2 * v[i] + (1.f - beta2) * gv * gv;
-    const float denom = sqrtf(vv) / bc2_sqrt + eps;
-    const float pv = p[i] * decay - step * mv / denom;
-    m[i] = mv;
-    v[i] = vv;
-    p[i] = pv;
-    if (low != nullptr) low[i] = from_f<Lo>(pv);
+    float pv[4], gv[4], mv[4], vv[4];
+    load4(p + 4 * i, pv);
+    load4(g + 4 * i, gv);
+    load4(m + 4 * i, mv);
+    load4(v + 4 * i, vv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float gj = gv[j] * gs;
+      mv[j] = beta1 * mv[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      pv[j] = pv[j] * decay - step * mv[j] / (sqrtf(vv[j]) / bc2_sqrt + eps);
+    }
+    store4(m + 4 * i, mv);
+    store4(v + 4 * i, vv);
+    store4(p + 4 * i, pv);
+    if (low != nullptr) store4(low + 4 * i, pv);
+  }
+  // tail (n not a multiple of 4)
+  for (long long i = n4 * 4 + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float gj = to_f(g[i]) * gs;
+    const float mj = beta1 * m[i] + (1.f - beta1) * gj;
+    const float vj = beta2 * v[i] + (1.f - beta2) * gj * gj;
+    const float pj = p[i] * decay - step * mj / (sqrtf(vj) / bc2_sqrt + eps);
+    m[i] = mj;
+    v[i] = vj;
+    p[i] = pj;
+    if (low != nullptr) low[i] = from_f<Lo>(pj);
   }
 }
 
@@ -182,7 +237,7 @@ void adamw_step(float* p, const void* g, float* m, float* v, void* low, long lon
   if (n == 0) return;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2s = sqrtf(1.f - powf(beta2, (float)step));
-  const int grid = ew_grid(n);
+  const int grid = ew_grid((n + 3) / 4);
   MB_DISPATCH_DTYPE(g_dtype, {
     using G = scalar_t;
     if (low == nullptr || low_dtype == kBF16) {

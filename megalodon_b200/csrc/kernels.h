@@ -21,14 +21,17 @@ void layer_norm_bwd(const void* dy, const void* x, const void* w, float w_off, c
 void timestep_norm_fwd(const void* x, const long long* prev_count, const void* prev_mean,
                        const void* prev_var, const void* gamma, float gamma_offset, const void* beta,
                        const bool* mask, void* y, long long* count_out, void* mean_out, void* var_out,
-                       float* cummean, float* cumrstd, float* gu, float* gv, int B, int L, int H, int G,
-                       float eps, int x_dtype, int w_dtype, cudaStream_t st);
+                       float* cummean, float* cumrstd, float* gu, float* gv, double* seg_scratch, int B, int L,
+                       int H, int G, float eps, int x_dtype, int w_dtype, cudaStream_t st);
+// scan segments per sequence; the forward pass needs 3 * B * nseg * G doubles of scratch, the backward
+// pass 4 * B * nseg * G doubles (+ B * L ints when a padding mask is given)
+int tsn_num_segments(int L);
 void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_out, const void* x,
                        const void* prev_mean, const long long* count_final, const float* cummean,
                        const float* cumrstd, const void* gamma, float gamma_offset, const bool* mask,
                        void* dx, void* dprev_mean, void* dprev_var, float* dgamma, float* dbeta,
-                       float* ux, float* ds, float* db, float* dux, float* dvx, int B, int L, int H, int G,
-                       int x_dtype, int w_dtype, cudaStream_t st);
+                       float* ux, float* ds, float* db, float* dux, float* dvx, double* seg_scratch,
+                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st);
 
 // ---- CEMA (cema_kernels.cu); complex tensors are interleaved (re, im) fp32
 constexpr int kCemaSegLen = 128;

@@ -26,7 +26,7 @@
 namespace mb {
 namespace {
 
-constexpr int kSeg = 32;  // segments per sequence in the scan kernels (threadIdx.y)
+constexpr int kSegLen = 32;  // time steps per scan segment
 
 template <typename T, int LPG>
 __global__ void tsn_group_stats_kernel(const T* __restrict__ x, float* __restrict__ gu,
@@ -55,71 +55,118 @@ __global__ void tsn_group_stats_kernel(const T* __restrict__ x, float* __restric
   }
 }
 
-// grid (ceil(G/32), B), block (32, kSeg)
-template <typename T>
-__global__ void tsn_scan_kernel(const float* __restrict__ gu, const float* __restrict__ gv,
-                                const bool* __restrict__ mask, const long long* __restrict__ prev_count,
-                                const T* __restrict__ prev_mean, const T* __restrict__ prev_var,
-                                float* __restrict__ cummean, float* __restrict__ cumrstd,
-                                long long* __restrict__ count_out, T* __restrict__ mean_out,
-                                T* __restrict__ var_out, int L, int G, float eps) {
-  __shared__ double sh_n[kSeg][32], sh_a[kSeg][32], sh_b[kSeg][32];
-  const int b = blockIdx.y;
-  const int g = blockIdx.x * 32 + threadIdx.x;
-  const int s = threadIdx.y;
-  const bool live = g < G;
-  const int Ls = (L + kSeg - 1) / kSeg;
-  const int t0 = min(L, s * Ls), t1 = min(L, t0 + Ls);
-  const float* gub = gu + (long long)b * L * G;
-  const float* gvb = gv + (long long)b * L * G;
+// ---- forward scan in three small kernels over segments of kSegLen steps:
+//   seg_sums   : (b, seg, g)  sums of (1, gu, gv + gu^2) over the segment's valid steps
+//   seg_prefix : (b, g)       exclusive prefix over segments, seeded with the carried statistics
+//   seg_apply  : (b, seg, g)  running mean / rstd inside the segment
+// Threads are consecutive in g, so every access is coalesced, and no thread
+// walks more than kSegLen (or L / kSegLen) dependent steps.
+__global__ void tsn_seg_sums_kernel(const float* __restrict__ gu, const float* __restrict__ gv,
+                                    const bool* __restrict__ mask, double* __restrict__ seg, int B, int L,
+                                    int G, int nseg) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (long long)B * nseg * G) return;
+  const int g = (int)(i % G);
+  const int sgi = (int)((i / G) % nseg);
+  const int b = (int)(i / ((long long)G * nseg));
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
+  const float* gub = gu + (long long)b * L * G + g;
+  const float* gvb = gv + (long long)b * L * G + g;
   const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
-
   double n = 0, a = 0, c = 0;
-  if (live) {
-    for (int t = t0; t < t1; ++t) {
-      if (mb_ && mb_[t]) continue;
-      const double u = gub[(long long)t * G + g], v = gvb[(long long)t * G + g];
-      n += 1.0;
-      a += u;
-      c += v + u * u;
-    }
-  }
-  sh_n[s][threadIdx.x] = n;
-  sh_a[s][threadIdx.x] = a;
-  sh_b[s][threadIdx.x] = c;
-  __syncthreads();
-  if (!live) return;
-  const double n0 = (double)prev_count[b];
-  const double u0 = to_f(prev_mean[(long long)b * G + g]);
-  const double v0 = to_f(prev_var[(long long)b * G + g]);
-  double cn = n0, s1 = n0 * u0, s2 = n0 * (v0 + u0 * u0);
-  for (int k = 0; k < s; ++k) {
-    cn += sh_n[k][threadIdx.x];
-    s1 += sh_a[k][threadIdx.x];
-    s2 += sh_b[k][threadIdx.x];
-  }
-  double mean = cn > 0.5 ? s1 / cn : u0;
-  double var = cn > 0.5 ? fmax(s2 / cn - mean * mean, 0.0) : v0;
-  float* cm = cummean + (long long)b * L * G;
-  float* cr = cumrstd + (long long)b * L * G;
+#pragma unroll 8
   for (int t = t0; t < t1; ++t) {
-    if (!(mb_ && mb_[t])) {
-      const double u = gub[(long long)t * G + g], v = gvb[(long long)t * G + g];
-      cn += 1.0;
-      s1 += u;
-      s2 += v + u * u;
-      mean = s1 / cn;
-      var = fmax(s2 / cn - mean * mean, 0.0);
-    }
-    // padded steps keep the running values, so cummean[t-1] is always the
-    // state *before* step t (the backward pass relies on that)
-    cm[(long long)t * G + g] = (float)mean;
-    cr[(long long)t * G + g] = (float)(1.0 / sqrt(var + (double)eps));
+    const double u = gub[(long long)t * G], v = gvb[(long long)t * G];
+    const double w = (mb_ && mb_[t]) ? 0.0 : 1.0;
+    n += w;
+    a += w * u;
+    c += w * (v + u * u);
   }
-  if (s == kSeg - 1) {
-    mean_out[(long long)b * G + g] = from_f<T>((float)mean);
-    var_out[(long long)b * G + g] = from_f<T>((float)var);
-    if (g == 0) count_out[b] = (long long)(cn + 0.5);
+  const long long total = (long long)B * nseg * G;
+  seg[i] = n;
+  seg[total + i] = a;
+  seg[2 * total + i] = c;
+}
+
+template <typename T>
+__global__ void tsn_seg_prefix_kernel(double* __restrict__ seg, const long long* __restrict__ prev_count,
+                                      const T* __restrict__ prev_mean, const T* __restrict__ prev_var,
+                                      long long* __restrict__ count_out, T* __restrict__ mean_out,
+                                      T* __restrict__ var_out, int B, int G, int nseg) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * G) return;
+  const int g = i % G, b = i / G;
+  const long long total = (long long)B * nseg * G;
+  const double n0 = (double)prev_count[b];
+  const double u0 = to_f(prev_mean[i]), v0 = to_f(prev_var[i]);
+  double cn = n0, s1 = n0 * u0, s2 = n0 * (v0 + u0 * u0);
+#pragma unroll 4
+  for (int k = 0; k < nseg; ++k) {
+    const long long idx = ((long long)b * nseg + k) * G + g;
+    const double dn = seg[idx], da = seg[total + idx], dc = seg[2 * total + idx];
+    seg[idx] = cn;
+    seg[total + idx] = s1;
+    seg[2 * total + idx] = s2;
+    cn += dn;
+    s1 += da;
+    s2 += dc;
+  }
+  double mean = u0, var = v0;
+  if (cn > 0.5) {
+    mean = s1 / cn;
+    var = fmax(s2 / cn - mean * mean, 0.0);
+  }
+  mean_out[i] = from_f<T>((float)mean);
+  var_out[i] = from_f<T>((float)var);
+  if (g == 0) count_out[b] = (long long)(cn + 0.5);
+}
+
+template <typename T>
+__global__ void tsn_seg_apply_kernel(const float* __restrict__ gu, const float* __restrict__ gv,
+                                     const bool* __restrict__ mask, const double* __restrict__ seg,
+                                     const T* __restrict__ prev_mean, const T* __restrict__ prev_var,
+                                     float* __restrict__ cummean, float* __restrict__ cumrstd, int B, int L,
+                                     int G, int nseg, float eps) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)B * nseg * G;
+  if (i >= total) return;
+  const int g = (int)(i % G);
+  const int sgi = (int)((i / G) % nseg);
+  const int b = (int)(i / ((long long)G * nseg));
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
+  const long long off = (long long)b * L * G + g;
+  const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
+  double cn = seg[i], s1 = seg[total + i], s2 = seg[2 * total + i];
+  double mean = to_f(prev_mean[b * G + g]), var = to_f(prev_var[b * G + g]);
+  if (cn > 0.5) {
+    mean = s1 / cn;
+    var = fmax(s2 / cn - mean * mean, 0.0);
+  }
+  for (int tb = t0; tb < t1; tb += 8) {
+    float us[8], vs[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const bool in = tb + j < t1;
+      us[j] = in ? gu[off + (long long)(tb + j) * G] : 0.f;
+      vs[j] = in ? gv[off + (long long)(tb + j) * G] : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int t = tb + j;
+      if (t >= t1) break;
+      if (!(mb_ && mb_[t])) {
+        const double u = us[j], v = vs[j];
+        cn += 1.0;
+        s1 += u;
+        s2 += v + u * u;
+        mean = s1 / cn;
+        var = fmax(s2 / cn - mean * mean, 0.0);
+      }
+      // padded steps keep the running values, so cummean[t-1] is always the
+      // state *before* step t (the backward pass relies on that)
+      cummean[off + (long long)t * G] = (float)mean;
+      cumrstd[off + (long long)t * G] = (float)(1.0 / sqrt(var + (double)eps));
+    }
   }
 }
 
@@ -187,102 +234,129 @@ __device__ __forceinline__ Affine affine_compose(const Affine& second, const Aff
           second.a * first.o1 + second.b * first.o2 + second.o1, second.a * first.o2 + second.o2};
 }
 
+// running count *including* step t
+__device__ __forceinline__ double count_at(const int* cumvalid, long long first_count, int b, int L, int t) {
+  return cumvalid ? (double)(first_count + cumvalid[(long long)b * L + t]) : (double)(first_count + t + 1);
+}
+
+// inclusive prefix count of non-padded steps, one thread per batch row (only used with a padding mask)
+__global__ void tsn_cumvalid_kernel(const bool* __restrict__ mask, int* __restrict__ cumvalid, int B, int L) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  int c = 0;
+  for (int t = 0; t < L; ++t) {
+    c += mask[(long long)b * L + t] ? 0 : 1;
+    cumvalid[(long long)b * L + t] = c;
+  }
+}
+
+struct StepIn {
+  const float *ux, *ds, *db, *cummean, *cumrstd;
+};
+
+__device__ __forceinline__ Affine tsn_step_map(const StepIn& in, long long i, int G, int t, double pm, double m0) {
+  const double c1 = (m0 - 1.0) / m0, c2 = 1.0 / m0;
+  const double prev_u = t == 0 ? pm : (double)in.cummean[i - G];
+  const double delta = (double)in.ux[i] - prev_u;
+  const double r = in.cumrstd[i];
+  const double r3ds = r * r * r * (double)in.ds[i];
+  Affine m;
+  m.a = c1;
+  m.b = -2.0 * c1 * c2 * delta;
+  m.o1 = -c1 * r * (double)in.db[i] + c1 * c2 * delta * r3ds;
+  m.o2 = -0.5 * c1 * r3ds;
+  return m;
+}
+
+// (b, seg, g): composite map of the segment's valid steps, taken from its last step to its first
 template <typename T>
-__global__ void tsn_bwd_scan_kernel(const float* __restrict__ ux, const float* __restrict__ ds,
-                                    const float* __restrict__ db, const float* __restrict__ cummean,
-                                    const float* __restrict__ cumrstd, const bool* __restrict__ mask,
-                                    const long long* __restrict__ count_final,
-                                    const T* __restrict__ prev_mean, const T* __restrict__ dmean_out,
-                                    const T* __restrict__ dvar_out, float* __restrict__ dux,
-                                    float* __restrict__ dvx, T* __restrict__ dprev_mean,
-                                    T* __restrict__ dprev_var, int L, int G) {
-  __shared__ double sh[4][kSeg][32];
-  __shared__ int sh_valid[kSeg];
-  const int b = blockIdx.y;
-  const int g = blockIdx.x * 32 + threadIdx.x;
-  const int s = threadIdx.y;
-  const bool live = g < G;
-  const int Ls = (L + kSeg - 1) / kSeg;
-  const int t0 = min(L, s * Ls), t1 = min(L, t0 + Ls);
+__global__ void tsn_bwd_seg_maps_kernel(StepIn in, const bool* __restrict__ mask, const int* __restrict__ cumvalid,
+                                        const long long* __restrict__ count_final,
+                                        const T* __restrict__ prev_mean, double* __restrict__ maps, int B, int L,
+                                        int G, int nseg) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)B * nseg * G;
+  if (i >= total) return;
+  const int g = (int)(i % G);
+  const int sgi = (int)((i / G) % nseg);
+  const int b = (int)(i / ((long long)G * nseg));
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
   const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
-  const long long off = (long long)b * L * G;
-
-  // number of valid steps in each segment (needed to recover the running count)
-  if (threadIdx.x == 0) {
-    int nv = 0;
-    for (int t = t0; t < t1; ++t) nv += !(mb_ && mb_[t]);
-    sh_valid[s] = nv;
-  }
-  __syncthreads();
-  // count *including* the last step of this segment
-  long long cnt_end = count_final[b];
-  for (int k = kSeg - 1; k > s; --k) cnt_end -= sh_valid[k];
-
-  const double pm = live ? (double)to_f(prev_mean[(long long)b * G + g]) : 0.0;
-
-  auto step_map = [&](int t, double m0) -> Affine {
-    const long long i = off + (long long)t * G + g;
-    const double c1 = (m0 - 1.0) / m0, c2 = 1.0 / m0;
-    const double prev_u = t == 0 ? pm : (double)cummean[i - G];
-    const double delta = (double)ux[i] - prev_u;
-    const double r = cumrstd[i];
-    const double r3ds = r * r * r * (double)ds[i];
-    Affine m;
-    m.a = c1;
-    m.b = -2.0 * c1 * c2 * delta;
-    m.o1 = -c1 * r * (double)db[i] + c1 * c2 * delta * r3ds;
-    m.o2 = -0.5 * c1 * r3ds;
-    return m;
-  };
-
+  const long long first = count_final[b] - (cumvalid ? cumvalid[(long long)b * L + L - 1] : L);
+  const double pm = to_f(prev_mean[b * G + g]);
+  const long long off = (long long)b * L * G + g;
   Affine seg = affine_identity();
-  if (live) {
-    long long m0 = cnt_end;
-    for (int t = t1 - 1; t >= t0; --t) {
-      if (mb_ && mb_[t]) continue;
-      seg = affine_compose(step_map(t, (double)m0), seg);
-      --m0;
-    }
+  for (int t = t1 - 1; t >= t0; --t) {
+    if (mb_ && mb_[t]) continue;
+    seg = affine_compose(tsn_step_map(in, off + (long long)t * G, G, t, pm, count_at(cumvalid, first, b, L, t)), seg);
   }
-  sh[0][s][threadIdx.x] = seg.a;
-  sh[1][s][threadIdx.x] = seg.b;
-  sh[2][s][threadIdx.x] = seg.o1;
-  sh[3][s][threadIdx.x] = seg.o2;
-  __syncthreads();
-  if (!live) return;
+  maps[i] = seg.a;
+  maps[total + i] = seg.b;
+  maps[2 * total + i] = seg.o1;
+  maps[3 * total + i] = seg.o2;
+}
 
-  double u = to_f(dmean_out[(long long)b * G + g]);
-  double v = to_f(dvar_out[(long long)b * G + g]);
-  for (int k = kSeg - 1; k > s; --k) {
-    const double a = sh[0][k][threadIdx.x], bb = sh[1][k][threadIdx.x];
-    const double nu = a * u + bb * v + sh[2][k][threadIdx.x];
-    v = a * v + sh[3][k][threadIdx.x];
+// (b, g): walk the segments from last to first; leaves each segment's incoming (u, v) in maps[0], maps[1]
+template <typename T>
+__global__ void tsn_bwd_seg_prefix_kernel(double* __restrict__ maps, const T* __restrict__ dmean_out,
+                                          const T* __restrict__ dvar_out, T* __restrict__ dprev_mean,
+                                          T* __restrict__ dprev_var, int B, int G, int nseg) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= B * G) return;
+  const int g = i % G, b = i / G;
+  const long long total = (long long)B * nseg * G;
+  double u = to_f(dmean_out[i]), v = to_f(dvar_out[i]);
+#pragma unroll 4
+  for (int k = nseg - 1; k >= 0; --k) {
+    const long long idx = ((long long)b * nseg + k) * G + g;
+    const double a = maps[idx], bb = maps[total + idx], o1 = maps[2 * total + idx], o2 = maps[3 * total + idx];
+    maps[idx] = u;
+    maps[total + idx] = v;
+    const double nu = a * u + bb * v + o1;
+    v = a * v + o2;
     u = nu;
   }
-  long long m0 = cnt_end;
+  dprev_mean[i] = from_f<T>((float)u);
+  dprev_var[i] = from_f<T>((float)v);
+}
+
+// (b, seg, g): replay the segment from its incoming state and emit d(ux), d(vx) per step
+template <typename T>
+__global__ void tsn_bwd_seg_apply_kernel(StepIn in, const bool* __restrict__ mask, const int* __restrict__ cumvalid,
+                                         const long long* __restrict__ count_final,
+                                         const T* __restrict__ prev_mean, const double* __restrict__ maps,
+                                         float* __restrict__ dux, float* __restrict__ dvx, int B, int L, int G,
+                                         int nseg) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long total = (long long)B * nseg * G;
+  if (i >= total) return;
+  const int g = (int)(i % G);
+  const int sgi = (int)((i / G) % nseg);
+  const int b = (int)(i / ((long long)G * nseg));
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
+  const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
+  const long long first = count_final[b] - (cumvalid ? cumvalid[(long long)b * L + L - 1] : L);
+  const double pm = to_f(prev_mean[b * G + g]);
+  const long long off = (long long)b * L * G + g;
+  double u = maps[i], v = maps[total + i];
   for (int t = t1 - 1; t >= t0; --t) {
-    const long long i = off + (long long)t * G + g;
+    const long long e = off + (long long)t * G;
     if (mb_ && mb_[t]) {
-      dux[i] = 0.f;
-      dvx[i] = 0.f;
+      dux[e] = 0.f;
+      dvx[e] = 0.f;
       continue;
     }
-    const double md = (double)m0;
+    const double md = count_at(cumvalid, first, b, L, t);
     const double c1 = (md - 1.0) / md, c2 = 1.0 / md;
-    const double prev_u = t == 0 ? pm : (double)cummean[i - G];
-    const double delta = (double)ux[i] - prev_u;
-    const double r = cumrstd[i];
-    const double du = u - r * (double)db[i];
-    const double dv = v - 0.5 * r * r * r * (double)ds[i];
-    dux[i] = (float)(c2 * du + 2.0 * c1 * c2 * dv * delta);
-    dvx[i] = (float)(c2 * dv);
+    const double prev_u = t == 0 ? pm : (double)in.cummean[e - G];
+    const double delta = (double)in.ux[e] - prev_u;
+    const double r = in.cumrstd[e];
+    const double du = u - r * (double)in.db[e];
+    const double dv = v - 0.5 * r * r * r * (double)in.ds[e];
+    dux[e] = (float)(c2 * du + 2.0 * c1 * c2 * dv * delta);
+    dvx[e] = (float)(c2 * dv);
     u = c1 * du - 2.0 * c1 * c2 * dv * delta;
     v = c1 * dv;
-    --m0;
-  }
-  if (s == 0) {
-    dprev_mean[(long long)b * G + g] = from_f<T>((float)u);
-    dprev_var[(long long)b * G + g] = from_f<T>((float)v);
   }
 }
 
@@ -350,6 +424,8 @@ int pick_lpg(int Dg) {
 
 }  // namespace
 
+int tsn_num_segments(int L) { return (L + kSegLen - 1) / kSegLen; }
+
 #define TSN_DISPATCH(xd, wd, ...)                                    \
   MB_DISPATCH_DTYPE(xd, {                                            \
     using T = scalar_t;                                              \
@@ -365,8 +441,8 @@ int pick_lpg(int Dg) {
 void timestep_norm_fwd(const void* x, const long long* prev_count, const void* prev_mean,
                        const void* prev_var, const void* gamma, float gamma_offset, const void* beta,
                        const bool* mask, void* y, long long* count_out, void* mean_out, void* var_out,
-                       float* cummean, float* cumrstd, float* gu, float* gv, int B, int L, int H, int G,
-                       float eps, int x_dtype, int w_dtype, cudaStream_t st) {
+                       float* cummean, float* cumrstd, float* gu, float* gv, double* seg_scratch, int B, int L,
+                       int H, int G, float eps, int x_dtype, int w_dtype, cudaStream_t st) {
   const long long rows = (long long)B * L;
   const int lpg = pick_lpg(H / G);
   TSN_DISPATCH(x_dtype, w_dtype, {
@@ -374,9 +450,15 @@ void timestep_norm_fwd(const void* x, const long long* prev_count, const void* p
       const long long threads = rows * G * LPG;
       tsn_group_stats_kernel<T, LPG><<<div_up(threads, 256), 256, 0, st>>>((const T*)x, gu, gv, rows, H, G);
     });
-    tsn_scan_kernel<T><<<dim3(div_up(G, 32), B), dim3(32, kSeg), 0, st>>>(
-        gu, gv, mask, prev_count, (const T*)prev_mean, (const T*)prev_var, cummean, cumrstd, count_out,
-        (T*)mean_out, (T*)var_out, L, G, eps);
+    const int nseg = tsn_num_segments(L);
+    const long long nsg = (long long)B * nseg * G;
+    tsn_seg_sums_kernel<<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, B, L, G, nseg);
+    tsn_seg_prefix_kernel<T><<<div_up((long long)B * G, 128), 128, 0, st>>>(
+        seg_scratch, prev_count, (const T*)prev_mean, (const T*)prev_var, count_out, (T*)mean_out, (T*)var_out,
+        B, G, nseg);
+    tsn_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, (const T*)prev_mean,
+                                                            (const T*)prev_var, cummean, cumrstd, B, L, G, nseg,
+                                                            eps);
     const int grid = (int)std::min<long long>(div_up(rows * H, 256), 148LL * 16);
     tsn_apply_kernel<T, W><<<grid, 256, 0, st>>>((const T*)x, cummean, cumrstd, (const W*)gamma,
                                                  gamma_offset, (const W*)beta, mask, (T*)y, rows, H, G);
@@ -387,8 +469,8 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
                        const void* prev_mean, const long long* count_final, const float* cummean,
                        const float* cumrstd, const void* gamma, float gamma_offset, const bool* mask,
                        void* dx, void* dprev_mean, void* dprev_var, float* dgamma, float* dbeta,
-                       float* ux, float* ds, float* db, float* dux, float* dvx, int B, int L, int H, int G,
-                       int x_dtype, int w_dtype, cudaStream_t st) {
+                       float* ux, float* ds, float* db, float* dux, float* dvx, double* seg_scratch,
+                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st) {
   const long long rows = (long long)B * L;
   const int lpg = pick_lpg(H / G);
   TSN_DISPATCH(x_dtype, w_dtype, {
@@ -397,9 +479,17 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
       tsn_group_grads_kernel<T, W, LPG><<<div_up(threads, 256), 256, 0, st>>>(
           (const T*)dy, (const T*)x, cummean, (const W*)gamma, gamma_offset, ux, ds, db, rows, H, G);
     });
-    tsn_bwd_scan_kernel<T><<<dim3(div_up(G, 32), B), dim3(32, kSeg), 0, st>>>(
-        ux, ds, db, cummean, cumrstd, mask, count_final, (const T*)prev_mean, (const T*)dmean_out,
-        (const T*)dvar_out, dux, dvx, (T*)dprev_mean, (T*)dprev_var, L, G);
+    const int nseg = tsn_num_segments(L);
+    const long long nsg = (long long)B * nseg * G;
+    if (mask != nullptr) tsn_cumvalid_kernel<<<div_up(B, 32), 32, 0, st>>>(mask, cumvalid, B, L);
+    const int* cv = mask != nullptr ? cumvalid : nullptr;
+    const StepIn in{ux, ds, db, cummean, cumrstd};
+    tsn_bwd_seg_maps_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
+                                                               seg_scratch, B, L, G, nseg);
+    tsn_bwd_seg_prefix_kernel<T><<<div_up((long long)B * G, 128), 128, 0, st>>>(
+        seg_scratch, (const T*)dmean_out, (const T*)dvar_out, (T*)dprev_mean, (T*)dprev_var, B, G, nseg);
+    tsn_bwd_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
+                                                                seg_scratch, dux, dvx, B, L, G, nseg);
     const int grid = (int)std::min<long long>(rows, 148LL * 4);
     tsn_bwd_apply_kernel<T, W><<<grid, kBwdThreads, 0, st>>>((const T*)dy, (const T*)x, cummean, cumrstd, ux, dux,
                                                      dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,

@@ -145,9 +145,13 @@ def cross_entropy(logits, target, weight=None, ignore_index: int = -100, label_s
 
 
 def adamw_step(param, grad, m, v, *, lr, beta1, beta2, eps, weight_decay, step, grad_scale=1.0,
-               low=None):
+               low=None, scale_ptr=None):
+    """`scale_ptr`: optional device scalar multiplied into the gradient (deferred clipping)."""
     if native_for(param):
         return _cuda().adamw_step(param, grad, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
-                                  weight_decay=weight_decay, step=step, grad_scale=grad_scale, low=low)
+                                  weight_decay=weight_decay, step=step, grad_scale=grad_scale, low=low,
+                                  scale_ptr=scale_ptr)
+    if scale_ptr is not None:
+        grad_scale = grad_scale * float(scale_ptr)
     return reference.adamw_step(param, grad, m, v, lr=lr, beta1=beta1, beta2=beta2, eps=eps,
                                 weight_decay=weight_decay, step=step, grad_scale=grad_scale, low=low)

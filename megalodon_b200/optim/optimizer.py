@@ -52,12 +52,17 @@ class FusedAdamW(Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        roots = set()
         for group in self.param_groups:
             b1, b2 = group["betas"]
             for p in group["params"]:
                 unit = getattr(p, "_fsdp_unit", None)
+                scale_ptr = None
                 if unit is not None:
                     unit._sync_comm()
+                    root = getattr(unit, "_root", unit)
+                    scale_ptr = root._clip_coef
+                    roots.add(root)
                 grad = p.grad if p.grad is not None else getattr(p, "_grad_shard", None)
                 if grad is None:
                     continue
@@ -74,11 +79,14 @@ class FusedAdamW(Optimizer):
                     low = p._lowp_shard
                 ops.adamw_step(p.data, grad, st["exp_avg"], st["exp_avg_sq"], lr=group["lr"],
                                beta1=b1, beta2=b2, eps=group["eps"],
-                               weight_decay=group["weight_decay"], step=st["step"], low=low)
+                               weight_decay=group["weight_decay"], step=st["step"], low=low,
+                               **({"scale_ptr": scale_ptr} if scale_ptr is not None else {}))
                 # master weights changed behind autograd's back: bump our own counter
                 p._master_version = getattr(p, "_master_version", 0) + 1
                 if low is not None:
                     p._lowp_version = (p._version, p._master_version)
+        for root in roots:
+            root._clip_coef = None
         return loss
 
     def zero_grad(self, set_to_none: bool = True) -> None:

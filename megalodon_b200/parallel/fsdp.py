@@ -146,6 +146,12 @@ class FullyShardedDataParallel(nn.Module):
         self.force_input_to_fp32 = force_input_to_fp32
         self.verbose = verbose
         self.materialize_fp32_grads = materialize_fp32_grads
+        # When True, `clip_grad_norm_` leaves the gradients untouched and hands its clipping
+        # coefficient (a device scalar) to `FusedAdamW`, which applies it while reading the
+        # gradients: one pass over gradient memory saved.  Gradients inspected between the two
+        # calls are then unclipped.
+        self.defer_grad_clip = False
+        self._clip_coef = None
         self.gradient_divide_factor = float(gradient_divide_factor if gradient_divide_factor is not None
                                             else self.world_size)
         self.training_state = TrainingState.IDLE
@@ -512,11 +518,16 @@ class FullyShardedDataParallel(nn.Module):
         if self.model_parallel_world_size > 1:
             dist.all_reduce(acc, group=self.model_parallel_process_group)
         norm, coef = cuda_ops.clip_coef(acc, max_norm)
-        for g in grads:
-            cuda_ops.scale_by_ptr(g, coef)
+        if getattr(self, "defer_grad_clip", False):
+            # the fused optimiser multiplies by `coef` while it reads the gradients
+            self._clip_coef = coef
+        else:
+            for g in grads:
+                cuda_ops.scale_by_ptr(g, coef)
         return norm
 
     def zero_grad(self, set_to_none: bool = True) -> None:
+        self._clip_coef = None
         for u in self._units():
             u.flat_param.grad = None
             u.flat_param._grad_shard = None
