@@ -416,6 +416,53 @@ void attn_softmax_bwd(const Tensor& p, Tensor& dp, int64_t L1, int64_t L2, bool 
                        stream());
 }
 
+// ------------------------------------------------------------------ peer-memory communication
+// Peer addresses are passed as integers (they come from the symmetric-memory rendezvous and are not
+// tensors of this process).  `counter` / `err` are small device tensors owned by the caller.
+void p2p_send(const Tensor& src, int64_t remote_dst, int64_t nbytes, int64_t remote_flag, int64_t seq,
+              int64_t local_ack, int64_t need_ack, Tensor& counter, int64_t timeout_ns, Tensor& err) {
+  check_cuda_contig(src, "src");
+  c10::cuda::CUDAGuard guard(src.device());
+  TORCH_CHECK(nbytes % 16 == 0 && nbytes <= (int64_t)(src.numel() * src.element_size()), "payload must be whole 16-byte words");
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(src.data_ptr()) % 16 == 0 && remote_dst % 16 == 0);
+  mb::p2p_send(src.data_ptr(), reinterpret_cast<void*>(remote_dst), nbytes, reinterpret_cast<unsigned int*>(remote_flag),
+               (unsigned int)seq, reinterpret_cast<const unsigned int*>(local_ack), (unsigned int)need_ack,
+               reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), (unsigned long long)timeout_ns,
+               err.data_ptr<int>(), stream());
+}
+
+void p2p_recv(Tensor& dst, int64_t local_slot, int64_t nbytes, int64_t local_flag, int64_t seq, int64_t remote_ack,
+              Tensor& counter, int64_t timeout_ns, Tensor& err) {
+  check_cuda_contig(dst, "dst");
+  c10::cuda::CUDAGuard guard(dst.device());
+  TORCH_CHECK(nbytes % 16 == 0 && nbytes <= (int64_t)(dst.numel() * dst.element_size()));
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0 && local_slot % 16 == 0);
+  mb::p2p_recv(dst.data_ptr(), reinterpret_cast<const void*>(local_slot), nbytes,
+               reinterpret_cast<const unsigned int*>(local_flag), (unsigned int)seq,
+               reinterpret_cast<unsigned int*>(remote_ack), reinterpret_cast<unsigned int*>(counter.data_ptr<int>()),
+               (unsigned long long)timeout_ns, err.data_ptr<int>(), stream());
+}
+
+// pads: int64 device tensor with the address of every rank's signal pad
+void peer_barrier(const Tensor& pads, int64_t rank, int64_t epoch, int64_t timeout_ns, Tensor& err) {
+  check_cuda_contig(pads, "pads");
+  c10::cuda::CUDAGuard guard(pads.device());
+  TORCH_CHECK(pads.scalar_type() == at::kLong && pads.numel() <= 32);
+  mb::peer_barrier(reinterpret_cast<unsigned int* const*>(pads.data_ptr<int64_t>()), (int)rank, (int)pads.numel(),
+                   (unsigned int)epoch, (unsigned long long)timeout_ns, err.data_ptr<int>(), stream());
+}
+
+// bufs: int64 device tensor with the address of every rank's copy of the buffer (same byte offset everywhere)
+void allreduce_sumsq(const Tensor& bufs, int64_t rank, int64_t nbytes, double scale, const OptTensor& sumsq,
+                     int64_t dtype) {
+  check_cuda_contig(bufs, "bufs");
+  c10::cuda::CUDAGuard guard(bufs.device());
+  TORCH_CHECK(bufs.scalar_type() == at::kLong && nbytes % 16 == 0);
+  if (sumsq.has_value()) TORCH_CHECK(sumsq->scalar_type() == at::kDouble && sumsq->numel() == 1);
+  mb::allreduce_sumsq(reinterpret_cast<void* const*>(bufs.data_ptr<int64_t>()), (int)rank, (int)bufs.numel(), nbytes,
+                      (float)scale, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (int)dtype, stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -439,4 +486,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm);
   m.def("attn_softmax_fwd", &attn_softmax_fwd);
   m.def("attn_softmax_bwd", &attn_softmax_bwd);
+  m.def("p2p_send", &p2p_send);
+  m.def("p2p_recv", &p2p_recv);
+  m.def("peer_barrier", &peer_barrier);
+  m.def("allreduce_sumsq", &allreduce_sumsq);
 }

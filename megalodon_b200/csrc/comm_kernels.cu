@@ -1,0 +1,254 @@
+// Communication kernels over peer-mapped ("symmetric") memory on an NVSwitch
+// box: every rank holds a buffer of the same size and knows the device address
+// of every peer's copy, so a kernel moves data with plain loads / stores over
+// NVLink and synchronises with flags it reads and writes itself.
+//
+//   p2p_send / p2p_recv   chunk-parallel state handoff: the sender stores the
+//                         payload straight into the receiver's mailbox slot and
+//                         raises a sequence-numbered flag there; the receiver
+//                         polls its own flag, copies the payload out and
+//                         acknowledges into the sender's memory (flow control).
+//                         Replaces the blocking NCCL send/recv pair of the
+//                         reference (modules/chunk_parallel/mappings.py:25-89).
+//   peer_barrier          all ranks exchange an epoch number through signal pads.
+//   allreduce_sumsq       sum over ranks of a buffer held in symmetric memory;
+//                         each rank reduces one slice by pulling it from every
+//                         peer, accumulates the squared norm of the reduced
+//                         slice on the way (the gradient-norm partial sum that
+//                         clipping needs) and pushes the result to every peer.
+//                         Replaces the bucketed all_reduce of grad_all_reduce
+//                         plus the separate norm pass (fairscale_fsdp.py:89-219).
+//
+// Every wait is bounded by a caller-supplied timeout; on expiry the kernel sets
+// `*err`, skips its remaining work and returns, so a missing peer shows up as a
+// Python exception instead of a hung GPU.  Only plain (non-multimem) peer
+// accesses are used here.
+#include "common.cuh"
+#include "kernels.h"
+
+namespace mb {
+namespace {
+
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_sys(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Wait until *flag >= want (unsigned, epochs only grow).  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want,
+                                             unsigned long long timeout_ns) {
+  if (ld_acquire_sys(flag) >= want) return true;
+  const unsigned long long t0 = now_ns();
+  unsigned int spins = 0;
+  while (ld_acquire_sys(flag) < want) {
+    if ((++spins & 0x3f) == 0 && now_ns() - t0 > timeout_ns) return false;
+    __nanosleep(64);
+  }
+  return true;
+}
+
+// Counts CTAs that have finished; returns true in exactly one thread of the last CTA to arrive.
+__device__ __forceinline__ bool last_block_done(unsigned int* counter) {
+  __shared__ bool is_last;
+  __threadfence_system();           // this CTA's (possibly remote) stores are ordered before the count
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int prev = atomicAdd(counter, 1u);
+    is_last = prev == gridDim.x - 1;
+    if (is_last) *counter = 0;      // ready for the next launch
+  }
+  __syncthreads();
+  return is_last && threadIdx.x == 0;
+}
+
+// payload: n16 16-byte words.  remote_* live in the receiver's memory, local_ack in ours.
+__global__ void p2p_send_kernel(const uint4* __restrict__ src, uint4* __restrict__ remote_dst, long long n16,
+                                unsigned int* remote_flag, unsigned int seq, const unsigned int* local_ack,
+                                unsigned int need_ack, unsigned int* counter, unsigned long long timeout_ns,
+                                int* err) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = (need_ack == 0 || wait_flag_ge(local_ack, need_ack, timeout_ns)) ? 1 : 0;
+  __syncthreads();
+  if (ok) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+         i += (long long)gridDim.x * blockDim.x)
+      remote_dst[i] = src[i];
+  } else if (threadIdx.x == 0) {
+    atomicExch(err, 11);            // slot still unacknowledged: receiver is gone or too far behind
+  }
+  const bool flagger = last_block_done(counter);
+  if (flagger && ok) st_release_sys(remote_flag, seq);
+}
+
+__global__ void p2p_recv_kernel(uint4* __restrict__ dst, const uint4* __restrict__ local_slot, long long n16,
+                                const unsigned int* local_flag, unsigned int seq, unsigned int* remote_ack,
+                                unsigned int* counter, unsigned long long timeout_ns, int* err) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) ok = wait_flag_ge(local_flag, seq, timeout_ns) ? 1 : 0;
+  __syncthreads();
+  if (ok) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
+         i += (long long)gridDim.x * blockDim.x)
+      dst[i] = local_slot[i];
+  } else if (threadIdx.x == 0) {
+    atomicExch(err, 12);            // the message never arrived
+  }
+  const bool acker = last_block_done(counter);
+  if (acker && ok && remote_ack != nullptr) st_release_sys(remote_ack, seq);
+}
+
+// Each rank writes `epoch` into slot [rank] of every peer's pad and waits until all slots of its own
+// pad reach `epoch`.  pads[p] is the address of rank p's pad (an array of `world` uint32).
+__global__ void peer_barrier_kernel(unsigned int* const* __restrict__ pads, int rank, int world, unsigned int epoch,
+                                    unsigned long long timeout_ns, int* err) {
+  const int p = threadIdx.x;
+  __threadfence_system();
+  if (p < world) st_release_sys(pads[p] + rank, epoch);
+  if (p < world && !wait_flag_ge(pads[rank] + p, epoch, timeout_ns)) atomicExch(err, 13);
+}
+
+template <typename T>
+struct Vec8;
+template <>
+struct Vec8<__nv_bfloat16> {
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __low2float(h[i]);
+      f[2 * i + 1] = __high2float(h[i]);
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+};
+template <>
+struct Vec8<__half> {
+  static __device__ __forceinline__ void unpack(const uint4& u, float (&f)[8]) {
+    const __half2* h = reinterpret_cast<const __half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      f[2 * i] = __low2float(h[i]);
+      f[2 * i + 1] = __high2float(h[i]);
+    }
+  }
+  static __device__ __forceinline__ uint4 pack(const float (&f)[8]) {
+    uint4 u;
+    __half2* h = reinterpret_cast<__half2*>(&u);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(f[2 * i], f[2 * i + 1]);
+    return u;
+  }
+};
+
+// 16-bit element types: 8 elements per 16-byte word.  bufs[p] = address of rank p's copy.
+// Rank r owns words [r * slice16, (r + 1) * slice16) of the n16-word buffer.
+template <typename T>
+__global__ void allreduce_sumsq_16bit_kernel(uint4* const* __restrict__ bufs, int rank, int world, long long n16,
+                                             long long slice16, float scale, double* __restrict__ sumsq) {
+  __shared__ float scratch[32];
+  const long long lo = (long long)rank * slice16;
+  const long long hi = min(n16, lo + slice16);
+  float ss = 0.f;
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+    for (int p = 0; p < world; ++p) {
+      const int src = (rank + p) % world;          // start with the local copy, then walk the peers
+      float f[8];
+      Vec8<T>::unpack(bufs[src][i], f);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) acc[j] += f[j];
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      acc[j] *= scale;
+      ss += acc[j] * acc[j];
+    }
+    const uint4 out = Vec8<T>::pack(acc);
+    for (int p = 0; p < world; ++p) bufs[(rank + p) % world][i] = out;
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
+}
+
+__global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int rank, int world, long long n16,
+                                           long long slice16, float scale, double* __restrict__ sumsq) {
+  __shared__ float scratch[32];
+  const long long lo = (long long)rank * slice16;
+  const long long hi = min(n16, lo + slice16);
+  float ss = 0.f;
+  for (long long i = lo + (long long)blockIdx.x * blockDim.x + threadIdx.x; i < hi;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int p = 0; p < world; ++p) {
+      const float4 f = bufs[(rank + p) % world][i];
+      acc.x += f.x; acc.y += f.y; acc.z += f.z; acc.w += f.w;
+    }
+    acc.x *= scale; acc.y *= scale; acc.z *= scale; acc.w *= scale;
+    ss += acc.x * acc.x + acc.y * acc.y + acc.z * acc.z + acc.w * acc.w;
+    for (int p = 0; p < world; ++p) bufs[(rank + p) % world][i] = acc;
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
+}
+
+}  // namespace
+
+void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
+              const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,
+              unsigned long long timeout_ns, int* err, cudaStream_t st) {
+  const long long n16 = nbytes / 16;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
+  p2p_send_kernel<<<grid, 256, 0, st>>>((const uint4*)src, (uint4*)remote_dst, n16, remote_flag, seq, local_ack,
+                                        need_ack, counter, timeout_ns, err);
+}
+
+void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
+              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* err,
+              cudaStream_t st) {
+  const long long n16 = nbytes / 16;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
+  p2p_recv_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (const uint4*)local_slot, n16, local_flag, seq, remote_ack,
+                                        counter, timeout_ns, err);
+}
+
+void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
+                  int* err, cudaStream_t st) {
+  peer_barrier_kernel<<<1, 32, 0, st>>>(pads, rank, world, epoch, timeout_ns, err);
+}
+
+void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
+                     int dtype, cudaStream_t st) {
+  const long long n16 = nbytes / 16;
+  const long long slice16 = (n16 + world - 1) / world;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(slice16, 256), 148LL * 4));
+  if (dtype == kBF16)
+    allreduce_sumsq_16bit_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16,
+                                                                    scale, sumsq);
+  else if (dtype == kF16)
+    allreduce_sumsq_16bit_kernel<__half><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16, scale,
+                                                             sumsq);
+  else
+    allreduce_sumsq_f32_kernel<<<grid, 256, 0, st>>>((float4* const*)bufs, rank, world, n16, slice16, scale, sumsq);
+}
+
+}  // namespace mb

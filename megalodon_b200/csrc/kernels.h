@@ -81,4 +81,16 @@ void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2,
 void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
                       int dtype, cudaStream_t st);
 
+// ---- peer-memory communication (comm_kernels.cu); pointers may address a peer GPU's memory
+void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
+              const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,
+              unsigned long long timeout_ns, int* err, cudaStream_t st);
+void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
+              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* err,
+              cudaStream_t st);
+void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
+                  int* err, cudaStream_t st);
+void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
+                     int dtype, cudaStream_t st);
+
 }  // namespace mb

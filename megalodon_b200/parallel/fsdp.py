@@ -468,6 +468,13 @@ class FullyShardedDataParallel(nn.Module):
         self.finish_backward()
         if self.chunk_parallel_world_size == 1 or self.chunk_group_is_sharded:
             return
+        fused = getattr(self, "_symm_allreduce", None)
+        if fused is not None:
+            # one pass over peer memory: sum over the chunk group + this rank's share of |g|^2
+            acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
+            fused.all_reduce_(self._grad_tensors(), sumsq=acc)
+            self._fused_sumsq = acc
+            return
         for g in self._grad_tensors():
             dist.all_reduce(g, group=self.chunk_parallel_process_group)
 
@@ -510,9 +517,15 @@ class FullyShardedDataParallel(nn.Module):
         coefficient that stays on the device (a no-op kernel when it is 1)."""
         from .. import ops
         from ..ops import cuda_ops
-        acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
-        for g in grads:
-            ops.sum_squares(g, acc)
+        acc = getattr(self, "_fused_sumsq", None)
+        if acc is not None:
+            # the fused chunk-group all-reduce already produced per-rank partial sums of squares
+            self._fused_sumsq = None
+            dist.all_reduce(acc, group=self.chunk_parallel_process_group)
+        else:
+            acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
+            for g in grads:
+                ops.sum_squares(g, acc)
         if self.world_size > 1:
             dist.all_reduce(acc, group=self.process_group)
         if self.model_parallel_world_size > 1:
@@ -528,6 +541,7 @@ class FullyShardedDataParallel(nn.Module):
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         self._clip_coef = None
+        self._fused_sumsq = None
         for u in self._units():
             u.flat_param.grad = None
             u.flat_param._grad_shard = None

@@ -1,0 +1,328 @@
+"""Peer-mapped ("symmetric") memory and the communication objects built on it.
+
+`SymmetricRegion` gives every rank of a process group a buffer of the same size
+and the device address of every peer's copy (allocation and the handle
+exchange go through `torch.distributed._symmetric_memory`; the data path is
+this framework's own kernels in `csrc/comm_kernels.cu`).
+
+On top of it:
+
+* `PeerMailbox` - the chunk-parallel state handoff.  A message is stored
+  straight into the neighbour's mailbox slot and announced with a
+  sequence-numbered flag; the receiver acknowledges into the sender's memory so
+  a slot is never overwritten before it was read.  Drop-in transport for
+  `chunk_parallel.mappings` (`set_handoff_transport("p2p", mailbox)`).
+* `SymmetricAllReduce` - sum of gradient buffers over the group fused with the
+  squared-norm partial sums needed for clipping.
+
+Both also run over `HostFabric`, an in-process emulation of the peer memory of
+all ranks, which is how the slot / sequence / acknowledgement protocol and the
+timeout paths are tested without GPUs.  Waiting never blocks forever: a wait
+that is not satisfied within `timeout_s` raises `PeerTimeout`.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+import torch.distributed as dist
+
+
+class PeerTimeout(RuntimeError):
+    """A bounded wait on a peer's flag ran out."""
+
+
+def _round_up(x: int, m: int) -> int:
+    return -(-x // m) * m
+
+
+# ----------------------------------------------------------------------------- memory
+class SymmetricRegion:
+    """`nbytes` of device memory on every rank of `group`, each rank knowing all addresses."""
+
+    def __init__(self, nbytes: int, group: Optional[dist.ProcessGroup], device: torch.device):
+        import torch.distributed._symmetric_memory as symm_mem
+        self.nbytes = _round_up(nbytes, 256)
+        self.group = group if group is not None else dist.group.WORLD
+        self.device = torch.device(device)
+        self.local = symm_mem.empty(self.nbytes, dtype=torch.uint8, device=self.device)
+        self.local.zero_()
+        torch.cuda.synchronize(self.device)
+        self.handle = symm_mem.rendezvous(self.local, self.group)
+        self.rank = int(self.handle.rank)
+        self.world = int(self.handle.world_size)
+        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
+        self.ptr_table = torch.tensor(self.ptrs, dtype=torch.int64, device=self.device)
+        dist.barrier(group=self.group)          # every rank has zeroed its copy
+
+    def view(self, offset: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
+        return self.local[offset:offset + nbytes].view(dtype)
+
+    def peer_ptr(self, rank: int, offset: int = 0) -> int:
+        return self.ptrs[rank] + offset
+
+    def ptr_table_at(self, offset: int) -> torch.Tensor:
+        return self.ptr_table + offset
+
+
+class HostFabric:
+    """In-process stand-in for the peer memory of `world` ranks (CPU tensors).
+    Used by the tests of the host-side protocol logic."""
+
+    def __init__(self, world: int, nbytes: int):
+        self.world = world
+        self.nbytes = _round_up(nbytes, 256)
+        self.mem = [torch.zeros(self.nbytes, dtype=torch.uint8) for _ in range(world)]
+        self.dropped_flags = 0        # fault injection: number of upcoming flag writes to lose
+
+    def region(self, rank: int) -> "HostRegion":
+        return HostRegion(self, rank)
+
+
+class HostRegion:
+    def __init__(self, fabric: HostFabric, rank: int):
+        self.fabric, self.rank, self.world, self.nbytes = fabric, rank, fabric.world, fabric.nbytes
+        self.local = fabric.mem[rank]
+        self.device = torch.device("cpu")
+
+    def u32(self, rank: int, offset: int) -> torch.Tensor:
+        return self.fabric.mem[rank][offset:offset + 4].view(torch.int32)
+
+    def bytes_of(self, rank: int, offset: int, nbytes: int) -> torch.Tensor:
+        return self.fabric.mem[rank][offset:offset + nbytes]
+
+
+# ----------------------------------------------------------------------------- mailbox
+class PeerMailbox:
+    """Line-topology mailbox between chunk-parallel neighbours.
+
+    Memory layout of every rank's region (identical everywhere):
+        [2 directions][n_slots] payload slots of slot_bytes
+        [2][n_slots] uint32 arrival flags     (written by the sender)
+        [2][n_slots] uint32 acknowledgements  (written by the receiver, into the sender's memory)
+    Direction 0 = forward activations (from the previous rank), 1 = backward gradients (from the
+    next rank).  Message k of a direction uses slot (k - 1) % n_slots with sequence number k.
+    """
+
+    FWD, BWD = 0, 1
+
+    def __init__(self, region, prev_rank: Optional[int], next_rank: Optional[int], slot_bytes: int,
+                 n_slots: int = 8, timeout_s: float = 30.0):
+        self.region = region
+        self.prev, self.next = prev_rank, next_rank       # ranks within the region's group
+        self.slot_bytes = _round_up(slot_bytes, 256)
+        self.n_slots = n_slots
+        self.timeout_ns = int(timeout_s * 1e9)
+        need = self.bytes_needed(slot_bytes, n_slots)
+        assert region.nbytes >= need, f"region of {region.nbytes} B is too small for the mailbox ({need} B)"
+        self.send_seq = [0, 0]
+        self.recv_seq = [0, 0]
+        self._is_host = isinstance(region, HostRegion)
+        if not self._is_host:
+            dev = region.device
+            self._counters = torch.zeros(4, dtype=torch.int32, device=dev)
+            self._err = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._stage: Dict[int, torch.Tensor] = {}
+
+    @staticmethod
+    def bytes_needed(slot_bytes: int, n_slots: int = 8) -> int:
+        return 2 * n_slots * _round_up(slot_bytes, 256) + 2 * 2 * n_slots * 4 + 256
+
+    # ---- layout
+    def _slot_off(self, direction: int, slot: int) -> int:
+        return (direction * self.n_slots + slot) * self.slot_bytes
+
+    def _flag_off(self, direction: int, slot: int) -> int:
+        return 2 * self.n_slots * self.slot_bytes + (direction * self.n_slots + slot) * 4
+
+    def _ack_off(self, direction: int, slot: int) -> int:
+        return self._flag_off(0, 0) + 2 * self.n_slots * 4 + (direction * self.n_slots + slot) * 4
+
+    @staticmethod
+    def _dir(direction) -> int:
+        return {"fwd": 0, "bwd": 1, 0: 0, 1: 1}[direction]
+
+    # ---- transport API used by chunk_parallel.mappings
+    def send(self, t: torch.Tensor, direction) -> None:
+        d = self._dir(direction)
+        peer = self.next if d == self.FWD else self.prev
+        assert peer is not None, "no neighbour in that direction"
+        nbytes = t.numel() * t.element_size()
+        assert nbytes <= self.slot_bytes, f"message of {nbytes} B exceeds the slot size {self.slot_bytes} B"
+        self.send_seq[d] += 1
+        seq = self.send_seq[d]
+        slot = (seq - 1) % self.n_slots
+        need_ack = max(0, seq - self.n_slots)       # the previous message in this slot must have been read
+        if self._is_host:
+            self._host_send(t, d, peer, slot, seq, need_ack, nbytes)
+        else:
+            src, padded = self._padded(t, nbytes)
+            from ..ops._ext import require
+            require().p2p_send(src, self.region.peer_ptr(peer, self._slot_off(d, slot)), padded,
+                               self.region.peer_ptr(peer, self._flag_off(d, slot)), seq,
+                               self.region.peer_ptr(self.region.rank, self._ack_off(d, slot)), need_ack,
+                               self._counters[d:d + 1], self.timeout_ns, self._err)
+
+    def recv(self, buf: torch.Tensor, direction) -> torch.Tensor:
+        d = self._dir(direction)
+        peer = self.prev if d == self.FWD else self.next
+        assert peer is not None, "no neighbour in that direction"
+        nbytes = buf.numel() * buf.element_size()
+        assert nbytes <= self.slot_bytes
+        self.recv_seq[d] += 1
+        seq = self.recv_seq[d]
+        slot = (seq - 1) % self.n_slots
+        if self._is_host:
+            self._host_recv(buf, d, peer, slot, seq, nbytes)
+        else:
+            dst, padded = self._padded(buf, nbytes, for_write=True)
+            from ..ops._ext import require
+            me = self.region.rank
+            require().p2p_recv(dst, self.region.peer_ptr(me, self._slot_off(d, slot)), padded,
+                               self.region.peer_ptr(me, self._flag_off(d, slot)), seq,
+                               self.region.peer_ptr(peer, self._ack_off(d, slot)), self._counters[2 + d:3 + d],
+                               self.timeout_ns, self._err)
+            if dst.data_ptr() != buf.data_ptr():
+                buf.view(-1).view(torch.uint8).copy_(dst.view(torch.uint8)[:nbytes])
+        return buf
+
+    def check(self) -> None:
+        """Raise `PeerTimeout` if one of the kernels gave up waiting (synchronises the device)."""
+        if self._is_host:
+            return
+        code = int(self._err.item())
+        if code:
+            self._err.zero_()
+            what = {11: "send: slot not acknowledged by the receiver", 12: "recv: message never arrived"}
+            raise PeerTimeout(what.get(code, f"peer wait timed out (code {code})"))
+
+    # ---- CUDA helpers
+    def _padded(self, t: torch.Tensor, nbytes: int, for_write: bool = False):
+        """The kernels move whole 16-byte words from 16-byte aligned addresses."""
+        padded = _round_up(nbytes, 16)
+        tc = t if t.is_contiguous() else t.contiguous()
+        if padded == nbytes and tc.data_ptr() % 16 == 0 and (tc is t or not for_write):
+            return tc, padded
+        stage = self._stage.get(padded)
+        if stage is None:
+            stage = torch.zeros(padded, dtype=torch.uint8, device=self.region.device)
+            self._stage[padded] = stage
+        if not for_write:
+            stage[:nbytes].copy_(tc.view(-1).view(torch.uint8))
+        return stage, padded
+
+    # ---- host emulation (same protocol, CPU tensors, no blocking)
+    def _host_send(self, t, d, peer, slot, seq, need_ack, nbytes):
+        r = self.region
+        if need_ack and int(r.u32(r.rank, self._ack_off(d, slot)).item()) < need_ack:
+            raise PeerTimeout("send: slot not acknowledged by the receiver")
+        r.bytes_of(peer, self._slot_off(d, slot), nbytes).copy_(t.detach().contiguous().view(-1).view(torch.uint8))
+        if r.fabric.dropped_flags > 0:
+            r.fabric.dropped_flags -= 1          # injected fault: the flag write is lost
+            return
+        r.u32(peer, self._flag_off(d, slot)).fill_(seq)
+
+    def _host_recv(self, buf, d, peer, slot, seq, nbytes):
+        r = self.region
+        if int(r.u32(r.rank, self._flag_off(d, slot)).item()) < seq:
+            self.recv_seq[d] -= 1
+            raise PeerTimeout("recv: message never arrived")
+        buf.view(-1).view(torch.uint8).copy_(r.bytes_of(r.rank, self._slot_off(d, slot), nbytes))
+        r.u32(peer, self._ack_off(d, slot)).fill_(seq)
+
+
+# ----------------------------------------------------------------------------- all-reduce + grad norm
+class SymmetricAllReduce:
+    """In-place sum over the group of tensors staged through a symmetric bucket,
+    returning the squared L2 norm of the reduced values (this rank's slice:
+    summing the returned partials over the group gives the full norm)."""
+
+    def __init__(self, region: SymmetricRegion, bucket_bytes: int, timeout_s: float = 30.0):
+        self.region = region
+        self.bucket_bytes = (bucket_bytes // 256) * 256
+        assert region.nbytes >= self.bytes_needed(bucket_bytes, region.world)
+        self.pad_off = self.bucket_bytes
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        dev = region.device
+        self._err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._bufs = region.ptr_table_at(0).contiguous()
+        self._pads = region.ptr_table_at(self.pad_off).contiguous()
+
+    @staticmethod
+    def bytes_needed(bucket_bytes: int, world: int) -> int:
+        return (bucket_bytes // 256) * 256 + _round_up(4 * world, 256)
+
+    def _barrier(self) -> None:
+        from ..ops._ext import require
+        self.epoch += 1
+        require().peer_barrier(self._pads, self.region.rank, self.epoch, self.timeout_ns, self._err)
+
+    @torch.no_grad()
+    def all_reduce_(self, tensors: List[torch.Tensor], sumsq: Optional[torch.Tensor] = None,
+                    scale: float = 1.0) -> None:
+        """Sum every tensor over the group in place; `sumsq` (fp64 scalar) accumulates
+        this rank's share of the squared norm of the results."""
+        from ..ops._ext import require
+        from ..ops.cuda_ops import _DT
+        ext = require()
+        for t in tensors:
+            flat = t.view(-1)
+            esize = flat.element_size()
+            per = self.bucket_bytes // esize
+            for lo in range(0, flat.numel(), per):
+                part = flat[lo:lo + per]
+                nbytes = part.numel() * esize
+                padded = _round_up(nbytes, 16 * self.region.world)
+                stage = self.region.view(0, padded, t.dtype)
+                stage[:part.numel()].copy_(part)
+                if padded != nbytes:
+                    stage[part.numel():].zero_()
+                self._barrier()                      # every rank has staged its bucket
+                ext.allreduce_sumsq(self._bufs, self.region.rank, padded, scale, sumsq, _DT[t.dtype])
+                self._barrier()                      # every rank has pushed its reduced slice
+                part.copy_(stage[:part.numel()])
+
+    def check(self) -> None:
+        code = int(self._err.item())
+        if code:
+            self._err.zero_()
+            raise PeerTimeout(f"peer barrier timed out (code {code})")
+
+
+# ----------------------------------------------------------------------------- wiring
+def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_bucket_mb: int = 256,
+                          timeout_s: float = 30.0):
+    """Switch a built (FSDP-wrapped) model to the peer-memory data paths of its
+    chunk-parallel group: the state handoff between neighbouring ranks goes
+    through a `PeerMailbox`, and (when gradients are replicated over the chunk
+    group) `grad_all_reduce()` uses `SymmetricAllReduce`.  Call on every rank of
+    the chunk group after `build_model`.  Returns (mailbox, allreduce | None)."""
+    from .chunk_parallel.mappings import set_handoff_transport
+    from .initialize import get_chunk_parallel_group, get_chunk_parallel_rank, get_chunk_parallel_world_size
+    cp = get_chunk_parallel_world_size()
+    if cp == 1:
+        return None, None
+    inner = model
+    while hasattr(inner, "_wrapped"):
+        inner = inner._wrapped
+    mega = inner.layers[0]
+    while hasattr(mega, "_wrapped"):
+        mega = mega._wrapped
+    mega = mega.mega
+    width = 2 * mega.timenorm.groups_per_partition + 2 * mega.local_mdim * mega.cema.ndim
+    slot_bytes = max_batch * width * 4
+    device = next(model.parameters()).device
+    group = get_chunk_parallel_group()
+    r = get_chunk_parallel_rank()
+    region = SymmetricRegion(PeerMailbox.bytes_needed(slot_bytes, n_slots), group, device)
+    mailbox = PeerMailbox(region, r - 1 if r > 0 else None, r + 1 if r + 1 < cp else None, slot_bytes,
+                          n_slots=n_slots, timeout_s=timeout_s)
+    set_handoff_transport("p2p", mailbox)
+    reducer = None
+    if not getattr(model, "chunk_group_is_sharded", False):
+        bucket = allreduce_bucket_mb << 20
+        ar_region = SymmetricRegion(SymmetricAllReduce.bytes_needed(bucket, cp), group, device)
+        reducer = SymmetricAllReduce(ar_region, bucket, timeout_s=timeout_s)
+        model._symm_allreduce = reducer
+    return mailbox, reducer

@@ -1,0 +1,183 @@
+"""Peer-memory communication on 2 GPUs of one box (child processes, NCCL for the
+bootstrap, NVLS off, plain peer loads/stores in the kernels)."""
+import os
+import socket
+import tempfile
+import traceback
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _need_gpus(n):
+    if not torch.cuda.is_available() or torch.cuda.device_count() < n:
+        pytest.skip(f"needs {n} GPUs")
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn, out_dir):
+    os.environ.update(RANK=str(rank), WORLD_SIZE=str(world), MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port),
+                      LOCAL_RANK=str(rank), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        res = fn(rank, world)
+        torch.save(res, os.path.join(out_dir, f"{rank}.pt"))
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        traceback.print_exc()
+        raise
+
+
+def _run(fn, world=2):
+    port = _free_port()
+    with tempfile.TemporaryDirectory() as d:
+        mp.spawn(_entry, args=(world, port, fn, d), nprocs=world, join=True)
+        return [torch.load(os.path.join(d, f"{r}.pt"), weights_only=False) for r in range(world)]
+
+
+def _mailbox_case(rank, world):
+    import torch.distributed as dist
+    from megalodon_b200.parallel.symm import PeerMailbox, PeerTimeout, SymmetricRegion
+    dev = torch.device("cuda", rank)
+    slot = 4096
+    region = SymmetricRegion(PeerMailbox.bytes_needed(slot, 2), None, dev)
+    box = PeerMailbox(region, rank - 1 if rank > 0 else None, rank + 1 if rank + 1 < world else None, slot,
+                      n_slots=2, timeout_s=0.5)
+    ok = True
+    # forward messages 0 -> 1 and gradients 1 -> 0, more than there are slots
+    for k in range(5):
+        if rank == 0:
+            box.send(torch.full((1000,), float(k), device=dev), "fwd")
+            back = torch.empty(37, device=dev, dtype=torch.bfloat16)       # odd size: exercises padding
+            box.recv(back, "bwd")
+            ok = ok and bool((back.float() == -k).all())
+        else:
+            got = torch.empty(1000, device=dev)
+            box.recv(got, "fwd")
+            ok = ok and bool((got == k).all())
+            box.send(torch.full((37,), -float(k), device=dev, dtype=torch.bfloat16), "bwd")
+        torch.cuda.synchronize()
+        box.check()
+    dist.barrier()
+    # a receive that nothing answers runs into its time limit and reports it; the context survives
+    timed_out = False
+    if rank == 1:
+        junk = torch.empty(16, device=dev)
+        box.recv(junk, "fwd")
+        torch.cuda.synchronize()
+        try:
+            box.check()
+        except PeerTimeout:
+            timed_out = True
+        box.recv_seq[0] -= 1                 # that message was never consumed
+    dist.barrier()
+    if rank == 0:
+        box.send(torch.arange(16.0, device=dev), "fwd")
+    else:
+        late = torch.empty(16, device=dev)
+        box.recv(late, "fwd")
+        torch.cuda.synchronize()
+        box.check()
+        ok = ok and bool((late == torch.arange(16.0, device=dev)).all())
+    torch.cuda.synchronize()
+    return ok, timed_out
+
+
+def test_peer_mailbox_two_gpus():
+    _need_gpus(2)
+    res = _run(_mailbox_case)
+    assert all(r[0] for r in res)
+    assert res[1][1], "the unanswered receive should have reported a timeout"
+
+
+def _allreduce_case(rank, world):
+    import torch.distributed as dist
+    from megalodon_b200.parallel.symm import SymmetricAllReduce, SymmetricRegion
+    dev = torch.device("cuda", rank)
+    bucket = 1 << 20
+    region = SymmetricRegion(SymmetricAllReduce.bytes_needed(bucket, world), None, dev)
+    ar = SymmetricAllReduce(region, bucket, timeout_s=5.0)
+    out = {}
+    for dtype in (torch.bfloat16, torch.float32):
+        torch.manual_seed(100 + rank)
+        ts = [torch.randn(n, device=dev).to(dtype) for n in (1000, 700001, 64)]      # spans several buckets
+        ref = [t.clone() for t in ts]
+        for t in ref:
+            dist.all_reduce(t)
+        acc = torch.zeros((), dtype=torch.float64, device=dev)
+        ar.all_reduce_(ts, sumsq=acc)
+        torch.cuda.synchronize()
+        ar.check()
+        dist.all_reduce(acc)
+        want = sum(t.double().pow(2).sum() for t in ts)
+        err = max((a.float() - b.float()).abs().max().item() for a, b in zip(ts, ref))
+        out[str(dtype)] = (err, abs(acc.item() - want.item()) / want.item())
+    return out
+
+
+def test_symmetric_allreduce_two_gpus():
+    _need_gpus(2)
+    res = _run(_allreduce_case)
+    for r in res:
+        assert r["torch.bfloat16"][0] < 5e-2 and r["torch.bfloat16"][1] < 1e-3, r
+        assert r["torch.float32"][0] < 1e-5 and r["torch.float32"][1] < 1e-5, r
+
+
+def _train_case(rank, world):
+    from megalodon_b200.config import ModelConf, OptimConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.optim import build_optimizer
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.parallel.chunk_parallel import set_handoff_transport
+    from megalodon_b200.parallel.symm import enable_peer_transport
+    from megalodon_b200.utils import clip_grad_norm_, set_random_seed
+    initialize_model_parallel(1, world)
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused", layerwise_ckpt=True)
+    toks = torch.randint(0, 512, (2, 513), generator=torch.Generator().manual_seed(0)).cuda()
+    x, y = toks[:, :-1], toks[:, 1:]
+    curves = {}
+    for transport in ("nccl", "p2p"):
+        set_random_seed(0)
+        set_handoff_transport("nccl")
+        model = build_model(cfg, "bf16", False, True)
+        if transport == "p2p":
+            box, reducer = enable_peer_transport(model, max_batch=2, n_slots=4, allreduce_bucket_mb=1, timeout_s=20.0)
+        opt, sched = build_optimizer(model, OptimConf(lr=3e-3, warmup=2), 20, "bf16")
+        curve = []
+        for _ in range(4):
+            loss = model(x, targets=y)[0].mean()
+            loss.backward()
+            model.grad_all_reduce()
+            norm = clip_grad_norm_(model, 1.0)
+            opt.step(); sched.step(); opt.zero_grad()
+            curve.append((loss.item(), float(norm)))
+        if transport == "p2p":
+            box.check()
+            reducer.check()
+        cuda_ops.check_kernel_errors()
+        curves[transport] = curve
+    set_handoff_transport("nccl")
+    return curves
+
+
+def test_chunk_parallel_training_over_peer_memory_matches_nccl():
+    _need_gpus(2)
+    res = _run(_train_case)
+    for r in res:
+        for (l0, n0), (l1, n1) in zip(r["nccl"], r["p2p"]):
+            assert abs(l0 - l1) < 5e-2, r
+            assert abs(n0 - n1) < 0.15 * max(1.0, n0), r
