@@ -154,6 +154,10 @@ def main():
                         shard_over_chunk_group=True)
     model._wrapped.seq_microbatch_chunks = 1
     model.defer_grad_clip = True      # clipping coefficient is applied inside the fused AdamW kernel
+    if world > 1:
+        # CEMA / TimestepNorm state goes from rank to rank through peer memory, not NCCL send/recv
+        from megalodon_b200.parallel.symm import enable_peer_transport
+        mailbox, _ = enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=60.0)
     opt, sched = build_optimizer(model, OptimConf(lr=1e-4, warmup=10, clip=1.0), 1000, "bf16")
     data = SyntheticTokens(cfg.vocab_size, 1, args.seq_len, seed=0)
     n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)
@@ -219,6 +223,8 @@ def main():
     wall_ms = (time.perf_counter() - t_wall) * 1e3
     clocks = sampler.stop()
     cuda_ops.check_kernel_errors()
+    if world > 1:
+        mailbox.check()
 
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)
@@ -237,7 +243,7 @@ def main():
                          f"v{cfg.value_dim} ffn{cfg.ffn_hidden_dim} swiglu N{cfg.cema_ndim} chunk{cfg.chunk_size} "
                          f"V{cfg.vocab_size}), {n_params / 1e9:.2f}B params",
                 "global_batch": 1, "seq_len": args.seq_len,
-                "parallelism": f"cp{world}" + ("+zero3_over_cp" if world > 1 else ""),
+                "parallelism": f"cp{world}" + ("+zero3_over_cp+p2p_handoff" if world > 1 else ""),
                 "activation_checkpointing": bool(cfg.layerwise_ckpt),
                 "optimizer": "AdamW fp32 master+moments, clip 1.0",
                 "gemm_backend": cuda_ops.gemm_backend(),

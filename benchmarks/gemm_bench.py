@@ -35,6 +35,8 @@ def time_it(fn, flush):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--only", default=None, help="run a single projection, e.g. wv/wr (for profiler captures)")
+    ap.add_argument("--no-cublas", action="store_true", help="skip the torch.matmul comparison")
     args = ap.parse_args()
     T = args.tokens
     dev = torch.device("cuda")
@@ -44,6 +46,8 @@ def main():
     print(f"{'layer':8s} {'pass':6s} {'M':>6s} {'N':>6s} {'K':>6s} {'tcgen05 ms':>11s} {'TFLOP/s':>8s} "
           f"{'cuBLAS ms':>10s} {'TFLOP/s':>8s} {'ratio':>6s}")
     for name, n_out, k_in in shapes:
+        if args.only is not None and name != args.only:
+            continue
         x = torch.randn(T, k_in, device=dev).bfloat16()
         w = torch.randn(n_out, k_in, device=dev).bfloat16()
         dy = torch.randn(T, n_out, device=dev).bfloat16()
@@ -55,7 +59,7 @@ def main():
         ]
         for pname, M, N, K, mine, ref in cases:
             t0 = time_it(mine, flush)
-            t1 = time_it(ref, flush)
+            t1 = t0 if args.no_cublas else time_it(ref, flush)
             fl = 2.0 * M * N * K / 1e9
             print(f"{name:8s} {pname:6s} {M:6d} {N:6d} {K:6d} {t0:11.3f} {fl / t0:8.1f} {t1:10.3f} {fl / t1:8.1f} "
                   f"{t1 / t0:6.2f}")
