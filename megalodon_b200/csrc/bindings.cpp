@@ -344,7 +344,8 @@ std::tuple<Tensor, Tensor> clip_coef(const Tensor& sumsq, double max_norm) {
 std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, const OptTensor& out,
                                             const OptTensor& bias, int64_t act, bool a_mn, bool b_mn,
                                             bool want_preact, int64_t out_dtype_code, int64_t mode, double alpha,
-                                            Tensor& err) {
+                                            Tensor& err, const std::vector<int64_t>& a_part_ptrs, int64_t a_first,
+                                            const std::vector<int64_t>& c_part_ptrs) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "operands must be CUDA tensors");
   c10::cuda::CUDAGuard guard(A.device());
   TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && A.dim() == B.dim(), "operands must both be 2-D or both 3-D");
@@ -353,8 +354,10 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
   TORCH_CHECK(A.stride(-1) == 1 && B.stride(-1) == 1, "last dim of the operands must be contiguous");
   const int batch = A.dim() == 3 ? (int)A.size(0) : 1;
   TORCH_CHECK(A.dim() == 2 || B.size(0) == batch, "batch sizes differ");
+  // with a gathered A, `A` is this rank's piece [M, K / parts] and only supplies shape, stride and dtype
+  const int a_parts = a_part_ptrs.empty() ? 1 : (int)a_part_ptrs.size();
   const int M = a_mn ? A.size(-1) : A.size(-2);
-  const int K = a_mn ? A.size(-2) : A.size(-1);
+  const int K = (a_mn ? A.size(-2) : A.size(-1)) * a_parts;
   const int N = b_mn ? B.size(-1) : B.size(-2);
   TORCH_CHECK((b_mn ? B.size(-2) : B.size(-1)) == K, "inner dimensions differ");
   TORCH_CHECK(reinterpret_cast<uintptr_t>(A.data_ptr()) % 16 == 0 && reinterpret_cast<uintptr_t>(B.data_ptr()) % 16 == 0,
@@ -383,11 +386,23 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
   const long long a_bs = A.dim() == 3 ? A.stride(0) : 0, b_bs = B.dim() == 3 ? B.stride(0) : 0;
   const long long c_bs = C.dim() == 3 ? C.stride(0) : 0;
   const int sms = at::cuda::getCurrentDeviceProperties()->multiProcessorCount;
+  mb::GemmPeerSpec peers;
+  TORCH_CHECK(a_part_ptrs.size() <= 8 && c_part_ptrs.size() <= 8, "at most 8 peers");
+  if (a_parts > 1) {
+    peers.a_parts = a_parts;
+    peers.a_first = (int)a_first;
+    for (int i = 0; i < a_parts; ++i) peers.a_ptrs[i] = reinterpret_cast<const void*>(a_part_ptrs[i]);
+  }
+  if (c_part_ptrs.size() > 1) {
+    peers.c_nparts = (int)c_part_ptrs.size();
+    for (size_t i = 0; i < c_part_ptrs.size(); ++i) peers.c_ptrs[i] = reinterpret_cast<void*>(c_part_ptrs[i]);
+  }
   const int rc = mb::gemm_bf16_tcgen05(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                        pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
                                        (int)act, M, N, K, A.stride(-2), B.stride(-2), C.stride(-2), a_mn, b_mn,
                                        (int)mode, (float)alpha, batch, a_bs, b_bs, c_bs, dtype_code(A),
-                                       (int)out_dtype_code, err.data_ptr<int>(), sms, stream());
+                                       (int)out_dtype_code, err.data_ptr<int>(), sms, stream(),
+                                       (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr);
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
 }
@@ -463,6 +478,15 @@ void allreduce_sumsq(const Tensor& bufs, int64_t rank, int64_t nbytes, double sc
                       (float)scale, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (int)dtype, stream());
 }
 
+// out = sum of `world` consecutive slots of out.numel() elements each
+void reduce_slots(const Tensor& slots, Tensor& out, int64_t world) {
+  check_cuda_contig(slots, "slots");
+  check_cuda_contig(out, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(slots.scalar_type() == out.scalar_type() && slots.numel() >= out.numel() * world);
+  mb::reduce_slots(slots.data_ptr(), out.data_ptr(), out.numel(), (int)world, dtype_code(out), stream());
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
@@ -483,7 +507,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sum_squares", &sum_squares);
   m.def("scale_by_ptr", &scale_by_ptr);
   m.def("clip_coef", &clip_coef);
-  m.def("gemm", &gemm);
+  m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("out"), py::arg("bias"), py::arg("act"), py::arg("a_mn"),
+        py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
+        py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
+        py::arg("c_part_ptrs") = std::vector<int64_t>());
+  m.def("reduce_slots", &reduce_slots);
   m.def("attn_softmax_fwd", &attn_softmax_fwd);
   m.def("attn_softmax_bwd", &attn_softmax_bwd);
   m.def("p2p_send", &p2p_send);

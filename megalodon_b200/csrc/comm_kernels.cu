@@ -211,7 +211,24 @@ __global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
 }
 
+template <typename T>
+__global__ void reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__ out, long long n, int world) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int w = 0; w < world; ++w) acc += to_f(slots[(long long)w * n + i]);
+    out[i] = from_f<T>(acc);
+  }
+}
+
 }  // namespace
+
+void reduce_slots(const void* slots, void* out, long long n, int world, int dtype, cudaStream_t st) {
+  if (n == 0) return;
+  const int grid = (int)std::min<long long>(div_up(n, 256), 148LL * 16);
+  MB_DISPATCH_DTYPE(dtype, (reduce_slots_kernel<scalar_t><<<grid, 256, 0, st>>>((const scalar_t*)slots, (scalar_t*)out,
+                                                                             n, world)));
+}
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
               const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,

@@ -41,6 +41,7 @@ constexpr int UMMA_K = 16;
 constexpr int kStages = 4;
 constexpr int kGemmThreads = 192;
 constexpr int kEpiWarps = 4;
+constexpr int kMaxPeers = 8;
 
 template <int BN>
 struct SmemLayout {
@@ -70,6 +71,17 @@ struct GemmParams {
   float alpha;         // C = alpha * acc (+ bias)
   int batch;           // independent problems sharing shapes (tensor maps carry their strides)
   long long c_batch_stride;   // elements between consecutive C (and preact) matrices
+  // all-gather -> GEMM: A is the concatenation along K of `a_parts` pieces of `a_part_k` columns, piece i
+  // read through tensor map i (a peer GPU's memory); the walk over K starts at piece `a_first`
+  int a_parts, a_part_k, a_first;
+  // GEMM -> reduce-scatter: column block i of `c_part_cols` columns is stored to c_parts[i] (row stride
+  // c_part_cols), a slot in the memory of the rank that owns those columns
+  int c_nparts, c_part_cols;
+  void* c_parts[kMaxPeers];
+};
+
+struct TmapArray {
+  CUtensorMap m[kMaxPeers];
 };
 
 struct TileCoord {
@@ -165,8 +177,8 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                    GemmParams p, int in_fmt) {
+gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ GemmParams p, int in_fmt) {
   using L = SmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -210,8 +222,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (elect_one()) {
-      prefetch_tmap(&tmap_a);
+      for (int i = 0; i < p.a_parts; ++i) prefetch_tmap(&tmaps_a.m[i]);
       prefetch_tmap(&tmap_b);
+      const int kb_shift = p.a_parts > 1 ? p.a_first * (p.a_part_k / BK) : 0;
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -226,12 +239,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           uint8_t* sa = smem + stage * L::stage_bytes;
           uint8_t* sb = sa + L::a_bytes;
           mbar_expect_tx(full_bar + stage, L::stage_bytes);
-          const int k0 = kb * BK;
+          // with a gathered A the K walk is rotated so that every rank starts on its own piece
+          const int kbr = p.a_parts > 1 ? (kb + kb_shift) % num_k : kb;
+          const int k0 = kbr * BK;
+          const int part = p.a_parts > 1 ? k0 / p.a_part_k : 0;
+          const int ka = p.a_parts > 1 ? k0 - part * p.a_part_k : k0;     // column inside the piece
+          const CUtensorMap* tmap_a = &tmaps_a.m[part];
           if constexpr (!A_MN) {
-            tma_load_3d(sa, &tmap_a, full_bar + stage, k0, m0, bz);
+            tma_load_3d(sa, tmap_a, full_bar + stage, ka, m0, bz);
           } else {
 #pragma unroll
-            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, &tmap_a, full_bar + stage, m0 + 64 * j, k0, bz);
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d(sa + j * 8192, tmap_a, full_bar + stage, m0 + 64 * j, ka, bz);
           }
           if constexpr (!B_MN) {
             tma_load_3d(sb, &tmap_b, full_bar + stage, k0, n0, bz);
@@ -324,13 +342,20 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_con
           }
         }
         if (row < p.M) {
-          const long long off = (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0;
-          if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
-          if (p.act == 1) {
+          if (p.c_nparts > 1) {
+            // push this 32-column chunk into the slot of the rank that owns these columns
+            const int owner = col0 / p.c_part_cols;
+            OutT* slot = reinterpret_cast<OutT*>(p.c_parts[owner]);
+            store_row32<OutT>(slot + (long long)row * p.c_part_cols + (col0 - owner * p.c_part_cols), v, nvalid);
+          } else {
+            const long long off = (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0;
+            if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
+            if (p.act == 1) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+              for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+            }
+            store_row32<OutT>(C + off, v, nvalid);
           }
-          store_row32<OutT>(C + off, v, nvalid);
         }
       }
       tcgen05_fence_before();
@@ -388,7 +413,7 @@ bool make_tmap_3d(CUtensorMap* out, const void* base, long long inner, long long
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
-static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt, int sms,
+static int launch_gemm(const TmapArray& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt, int sms,
                        cudaStream_t st) {
   using L = SmemLayout<BN>;
   auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, OutT>;
@@ -408,19 +433,43 @@ static int launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmP
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
-                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st) {
+                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
+                      const GemmPeerSpec* peers) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA wants 16-byte strides; the vectorised epilogue wants 16-byte aligned rows of C
   if (lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return -1;
   if (batch > 1 && (a_bs % 8 != 0 || b_bs % 8 != 0 || c_bs % 8 != 0)) return -1;
   const int BN = 256;
-  CUtensorMap ta, tb;
-  bool ok = a_mn ? make_tmap_3d(&ta, A, M, K, batch, lda, a_bs, 64, 64, in_dtype)
-                 : make_tmap_3d(&ta, A, K, M, batch, lda, a_bs, BK, BM, in_dtype);
+  TmapArray ta;
+  CUtensorMap tb;
+  GemmParams p{};
+  p.M = M; p.N = N; p.K = K; p.C = C; p.preact = preact; p.bias = bias; p.bias_dtype = bias_dtype; p.act = act;
+  p.err = err; p.ldc = ldc; p.mode = mode; p.alpha = alpha; p.batch = batch; p.c_batch_stride = c_bs;
+  p.a_parts = 1; p.a_part_k = K; p.a_first = 0; p.c_nparts = 1; p.c_part_cols = N;
+  bool ok = true;
+  if (peers != nullptr && peers->a_parts > 1) {
+    // gathered A: K-major pieces [M, K / parts] living on different GPUs
+    if (a_mn || batch != 1 || peers->a_parts > kMaxPeers || K % peers->a_parts != 0) return -6;
+    p.a_parts = peers->a_parts;
+    p.a_part_k = K / peers->a_parts;
+    p.a_first = peers->a_first;
+    if (p.a_part_k % BK != 0) return -6;
+    for (int i = 0; i < p.a_parts; ++i)
+      ok = ok && make_tmap_3d(&ta.m[i], peers->a_ptrs[i], p.a_part_k, M, 1, lda, 0, BK, BM, in_dtype);
+  } else {
+    ok = a_mn ? make_tmap_3d(&ta.m[0], A, M, K, batch, lda, a_bs, 64, 64, in_dtype)
+              : make_tmap_3d(&ta.m[0], A, K, M, batch, lda, a_bs, BK, BM, in_dtype);
+  }
+  if (peers != nullptr && peers->c_nparts > 1) {
+    if (batch != 1 || peers->c_nparts > kMaxPeers || N % peers->c_nparts != 0) return -7;
+    p.c_nparts = peers->c_nparts;
+    p.c_part_cols = N / peers->c_nparts;
+    if (p.c_part_cols % 32 != 0) return -7;
+    for (int i = 0; i < p.c_nparts; ++i) p.c_parts[i] = peers->c_ptrs[i];
+  }
   ok = ok && (b_mn ? make_tmap_3d(&tb, B, N, K, batch, ldb, b_bs, 64, 64, in_dtype)
                    : make_tmap_3d(&tb, B, K, N, batch, ldb, b_bs, BK, BN, in_dtype));
   if (!ok) return -4;
-  GemmParams p{M, N, K, C, preact, bias, bias_dtype, act, err, ldc, mode, alpha, batch, c_bs};
   const int fmt = in_dtype == kBF16 ? 1 : 0;
 #define GEMM_CASE(AMN, BMN)                                                                              \
   if (a_mn == AMN && b_mn == BMN) {                                                                      \

@@ -69,10 +69,24 @@ void clip_coef(const double* sumsq, float max_norm, float* norm_out, float* coef
 // lda / ldb / ldc: row strides in elements (multiples of 8).  mode: 0 dense, 1..3 causal tile structure
 // (see gemm_sm100.cu).  The result is scaled by alpha before bias / activation.  `batch` independent
 // problems of the same shape are addressed through the batch strides a_bs / b_bs / c_bs (elements).
+// Operands / results spread over peer GPUs (fused all-gather -> GEMM and GEMM -> reduce-scatter):
+//   a_parts > 1: A = [A_0 | A_1 | ...] along K, piece i at a_ptrs[i] (row stride lda, K / a_parts columns
+//                each), possibly in a peer's memory; the K walk starts at piece a_first (the local one)
+//   c_nparts > 1: column block i of the result (N / c_nparts columns) is stored to c_ptrs[i], laid out
+//                [M, N / c_nparts]; nothing is written to C
+struct GemmPeerSpec {
+  int a_parts = 1, a_first = 0;
+  const void* a_ptrs[8] = {};
+  int c_nparts = 1;
+  void* c_ptrs[8] = {};
+};
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
-                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st);
+                      int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
+                      const GemmPeerSpec* peers = nullptr);
+// out[i] = sum over `world` slots of slot_w[i] (slots are consecutive, `n` elements each)
+void reduce_slots(const void* slots, void* out, long long n, int world, int dtype, cudaStream_t st);
 
 // ---- attention softmax (attention_kernels.cu)
 void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2, long long ld, bool causal,

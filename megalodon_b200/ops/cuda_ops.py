@@ -72,7 +72,7 @@ def _tma_ok(t: Tensor) -> bool:
 def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str] = None, *,
          a_mn: bool = False, b_mn: bool = False, want_preact: bool = False,
          out_dtype: Optional[torch.dtype] = None, out: Optional[Tensor] = None, mode: int = 0,
-         alpha: float = 1.0):
+         alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None):
     """C = act(alpha * A B^T + bias).  `a_mn` / `b_mn`: operand is stored [K, rows].
     Operands may be 2-D or 3-D (batched) strided views with a contiguous last
     dim.  `mode` 1..3 exploits causal structure (see gemm_sm100.cu).  Returns
@@ -81,6 +81,17 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
     native = (_GEMM_BACKEND[0] == "tcgen05" and a.dtype in (torch.bfloat16, torch.float16)
               and _tma_ok(a) and _tma_ok(b) and (out is None or _tma_ok(out))
               and (b.shape[-1] if b_mn else b.shape[-2]) % 8 == 0)
+    if a_part_ptrs or c_part_ptrs:
+        if not native:
+            raise RuntimeError("peer-memory GEMM needs the tcgen05 backend and TMA-compatible operands")
+        _bump()
+        res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
+                                 _DT[out_dtype], mode, alpha, _err_flag(a.device),
+                                 a_part_ptrs=list(a_part_ptrs or []), a_first=a_first,
+                                 c_part_ptrs=list(c_part_ptrs or []))
+        if rc != 0:
+            raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
+        return res, pre
     if not native:
         A = a.transpose(-1, -2) if a_mn else a
         Bm = b if b_mn else b.transpose(-1, -2)

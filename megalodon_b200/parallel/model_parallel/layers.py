@@ -119,6 +119,10 @@ class ColumnParallelLinear(torch.nn.Module):
         return gather_from_model_parallel_region(self.weight.data.t()).t()
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:
+        from .. import tp_comm
+        if self.input_is_parallel and not self.gather_output and tp_comm.usable(input_):
+            # all-gather of the feature-sharded input fused into the GEMM (peer-memory TMA loads)
+            return tp_comm.AGLinear.apply(input_, self.weight, self.bias, self.activation)
         if self.input_is_parallel:
             x = gather_copy_model_parallel_region(input_)
         else:
@@ -164,7 +168,12 @@ class RowParallelLinear(torch.nn.Module):
         return gather_from_model_parallel_region(self.weight.data)
 
     def forward(self, input_: torch.Tensor) -> torch.Tensor:
+        from .. import tp_comm
         x = input_ if self.input_is_parallel else scatter_to_model_parallel_region(input_)
+        if self.parallel_output and tp_comm.usable(x):
+            # reduce-scatter fused into the GEMM epilogue (partials pushed into the owners' memory)
+            y = tp_comm.LinearRS.apply(x, self.weight)
+            return y if self.bias is None else y + self.bias
         y = ops.linear(x, self.weight, None, None)
         if self.parallel_output:
             y = reduce_scatter_model_parallel_region(y)

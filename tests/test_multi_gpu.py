@@ -181,3 +181,82 @@ def test_chunk_parallel_training_over_peer_memory_matches_nccl():
         for (l0, n0), (l1, n1) in zip(r["nccl"], r["p2p"]):
             assert abs(l0 - l1) < 5e-2, r
             assert abs(n0 - n1) < 0.15 * max(1.0, n0), r
+
+
+def _tp_case(rank, world):
+    import torch.distributed as dist
+    from megalodon_b200.parallel import initialize_model_parallel, get_model_parallel_group
+    from megalodon_b200.parallel.tp_comm import TensorParallelWorkspace
+    from megalodon_b200.ops import cuda_ops
+    initialize_model_parallel(world, 1)
+    dev = torch.device("cuda", rank)
+    group = get_model_parallel_group()
+    M, K, N = 384, 512, 768
+    ws = TensorParallelWorkspace(group, dev, max_tokens=M, part_features=max(K, N) // world, timeout_s=10.0)
+    g = torch.Generator(device="cpu").manual_seed(0)
+    x_full = torch.randn(M, K, generator=g).bfloat16().to(dev)
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().to(dev)
+    out = {}
+    # all-gather -> GEMM: every rank holds a K-slice of x
+    x_part = x_full[:, rank * (K // world):(rank + 1) * (K // world)].contiguous()
+    for trial in range(3):
+        y, _ = ws.ag_gemm(x_part, w)
+    ref = x_full.float() @ w.float().t()
+    out["ag"] = (y.float() - ref).abs().max().item() / ref.abs().max().item()
+    # GEMM -> reduce-scatter: every rank holds a K-slice of x and of w, the sum is split over N
+    w_part = w[:, rank * (K // world):(rank + 1) * (K // world)].contiguous()
+    for trial in range(3):
+        y_rs = ws.gemm_rs(x_part, w_part)
+    ref_rs = ref[:, rank * (N // world):(rank + 1) * (N // world)]
+    out["rs"] = (y_rs.float() - ref_rs).abs().max().item() / ref.abs().max().item()
+    torch.cuda.synchronize()
+    ws.check()
+    cuda_ops.check_kernel_errors()
+    return out
+
+
+def test_fused_tensor_parallel_gemms_two_gpus():
+    _need_gpus(2)
+    for r in _run(_tp_case):
+        assert r["ag"] < 2e-2 and r["rs"] < 2e-2, r
+
+
+def _tp_model_case(rank, world):
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.parallel.tp_comm import disable_tp_fused, enable_tp_fused
+    from megalodon_b200.utils import set_random_seed
+    initialize_model_parallel(world, 1)
+    cfg = ModelConf(num_layers=2, model_dim=512, num_heads=2, z_dim=256, value_dim=1024, ffn_hidden_dim=1024,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    toks = torch.randint(0, 512, (2, 257), generator=torch.Generator().manual_seed(0)).cuda()
+    x, y = toks[:, :-1], toks[:, 1:]
+    res = {}
+    for fused in (False, True):
+        set_random_seed(0)
+        model = build_model(cfg, "bf16", False, True, materialize_fp32_grads=True)
+        if fused:
+            ws = enable_tp_fused(model, max_tokens=512, timeout_s=20.0)
+        loss = model(x, targets=y)[0].mean()
+        loss.backward()
+        model.finish_backward()
+        grads = torch.cat([p.grad.flatten() for p in model.parameters()])
+        if fused:
+            torch.cuda.synchronize()
+            ws.check()
+            disable_tp_fused()
+        cuda_ops.check_kernel_errors()
+        res[fused] = (loss.item(), grads.float().cpu())
+    return res
+
+
+def test_model_parallel_training_with_fused_collectives_matches_nccl():
+    _need_gpus(2)
+    for r in _run(_tp_model_case):
+        (l0, g0), (l1, g1) = r[False], r[True]
+        assert abs(l0 - l1) < 2e-2, (l0, l1)
+        rel = (g0 - g1).norm() / (g0.norm() + 1e-6)
+        assert rel < 5e-2, rel
