@@ -302,6 +302,9 @@ ModelStore = {
                           ffn_hidden_dim=11264, chunk_size=2048, norm_num_groups=64),
     "mega7.3B": ModelConf(num_layers=32, model_dim=4096, num_heads=4, z_dim=1024, value_dim=8192,
                           ffn_hidden_dim=8192, chunk_size=2048, norm_num_groups=64, swiglu=True),
+    # small shape for plumbing / correctness runs on CPU
+    "mega_tiny": ModelConf(num_layers=2, model_dim=128, num_heads=1, z_dim=32, value_dim=256, ffn_hidden_dim=256,
+                           cema_ndim=4, chunk_size=64, norm_num_groups=32, swiglu=True),
     # the 7B shape used for the long-context throughput benchmark
     "mega7B_32k": ModelConf(num_layers=32, model_dim=4096, num_heads=4, z_dim=1024, value_dim=8192,
                             ffn_hidden_dim=11264, chunk_size=4096, norm_num_groups=64, swiglu=True,
