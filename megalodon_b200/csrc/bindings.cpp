@@ -431,6 +431,82 @@ void attn_softmax_bwd(const Tensor& p, Tensor& dp, int64_t L1, int64_t L2, bool 
                        stream());
 }
 
+// ------------------------------------------------------------------ SequenceNorm pieces, dropout, CEMA coefficients
+// sums over valid time steps per (b, h): (sum u, sum u*v) or (sum u, sum u^2) when v is None
+std::tuple<Tensor, Tensor> time_sums(const Tensor& u, const OptTensor& v, const OptTensor& mask, bool length_last) {
+  check_cuda_contig(u, "u");
+  c10::cuda::CUDAGuard guard(u.device());
+  TORCH_CHECK(u.dim() == 3);
+  const int B = u.size(0), L = length_last ? u.size(2) : u.size(1), H = length_last ? u.size(1) : u.size(2);
+  auto f32 = u.options().dtype(at::kFloat);
+  Tensor s1 = torch::empty({B, H}, f32), s2 = torch::empty({B, H}, f32);
+  if (v.has_value()) check_cuda_contig(*v, "v");
+  mb::time_sums(u.data_ptr(), opt_ptr(v), mask.has_value() ? mask->data_ptr<bool>() : nullptr, s1.data_ptr<float>(),
+                s2.data_ptr<float>(), B, L, H, length_last, dtype_code(u), stream());
+  return {s1, s2};
+}
+
+// out = a[b,h] * p + c[b,h] * q + d[b,h], zero on padded steps
+Tensor affine_apply(const Tensor& p, const OptTensor& q, const Tensor& a, const OptTensor& c, const Tensor& d,
+                    const OptTensor& mask, bool length_last) {
+  check_cuda_contig(p, "p");
+  c10::cuda::CUDAGuard guard(p.device());
+  const int B = p.size(0), L = length_last ? p.size(2) : p.size(1), H = length_last ? p.size(1) : p.size(2);
+  TORCH_CHECK(a.scalar_type() == at::kFloat && d.scalar_type() == at::kFloat && a.is_contiguous() && d.is_contiguous());
+  TORCH_CHECK(q.has_value() == c.has_value());
+  Tensor out = torch::empty_like(p);
+  mb::affine_apply(p.data_ptr(), opt_ptr(q), a.data_ptr<float>(), c.has_value() ? c->data_ptr<float>() : nullptr,
+                   d.data_ptr<float>(), mask.has_value() ? mask->data_ptr<bool>() : nullptr, out.data_ptr(), B, L, H,
+                   length_last, dtype_code(p), stream());
+  return out;
+}
+
+Tensor dropout(const Tensor& x, double p, int64_t seed, int64_t offset) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty_like(x);
+  mb::dropout_apply(x.data_ptr(), out.data_ptr(), x.numel(), (float)p, (unsigned long long)seed,
+                    (unsigned long long)offset, dtype_code(x), stream());
+  return out;
+}
+
+// p [D,N] f32, logq / gamma [D,N,2] f32, h [B,D,N,2] f32 or None -> (k [D,L], bias [B,D,L] or None)
+std::tuple<Tensor, OptTensor> ema_parameters_fwd(const Tensor& p, const Tensor& logq, const Tensor& gamma,
+                                                 const OptTensor& h, int64_t L) {
+  check_cuda_contig(p, "p");
+  check_cuda_contig(logq, "logq");
+  check_cuda_contig(gamma, "gamma");
+  c10::cuda::CUDAGuard guard(p.device());
+  const int D = p.size(0), N = p.size(1);
+  const int B = h.has_value() ? h->size(0) : 0;
+  Tensor k = torch::empty({D, L}, p.options());
+  OptTensor bias;
+  if (h.has_value()) { check_cuda_contig(*h, "h"); bias = torch::empty({B, D, L}, p.options()); }
+  mb::ema_parameters_fwd(p.data_ptr<float>(), logq.data_ptr<float>(), gamma.data_ptr<float>(),
+                         h.has_value() ? h->data_ptr<float>() : nullptr, k.data_ptr<float>(),
+                         bias.has_value() ? bias->data_ptr<float>() : nullptr, B, D, N, (int)L, stream());
+  return {k, bias};
+}
+
+// returns dp [D,N], dq [D,N,2], dgamma [D,N,2], dh [B,D,N,2] or None
+std::vector<OptTensor> ema_parameters_bwd(const OptTensor& dk, const OptTensor& dbias, const Tensor& p,
+                                          const Tensor& logq, const Tensor& gamma, const OptTensor& h, int64_t L) {
+  c10::cuda::CUDAGuard guard(p.device());
+  const int D = p.size(0), N = p.size(1);
+  const int B = h.has_value() ? h->size(0) : 0;
+  Tensor dp = torch::empty_like(p), dq = torch::empty_like(logq), dg = torch::empty_like(gamma);
+  OptTensor dh;
+  if (h.has_value()) dh = torch::zeros_like(*h);
+  if (dk.has_value()) check_cuda_contig(*dk, "dk");
+  if (dbias.has_value()) check_cuda_contig(*dbias, "dbias");
+  mb::ema_parameters_bwd(dk.has_value() ? dk->data_ptr<float>() : nullptr,
+                         dbias.has_value() ? dbias->data_ptr<float>() : nullptr, p.data_ptr<float>(),
+                         logq.data_ptr<float>(), gamma.data_ptr<float>(), h.has_value() ? h->data_ptr<float>() : nullptr,
+                         dp.data_ptr<float>(), dq.data_ptr<float>(), dg.data_ptr<float>(),
+                         dh.has_value() ? dh->data_ptr<float>() : nullptr, B, D, N, (int)L, stream());
+  return {dp, dq, dg, dh};
+}
+
 // ------------------------------------------------------------------ peer-memory communication
 // Peer addresses are passed as integers (they come from the symmetric-memory rendezvous and are not
 // tensors of this process).  `counter` / `err` are small device tensors owned by the caller.
@@ -512,6 +588,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>());
   m.def("reduce_slots", &reduce_slots);
+  m.def("time_sums", &time_sums);
+  m.def("affine_apply", &affine_apply);
+  m.def("dropout", &dropout);
+  m.def("ema_parameters_fwd", &ema_parameters_fwd);
+  m.def("ema_parameters_bwd", &ema_parameters_bwd);
   m.def("attn_softmax_fwd", &attn_softmax_fwd);
   m.def("attn_softmax_bwd", &attn_softmax_bwd);
   m.def("p2p_send", &p2p_send);

@@ -95,6 +95,21 @@ void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2,
 void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
                       int dtype, cudaStream_t st);
 
+// ---- SequenceNorm pieces and dropout (sequence_norm_kernels.cu)
+void time_sums(const void* u, const void* v, const bool* mask, float* s1, float* s2, int B, int L, int H,
+               bool length_last, int dtype, cudaStream_t st);
+void affine_apply(const void* p, const void* q, const float* a, const float* c, const float* d, const bool* mask,
+                  void* out, int B, int L, int H, bool length_last, int dtype, cudaStream_t st);
+void dropout_apply(const void* x, void* out, long long n, float p, unsigned long long seed,
+                   unsigned long long offset, int dtype, cudaStream_t st);
+
+// ---- explicit CEMA kernel / bias (ema_kernels.cu); complex arrays are interleaved fp32
+void ema_parameters_fwd(const float* p, const float* logq, const float* gamma, const float* h, float* k,
+                        float* bias, int B, int D, int N, int L, cudaStream_t st);
+void ema_parameters_bwd(const float* dk, const float* dbias, const float* p, const float* logq, const float* gamma,
+                        const float* h, float* dp, float* dq, float* dgamma, float* dh, int B, int D, int N, int L,
+                        cudaStream_t st);
+
 // ---- peer-memory communication (comm_kernels.cu); pointers may address a peer GPU's memory
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
               const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,

@@ -286,8 +286,92 @@ def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask,
                                eps, gamma_offset)
 
 
+class _SequenceNorm(torch.autograd.Function):
+    """Two bandwidth-bound kernels per direction (time sums, affine apply); the [B, H]-sized
+    statistics in between are combined here with a handful of tiny tensor ops."""
+
+    @staticmethod
+    def forward(ctx, x, gamma, beta, mask, groups, eps, length_last):
+        xc = x.contiguous()
+        B = xc.shape[0]
+        L = xc.shape[2] if length_last else xc.shape[1]
+        H = xc.shape[1] if length_last else xc.shape[2]
+        mk = None if mask is None else mask.contiguous()
+        _bump(2)
+        s1, s2 = _C().time_sums(xc, None, mk, length_last)
+        count = torch.full((B, 1), float(L), device=x.device) if mk is None else \
+            (~mk).sum(1, keepdim=True).float().clamp_min(1.0)
+        g32, b32 = gamma.float(), beta.float()
+        if groups is None:
+            n = count
+            mean = s1 / n
+            var = (s2 / n - mean * mean).clamp_min(0.0)
+        else:
+            D = H // groups
+            n = count * D
+            mean = (s1.view(B, groups, D).sum(-1) / n)
+            var = (s2.view(B, groups, D).sum(-1) / n - mean * mean).clamp_min(0.0)
+            mean = mean.repeat_interleave(D, dim=1)
+            var = var.repeat_interleave(D, dim=1)
+        rstd = torch.rsqrt(var + eps)
+        A = (rstd * g32).contiguous()
+        y = _C().affine_apply(xc, None, A, None, (b32 - mean * A).contiguous(), mk, length_last)
+        ctx.save_for_backward(xc, mean, rstd, g32, mk if mk is not None else torch.empty(0, device=x.device), n)
+        ctx.meta = (groups, length_last, mk is not None, gamma.dtype, beta.dtype)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, mean, rstd, g32, mk, n = ctx.saved_tensors
+        groups, length_last, has_mask, gdt, bdt = ctx.meta
+        mk = mk if has_mask else None
+        dyc = dy.contiguous()
+        B, H = mean.shape
+        _bump(2)
+        db, ds = _C().time_sums(dyc, xc, mk, length_last)          # sum dy, sum dy * x   [B, H]
+        c = 1.0 / n
+        if groups is None:
+            dv = 0.5 * rstd ** 3 * g32 * (mean * db - ds)
+            du = -rstd * g32 * db
+        else:
+            D = H // groups
+            dsg = (ds * g32).view(B, groups, D).sum(-1).repeat_interleave(D, dim=1)
+            dbg = (db * g32).view(B, groups, D).sum(-1).repeat_interleave(D, dim=1)
+            dv = 0.5 * rstd ** 3 * (mean * dbg - dsg)
+            du = -rstd * dbg
+        A = (rstd * g32).contiguous()
+        Bc = (2.0 * c * dv).contiguous()
+        Cc = (c * du - Bc * mean).contiguous()
+        dx = _C().affine_apply(dyc, xc, A, Bc, Cc, mk, length_last)
+        dgamma = (rstd * (ds - mean * db)).sum(0).to(gdt)
+        dbeta = db.sum(0).to(bdt)
+        return dx, dgamma, dbeta, None, None, None, None
+
+
 def sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last):
-    return reference.sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
+    return _SequenceNorm.apply(x, gamma, beta, padding_mask, num_groups, eps, length_last)
+
+
+class _Dropout(torch.autograd.Function):
+    """Philox mask regenerated in backward from (seed, offset); nothing is stored."""
+
+    @staticmethod
+    def forward(ctx, x, p):
+        # the offset comes from the CPU generator, whose state activation checkpointing restores,
+        # so a recomputed forward draws the same mask
+        ctx.key = (torch.initial_seed() & ((1 << 62) - 1), int(torch.randint(0, 2 ** 62, (1,)).item()))
+        ctx.p = p
+        _bump()
+        return _C().dropout(x.contiguous(), p, *ctx.key)
+
+    @staticmethod
+    def backward(ctx, g):
+        _bump()
+        return _C().dropout(g.contiguous(), ctx.p, *ctx.key), None
+
+
+def dropout(x, p):
+    return _Dropout.apply(x, float(p))
 
 
 # ----------------------------------------------------------------------------- CEMA
@@ -338,12 +422,47 @@ def cema(x, p, q, gamma, omega, hx, compute_last_state: bool):
     return _CEMA.apply(x, p, q, gamma, omega, hx, compute_last_state)
 
 
+class _EMAParameters(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, p, q, gamma, hx, length):
+        D = p.shape[0]
+        p2 = p.reshape(D, -1).float().contiguous()
+        N = p2.shape[1]
+        logq = _c2r(q.reshape(D, N).log())
+        g2 = _c2r(gamma.reshape(D, N))
+        h2 = None if hx is None else _c2r(hx)
+        _bump(1 if hx is None else 2)
+        k, b = _C().ema_parameters_fwd(p2, logq, g2, h2, length)
+        ctx.save_for_backward(p2, logq, g2, h2 if h2 is not None else torch.empty(0, device=p.device))
+        ctx.meta = (p.shape, q.shape, gamma.shape, hx is not None, length, p.dtype)
+        return k, b
+
+    @staticmethod
+    def backward(ctx, dk, db):
+        p2, logq, g2, h2 = ctx.saved_tensors
+        ps, qs, gs, has_h, length, pdt = ctx.meta
+        _bump()
+        dp, dq, dg, dh = _C().ema_parameters_bwd(None if dk is None else dk.float().contiguous(),
+                                                 None if db is None else db.float().contiguous(), p2, logq, g2,
+                                                 h2 if has_h else None, length)
+        return (dp.view(ps).to(pdt), torch.view_as_complex(dq).view(qs), torch.view_as_complex(dg).view(gs),
+                torch.view_as_complex(dh) if has_h else None, None)
+
+
 def ema_parameters(p, q, gamma, hx, length):
-    return reference.ema_parameters(p, q, gamma, hx, length)
+    return _EMAParameters.apply(p, q, gamma, hx, length)
 
 
 def ema_hidden(x, p, q, hx):
-    return reference.ema_hidden(x, p, q, hx)
+    """Last CEMA state of x [B, D, L]: the fused scan run with gamma = omega = 0."""
+    D = x.shape[1]
+    N = p.reshape(D, -1).shape[1]
+    if N not in (1, 2, 4, 8, 16, 32):
+        return reference.ema_hidden(x, p, q, hx)
+    zg = torch.zeros(D, N, dtype=torch.complex64, device=x.device)
+    zo = torch.zeros(D, device=x.device)
+    _, h = _CEMA.apply(x.transpose(1, 2), p, q, zg, zo, hx, True)
+    return h
 
 
 def fftconv(x, k):

@@ -71,4 +71,9 @@ class _Dropout(torch.autograd.Function):
 def memory_efficient_dropout(x: torch.Tensor, p: float = 0.0, training: bool = True) -> torch.Tensor:
     if not training or p == 0.0:
         return x
+    if x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.float16):
+        from ._ext import native_for
+        if native_for(x):
+            from . import cuda_ops
+            return cuda_ops.dropout(x, p)      # Philox mask generated in the kernel
     return _Dropout.apply(x, p, training)

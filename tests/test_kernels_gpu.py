@@ -346,3 +346,82 @@ def test_attention_softmax_op():
     assert torch.allclose(y.sum(-1), torch.ones_like(y.sum(-1)), atol=1e-4)
     frac = (y == 0).float().mean().item()
     assert 0.4 < frac < 0.6, frac
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("groups,length_last,masked", [(None, False, False), (None, True, True), (4, False, True),
+                                                       (8, True, False)])
+def test_sequence_norm(dtype, groups, length_last, masked):
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(10)
+    dev = _dev()
+    B, L, H = 3, 150, 64
+    x = torch.randn(B, L, H, device=dev) * 2 + 0.5
+    if length_last:
+        x = x.transpose(1, 2).contiguous()
+    x = x.to(dtype)
+    gamma = (torch.randn(H, device=dev) * 0.3 + 1).to(dtype)
+    beta = (torch.randn(H, device=dev) * 0.3).to(dtype)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool, device=dev)
+        mask[0, 100:] = True
+        mask[2, 7] = True
+    g = torch.randn_like(x)
+    res = []
+    for mod in (ops, reference):
+        leaves = [t.clone().requires_grad_() for t in (x, gamma, beta)]
+        y = mod.sequence_norm(leaves[0], leaves[1], leaves[2], mask, groups, 1e-5, length_last)
+        y.backward(g)
+        res.append((y, [t.grad for t in leaves]))
+    atol, rtol = (1e-4, 1e-3) if dtype == torch.float32 else (4e-2, 4e-2)
+    _close(res[0][0], res[1][0], atol, rtol, "seqnorm y")
+    for n, s, a, b in zip(("dx", "dgamma", "dbeta"), (4, 60, 60), res[0][1], res[1][1]):
+        _close(a, b, atol * s, rtol * 3, f"seqnorm {n}")
+
+
+def test_ema_parameters_hidden_and_dropout():
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(11)
+    dev = _dev()
+    B, D, N, L = 2, 12, 16, 200
+    p, q, gamma, _ = _cema_coeffs(D, N, dev)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2, device=dev))
+    gk = torch.randn(D, L, device=dev)
+    gb = torch.randn(B, D, L, device=dev)
+    res = []
+    for mod in (ops, reference):
+        leaves = [t.clone().requires_grad_() for t in (p, q, gamma, hx)]
+        k, b = mod.ema_parameters(leaves[0], leaves[1], leaves[2], leaves[3], L)
+        ((k * gk).sum() + (b * gb).sum()).backward()
+        res.append((k, b, [t.grad for t in leaves]))
+    _close(res[0][0], res[1][0], 2e-4, 2e-3, "ema k")
+    _close(res[0][1], res[1][1], 2e-4, 2e-3, "ema b")
+    for n, a, b_ in zip(("dp", "dq", "dgamma", "dh"), res[0][2], res[1][2]):
+        if a.is_complex():
+            a, b_ = torch.view_as_real(a), torch.view_as_real(b_)
+        _close(a, b_, 2e-3 * (b_.abs().max().item() + 1), 5e-3, f"ema {n}")
+    # ema_hidden
+    x = torch.randn(B, D, L, device=dev)
+    gh = torch.view_as_complex(torch.randn(B, D, N, 2, device=dev))
+    res = []
+    for mod in (ops, reference):
+        leaves = [t.clone().requires_grad_() for t in (x, p, q, hx)]
+        h = mod.ema_hidden(leaves[0], leaves[1], leaves[2], leaves[3])
+        (torch.view_as_real(h) * torch.view_as_real(gh)).sum().backward()
+        res.append((h, [t.grad for t in leaves]))
+    _close(torch.view_as_real(res[0][0]), torch.view_as_real(res[1][0]), 1e-3, 1e-2, "ema_hidden h")
+    for n, a, b_ in zip(("dx", "dp", "dq", "dh"), res[0][1], res[1][1]):
+        if a.is_complex():
+            a, b_ = torch.view_as_real(a), torch.view_as_real(b_)
+        _close(a, b_, 2e-3 * (b_.abs().max().item() + 1), 1e-2, f"ema_hidden {n}")
+    # dropout: keeps ~1-p of the entries, scales them, and backward applies the same mask
+    t = torch.randn(1 << 16, device=dev).requires_grad_()
+    y = ops.memory_efficient_dropout(t, 0.25, True)
+    kept = (y != 0)
+    assert 0.72 < kept.float().mean().item() < 0.78
+    assert torch.allclose(y[kept], t.detach()[kept] / 0.75, rtol=1e-5)
+    y.backward(torch.ones_like(y))
+    assert torch.equal(t.grad != 0, kept)
