@@ -26,6 +26,9 @@ import sys
 import threading
 import time
 
+# before CUDA initialises: peer-waiting kernels must never be held up by a lazy kernel load
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
@@ -157,7 +160,8 @@ def main():
     if world > 1:
         # CEMA / TimestepNorm state goes from rank to rank through peer memory, not NCCL send/recv
         from megalodon_b200.parallel.symm import enable_peer_transport
-        mailbox, _ = enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=60.0)
+        peer_timeout = float(os.environ.get("MEGALODON_B200_PEER_TIMEOUT_S", "60"))
+        mailbox, _ = enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=peer_timeout)
     opt, sched = build_optimizer(model, OptimConf(lr=1e-4, warmup=10, clip=1.0), 1000, "bf16")
     data = SyntheticTokens(cfg.vocab_size, 1, args.seq_len, seed=0)
     n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)
@@ -180,10 +184,22 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
+    def check_peers():
+        # a bounded device-side wait that ran out shows up here instead of slowing every later step
+        cuda_ops.check_kernel_errors()
+        if world > 1:
+            mailbox.check()
+            rs = getattr(model, "_symm_rs", None)
+            if rs is not None:
+                rs.check()
+
+    for i in range(args.warmup):
         x, y = next(data)
         last = step(x, y, True)
-    cuda_ops.check_kernel_errors()
+        torch.cuda.synchronize()
+        check_peers()
+        if os.environ.get("MEGALODON_B200_BENCH_VERBOSE"):
+            print(f"[rank {rank}] warmup step {i} loss {last:.4f}", file=sys.stderr, flush=True)
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -194,20 +210,35 @@ def main():
     barrier()
     launches0 = cuda_ops.count_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    marks = []           # per step: events at the phase boundaries (recording an event costs no device time)
+
+    def mark():
+        ev = torch.cuda.Event(enable_timing=True)
+        ev.record()
+        return ev
+
     e0.record()
     for _ in range(args.steps):
+        m = [mark()]
         tok_loss, _ = model(xd, targets=yd)
         loss = tok_loss.mean()
+        m.append(mark())
         loss.backward()
+        m.append(mark())
         model.grad_all_reduce()
         clip_grad_norm_(model, 1.0)
+        m.append(mark())
         opt.step()
         sched.step()
         opt.zero_grad()
+        m.append(mark())
+        marks.append(m)
     e1.record()
     barrier()
     dev_ms = e0.elapsed_time(e1)
     launches = cuda_ops.count_launches() - launches0
+    phase_names = ["forward", "backward", "grad_reduce_clip", "optimizer"]
+    phases = {n: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / args.steps for i, n in enumerate(phase_names)}
 
     # ---- region 2: end to end (H2D of the tokens from pinned memory, D2H of the loss, every step)
     barrier()
@@ -255,6 +286,7 @@ def main():
                     "wall_ms_per_step": wall_ms / args.steps,
                     "h2d_bytes_per_step": 2 * args.seq_len * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "phases_ms_rank0": {k: round(v, 1) for k, v in phases.items()},
         }
         if args.layers is not None:
             out["invalid"] = "reduced depth (debug run)"

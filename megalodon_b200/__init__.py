@@ -1,3 +1,16 @@
 """megalodon_b200: a Blackwell-native (sm_100a) Megalodon training and
 inference framework."""
+import os as _os
+
+# Kernels of this package wait on flags that another rank's kernels write (the
+# peer mailbox, the flag barriers of the symmetric collectives).  With CUDA's
+# default lazy module loading, the first launch of any not-yet-loaded kernel may
+# have to wait for running kernels to drain; if the running kernel is one of
+# those waits, and the peer it waits for is in turn waiting for the kernel being
+# loaded, both ranks stall until the bounded waits give up.  Loading every
+# kernel when its module is registered removes that dependency.  The variable
+# is read when CUDA initialises, so it is set at import time, before the first
+# CUDA call; an explicit setting by the user is left alone.
+_os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+
 __version__ = "0.1.0"

@@ -554,6 +554,18 @@ void allreduce_sumsq(const Tensor& bufs, int64_t rank, int64_t nbytes, double sc
                       (float)scale, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (int)dtype, stream());
 }
 
+void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& out,
+                          const OptTensor& sumsq, bool accumulate) {
+  check_cuda_contig(bufs, "bufs");
+  check_cuda_contig(out, "out");
+  c10::cuda::CUDAGuard guard(out.device());
+  TORCH_CHECK(bufs.scalar_type() == at::kLong);
+  mb::reduce_scatter_sumsq(reinterpret_cast<const void* const*>(bufs.data_ptr<int64_t>()), (int)rank,
+                           (int)bufs.numel(), out.numel(), (float)scale, out.data_ptr(),
+                           sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, accumulate, (int)in_dtype,
+                           dtype_code(out), stream());
+}
+
 // out = sum of `world` consecutive slots of out.numel() elements each
 void reduce_slots(const Tensor& slots, Tensor& out, int64_t world) {
   check_cuda_contig(slots, "slots");
@@ -588,6 +600,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>());
   m.def("reduce_slots", &reduce_slots);
+  m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
   m.def("time_sums", &time_sums);
   m.def("affine_apply", &affine_apply);
   m.def("dropout", &dropout);

@@ -211,6 +211,29 @@ __global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
 }
 
+// Reduce-scatter by pull: this rank sums ITS slice of every peer's staged buffer in fp32, scales it
+// (gradient averaging), stores it to a local shard in the output dtype and accumulates the squared
+// norm of what it stored.  One pass replaces reduce-scatter + cast/scale + the gradient-norm pass.
+template <typename T, typename O>
+__global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, int rank, int world,
+                                            long long shard_n, float scale, O* __restrict__ out,
+                                            double* __restrict__ sumsq, bool accumulate) {
+  __shared__ float scratch[32];
+  const long long lo = (long long)rank * shard_n;
+  float ss = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < shard_n;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int p = 0; p < world; ++p) acc += to_f(bufs[(rank + p) % world][lo + i]);
+    acc *= scale;
+    if (accumulate) acc += to_f(out[i]);
+    ss += acc * acc;
+    out[i] = from_f<O>(acc);
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
+}
+
 template <typename T>
 __global__ void reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__ out, long long n, int world) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -228,6 +251,22 @@ void reduce_slots(const void* slots, void* out, long long n, int world, int dtyp
   const int grid = (int)std::min<long long>(div_up(n, 256), 148LL * 16);
   MB_DISPATCH_DTYPE(dtype, (reduce_slots_kernel<scalar_t><<<grid, 256, 0, st>>>((const scalar_t*)slots, (scalar_t*)out,
                                                                              n, world)));
+}
+
+void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
+                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, cudaStream_t st) {
+  if (shard_n == 0) return;
+  const int grid = (int)std::min<long long>(div_up(shard_n, 256), 148LL * 8);
+  MB_DISPATCH_DTYPE(in_dtype, {
+    using T = scalar_t;
+    if (out_dtype == kF32 && in_dtype != kF32) {
+      reduce_scatter_sumsq_kernel<T, float><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
+                                                                 (float*)out, sumsq, accumulate);
+    } else {
+      reduce_scatter_sumsq_kernel<T, T><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
+                                                             (T*)out, sumsq, accumulate);
+    }
+  });
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,

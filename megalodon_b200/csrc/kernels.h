@@ -119,6 +119,9 @@ void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigne
               cudaStream_t st);
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
                   int* err, cudaStream_t st);
+// out[i] (+)= scale * sum_p bufs[p][rank * shard_n + i]; out dtype = in dtype or fp32; sumsq += |out|^2
+void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
+                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, cudaStream_t st);
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
                      int dtype, cudaStream_t st);
 

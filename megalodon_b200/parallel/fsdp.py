@@ -49,6 +49,8 @@ import torch
 import torch.distributed as dist
 import torch.nn as nn
 
+from contextlib import nullcontext as _nullcontext
+
 from .utils import all_gather_flat, reduce_scatter_flat
 
 ALIGN = 64
@@ -389,11 +391,36 @@ class FullyShardedDataParallel(nn.Module):
         p = self.flat_param
         red_dtype = torch.float32 if (self.fp32_reduce_scatter or not self.mixed_precision) else self.compute_dtype
         g = flat_grad if flat_grad.dtype == red_dtype else flat_grad.to(red_dtype)
+        root = self._root
+        fused_rs = getattr(root, "_symm_rs", None)
+        if self.world_size > 1 and fused_rs is not None and flat_grad.dtype == fused_rs.dtype:
+            # peer-memory reduce-scatter: sum + 1/dp scale + cast + |g|^2 partial in one kernel
+            accumulate = p._grad_shard is not None
+            shard = p._grad_shard if accumulate else torch.empty(self._shard_numel, dtype=red_dtype, device=g.device)
+            if getattr(root, "_fused_sumsq", None) is None:
+                root._fused_sumsq = torch.zeros((), dtype=torch.float64, device=g.device)
+                root._fused_sumsq_complete = True
+                root._fused_sumsq_kind = "reduce_scatter"
+            if accumulate:
+                root._fused_sumsq_complete = False     # norm of a sum is not the sum of norms
+            stream = root._comm_stream
+            if stream is not None:
+                stream.wait_stream(torch.cuda.current_stream())
+            with (torch.cuda.stream(stream) if stream is not None else _nullcontext()):
+                fused_rs.reduce_scatter(flat_grad, shard, 1.0 / self.gradient_divide_factor,
+                                        root._fused_sumsq, accumulate)
+            if stream is not None:
+                flat_grad.record_stream(stream)
+                shard.record_stream(stream)
+                root._pending.append(True)
+            p._grad_shard = shard
+            if self.reshard_after_forward and not self._is_root:
+                self._free_full()
+            return None
         if self.world_size > 1:
             if self.gradient_divide_factor != 1.0:
                 g = g / self.gradient_divide_factor
             shard = torch.empty(self._shard_numel, dtype=red_dtype, device=g.device)
-            root = self._root
             if root._comm_stream is not None:
                 root._comm_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(root._comm_stream):
@@ -474,6 +501,7 @@ class FullyShardedDataParallel(nn.Module):
             acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
             fused.all_reduce_(self._grad_tensors(), sumsq=acc)
             self._fused_sumsq = acc
+            self._fused_sumsq_kind = "allreduce"
             return
         for g in self._grad_tensors():
             dist.all_reduce(g, group=self.chunk_parallel_process_group)
@@ -518,7 +546,14 @@ class FullyShardedDataParallel(nn.Module):
         from .. import ops
         from ..ops import cuda_ops
         acc = getattr(self, "_fused_sumsq", None)
-        if acc is not None:
+        if acc is not None and getattr(self, "_fused_sumsq_kind", "") == "reduce_scatter":
+            # the fused reduce-scatter already accumulated |shard|^2 (valid unless micro-batches were summed)
+            self._fused_sumsq = None
+            if not getattr(self, "_fused_sumsq_complete", True):
+                acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
+                for g in grads:
+                    ops.sum_squares(g, acc)
+        elif acc is not None:
             # the fused chunk-group all-reduce already produced per-rank partial sums of squares
             self._fused_sumsq = None
             dist.all_reduce(acc, group=self.chunk_parallel_process_group)

@@ -290,6 +290,54 @@ class SymmetricAllReduce:
             raise PeerTimeout(f"peer barrier timed out (code {code})")
 
 
+class SymmetricReduceScatter:
+    """Gradient reduce-scatter of an FSDP unit by pulling from peer memory, fused with the averaging
+    scale, the cast to the shard dtype and the squared-norm partial sum used for clipping.  Two staging
+    buffers alternate, so one flag barrier per unit is enough (see `reduce_scatter`)."""
+
+    def __init__(self, group, device, max_numel: int, dtype: torch.dtype, timeout_s: float = 60.0):
+        self.world = dist.get_world_size(group)
+        self.rank = dist.get_rank(group)
+        self.dtype = dtype
+        esize = torch.empty(0, dtype=dtype).element_size()
+        self.stage_bytes = _round_up(max_numel * esize, 256)
+        self.pad_off = 2 * self.stage_bytes
+        self.region = SymmetricRegion(self.pad_off + _round_up(4 * self.world, 256), group, device)
+        self._pads = self.region.ptr_table_at(self.pad_off).contiguous()
+        self._bufs = [self.region.ptr_table_at(0).contiguous(), self.region.ptr_table_at(self.stage_bytes).contiguous()]
+        self._err = torch.zeros(1, dtype=torch.int32, device=device)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        self._toggle = 0
+
+    @torch.no_grad()
+    def reduce_scatter(self, flat_grad: torch.Tensor, out_shard: torch.Tensor, scale: float,
+                       sumsq: Optional[torch.Tensor], accumulate: bool = False) -> None:
+        """out_shard (+)= scale * (this rank's slice of the sum over ranks of flat_grad).
+
+        Staging buffer t is rewritten two calls later; by then every peer has passed the barrier of
+        the call in between, which its stream reaches only after its own read of buffer t finished."""
+        from ..ops._ext import require
+        from ..ops.cuda_ops import _DT
+        ext = require()
+        n = flat_grad.numel()
+        assert n * flat_grad.element_size() <= self.stage_bytes and flat_grad.dtype == self.dtype
+        assert n == out_shard.numel() * self.world
+        t = self._toggle
+        self._toggle ^= 1
+        stage = self.region.view(t * self.stage_bytes, n * flat_grad.element_size(), flat_grad.dtype)
+        stage.copy_(flat_grad.view(-1))
+        self.epoch += 1
+        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
+        ext.reduce_scatter_sumsq(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, out_shard, sumsq, accumulate)
+
+    def check(self) -> None:
+        code = int(self._err.item())
+        if code:
+            self._err.zero_()
+            raise PeerTimeout(f"reduce-scatter peer barrier timed out (code {code})")
+
+
 # ----------------------------------------------------------------------------- wiring
 def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_bucket_mb: int = 256,
                           timeout_s: float = 30.0):
@@ -303,6 +351,11 @@ def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_
     cp = get_chunk_parallel_world_size()
     if cp == 1:
         return None, None
+    import os
+    import warnings
+    if os.environ.get("CUDA_MODULE_LOADING", "").upper() != "EAGER":
+        warnings.warn("CUDA_MODULE_LOADING is not EAGER: a lazy kernel load behind a kernel that waits for a peer "
+                      "can stall both ranks until the bounded waits time out")
     inner = model
     while hasattr(inner, "_wrapped"):
         inner = inner._wrapped
@@ -319,6 +372,9 @@ def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_
     mailbox = PeerMailbox(region, r - 1 if r > 0 else None, r + 1 if r + 1 < cp else None, slot_bytes,
                           n_slots=n_slots, timeout_s=timeout_s)
     set_handoff_transport("p2p", mailbox)
+    if (getattr(model, "world_size", 1) > 1 and getattr(model, "mixed_precision", False)
+            and os.environ.get("MEGALODON_B200_PEER_RS", "1") == "1"):
+        enable_peer_reduce_scatter(model, timeout_s=timeout_s)
     reducer = None
     if not getattr(model, "chunk_group_is_sharded", False):
         bucket = allreduce_bucket_mb << 20
@@ -326,3 +382,17 @@ def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_
         reducer = SymmetricAllReduce(ar_region, bucket, timeout_s=timeout_s)
         model._symm_allreduce = reducer
     return mailbox, reducer
+
+
+def enable_peer_reduce_scatter(model, timeout_s: float = 60.0) -> Optional[SymmetricReduceScatter]:
+    """Replace the NCCL reduce-scatter of every FSDP unit of `model` by the fused peer-memory kernel
+    (reduce + scale + cast + gradient-norm partial sums)."""
+    if getattr(model, "world_size", 1) <= 1:
+        return None
+    units = model._units()
+    biggest = max(u._numel_padded for u in units)
+    device = next(model.parameters()).device
+    rs = SymmetricReduceScatter(model.process_group, device, biggest, model.compute_dtype, timeout_s=timeout_s)
+    model._lazy_init()
+    model._symm_rs = rs
+    return rs

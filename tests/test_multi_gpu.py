@@ -260,3 +260,49 @@ def test_model_parallel_training_with_fused_collectives_matches_nccl():
         assert abs(l0 - l1) < 2e-2, (l0, l1)
         rel = (g0 - g1).norm() / (g0.norm() + 1e-6)
         assert rel < 5e-2, rel
+
+
+def _fsdp_rs_case(rank, world):
+    from megalodon_b200.config import ModelConf, OptimConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.optim import build_optimizer
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.parallel.symm import enable_peer_reduce_scatter
+    from megalodon_b200.utils import clip_grad_norm_, set_random_seed
+    initialize_model_parallel(1, 1)            # data parallel = world
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    toks = torch.randint(0, 512, (4, 257), generator=torch.Generator().manual_seed(0))
+    toks = toks[rank * 2:(rank + 1) * 2].cuda()
+    x, y = toks[:, :-1], toks[:, 1:]
+    curves = {}
+    for fused in (False, True):
+        set_random_seed(0)
+        model = build_model(cfg, "bf16", False, True)
+        if fused:
+            rs = enable_peer_reduce_scatter(model, timeout_s=20.0)
+        opt, sched = build_optimizer(model, OptimConf(lr=3e-3, warmup=2), 20, "bf16")
+        curve = []
+        for _ in range(4):
+            loss = model(x, targets=y)[0].mean()
+            loss.backward()
+            model.grad_all_reduce()
+            norm = clip_grad_norm_(model, 1.0)
+            opt.step(); sched.step(); opt.zero_grad()
+            curve.append((loss.item(), float(norm)))
+        if fused:
+            torch.cuda.synchronize()
+            rs.check()
+        cuda_ops.check_kernel_errors()
+        curves[fused] = curve
+    return curves
+
+
+def test_fsdp_with_peer_memory_reduce_scatter_matches_nccl():
+    _need_gpus(2)
+    for r in _run(_fsdp_rs_case):
+        for (l0, n0), (l1, n1) in zip(r[False], r[True]):
+            assert abs(l0 - l1) < 5e-2, r
+            assert abs(n0 - n1) < 0.1 * max(1.0, n0), r
