@@ -41,6 +41,9 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--kernel-profile", default=None,
+                    help="after the timed regions, run one more step under torch.profiler and write a per-kernel "
+                         "summary to this path (rank number appended); never part of a reported number")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--model", default="mega7B_32k")
@@ -256,6 +259,41 @@ def main():
     cuda_ops.check_kernel_errors()
     if world > 1:
         mailbox.check()
+
+    if args.kernel_profile:
+        import collections
+        from torch.profiler import ProfilerActivity, profile
+        barrier()
+        p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            p0.record()
+            step(x, y, False)
+            p1.record()
+            torch.cuda.synchronize()
+        agg = collections.defaultdict(lambda: [0.0, 0])
+        spans = []
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                agg[e.name][0] += e.device_time
+                agg[e.name][1] += 1
+                spans.append((e.time_range.start, e.time_range.end))
+        spans.sort()
+        busy, cur_s, cur_e = 0.0, None, None          # union of kernel intervals = time the GPU was not idle
+        for a, b in spans:
+            if cur_e is None or a > cur_e:
+                if cur_e is not None:
+                    busy += cur_e - cur_s
+                cur_s, cur_e = a, b
+            else:
+                cur_e = max(cur_e, b)
+        if cur_e is not None:
+            busy += cur_e - cur_s
+        tot = sum(v[0] for v in agg.values())
+        with open(f"{args.kernel_profile}.rank{rank}", "w") as f:
+            f.write(f"step (CUDA events, under the profiler) {p0.elapsed_time(p1):.1f} ms; sum of kernel times "
+                    f"{tot / 1e3:.1f} ms; GPU busy (union of kernel intervals) {busy / 1e3:.1f} ms\n")
+            for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:45]:
+                f.write(f"{t / 1e3:9.2f} ms {100 * t / tot:5.1f}% {n:6d}x {t / n:9.1f} us  {name[:120]}\n")
 
     if world > 1:
         t = torch.tensor([dev_ms, e2e_ms], device="cuda", dtype=torch.float64)

@@ -160,6 +160,8 @@ class FullyShardedDataParallel(nn.Module):
         self._is_root: Optional[bool] = None
         self._wrapped = module
         self._comm_stream = None
+        self._gather_stream = None
+        self._gather_event = None
         self._pending: List[Any] = []
 
         self._flatten(module, compute_device)
@@ -312,6 +314,38 @@ class FullyShardedDataParallel(nn.Module):
         all_gather_flat(self._full.data, shard, self.process_group)
         self._full_version = _ver(self.flat_param)
 
+    def _prefetch_gathers(self) -> None:
+        """Root only: all-gather every unit whose full buffer stays resident
+        between forward and backward, on a side stream, as soon as the step starts.
+
+        With the all-gathers on the compute stream the ranks of a chunk-parallel
+        group advance in lockstep layer by layer (a collective completes only when
+        every rank has reached it), while the state handoff makes rank r start a
+        layer only after rank r-1 finished it: together that serialises the ranks.
+        Issued up front on their own stream the gathers depend on nothing but the
+        optimizer step, and each unit's forward waits only for its own event."""
+        if self.compute_device.type != "cuda":
+            return
+        stale = [u for u in self._units()
+                 if u.world_size > 1 and (u._is_root or not u.reshard_after_forward) and not u._full_is_valid()]
+        if not stale:
+            return
+        shards = [u._lowp_shard() for u in stale]          # casts (if any) run on the compute stream
+        for u, shard in zip(stale, shards):
+            if u._full is None:
+                u._full = torch.empty(u._numel_padded, dtype=shard.dtype, device=shard.device)
+        if self._gather_stream is None:
+            self._gather_stream = torch.cuda.Stream(self.compute_device)
+        gs = self._gather_stream
+        gs.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(gs):
+            for u, shard in zip(stale, shards):
+                all_gather_flat(u._full.data, shard, u.process_group)
+                u._full_version = _ver(u.flat_param)
+                ev = torch.cuda.Event()
+                ev.record(gs)
+                u._gather_event = ev
+
     def _free_full(self) -> None:
         if self.world_size > 1 and self._full is not None:
             self._full.untyped_storage().resize_(0)
@@ -331,6 +365,11 @@ class FullyShardedDataParallel(nn.Module):
     def forward(self, *args, **kwargs):
         self._lazy_init()
         p = self.flat_param
+        if self._is_root and self.world_size > 1:
+            self._prefetch_gathers()
+        if self._gather_event is not None:
+            torch.cuda.current_stream().wait_event(self._gather_event)
+            self._gather_event = None
         if not self._full_is_valid():
             self._gather_full()
         want_grad = torch.is_grad_enabled() and p.requires_grad
