@@ -50,10 +50,13 @@ __device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned 
                                              unsigned long long timeout_ns) {
   if (ld_acquire_sys(flag) >= want) return true;
   const unsigned long long t0 = now_ns();
-  unsigned int spins = 0;
+  // Exponential back-off up to 2 us per poll: a waiting warp shares its SM with whatever compute
+  // kernel runs on the other streams, and a tight poll loop steals issue slots from it.
+  unsigned int spins = 0, pause_ns = 32;
   while (ld_acquire_sys(flag) < want) {
     if ((++spins & 0x3f) == 0 && now_ns() - t0 > timeout_ns) return false;
-    __nanosleep(64);
+    __nanosleep(pause_ns);
+    if (pause_ns < 2048) pause_ns <<= 1;
   }
   return true;
 }
@@ -244,6 +247,16 @@ __global__ void reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__
   }
 }
 
+// Kernels of this file run on side streams next to the persistent GEMM, whose CTAs need nearly all of
+// an SM's shared memory.  An SM's L1 / shared-memory split is fixed while any CTA is resident on it,
+// so a waiting CTA launched with the default (L1-heavy) split keeps a GEMM CTA off that SM until the
+// wait ends, and a statically scheduled persistent kernel then runs at the pace of the CTA that
+// started late.  Asking for the largest shared-memory carve-out makes the two co-resident.
+template <typename K>
+void prefer_max_shared(K kernel) {
+  cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+}
+
 }  // namespace
 
 void reduce_slots(const void* slots, void* out, long long n, int world, int dtype, cudaStream_t st) {
@@ -260,9 +273,11 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
   MB_DISPATCH_DTYPE(in_dtype, {
     using T = scalar_t;
     if (out_dtype == kF32 && in_dtype != kF32) {
+      prefer_max_shared(reduce_scatter_sumsq_kernel<T, float>);
       reduce_scatter_sumsq_kernel<T, float><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
                                                                  (float*)out, sumsq, accumulate);
     } else {
+      prefer_max_shared(reduce_scatter_sumsq_kernel<T, T>);
       reduce_scatter_sumsq_kernel<T, T><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
                                                              (T*)out, sumsq, accumulate);
     }
@@ -274,6 +289,7 @@ void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int*
               unsigned long long timeout_ns, int* err, cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
+  prefer_max_shared(p2p_send_kernel);
   p2p_send_kernel<<<grid, 256, 0, st>>>((const uint4*)src, (uint4*)remote_dst, n16, remote_flag, seq, local_ack,
                                         need_ack, counter, timeout_ns, err);
 }
@@ -283,12 +299,14 @@ void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigne
               cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
+  prefer_max_shared(p2p_recv_kernel);
   p2p_recv_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (const uint4*)local_slot, n16, local_flag, seq, remote_ack,
                                         counter, timeout_ns, err);
 }
 
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
                   int* err, cudaStream_t st) {
+  prefer_max_shared(peer_barrier_kernel);
   peer_barrier_kernel<<<1, 32, 0, st>>>(pads, rank, world, epoch, timeout_ns, err);
 }
 
@@ -297,14 +315,18 @@ void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, f
   const long long n16 = nbytes / 16;
   const long long slice16 = (n16 + world - 1) / world;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(slice16, 256), 148LL * 4));
-  if (dtype == kBF16)
+  if (dtype == kBF16) {
+    prefer_max_shared(allreduce_sumsq_16bit_kernel<__nv_bfloat16>);
     allreduce_sumsq_16bit_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16,
                                                                     scale, sumsq);
-  else if (dtype == kF16)
+  } else if (dtype == kF16) {
+    prefer_max_shared(allreduce_sumsq_16bit_kernel<__half>);
     allreduce_sumsq_16bit_kernel<__half><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16, scale,
                                                              sumsq);
-  else
+  } else {
+    prefer_max_shared(allreduce_sumsq_f32_kernel);
     allreduce_sumsq_f32_kernel<<<grid, 256, 0, st>>>((float4* const*)bufs, rank, world, n16, slice16, scale, sumsq);
+  }
 }
 
 }  // namespace mb

@@ -113,7 +113,8 @@ def _cema_coeffs(D, N, dev):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,L,D,N,with_h", [(2, 37, 24, 16, True), (1, 300, 40, 16, True),
                                             (2, 260, 16, 4, False), (1, 1, 32, 16, True),
-                                            (2, 513, 8, 8, True)])
+                                            (2, 513, 8, 8, True), (1, 1024, 256, 16, True),
+                                            (1, 200, 136, 32, True), (2, 129, 128, 16, False)])
 def test_cema(dtype, B, L, D, N, with_h):
     from megalodon_b200 import ops
     from megalodon_b200.ops import reference
