@@ -240,6 +240,7 @@ def main():
     barrier()
     dev_ms = e0.elapsed_time(e1)
     launches = cuda_ops.count_launches() - launches0
+    steps_ms = [marks[i][0].elapsed_time(marks[i][4]) for i in range(args.steps)]
     phase_names = ["forward", "backward", "grad_reduce_clip", "optimizer"]
     phases = {n: sum(m[i].elapsed_time(m[i + 1]) for m in marks) / args.steps for i, n in enumerate(phase_names)}
 
@@ -325,6 +326,7 @@ def main():
                     "h2d_bytes_per_step": 2 * args.seq_len * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
             "phases_ms_rank0": {k: round(v, 1) for k, v in phases.items()},
+            "steps_ms_rank0": [round(v, 1) for v in steps_ms],
         }
         if args.layers is not None:
             out["invalid"] = "reduced depth (debug run)"

@@ -120,12 +120,126 @@ __global__ void attn_softmax_bwd_kernel(const T* __restrict__ p, T* __restrict__
   }
 }
 
+
+// 16-byte variants: a thread owns up to kSmVecPerThread groups of 8 consecutive columns.  Requires
+// L2 % 8 == 0, ld % 8 == 0 and a 16-byte aligned base, so every group is either entirely inside or
+// entirely outside [0, zero_to) (zero_to is a multiple of 128 or L2 itself).
+constexpr int kSmVecPerThread = kSmMaxPerThread / 8;
+
+template <typename T>
+__global__ void attn_softmax_fwd_vec_kernel(T* __restrict__ s, float* __restrict__ lse, int L1, int L2,
+                                            long long ld, bool causal, float drop_p, unsigned long long seed,
+                                            unsigned long long offset) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int pos = (int)(row % L1);
+  const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
+  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  T* sr = s + row * ld;
+  float v[kSmVecPerThread][8];
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < kSmVecPerThread; ++i) {
+    const int c0 = (threadIdx.x + i * kSmThreads) * 8;
+    if (c0 < n) {
+      load8(sr + c0, v[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int c = c0 + j;
+        if (c >= n) v[i][j] = -INFINITY;
+        else if (drop_p > 0.f && uniform01(seed, offset, (unsigned long long)row * L2 + c) < drop_p)
+          v[i][j] = -INFINITY;
+        m = fmaxf(m, v[i][j]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[i][j] = -INFINITY;
+    }
+  }
+  m = block_max(m, scratch);
+  float sum = 0.f;
+  if (m > -INFINITY) {
+    const float ml2 = m * 1.4426950408889634f;
+#pragma unroll
+    for (int i = 0; i < kSmVecPerThread; ++i) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        v[i][j] = exp2f(fmaf(v[i][j], 1.4426950408889634f, -ml2));      // exp2(-inf) = 0 for masked entries
+        sum += v[i][j];
+      }
+    }
+  }
+  sum = block_sum(sum, scratch);
+  const float inv = (m > -INFINITY && sum > 0.f) ? 1.f / sum : 0.f;
+#pragma unroll
+  for (int i = 0; i < kSmVecPerThread; ++i) {
+    const int c0 = (threadIdx.x + i * kSmThreads) * 8;
+    if (c0 < zero_to) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = (m > -INFINITY) ? v[i][j] * inv : 0.f;
+      store8(sr + c0, o);
+    }
+  }
+  if (lse != nullptr && threadIdx.x == 0) lse[row] = sum > 0.f ? m + logf(sum) : -INFINITY;
+}
+
+template <typename T>
+__global__ void attn_softmax_bwd_vec_kernel(const T* __restrict__ p, T* __restrict__ dp, int L1, int L2,
+                                            long long ld, bool causal) {
+  __shared__ float scratch[32];
+  const long long row = blockIdx.x;
+  const int pos = (int)(row % L1);
+  const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
+  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  const T* pr = p + row * ld;
+  T* dr = dp + row * ld;
+  float pv[kSmVecPerThread][8], gv[kSmVecPerThread][8];
+  float dot = 0.f;
+#pragma unroll
+  for (int i = 0; i < kSmVecPerThread; ++i) {
+    const int c0 = (threadIdx.x + i * kSmThreads) * 8;
+    if (c0 < n) {
+      load8(pr + c0, pv[i]);
+      load8(dr + c0, gv[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (c0 + j >= n) pv[i][j] = gv[i][j] = 0.f;
+        dot = fmaf(pv[i][j], gv[i][j], dot);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) pv[i][j] = gv[i][j] = 0.f;
+    }
+  }
+  dot = block_sum(dot, scratch);
+#pragma unroll
+  for (int i = 0; i < kSmVecPerThread; ++i) {
+    const int c0 = (threadIdx.x + i * kSmThreads) * 8;
+    if (c0 < zero_to) {
+      float o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = pv[i][j] * (gv[i][j] - dot);
+      store8(dr + c0, o);
+    }
+  }
+}
+
+inline bool softmax_vec_ok(const void* base, int L2, long long ld, int dtype) {
+  return L2 % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 31) == 0;
+}
+
 }  // namespace
 
 void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2, long long ld, bool causal,
                       float dropkey_p, unsigned long long seed, unsigned long long offset, int dtype,
                       cudaStream_t st) {
   if (rows == 0) return;
+  if (softmax_vec_ok(s_inout, L2, ld, dtype)) {
+    MB_DISPATCH_DTYPE(dtype, (attn_softmax_fwd_vec_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
+                                 (scalar_t*)s_inout, lse, L1, L2, ld, causal, dropkey_p, seed, offset)));
+    return;
+  }
   MB_DISPATCH_DTYPE(dtype, (attn_softmax_fwd_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
                                (scalar_t*)s_inout, lse, L1, L2, ld, causal, dropkey_p, seed, offset)));
 }
@@ -133,6 +247,11 @@ void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2,
 void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
                       int dtype, cudaStream_t st) {
   if (rows == 0) return;
+  if (softmax_vec_ok(p, L2, ld, dtype) && (reinterpret_cast<uintptr_t>(dp_inout) & 31) == 0) {
+    MB_DISPATCH_DTYPE(dtype, (attn_softmax_bwd_vec_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
+                                 (const scalar_t*)p, (scalar_t*)dp_inout, L1, L2, ld, causal)));
+    return;
+  }
   MB_DISPATCH_DTYPE(dtype, (attn_softmax_bwd_kernel<scalar_t><<<(unsigned)rows, kSmThreads, 0, st>>>(
                                (const scalar_t*)p, (scalar_t*)dp_inout, L1, L2, ld, causal)));
 }

@@ -7,19 +7,42 @@
 namespace mb {
 namespace {
 
+// n8 groups of 8 elements through 16-byte accesses, then a scalar tail of n - 8 * n8 elements
 template <typename T>
 __global__ void swiglu_fwd_kernel(const T* __restrict__ a, const T* __restrict__ b, T* __restrict__ out,
-                                  long long n) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x)
-    out[i] = from_f<T>(silu_f(to_f(a[i])) * to_f(b[i]));
+                                  long long n, long long n8) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = tid; i < n8; i += stride) {
+    float av[8], bv[8], o[8];
+    load8(a + 8 * i, av);
+    load8(b + 8 * i, bv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o[j] = silu_f(av[j]) * bv[j];
+    store8(out + 8 * i, o);
+  }
+  for (long long i = 8 * n8 + tid; i < n; i += stride) out[i] = from_f<T>(silu_f(to_f(a[i])) * to_f(b[i]));
 }
 
 template <typename T>
 __global__ void swiglu_bwd_kernel(const T* __restrict__ g, const T* __restrict__ a, const T* __restrict__ b,
-                                  T* __restrict__ da, T* __restrict__ db, long long n) {
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
-       i += (long long)gridDim.x * blockDim.x) {
+                                  T* __restrict__ da, T* __restrict__ db, long long n, long long n8) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = tid; i < n8; i += stride) {
+    float gv[8], av[8], bv[8], oa[8], ob[8];
+    load8(g + 8 * i, gv);
+    load8(a + 8 * i, av);
+    load8(b + 8 * i, bv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      oa[j] = gv[j] * bv[j] * silu_grad_f(av[j]);
+      ob[j] = gv[j] * silu_f(av[j]);
+    }
+    store8(da + 8 * i, oa);
+    store8(db + 8 * i, ob);
+  }
+  for (long long i = 8 * n8 + tid; i < n; i += stride) {
     const float gv = to_f(g[i]), av = to_f(a[i]), bv = to_f(b[i]);
     da[i] = from_f<T>(gv * bv * silu_grad_f(av));
     db[i] = from_f<T>(gv * silu_f(av));
@@ -198,15 +221,19 @@ int ew_grid(long long n) { return (int)std::min<long long>(div_up(n, 256), 148LL
 }  // namespace
 
 void swiglu_fwd(const void* a, const void* b, void* out, long long n, int dtype, cudaStream_t st) {
-  MB_DISPATCH_DTYPE(dtype, (swiglu_fwd_kernel<scalar_t><<<ew_grid(n), 256, 0, st>>>(
-                               (const scalar_t*)a, (const scalar_t*)b, (scalar_t*)out, n)));
+  if (n == 0) return;
+  const long long n8 = (aligned32(a) && aligned32(b) && aligned32(out)) ? n / 8 : 0;
+  MB_DISPATCH_DTYPE(dtype, (swiglu_fwd_kernel<scalar_t><<<ew_grid(std::max(n8, n - 8 * n8)), 256, 0, st>>>(
+                               (const scalar_t*)a, (const scalar_t*)b, (scalar_t*)out, n, n8)));
 }
 
 void swiglu_bwd(const void* g, const void* a, const void* b, void* da, void* db, long long n, int dtype,
                 cudaStream_t st) {
-  MB_DISPATCH_DTYPE(dtype, (swiglu_bwd_kernel<scalar_t><<<ew_grid(n), 256, 0, st>>>(
+  if (n == 0) return;
+  const long long n8 = (aligned32(g) && aligned32(a) && aligned32(b) && aligned32(da) && aligned32(db)) ? n / 8 : 0;
+  MB_DISPATCH_DTYPE(dtype, (swiglu_bwd_kernel<scalar_t><<<ew_grid(std::max(n8, n - 8 * n8)), 256, 0, st>>>(
                                (const scalar_t*)g, (const scalar_t*)a, (const scalar_t*)b, (scalar_t*)da,
-                               (scalar_t*)db, n)));
+                               (scalar_t*)db, n, n8)));
 }
 
 void rotary_apply(const void* x, const float* freqs, void* out, long long rows, int L, int H, int Dh,
