@@ -48,7 +48,7 @@ def parse():
     ap.add_argument("--seq-len", type=int, default=32768)
     ap.add_argument("--model", default="mega7B_32k")
     ap.add_argument("--layers", type=int, default=None, help="override depth (debugging only; marks the run invalid)")
-    ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "cublas"])
+    ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_1cta", "cublas"])
     ap.add_argument("--no-ckpt", action="store_true")
     return ap.parse_args()
 

@@ -10,8 +10,8 @@
 //
 // Layout: `rows` rows of length L2 with row stride `ld`; row index modulo L1 is
 // the query position.  The forward pass also writes zeros to the masked columns
-// up to the next multiple of 128, because the causal GEMMs that follow read
-// whole 128-wide diagonal blocks; columns further right are never read by them
+// up to the next multiple of 256, because the causal GEMMs that follow read
+// whole diagonal tiles of up to 256 rows; columns further right are never read by them
 // and are left untouched (they may hold uninitialised scores).
 #include "common.cuh"
 #include "kernels.h"
@@ -20,6 +20,7 @@ namespace mb {
 namespace {
 
 constexpr int kSmThreads = 256;
+constexpr int kCausalTile = 256;      // row extent of the largest GEMM tile that reads the diagonal blocks
 constexpr int kSmMaxPerThread = 32;   // rows up to 8192 columns
 
 // Philox4x32-10 counter-based generator (Salmon et al. 2011): 4 x 32 random bits per counter.
@@ -54,7 +55,7 @@ __global__ void attn_softmax_fwd_kernel(T* __restrict__ s, float* __restrict__ l
   const long long row = blockIdx.x;
   const int pos = (int)(row % L1);
   const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;      // visible columns
-  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;  // masked columns that must read as 0
+  const int zero_to = causal ? min(L2, ((n + kCausalTile - 1) / kCausalTile) * kCausalTile) : L2;  // masked columns that must read as 0
   T* sr = s + row * ld;
   float v[kSmMaxPerThread];
   float m = -INFINITY;
@@ -96,7 +97,7 @@ __global__ void attn_softmax_bwd_kernel(const T* __restrict__ p, T* __restrict__
   const long long row = blockIdx.x;
   const int pos = (int)(row % L1);
   const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
-  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  const int zero_to = causal ? min(L2, ((n + kCausalTile - 1) / kCausalTile) * kCausalTile) : L2;
   const T* pr = p + row * ld;
   T* dr = dp + row * ld;
   float pv[kSmMaxPerThread], gv[kSmMaxPerThread];
@@ -134,7 +135,7 @@ __global__ void attn_softmax_fwd_vec_kernel(T* __restrict__ s, float* __restrict
   const long long row = blockIdx.x;
   const int pos = (int)(row % L1);
   const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
-  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  const int zero_to = causal ? min(L2, ((n + kCausalTile - 1) / kCausalTile) * kCausalTile) : L2;
   T* sr = s + row * ld;
   float v[kSmVecPerThread][8];
   float m = -INFINITY;
@@ -191,7 +192,7 @@ __global__ void attn_softmax_bwd_vec_kernel(const T* __restrict__ p, T* __restri
   const long long row = blockIdx.x;
   const int pos = (int)(row % L1);
   const int n = causal ? max(0, min(L2, L2 - L1 + pos + 1)) : L2;
-  const int zero_to = causal ? min(L2, ((n + 127) / 128) * 128) : L2;
+  const int zero_to = causal ? min(L2, ((n + kCausalTile - 1) / kCausalTile) * kCausalTile) : L2;
   const T* pr = p + row * ld;
   T* dr = dp + row * ld;
   float pv[kSmVecPerThread][8], gv[kSmVecPerThread][8];

@@ -611,5 +611,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("p2p_send", &p2p_send);
   m.def("p2p_recv", &p2p_recv);
   m.def("peer_barrier", &peer_barrier);
+  m.def("gemm_set_cta_pairs", [](bool on) { mb::gemm_set_cta_pairs(on); });
+  m.def("gemm_pair_max_active_clusters", []() { return mb::gemm_pair_max_active_clusters(); });
   m.def("allreduce_sumsq", &allreduce_sumsq);
 }

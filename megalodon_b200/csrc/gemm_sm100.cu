@@ -24,6 +24,7 @@
 #include <cuda_fp16.h>
 #include <cuda_runtime.h>
 
+#include <cstdio>
 #include <mutex>
 
 #include "common.cuh"
@@ -374,6 +375,251 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
   }
 }
 
+// ---------------------------------------------------------------------- CTA-pair variant
+// Same roles and pipeline, but two CTAs of a 2-CTA cluster share one 256 x 256 output tile through
+// tcgen05.mma.cta_group::2: CTA r stages rows [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of
+// B, so each SM streams 32 KiB per k-block instead of 48 KiB and the ring is 6 stages deep.  The even
+// CTA issues the MMAs; every "stage consumed" and "accumulator ready" signal is committed once to
+// each CTA's barrier, and both CTAs' epilogue warps release the accumulator on the even CTA's barrier.
+constexpr int kPairStages = 6;
+constexpr int kPairBM = 256;      // rows of the pair's tile
+constexpr int kPairBN = 256;
+
+struct PairSmem {
+  static constexpr int a_bytes = BM * BK * 2;                 // this CTA's 128 rows of A
+  static constexpr int b_bytes = (kPairBN / 2) * BK * 2;      // this CTA's 128 rows of B
+  static constexpr int stage_bytes = a_bytes + b_bytes;       // 32 KiB
+  static constexpr int bar_offset = kPairStages * stage_bytes;
+  static constexpr int total = bar_offset + 256 + 1024;
+};
+
+__device__ __forceinline__ bool pair_tile_skipped(const GemmParams& p, int m0, int n0) {
+  return p.mode == 1 && n0 > m0 + kPairBM - 1;
+}
+
+__device__ __forceinline__ void pair_k_range(const GemmParams& p, int m0, int num_k, int& kb0, int& kb1) {
+  kb0 = 0;
+  kb1 = num_k;
+  if (p.mode == 2) kb1 = min(num_k, (m0 + kPairBM + BK - 1) / BK);
+  if (p.mode == 3) kb0 = min(num_k - 1, m0 / BK);
+}
+
+template <bool A_MN, bool B_MN, typename OutT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const __grid_constant__ GemmParams p, int in_fmt) {
+  using L = PairSmem;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::bar_offset);     // used in the even CTA only
+  uint64_t* empty_bar = full_bar + kPairStages;                               // one set per CTA
+  uint64_t* tmem_full = empty_bar + kPairStages;                              // one set per CTA
+  uint64_t* tmem_empty = tmem_full + 2;                                       // used in the even CTA only
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_holder + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();          // 0 = even CTA (issues the MMAs), 1 = its peer
+  const int pair = blockIdx.x >> 1;
+  const int num_pairs = gridDim.x >> 1;
+  const int num_m = (p.M + kPairBM - 1) / kPairBM;
+  const int num_n = (p.N + kPairBN - 1) / kPairBN;
+  const int tiles_per_batch = num_m * num_n;
+  const int num_tiles = tiles_per_batch * p.batch;
+  const int num_k = (p.K + BK - 1) / BK;
+  constexpr uint32_t kTmemCols = 2 * kPairBN;       // two accumulators of 256 columns
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kPairStages; ++i) {
+      mbar_init(full_bar + i, 2);                   // one arrive.expect_tx from each CTA's producer
+      mbar_init(empty_bar + i, 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(tmem_full + i, 1);
+      mbar_init(tmem_empty + i, 2 * kEpiWarps);     // epilogue warps of both CTAs
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc_pair(tmem_holder, kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                               // the peer's barriers exist before anything signals them
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (elect_one()) {
+      for (int i = 0; i < p.a_parts; ++i) prefetch_tmap(&tmaps_a.m[i]);
+      prefetch_tmap(&tmap_b);
+      const int kb_shift = p.a_parts > 1 ? p.a_first * (p.a_part_k / BK) : 0;
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int bz = tile / tiles_per_batch;
+        const int t = tile - bz * tiles_per_batch;
+        const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+        if (pair_tile_skipped(p, m0, n0)) continue;
+        const int my_m = m0 + (int)rank * BM;
+        const int my_n = n0 + (int)rank * (kPairBN / 2);
+        int kb0, kb1;
+        pair_k_range(p, m0, num_k, kb0, kb1);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
+          uint8_t* sa = smem + stage * L::stage_bytes;
+          uint8_t* sb = sa + L::a_bytes;
+          const uint32_t full0 = map_to_cta(smem_u32(full_bar + stage), 0);
+          mbar_expect_tx_cluster(full0, L::stage_bytes);
+          const int kbr = p.a_parts > 1 ? (kb + kb_shift) % num_k : kb;
+          const int k0 = kbr * BK;
+          const int part = p.a_parts > 1 ? k0 / p.a_part_k : 0;
+          const int ka = p.a_parts > 1 ? k0 - part * p.a_part_k : k0;
+          const CUtensorMap* tmap_a = &tmaps_a.m[part];
+          if constexpr (!A_MN) {
+            tma_load_3d_pair(sa, tmap_a, full0, ka, my_m, bz);
+          } else {
+#pragma unroll
+            for (int j = 0; j < BM / 64; ++j) tma_load_3d_pair(sa + j * 8192, tmap_a, full0, my_m + 64 * j, ka, bz);
+          }
+          if constexpr (!B_MN) {
+            tma_load_3d_pair(sb, &tmap_b, full0, k0, my_n, bz);
+          } else {
+#pragma unroll
+            for (int j = 0; j < kPairBN / 128; ++j)
+              tma_load_3d_pair(sb + j * 8192, &tmap_b, full0, my_n + 64 * j, k0, bz);
+          }
+          if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+        }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (rank == 0 && elect_one()) {
+      const uint32_t idesc = make_idesc_f16(kPairBM, kPairBN, in_fmt, A_MN ? 1 : 0, B_MN ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int bz = tile / tiles_per_batch;
+        const int t = tile - bz * tiles_per_batch;
+        const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+        if (pair_tile_skipped(p, m0, n0)) continue;
+        int kb0, kb1;
+        pair_k_range(p, m0, num_k, kb0, kb1);
+        if (!wait_or_abort(tmem_empty + acc, acc_phase ^ 1, abort_flag)) { ok = false; break; }
+        tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * kPairBN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!wait_or_abort(full_bar + stage, phase, abort_flag)) { ok = false; break; }
+          tcgen05_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * L::stage_bytes);
+          const uint32_t sb = sa + L::a_bytes;
+#pragma unroll
+          for (int kk = 0; kk < BK / UMMA_K; ++kk) {
+            const uint64_t da = A_MN ? make_smem_desc(sa + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sa + kk * 32, 16, 1024);
+            const uint64_t db = B_MN ? make_smem_desc(sb + kk * 2048, 8192, 1024)
+                                     : make_smem_desc(sb + kk * 32, 16, 1024);
+            umma_f16_pair(d_tmem, da, db, idesc, (kb != kb0 || kk != 0) ? 1u : 0u);
+          }
+          // the stage is reusable in both CTAs once these MMAs have read it
+          const uint32_t e = smem_u32(empty_bar + stage);
+          umma_commit_pair(e);
+          umma_commit_pair(map_to_cta(e, 1));
+          if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+        }
+        if (!ok) break;
+        const uint32_t f = smem_u32(tmem_full + acc);
+        umma_commit_pair(f);
+        umma_commit_pair(map_to_cta(f, 1));
+        if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+      }
+      if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const int quarter = warp & 3;
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    bool ok = true;
+    OutT* C = reinterpret_cast<OutT*>(p.C);
+    OutT* P = reinterpret_cast<OutT*>(p.preact);
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      const int bz = tile / tiles_per_batch;
+      const int t = tile - bz * tiles_per_batch;
+      const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+      if (pair_tile_skipped(p, m0, n0)) continue;
+      if (!wait_or_abort(tmem_full + acc, acc_phase, abort_flag)) { ok = false; break; }
+      tcgen05_fence_after();
+      const int row = m0 + (int)rank * BM + quarter * 32 + lane;
+      const uint32_t t_row = tmem_base + acc * kPairBN + ((uint32_t)(quarter * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < kPairBN / 32; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c * 32, r);
+        tmem_ld_wait();
+        const int col0 = n0 + c * 32;
+        if (col0 >= p.N) continue;            // warp-uniform
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
+        const int nvalid = min(32, p.N - col0);
+        if (p.bias != nullptr) {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            if (i < nvalid) {
+              float bv;
+              if (p.bias_dtype == kF32) bv = reinterpret_cast<const float*>(p.bias)[col0 + i];
+              else if (p.bias_dtype == kBF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col0 + i]);
+              else bv = __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + i]);
+              v[i] += bv;
+            }
+          }
+        }
+        if (row < p.M) {
+          if (p.c_nparts > 1) {
+            const int owner = col0 / p.c_part_cols;
+            OutT* slot = reinterpret_cast<OutT*>(p.c_parts[owner]);
+            store_row32<OutT>(slot + (long long)row * p.c_part_cols + (col0 - owner * p.c_part_cols), v, nvalid);
+          } else {
+            const long long off = (long long)bz * p.c_batch_stride + (long long)row * p.ldc + col0;
+            if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
+            if (p.act == 1) {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+            }
+            store_row32<OutT>(C + off, v, nvalid);
+          }
+        }
+      }
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
+      if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+    }
+    if (!ok && lane == 0) { *abort_flag = 1; atomicExch(p.err, 3); }
+  }
+
+  // Neither CTA may leave (or free tensor memory) while the other can still signal its barriers,
+  // read its shared memory or write its accumulator.
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
 // ---------------------------------------------------------------------- host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
@@ -401,15 +647,28 @@ bool make_tmap_3d(CUtensorMap* out, const void* base, long long inner, long long
                   long long row_stride, long long batch_stride, int box_inner, int box_outer, int elem_dtype) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) return false;
+  // The encoder is a driver entry point and needs a current context; a thread that has made no
+  // runtime call yet (the autograd engine's worker on its first backward) has none bound.
+  static thread_local bool context_bound = false;
+  if (!context_bound) {
+    cudaFree(nullptr);
+    context_bound = true;
+  }
   if (batch <= 1) batch_stride = row_stride * outer;      // unused, but must be a valid stride
   const cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)(batch < 1 ? 1 : batch)};
   const cuuint64_t strides[2] = {(cuuint64_t)row_stride * 2, (cuuint64_t)batch_stride * 2};
   const cuuint32_t box[3] = {(cuuint32_t)box_inner, (cuuint32_t)box_outer, 1};
   const cuuint32_t estr[3] = {1, 1, 1};
   const CUtensorMapDataType dt = elem_dtype == kBF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  return fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  const CUresult res = fn(out, dt, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (res != CUDA_SUCCESS)
+    fprintf(stderr,
+            "tensor map encode failed (CUresult %d): base %p dims {%llu, %llu, %llu} strides {%llu, %llu} B box {%u, %u}\n",
+            (int)res, base, (unsigned long long)dims[0], (unsigned long long)dims[1], (unsigned long long)dims[2],
+            (unsigned long long)strides[0], (unsigned long long)strides[1], box[0], box[1]);
+  return res == CUDA_SUCCESS;
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
@@ -427,6 +686,25 @@ static int launch_gemm(const TmapArray& ta, const CUtensorMap& tb, const GemmPar
   kern<<<grid, kGemmThreads, L::total, st>>>(ta, tb, p, in_fmt);
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
+
+template <bool A_MN, bool B_MN, typename OutT>
+static int launch_gemm_pair(const TmapArray& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt, int sms,
+                            cudaStream_t st) {
+  using L = PairSmem;
+  auto kern = gemm_tcgen05_pair_kernel<A_MN, B_MN, OutT>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total) != cudaSuccess) return -2;
+    configured = true;
+  }
+  const int tiles = ((p.M + kPairBM - 1) / kPairBM) * ((p.N + kPairBN - 1) / kPairBN) * p.batch;
+  const int pairs = sms / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, kGemmThreads, L::total, st>>>(ta, tb, p, in_fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
+static bool g_use_pair = true;
 
 // Returns 0 on success, negative on a host-side failure.  `err` is a device int
 // that the kernel sets non-zero if one of its bounded waits gives up.
@@ -467,10 +745,26 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
     if (p.c_part_cols % 32 != 0) return -7;
     for (int i = 0; i < p.c_nparts; ++i) p.c_parts[i] = peers->c_ptrs[i];
   }
+  const bool pair = g_use_pair && M > BM && num_sms >= 2;
+  if (!ok) return -41;
   ok = ok && (b_mn ? make_tmap_3d(&tb, B, N, K, batch, ldb, b_bs, 64, 64, in_dtype)
-                   : make_tmap_3d(&tb, B, K, N, batch, ldb, b_bs, BK, BN, in_dtype));
+                   : make_tmap_3d(&tb, B, K, N, batch, ldb, b_bs, BK, pair ? kPairBN / 2 : BN, in_dtype));
   if (!ok) return -4;
   const int fmt = in_dtype == kBF16 ? 1 : 0;
+  if (pair) {
+#define GEMM_PAIR_CASE(AMN, BMN)                                                                        \
+  if (a_mn == AMN && b_mn == BMN) {                                                                     \
+    if (out_dtype == kBF16) return launch_gemm_pair<AMN, BMN, __nv_bfloat16>(ta, tb, p, fmt, num_sms, st); \
+    if (out_dtype == kF16) return launch_gemm_pair<AMN, BMN, __half>(ta, tb, p, fmt, num_sms, st);      \
+    return launch_gemm_pair<AMN, BMN, float>(ta, tb, p, fmt, num_sms, st);                              \
+  }
+    GEMM_PAIR_CASE(false, false)
+    GEMM_PAIR_CASE(false, true)
+    GEMM_PAIR_CASE(true, true)
+    GEMM_PAIR_CASE(true, false)
+#undef GEMM_PAIR_CASE
+    return -5;
+  }
 #define GEMM_CASE(AMN, BMN)                                                                              \
   if (a_mn == AMN && b_mn == BMN) {                                                                      \
     if (out_dtype == kBF16) return launch_gemm<256, AMN, BMN, __nv_bfloat16>(ta, tb, p, fmt, num_sms, st); \
@@ -483,6 +777,28 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
   GEMM_CASE(true, false)
 #undef GEMM_CASE
   return -5;
+}
+
+void gemm_set_cta_pairs(bool on) { g_use_pair = on; }
+
+// How many CTA pairs of the pair kernel the device can hold at once (diagnostic).
+int gemm_pair_max_active_clusters() {
+  auto kern = gemm_tcgen05_pair_kernel<false, false, __nv_bfloat16>;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, PairSmem::total) != cudaSuccess) return -1;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(148, 1, 1);
+  cfg.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg.dynamicSmemBytes = PairSmem::total;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  int n = -1;
+  if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) return -2;
+  return n;
 }
 
 }  // namespace mb

@@ -39,8 +39,13 @@ def _bump(n: int = 1) -> None:
 
 
 def set_gemm_backend(name: str) -> None:
-    """"tcgen05": this framework's kernel; "cublas": torch.matmul (baseline only)."""
-    assert name in ("tcgen05", "cublas")
+    """"tcgen05": this framework's kernel (CTA pairs, 256 x 256 tiles, for more than 128 rows);
+    "tcgen05_1cta": the same kernel family restricted to single-CTA 128 x 256 tiles;
+    "cublas": torch.matmul (baseline only)."""
+    assert name in ("tcgen05", "tcgen05_1cta", "cublas")
+    if name.startswith("tcgen05"):
+        require().gemm_set_cta_pairs(name == "tcgen05")
+        name = "tcgen05"
     _GEMM_BACKEND[0] = name
 
 
