@@ -345,7 +345,7 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
                                             const OptTensor& bias, int64_t act, bool a_mn, bool b_mn,
                                             bool want_preact, int64_t out_dtype_code, int64_t mode, double alpha,
                                             Tensor& err, const std::vector<int64_t>& a_part_ptrs, int64_t a_first,
-                                            const std::vector<int64_t>& c_part_ptrs) {
+                                            const std::vector<int64_t>& c_part_ptrs, bool accumulate) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "operands must be CUDA tensors");
   c10::cuda::CUDAGuard guard(A.device());
   TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && A.dim() == B.dim(), "operands must both be 2-D or both 3-D");
@@ -402,7 +402,8 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
                                        (int)act, M, N, K, A.stride(-2), B.stride(-2), C.stride(-2), a_mn, b_mn,
                                        (int)mode, (float)alpha, batch, a_bs, b_bs, c_bs, dtype_code(A),
                                        (int)out_dtype_code, err.data_ptr<int>(), sms, stream(),
-                                       (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr);
+                                       (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr,
+                                       accumulate && out.has_value());
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
 }
@@ -598,7 +599,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("out"), py::arg("bias"), py::arg("act"), py::arg("a_mn"),
         py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
-        py::arg("c_part_ptrs") = std::vector<int64_t>());
+        py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
   m.def("time_sums", &time_sums);

@@ -70,6 +70,7 @@ struct GemmParams {
   long long ldc;       // elements
   int mode;            // 0 dense, 1..3 see above
   float alpha;         // C = alpha * acc (+ bias)
+  int accumulate;      // 1: C += alpha * acc (+ bias); the old C is read in the epilogue
   int batch;           // independent problems sharing shapes (tensor maps carry their strides)
   long long c_batch_stride;   // elements between consecutive C (and preact) matrices
   // all-gather -> GEMM: A is the concatenation along K of `a_parts` pieces of `a_part_k` columns, piece i
@@ -173,6 +174,22 @@ __device__ __forceinline__ void store_row32<float>(float* dst, const float (&v)[
       reinterpret_cast<float4*>(dst)[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
   } else {
     for (int i = 0; i < nvalid; ++i) dst[i] = v[i];
+  }
+}
+
+// v[i] += dst[i] for the first nvalid of 32 consecutive elements (accumulating epilogue)
+template <typename OutT>
+__device__ __forceinline__ void add_row32(const OutT* src, float (&v)[32], int nvalid) {
+  if (nvalid >= 32) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      float t[8];
+      load8(src + 8 * i, t);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v[8 * i + j] += t[j];
+    }
+  } else {
+    for (int i = 0; i < nvalid; ++i) v[i] += to_f(src[i]);
   }
 }
 
@@ -350,6 +367,7 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
             store_row32<OutT>(slot + (long long)row * p.c_part_cols + (col0 - owner * p.c_part_cols), v, nvalid);
           } else {
             const long long off = (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0;
+            if (p.accumulate) add_row32<OutT>(C + off, v, nvalid);
             if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
             if (p.act == 1) {
 #pragma unroll
@@ -592,6 +610,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
             store_row32<OutT>(slot + (long long)row * p.c_part_cols + (col0 - owner * p.c_part_cols), v, nvalid);
           } else {
             const long long off = (long long)bz * p.c_batch_stride + (long long)row * p.ldc + col0;
+            if (p.accumulate) add_row32<OutT>(C + off, v, nvalid);
             if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
             if (p.act == 1) {
 #pragma unroll
@@ -712,7 +731,7 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
-                      const GemmPeerSpec* peers) {
+                      const GemmPeerSpec* peers, bool accumulate) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA wants 16-byte strides; the vectorised epilogue wants 16-byte aligned rows of C
   if (lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return -1;
@@ -724,6 +743,7 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
   p.M = M; p.N = N; p.K = K; p.C = C; p.preact = preact; p.bias = bias; p.bias_dtype = bias_dtype; p.act = act;
   p.err = err; p.ldc = ldc; p.mode = mode; p.alpha = alpha; p.batch = batch; p.c_batch_stride = c_bs;
   p.a_parts = 1; p.a_part_k = K; p.a_first = 0; p.c_nparts = 1; p.c_part_cols = N;
+  p.accumulate = accumulate ? 1 : 0;
   bool ok = true;
   if (peers != nullptr && peers->a_parts > 1) {
     // gathered A: K-major pieces [M, K / parts] living on different GPUs

@@ -84,7 +84,7 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
-                      const GemmPeerSpec* peers = nullptr);
+                      const GemmPeerSpec* peers = nullptr, bool accumulate = false);
 // Whether GEMMs with more than 128 rows run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); on by default.
 void gemm_set_cta_pairs(bool on);
 int gemm_pair_max_active_clusters();

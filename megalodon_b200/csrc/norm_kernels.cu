@@ -6,6 +6,8 @@
 // `weight[j] + weight_offset` evaluated in fp32 (the modules store zero-centred
 // weights and pass offset 1), which keeps small weights exact under bf16
 // parameters.  Statistics are fp32; `rstd` (and `mean`) are saved for backward.
+#include <initializer_list>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -141,9 +143,205 @@ __global__ void norm_bwd_kernel(const T* __restrict__ dy, const T* __restrict__ 
   }
 }
 
+// ---------------------------------------------------------------- 16-byte variants
+// A row lives in registers: thread t of the ROW_THREADS that share a row owns the 8-element groups
+// t, t + ROW_THREADS, ... (at most VPT of them), so x and dy are read once and every access is 16
+// bytes (two for fp32).  Needs D % 8 == 0, D <= ROW_THREADS * 8 * VPT and 32-byte aligned pointers.
+constexpr int kMaxVecVPT = 4;
+
+template <typename T, typename W, bool LAYER, int ROW_THREADS, int kVecVPT>
+__global__ void norm_fwd_vec_kernel(const T* __restrict__ x, const W* __restrict__ weight,
+                                    const W* __restrict__ bias, float weight_offset, T* __restrict__ y,
+                                    float* __restrict__ mean_out, float* __restrict__ rstd_out, long long M,
+                                    int D, float eps) {
+  __shared__ float scratch[32];
+  const int rows_per_cta = blockDim.x / ROW_THREADS;
+  const int sub = threadIdx.x / ROW_THREADS;
+  const int t = threadIdx.x % ROW_THREADS;
+  const int nvec = D / 8;
+  for (long long row = (long long)blockIdx.x * rows_per_cta + sub; row < M + sub;
+       row += (long long)gridDim.x * rows_per_cta) {
+    const bool live = row < M;
+    const T* xr = x + (live ? row : 0) * D;
+    float v[kVecVPT][8];
+    float s = 0.f, ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (live && g < nvec) {
+        load8(xr + 8 * g, v[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          s += v[i][j];
+          ss = fmaf(v[i][j], v[i][j], ss);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[i][j] = 0.f;
+      }
+    }
+    float mean = 0.f, var;
+    if constexpr (LAYER) {
+      s = row_sum<ROW_THREADS>(s, scratch);
+      mean = s / D;
+      float sq = 0.f;
+#pragma unroll
+      for (int i = 0; i < kVecVPT; ++i) {
+        if (t + i * ROW_THREADS < nvec) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float d = v[i][j] - mean;
+            sq = fmaf(d, d, sq);
+          }
+        }
+      }
+      var = row_sum<ROW_THREADS>(live ? sq : 0.f, scratch) / D;
+    } else {
+      var = row_sum<ROW_THREADS>(ss, scratch) / D;
+    }
+    if (!live) continue;
+    const float rstd = rsqrtf(var + eps);
+    T* yr = y + row * D;
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (g < nvec) {
+        float o[8], w[8], b[8];
+        if (weight != nullptr) load8(weight + 8 * g, w);
+        if (LAYER && bias != nullptr) load8(bias + 8 * g, b);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          float r = (v[i][j] - mean) * rstd;
+          if (weight != nullptr) r *= w[j] + weight_offset;
+          if (LAYER && bias != nullptr) r += b[j];
+          o[j] = r;
+        }
+        store8(yr + 8 * g, o);
+      }
+    }
+    if (t == 0) {
+      rstd_out[row] = rstd;
+      if (LAYER) mean_out[row] = mean;
+    }
+  }
+}
+
+template <typename T, typename W, bool LAYER, int ROW_THREADS, int kVecVPT>
+__global__ void norm_bwd_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                    const W* __restrict__ weight, float weight_offset,
+                                    const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
+                                    T* __restrict__ dx, float* __restrict__ dweight, float* __restrict__ dbias,
+                                    long long M, int D) {
+  __shared__ float scratch[32];
+  const int rows_per_cta = blockDim.x / ROW_THREADS;
+  const int sub = threadIdx.x / ROW_THREADS;
+  const int t = threadIdx.x % ROW_THREADS;
+  const int nvec = D / 8;
+  float acc_w[kVecVPT][8], acc_b[kVecVPT][8], w[kVecVPT][8];
+#pragma unroll
+  for (int i = 0; i < kVecVPT; ++i) {
+    const int g = t + i * ROW_THREADS;
+    if (weight != nullptr && g < nvec) {
+      load8(weight + 8 * g, w[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[i][j] += weight_offset;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) w[i][j] = 1.f;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc_w[i][j] = acc_b[i][j] = 0.f;
+  }
+  for (long long row = (long long)blockIdx.x * rows_per_cta + sub; row < M + sub;
+       row += (long long)gridDim.x * rows_per_cta) {
+    const bool live = row < M;
+    const long long r = live ? row : 0;
+    const float rstd = rstd_in[r];
+    const float mean = LAYER ? mean_in[r] : 0.f;
+    float g8[kVecVPT][8], xh[kVecVPT][8];
+    float c1 = 0.f, c2 = 0.f;
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (live && g < nvec) {
+        load8(dy + r * D + 8 * g, g8[i]);
+        load8(x + r * D + 8 * g, xh[i]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          xh[i][j] = (xh[i][j] - mean) * rstd;
+          const float gw = g8[i][j] * w[i][j];
+          c1 = fmaf(gw, xh[i][j], c1);
+          c2 += gw;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g8[i][j] = xh[i][j] = 0.f;
+      }
+    }
+    c1 = row_sum<ROW_THREADS>(c1, scratch) / D;
+    if constexpr (LAYER) c2 = row_sum<ROW_THREADS>(c2, scratch) / D; else c2 = 0.f;
+    if (!live) continue;
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (g < nvec) {
+        float o[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = rstd * (g8[i][j] * w[i][j] - xh[i][j] * c1 - c2);
+          acc_w[i][j] = fmaf(g8[i][j], xh[i][j], acc_w[i][j]);
+          acc_b[i][j] += g8[i][j];
+        }
+        store8(dx + row * D + 8 * g, o);
+      }
+    }
+  }
+  if (dweight != nullptr) {
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (g < nvec) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          atomicAdd(dweight + 8 * g + j, acc_w[i][j]);
+          if (LAYER && dbias != nullptr) atomicAdd(dbias + 8 * g + j, acc_b[i][j]);
+        }
+      }
+    }
+  }
+}
+
+// smallest number of 8-element groups per thread that covers a row of D elements
+#define VPT_SWITCH(D, ROW_THREADS, ...)                                       \
+  do {                                                                        \
+    if ((D) <= (ROW_THREADS) * 8) { constexpr int VPT = 1; __VA_ARGS__; }     \
+    else if ((D) <= (ROW_THREADS) * 16) { constexpr int VPT = 2; __VA_ARGS__; } \
+    else { constexpr int VPT = 4; __VA_ARGS__; }                              \
+  } while (0)
+
+inline bool vec_ok(int D, int row_threads, std::initializer_list<const void*> ptrs) {
+  if (D % 8 != 0 || D > row_threads * 8 * kMaxVecVPT) return false;
+  for (const void* q : ptrs)
+    if (q != nullptr && !aligned32(q)) return false;
+  return true;
+}
+
 template <typename T, typename W, bool LAYER>
 void launch_fwd(const void* x, const void* w, const void* b, float off, void* y, float* mean, float* rstd,
                 long long M, int D, float eps, cudaStream_t st) {
+  if (D <= 1024 && vec_ok(D, 32, {x, w, b, y})) {
+    const int threads = 128, rows = threads / 32;
+    const int grid = (int)std::min<long long>((M + rows - 1) / rows, 148LL * 16);
+    VPT_SWITCH(D, 32, (norm_fwd_vec_kernel<T, W, LAYER, 32, VPT><<<grid, threads, 0, st>>>(
+                           (const T*)x, (const W*)w, (const W*)b, off, (T*)y, mean, rstd, M, D, eps)));
+    return;
+  }
+  if (D > 1024 && vec_ok(D, 256, {x, w, b, y})) {
+    const int grid = (int)std::min<long long>(M, 148LL * 8);
+    VPT_SWITCH(D, 256, (norm_fwd_vec_kernel<T, W, LAYER, 256, VPT><<<grid, 256, 0, st>>>(
+                            (const T*)x, (const W*)w, (const W*)b, off, (T*)y, mean, rstd, M, D, eps)));
+    return;
+  }
   if (D <= 1024) {
     const int threads = 128, rows = threads / 32;
     const int grid = (int)std::min<long long>((M + rows - 1) / rows, 148LL * 16);
@@ -160,6 +358,19 @@ void launch_fwd(const void* x, const void* w, const void* b, float off, void* y,
 template <typename T, typename W, bool LAYER>
 void launch_bwd(const void* dy, const void* x, const void* w, float off, const float* mean,
                 const float* rstd, void* dx, float* dw, float* db, long long M, int D, cudaStream_t st) {
+  if (D <= 1024 && vec_ok(D, 32, {dy, x, w, dx})) {
+    const int threads = 128, rows = threads / 32;
+    const int grid = (int)std::min<long long>((M + rows - 1) / rows, 148LL * 4);
+    VPT_SWITCH(D, 32, (norm_bwd_vec_kernel<T, W, LAYER, 32, VPT><<<grid, threads, 0, st>>>(
+                           (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D)));
+    return;
+  }
+  if (D > 1024 && vec_ok(D, 256, {dy, x, w, dx})) {
+    const int grid = (int)std::min<long long>(M, 148LL * 4);
+    VPT_SWITCH(D, 256, (norm_bwd_vec_kernel<T, W, LAYER, 256, VPT><<<grid, 256, 0, st>>>(
+                            (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D)));
+    return;
+  }
   if (D <= 1024) {
     const int threads = 128, rows = threads / 32;
     const int grid = (int)std::min<long long>((M + rows - 1) / rows, 148LL * 4);

@@ -23,6 +23,8 @@
 #include "common.cuh"
 #include "kernels.h"
 
+#include <initializer_list>
+
 namespace mb {
 namespace {
 
@@ -406,6 +408,190 @@ __global__ void tsn_bwd_apply_kernel(const T* __restrict__ dy, const T* __restri
   }
 }
 
+// ---------------------------------------------------------------- 16-byte variants of the four
+// kernels that touch the activations.  A group of Dg features is read by VL = Dg / 8 adjacent lanes,
+// one 8-element vector each, kept in registers (x is read once); needs Dg % 8 == 0, VL a power of
+// two <= 32 and 32-byte aligned pointers.
+template <typename T, int VL>
+__global__ void tsn_group_stats_vec_kernel(const T* __restrict__ x, float* __restrict__ gu, float* __restrict__ gv,
+                                           long long ngroups) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long grp = gid / VL;
+  const int l = (int)(gid % VL);
+  const bool live = grp < ngroups;
+  float v[8];
+  float s = 0.f;
+  if (live) {
+    load8(x + (grp * VL + l) * 8, v);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) s += v[j];
+  }
+  s = subwarp_sum<VL>(s);
+  const float mean = s / (VL * 8);
+  float q = 0.f;
+  if (live) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float d = v[j] - mean;
+      q = fmaf(d, d, q);
+    }
+  }
+  q = subwarp_sum<VL>(q);
+  if (live && l == 0) {
+    gu[grp] = mean;
+    gv[grp] = q / (VL * 8);
+  }
+}
+
+template <typename T, typename W>
+__global__ void tsn_apply_vec_kernel(const T* __restrict__ x, const float* __restrict__ cummean,
+                                     const float* __restrict__ cumrstd, const W* __restrict__ gamma,
+                                     float gamma_offset, const W* __restrict__ beta, const bool* __restrict__ mask,
+                                     T* __restrict__ y, long long rows, int H, int G) {
+  const int Dg = H / G;
+  const int hv = H / 8;
+  const long long total = rows * hv;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / hv;
+    const int j0 = (int)(i - row * hv) * 8;
+    float o[8];
+    if (mask && mask[row]) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = 0.f;
+    } else {
+      const long long sg = row * G + j0 / Dg;
+      const float u = cummean[sg], r = cumrstd[sg];
+      float xv[8], gm[8], bt[8];
+      load8(x + row * H + j0, xv);
+      load8(gamma + j0, gm);
+      load8(beta + j0, bt);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = fmaf((xv[j] - u) * r, gm[j] + gamma_offset, bt[j]);
+    }
+    store8(y + row * H + j0, o);
+  }
+}
+
+template <typename T, typename W, int VL>
+__global__ void tsn_group_grads_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                           const float* __restrict__ cummean, const W* __restrict__ gamma,
+                                           float gamma_offset, float* __restrict__ ux, float* __restrict__ ds,
+                                           float* __restrict__ db, long long ngroups, int G) {
+  const long long gid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long grp = gid / VL;
+  const int l = (int)(gid % VL);
+  const bool live = grp < ngroups;
+  float sx = 0.f, s1 = 0.f, s2 = 0.f;
+  if (live) {
+    const int g = (int)(grp % G);
+    const float u = cummean[grp];
+    float xv[8], gy[8], gm[8];
+    load8(x + (grp * VL + l) * 8, xv);
+    load8(dy + (grp * VL + l) * 8, gy);
+    load8(gamma + ((long long)g * VL + l) * 8, gm);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gw = gy[j] * (gm[j] + gamma_offset);
+      sx += xv[j];
+      s1 = fmaf(gw, xv[j] - u, s1);
+      s2 += gw;
+    }
+  }
+  sx = subwarp_sum<VL>(sx);
+  s1 = subwarp_sum<VL>(s1);
+  s2 = subwarp_sum<VL>(s2);
+  if (live && l == 0) {
+    ux[grp] = sx / (VL * 8);
+    ds[grp] = s1;
+    db[grp] = s2;
+  }
+}
+
+// One CTA walks a strip of rows; thread t owns the 8-element column groups t, t + 256, ... (VPT of them)
+template <typename T, typename W, int VPT>
+__global__ void tsn_bwd_apply_vec_kernel(const T* __restrict__ dy, const T* __restrict__ x,
+                                         const float* __restrict__ cummean, const float* __restrict__ cumrstd,
+                                         const float* __restrict__ ux, const float* __restrict__ dux,
+                                         const float* __restrict__ dvx, const W* __restrict__ gamma,
+                                         float gamma_offset, const bool* __restrict__ mask, T* __restrict__ dx,
+                                         float* __restrict__ dgamma, float* __restrict__ dbeta, long long rows,
+                                         int H, int G) {
+  const int Dg = H / G;
+  const int hv = H / 8;
+  const float inv_d = 1.f / Dg;
+  float acc_g[VPT][8], acc_b[VPT][8], gm[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * kBwdThreads;
+    if (c < hv) {
+      load8(gamma + c * 8, gm[i]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gm[i][j] += gamma_offset;
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc_g[i][j] = acc_b[i][j] = 0.f;
+  }
+  for (long long row = blockIdx.x; row < rows; row += gridDim.x) {
+    const bool pad = mask && mask[row];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * kBwdThreads;
+      if (c >= hv) continue;
+      const long long e = row * H + c * 8;
+      float o[8];
+      if (pad) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = 0.f;
+      } else {
+        const long long sg = row * G + (c * 8) / Dg;
+        const float r = cumrstd[sg], u = cummean[sg], uxv = ux[sg];
+        const float a = dux[sg] * inv_d, b2 = 2.f * dvx[sg] * inv_d;
+        float gy[8], xv[8];
+        load8(dy + e, gy);
+        load8(x + e, xv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          o[j] = fmaf(gy[j] * r, gm[i][j], fmaf(b2, xv[j] - uxv, a));
+          acc_g[i][j] = fmaf(gy[j] * r, xv[j] - u, acc_g[i][j]);
+          acc_b[i][j] += gy[j];
+        }
+      }
+      store8(dx + e, o);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * kBwdThreads;
+    if (c < hv) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        atomicAdd(dgamma + c * 8 + j, acc_g[i][j]);
+        atomicAdd(dbeta + c * 8 + j, acc_b[i][j]);
+      }
+    }
+  }
+}
+
+inline bool tsn_vec_ok(int H, int G, std::initializer_list<const void*> ptrs) {
+  const int Dg = H / G;
+  const int vl = Dg / 8;
+  if (Dg % 8 != 0 || vl > 32 || (vl & (vl - 1)) != 0 || H > kBwdThreads * 8 * 4) return false;
+  for (const void* q : ptrs)
+    if (q != nullptr && !aligned32(q)) return false;
+  return true;
+}
+
+#define VL_SWITCH(vl, ...)                                   \
+  switch (vl) {                                              \
+    case 1: { constexpr int VL = 1; __VA_ARGS__; } break;    \
+    case 2: { constexpr int VL = 2; __VA_ARGS__; } break;    \
+    case 4: { constexpr int VL = 4; __VA_ARGS__; } break;    \
+    case 8: { constexpr int VL = 8; __VA_ARGS__; } break;    \
+    case 16: { constexpr int VL = 16; __VA_ARGS__; } break;  \
+    default: { constexpr int VL = 32; __VA_ARGS__; } break;  \
+  }
+
 int pick_lpg(int Dg) {
   int l = 1;
   while (l * 2 <= Dg && l < 32) l *= 2;
@@ -446,10 +632,18 @@ void timestep_norm_fwd(const void* x, const long long* prev_count, const void* p
   const long long rows = (long long)B * L;
   const int lpg = pick_lpg(H / G);
   TSN_DISPATCH(x_dtype, w_dtype, {
-    LPG_SWITCH(lpg, {
-      const long long threads = rows * G * LPG;
-      tsn_group_stats_kernel<T, LPG><<<div_up(threads, 256), 256, 0, st>>>((const T*)x, gu, gv, rows, H, G);
-    });
+    const bool vec = tsn_vec_ok(H, G, {x, y, gamma, beta});
+    if (vec) {
+      VL_SWITCH(H / G / 8, {
+        const long long threads = rows * G * VL;
+        tsn_group_stats_vec_kernel<T, VL><<<div_up(threads, 256), 256, 0, st>>>((const T*)x, gu, gv, rows * G);
+      });
+    } else {
+      LPG_SWITCH(lpg, {
+        const long long threads = rows * G * LPG;
+        tsn_group_stats_kernel<T, LPG><<<div_up(threads, 256), 256, 0, st>>>((const T*)x, gu, gv, rows, H, G);
+      });
+    }
     const int nseg = tsn_num_segments(L);
     const long long nsg = (long long)B * nseg * G;
     tsn_seg_sums_kernel<<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, B, L, G, nseg);
@@ -459,9 +653,15 @@ void timestep_norm_fwd(const void* x, const long long* prev_count, const void* p
     tsn_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, (const T*)prev_mean,
                                                             (const T*)prev_var, cummean, cumrstd, B, L, G, nseg,
                                                             eps);
-    const int grid = (int)std::min<long long>(div_up(rows * H, 256), 148LL * 16);
-    tsn_apply_kernel<T, W><<<grid, 256, 0, st>>>((const T*)x, cummean, cumrstd, (const W*)gamma,
-                                                 gamma_offset, (const W*)beta, mask, (T*)y, rows, H, G);
+    if (vec) {
+      const int grid = (int)std::min<long long>(div_up(rows * (H / 8), 256), 148LL * 16);
+      tsn_apply_vec_kernel<T, W><<<grid, 256, 0, st>>>((const T*)x, cummean, cumrstd, (const W*)gamma,
+                                                       gamma_offset, (const W*)beta, mask, (T*)y, rows, H, G);
+    } else {
+      const int grid = (int)std::min<long long>(div_up(rows * H, 256), 148LL * 16);
+      tsn_apply_kernel<T, W><<<grid, 256, 0, st>>>((const T*)x, cummean, cumrstd, (const W*)gamma,
+                                                   gamma_offset, (const W*)beta, mask, (T*)y, rows, H, G);
+    }
   });
 }
 
@@ -474,11 +674,20 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
   const long long rows = (long long)B * L;
   const int lpg = pick_lpg(H / G);
   TSN_DISPATCH(x_dtype, w_dtype, {
-    LPG_SWITCH(lpg, {
-      const long long threads = rows * G * LPG;
-      tsn_group_grads_kernel<T, W, LPG><<<div_up(threads, 256), 256, 0, st>>>(
-          (const T*)dy, (const T*)x, cummean, (const W*)gamma, gamma_offset, ux, ds, db, rows, H, G);
-    });
+    const bool vec = tsn_vec_ok(H, G, {dy, x, dx, gamma});
+    if (vec) {
+      VL_SWITCH(H / G / 8, {
+        const long long threads = rows * G * VL;
+        tsn_group_grads_vec_kernel<T, W, VL><<<div_up(threads, 256), 256, 0, st>>>(
+            (const T*)dy, (const T*)x, cummean, (const W*)gamma, gamma_offset, ux, ds, db, rows * G, G);
+      });
+    } else {
+      LPG_SWITCH(lpg, {
+        const long long threads = rows * G * LPG;
+        tsn_group_grads_kernel<T, W, LPG><<<div_up(threads, 256), 256, 0, st>>>(
+            (const T*)dy, (const T*)x, cummean, (const W*)gamma, gamma_offset, ux, ds, db, rows, H, G);
+      });
+    }
     const int nseg = tsn_num_segments(L);
     const long long nsg = (long long)B * nseg * G;
     if (mask != nullptr) tsn_cumvalid_kernel<<<div_up(B, 32), 32, 0, st>>>(mask, cumvalid, B, L);
@@ -491,6 +700,21 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
     tsn_bwd_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
                                                                 seg_scratch, dux, dvx, B, L, G, nseg);
     const int grid = (int)std::min<long long>(rows, 148LL * 4);
+    if (vec) {
+      const int hv = H / 8;
+      if (hv <= kBwdThreads)
+        tsn_bwd_apply_vec_kernel<T, W, 1><<<grid, kBwdThreads, 0, st>>>(
+            (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
+            dgamma, dbeta, rows, H, G);
+      else if (hv <= 2 * kBwdThreads)
+        tsn_bwd_apply_vec_kernel<T, W, 2><<<grid, kBwdThreads, 0, st>>>(
+            (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
+            dgamma, dbeta, rows, H, G);
+      else
+        tsn_bwd_apply_vec_kernel<T, W, 4><<<grid, kBwdThreads, 0, st>>>(
+            (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
+            dgamma, dbeta, rows, H, G);
+    } else
     tsn_bwd_apply_kernel<T, W><<<grid, kBwdThreads, 0, st>>>((const T*)dy, (const T*)x, cummean, cumrstd, ux, dux,
                                                      dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
                                                      dgamma, dbeta, rows, H, G);

@@ -77,8 +77,9 @@ def _tma_ok(t: Tensor) -> bool:
 def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str] = None, *,
          a_mn: bool = False, b_mn: bool = False, want_preact: bool = False,
          out_dtype: Optional[torch.dtype] = None, out: Optional[Tensor] = None, mode: int = 0,
-         alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None):
-    """C = act(alpha * A B^T + bias).  `a_mn` / `b_mn`: operand is stored [K, rows].
+         alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None, accumulate: bool = False):
+    """C = act(alpha * A B^T + bias), or with `accumulate` (needs `out`) C += alpha * A B^T + bias.
+    `a_mn` / `b_mn`: operand is stored [K, rows].
     Operands may be 2-D or 3-D (batched) strided views with a contiguous last
     dim.  `mode` 1..3 exploits causal structure (see gemm_sm100.cu).  Returns
     (C, preact | None)."""
@@ -109,12 +110,16 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
         if mode == 1:       # the kernel leaves tiles above the diagonal unwritten; nothing reads them
             pass
         if out is not None:
-            out.copy_(res)
+            if accumulate:
+                out.add_(res.to(out.dtype))
+            else:
+                out.copy_(res)
             res = out
         return res.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
     _bump()
     res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
-                             _DT[out_dtype], mode, alpha, _err_flag(a.device))
+                             _DT[out_dtype], mode, alpha, _err_flag(a.device),
+                             accumulate=bool(accumulate and out is not None))
     if rc != 0:
         raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
     return res, pre
@@ -127,6 +132,7 @@ class _Linear(torch.autograd.Function):
         need_pre = act is not None and any(ctx.needs_input_grad[:3])
         y, pre = gemm(x2, w, b, act, want_preact=need_pre)
         ctx.save_for_backward(x2, w, pre if pre is not None else torch.empty(0, device=x.device))
+        ctx.wgrad_sink = getattr(w, "_wgrad_sink", None)
         ctx.has_bias = b is not None
         ctx.act = act
         ctx.x_shape = x.shape
@@ -144,7 +150,15 @@ class _Linear(torch.autograd.Function):
             dx, _ = gemm(g, w, None, None, b_mn=True)          # [M, N] x [N, K] -> [M, K]
             dx = dx.view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
-            dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)   # [M, N]^T x [M, K] -> [N, K]
+            # A weight that is a view into an FSDP unit's flat buffer carries the matching view of the
+            # unit's flat gradient: the weight gradient is accumulated there by the GEMM epilogue and
+            # nothing is handed to autograd (no per-parameter tensor, no concatenation, no add).
+            sink = ctx.wgrad_sink
+            target = sink() if sink is not None else None
+            if target is not None and target.dtype == g.dtype:
+                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=True)
+            else:
+                dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)   # [M, N]^T x [M, K] -> [N, K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
             db = g.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
         return dx, dw, db, None

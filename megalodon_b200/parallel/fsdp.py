@@ -20,9 +20,14 @@ Design of one unit
   wrapped module *views* of it, run, optionally free the full buffer
   (`reshard_after_forward`).  The storage is resized in place so views and
   tensors saved for backward stay valid once it is re-gathered.
-* Backward: a hook on the unit's outputs re-gathers the parameters if needed;
-  a hook on the flat leaf fires once every parameter gradient of the unit is
-  known and launches the reduce-scatter (on a side stream on GPUs).
+* Backward: a hook on the unit's outputs re-gathers the parameters if needed.
+  The parameter views are the outputs of one autograd node per iteration
+  (`_FlatViews`); its backward runs once every parameter gradient of a forward
+  call is known, writes them into the unit's flat gradient buffer and, after
+  the last call, launches the reduce-scatter (on a side stream on GPUs).
+  Weights consumed by the native linear op skip even that copy: their view
+  carries a handle to the matching slice of the flat gradient and the weight-
+  gradient GEMM accumulates straight into it.
 * The gradient shard stays in the reduction dtype (`_grad_shard`).  The fused
   optimiser reads it directly; for generic optimisers an fp32 `.grad` is
   materialised (`materialize_fp32_grads`).
@@ -44,6 +49,8 @@ import math
 from collections import OrderedDict
 from enum import Enum, auto
 from typing import Any, Dict, Iterator, List, Optional, Tuple, Union
+
+import functools
 
 import torch
 import torch.distributed as dist
@@ -91,6 +98,23 @@ def calc_grad_norm(grads: List[torch.Tensor], norm_type: float) -> torch.Tensor:
         return torch.stack([g.detach().abs().max().float() for g in grads]).max()
     parts = torch.stack([torch.linalg.vector_norm(g.detach().float(), norm_type) for g in grads])
     return torch.linalg.vector_norm(parts, norm_type)
+
+
+class _FlatViews(torch.autograd.Function):
+    """leaf -> one view per parameter of the unit.  Backward receives every parameter gradient of one
+    forward call at once: the point where the unit knows that call's gradients are complete."""
+
+    @staticmethod
+    def forward(ctx, leaf: torch.Tensor, unit: "FullyShardedDataParallel"):
+        ctx.unit = unit
+        ctx.set_materialize_grads(False)
+        base = leaf.detach()
+        return tuple(base[info.offset:info.offset + info.numel].view(info.shape) for info in unit._infos)
+
+    @staticmethod
+    def backward(ctx, *grads):
+        ctx.unit._collect_grads(grads)
+        return None, None
 
 
 class FullyShardedDataParallel(nn.Module):
@@ -168,6 +192,7 @@ class FullyShardedDataParallel(nn.Module):
         self.compute_device = self.flat_param.device
         self._full: Optional[torch.Tensor] = None          # gathered compute-dtype buffer
         self._full_leaf: Optional[torch.Tensor] = None
+        self._flat_grad: Optional[torch.Tensor] = None     # this iteration's gradients, compute dtype
         self._full_version = -1
         self._bwd_hook_armed = False
         self._calls = 0
@@ -350,16 +375,37 @@ class FullyShardedDataParallel(nn.Module):
         if self.world_size > 1 and self._full is not None:
             self._full.untyped_storage().resize_(0)
 
-    def _set_views(self, leaf: torch.Tensor) -> None:
-        sizes = []
-        for i, info in enumerate(self._infos):
-            nxt = self._infos[i + 1].offset if i + 1 < len(self._infos) else self._numel_padded
-            sizes.append(nxt - info.offset)
-        chunks = torch.split(leaf, sizes)
-        for info, c in zip(self._infos, chunks):
-            v = c[:info.numel].view(info.shape)
+    def _set_views(self, leaf: torch.Tensor, track: bool = False) -> None:
+        """Hand the wrapped modules views of `leaf`.  With `track` the views come out of `_FlatViews`
+        so their gradients flow back into the unit's flat gradient buffer."""
+        if track:
+            views = _FlatViews.apply(leaf, self)
+        else:
+            views = [leaf[info.offset:info.offset + info.numel].view(info.shape) for info in self._infos]
+        direct = track and leaf.is_cuda and leaf.dtype in (torch.bfloat16, torch.float16)
+        for info, v in zip(self._infos, views):
+            if direct and len(info.shape) == 2:
+                v._wgrad_sink = functools.partial(self._grad_view, info)
             for mod, pname, _ in info.owners:
                 mod.__dict__[pname] = v
+
+    def _grad_buffer(self) -> torch.Tensor:
+        """Flat gradient of this iteration in compute dtype, zero-filled on first use."""
+        if self._flat_grad is None:
+            self._flat_grad = torch.zeros(self._numel_padded, dtype=self._full.dtype, device=self._full.device)
+        return self._flat_grad
+
+    def _grad_view(self, info: "_ParamInfo") -> torch.Tensor:
+        return self._grad_buffer()[info.offset:info.offset + info.numel].view(info.shape)
+
+    def _collect_grads(self, grads) -> None:
+        """Backward of `_FlatViews`: add the gradients autograd produced (everything except weights
+        whose GEMM already accumulated into the buffer), then see whether the unit is complete."""
+        buf = self._grad_buffer()
+        for info, g in zip(self._infos, grads):
+            if g is not None:
+                buf[info.offset:info.offset + info.numel].add_(g.reshape(-1).to(buf.dtype))
+        self._post_backward()
 
     # ------------------------------------------------------------------ forward / backward
     def forward(self, *args, **kwargs):
@@ -379,11 +425,10 @@ class FullyShardedDataParallel(nn.Module):
             # gradients of all calls accumulate into one flat buffer.
             if self._full_leaf is None:
                 leaf = self._full.detach().requires_grad_(True)
-                leaf.register_post_accumulate_grad_hook(self._post_backward)
                 self._full_leaf = leaf
                 self._calls = 0
                 self._fires = 0
-                self._set_views(leaf)
+                self._set_views(leaf, track=True)
             self._calls += 1
         else:
             self._set_views(self._full)
@@ -415,17 +460,17 @@ class FullyShardedDataParallel(nn.Module):
         visit(out)
         return out
 
-    def _post_backward(self, leaf: torch.Tensor):
-        """Runs whenever autograd has accumulated into the flat leaf.  With an
-        activation-checkpointed block that is once per forward call of this
-        iteration (each recomputation runs its own backward); otherwise once."""
+    def _post_backward(self, force: bool = False):
+        """Runs whenever the gradients of one forward call have been collected.  With an
+        activation-checkpointed block that is once per forward call of this iteration (each
+        recomputation runs its own backward); otherwise once."""
         from .checkpoint import CheckpointWrapper
         self._fires += 1
         expected = self._calls if isinstance(self._wrapped, CheckpointWrapper) else 1
-        if self._fires < expected:
-            return None          # keep accumulating in leaf.grad
-        flat_grad = leaf.grad
-        leaf.grad = None
+        if self._fires < expected and not force:
+            return None          # keep accumulating in the flat gradient buffer
+        flat_grad = self._grad_buffer()
+        self._flat_grad = None
         self._full_leaf = None
         p = self.flat_param
         red_dtype = torch.float32 if (self.fp32_reduce_scatter or not self.mixed_precision) else self.compute_dtype
@@ -495,12 +540,10 @@ class FullyShardedDataParallel(nn.Module):
         self._lazy_init()
         from .checkpoint import CheckpointWrapper
         for u in self._units():
-            leaf = u._full_leaf
-            if leaf is None:
+            if u._full_leaf is None:
                 continue
-            if leaf.grad is not None:      # backward ended before every expected accumulation arrived
-                u._fires = (u._calls if isinstance(u._wrapped, CheckpointWrapper) else 1) - 1
-                u._post_backward(leaf)
+            if u._flat_grad is not None:   # backward ended before every expected collection arrived
+                u._post_backward(force=True)
             else:
                 u._full_leaf = None
         self._sync_comm()
