@@ -366,7 +366,8 @@ void launch_bwd(const void* dy, const void* x, const void* w, float off, const f
     return;
   }
   if (D > 1024 && vec_ok(D, 256, {dy, x, w, dx})) {
-    const int grid = (int)std::min<long long>(M, 148LL * 4);
+    // one resident wave: the per-CTA column sums end in D atomics each, and those dominate beyond that
+    const int grid = (int)std::min<long long>(M, 148LL * 2);
     VPT_SWITCH(D, 256, (norm_bwd_vec_kernel<T, W, LAYER, 256, VPT><<<grid, 256, 0, st>>>(
                             (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D)));
     return;

@@ -699,7 +699,7 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
         seg_scratch, (const T*)dmean_out, (const T*)dvar_out, (T*)dprev_mean, (T*)dprev_var, B, G, nseg);
     tsn_bwd_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
                                                                 seg_scratch, dux, dvx, B, L, G, nseg);
-    const int grid = (int)std::min<long long>(rows, 148LL * 4);
+    const int grid = (int)std::min<long long>(rows, vec ? 148LL * 2 : 148LL * 4);
     if (vec) {
       const int hv = H / 8;
       if (hv <= kBwdThreads)
