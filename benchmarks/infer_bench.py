@@ -1,0 +1,163 @@
+"""Inference benchmark: chunk-parallel prefill throughput and per-token decode latency.
+
+    # prefill: the prompt is split over N chunk-parallel GPUs, CEMA / TimestepNorm state handed on
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        benchmarks/infer_bench.py --phase prefill [--prompt-len 131072]
+    # decode: model parallel over N GPUs (N <= number of heads), recurrent cache, greedy
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        benchmarks/infer_bench.py --phase decode [--batches 1,4,16] [--gen-len 256]
+
+The two phases use different process-group layouts, so they are separate launches; the decode phase
+fills its cache by prefilling a short prompt (one full chunk plus a remainder) through the cache path.
+Random-init bf16 weights, uniform random prompt.  Timing: CUDA events after warm-up, max over ranks.
+Rank 0 prints one JSON line per phase.
+"""
+import argparse
+import dataclasses
+import json
+import os
+import sys
+
+os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--phase", choices=["prefill", "decode"], required=True)
+    ap.add_argument("--model", default="mega7B_32k")
+    ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (not a valid result)")
+    ap.add_argument("--prompt-len", type=int, default=None, help="prefill: total prompt tokens (default 16384 per GPU)")
+    ap.add_argument("--batches", default="1,4,16")
+    ap.add_argument("--gen-len", type=int, default=256)
+    ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--eager", action="store_true", help="decode through the regular cache path instead of the "
+                                                         "graph-replayed fixed-shape session")
+    args = ap.parse_args()
+
+    import torch
+    import torch.distributed as dist
+    from megalodon_b200.models.mega import ModelStore, build_model
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import init_torch_distributed, initialize_model_parallel
+    from megalodon_b200.utils import init_cache, set_random_seed
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    rank = 0
+    if world > 1:
+        rank = init_torch_distributed().global_rank
+    cfg = dataclasses.replace(ModelStore[args.model])
+    if args.layers is not None:
+        cfg.num_layers = args.layers
+    cfg.layerwise_ckpt = False
+    cfg.dropout = cfg.hidden_dropout = cfg.attention_dropout = 0.0
+    set_random_seed(1234)
+
+    def maxed(ms):
+        if world > 1:
+            t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return float(t.item())
+        return ms
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    if args.phase == "prefill":
+        if world > 1:
+            initialize_model_parallel(1, world)
+        model = build_model(cfg, "bf16", reshard_after_forward=False, shard_over_chunk_group=True)
+        model.eval()
+        model._wrapped.seq_microbatch_chunks = 1
+        if world > 1:
+            from megalodon_b200.parallel.symm import enable_peer_transport
+            enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=30.0)
+        P = args.prompt_len or 16384 * world
+        assert P % (world * cfg.chunk_size) == 0
+        g = torch.Generator().manual_seed(0)
+        toks = torch.randint(0, cfg.vocab_size, (1, P), generator=g).cuda()
+        with torch.no_grad():
+            for _ in range(2):
+                logits, _ = model(toks)
+            del logits
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            for _ in range(args.reps):
+                logits, _ = model(toks)
+                nxt = logits[:, -1].argmax(-1)          # what a generation loop would read
+                del logits
+            e1.record()
+            barrier()
+        ms = maxed(e0.elapsed_time(e1) / args.reps)
+        cuda_ops.check_kernel_errors()
+        if rank == 0:
+            out = {"metric": "prefill tokens/s", "value": P / (ms / 1e3), "unit": "tokens/s", "n_gpus": world,
+                   "ms": ms, "dtype": "bf16", "data": "synthetic",
+                   "config": {"model": f"{args.model} L{cfg.num_layers}", "prompt_len": P, "parallelism": f"cp{world}",
+                              "chunk": cfg.chunk_size}}
+            if args.layers is not None:
+                out["invalid"] = "reduced depth (debug run)"
+            print(json.dumps(out))
+    else:
+        if world > 1:
+            initialize_model_parallel(world, 1)
+        model = build_model(cfg, "bf16", reshard_after_forward=False)
+        model.eval()
+        inner = model
+        while hasattr(inner, "_wrapped"):
+            inner = inner._wrapped
+        c = cfg.chunk_size
+        results = {}
+        with torch.inference_mode():
+            for B in [int(b) for b in args.batches.split(",")]:
+                g = torch.Generator().manual_seed(B)
+                prompt = torch.randint(0, cfg.vocab_size, (B, c + 17), generator=g).cuda()
+                cache = init_cache(B, inner, torch.bfloat16, device=prompt.device)
+                _, cache = model(prompt[:, :c], cache=cache)            # one whole chunk
+                logits, cache = model(prompt[:, c:], cache=cache)       # remainder of the prompt
+                tok = logits[:, -1].argmax(-1, keepdim=True)
+                if args.eager:
+                    state = {"cache": cache}
+
+                    def step(tok):
+                        lg, state["cache"] = model(tok, cache=state["cache"])
+                        return lg[:, -1].argmax(-1, keepdim=True)
+                else:
+                    from megalodon_b200.decoding import DecodeSession
+                    sess = DecodeSession(model, B, torch.bfloat16)
+                    sess.load_cache(cache)
+
+                    def step(tok):
+                        return sess.step(tok).argmax(-1, keepdim=True)
+                for _ in range(8):                                       # warm-up decode steps (and graph capture)
+                    tok = step(tok)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.gen_len):
+                    tok = step(tok)
+                e1.record()
+                barrier()
+                results[B] = maxed(e0.elapsed_time(e1) / args.gen_len)
+        cuda_ops.check_kernel_errors()
+        if rank == 0:
+            out = {"metric": "decode ms/token", "value": results, "unit": "ms", "n_gpus": world,
+                   "higher_is_better": False, "dtype": "bf16", "data": "synthetic",
+                   "config": {"model": f"{args.model} L{cfg.num_layers}", "parallelism": f"mp{world}",
+                              "gen_len": args.gen_len, "prompt_len": c + 17, "sampling": "greedy",
+                              "path": "eager cache path" if args.eager else "CUDA-graph decode session"}}
+            if args.layers is not None:
+                out["invalid"] = "reduced depth (debug run)"
+            print(json.dumps(out))
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -408,6 +408,28 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
   return {C, pre, (int64_t)rc};
 }
 
+// x [M <= 16, K], w [N, K] (rows contiguous) -> y [M, N]; returns an empty optional if the kernel does not apply
+OptTensor gemv_small_m(const Tensor& x, const Tensor& w, const OptTensor& bias, int64_t act, int64_t out_dtype_code,
+                       double alpha) {
+  TORCH_CHECK(x.is_cuda() && w.is_cuda() && x.dim() == 2 && w.dim() == 2 && x.size(1) == w.size(1));
+  TORCH_CHECK(x.stride(1) == 1 && w.stride(1) == 1 && x.scalar_type() == w.scalar_type());
+  c10::cuda::CUDAGuard guard(x.device());
+  const int M = x.size(0), K = x.size(1), N = w.size(0);
+  at::ScalarType odt = out_dtype_code == 0 ? at::kFloat : (out_dtype_code == 1 ? at::kBFloat16 : at::kHalf);
+  Tensor y = torch::empty({M, N}, x.options().dtype(odt));
+  int bias_code = 0;
+  if (bias.has_value()) {
+    check_cuda_contig(*bias, "bias");
+    bias_code = dtype_code(*bias);
+    TORCH_CHECK(bias->numel() == N);
+  }
+  const bool ok = mb::gemv_small_m(x.data_ptr(), w.data_ptr(), opt_ptr(bias), bias_code, y.data_ptr(), M, N, K,
+                                   x.stride(0), w.stride(0), y.stride(0), (float)alpha, (int)act, dtype_code(x),
+                                   (int)out_dtype_code, stream());
+  if (!ok) return OptTensor();
+  return y;
+}
+
 // ------------------------------------------------------------------ attention softmax (in place)
 // s [..., L1, L2] with contiguous last dim and uniform row stride; returns lse [rows] (fp32)
 Tensor attn_softmax_fwd(Tensor& s, int64_t L1, int64_t L2, bool causal, double drop_p, int64_t seed,
@@ -600,6 +622,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false);
+  m.def("gemv_small_m", &gemv_small_m);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
   m.def("time_sums", &time_sums);

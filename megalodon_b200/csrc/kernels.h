@@ -85,6 +85,10 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
                       const GemmPeerSpec* peers = nullptr, bool accumulate = false);
+// y = act(alpha x w^T + bias) for M <= 16 rows of x (gemv_kernels.cu); false if the shapes do not qualify
+bool gemv_small_m(const void* x, const void* w, const void* bias, int bias_dtype, void* y, int M, int N, int K,
+                  long long ldx, long long ldw, long long ldy, float alpha, int act, int in_dtype, int out_dtype,
+                  cudaStream_t st);
 // Whether GEMMs with more than 128 rows run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); on by default.
 void gemm_set_cta_pairs(bool on);
 int gemm_pair_max_active_clusters();

@@ -73,6 +73,9 @@ class _InnerAttention(nn.Module):
         if slen <= c:
             xq, xk = apply_rotary_emb(xq, xk, freqs_cis, backward=False)
 
+        if cache is not None and isinstance(cache[2], torch.Tensor):
+            return self._static_step(xq, xk, xv, cache)
+
         new_cache = None
         clen = slen
         if cache is not None:
@@ -104,6 +107,24 @@ class _InnerAttention(nn.Module):
             causal = not (slen == 1 and cache is not None)
             out = ops.attention(xq, xk, xv, 1.0, self.dropout, causal, self.training)
         return out.reshape(bs, slen, -1), new_cache
+
+    def _static_step(self, xq: Tensor, xk: Tensor, xv: Tensor, cache):
+        """One decode step against fixed-size buffers: `cache = (k_buf, v_buf, pos)` with
+        k_buf / v_buf [B, H, chunk, d] and `pos` a device index tensor [1] holding the position of
+        this token inside its chunk.  Shapes never change and nothing is read back to the host, so
+        the step can be captured in a CUDA graph; keys beyond `pos` (stale entries of the previous
+        chunk) are masked, which is the same as the tail cache emptying at a chunk boundary.  The
+        head-major layout makes both products plain batched matmuls over the buffers (no copies)."""
+        k_buf, v_buf, pos = cache
+        bs, slen = xq.shape[:2]
+        assert slen == 1, "the static cache takes one token per step"
+        k_buf.index_copy_(2, pos, xk.transpose(1, 2).to(k_buf.dtype))
+        v_buf.index_copy_(2, pos, xv.transpose(1, 2).to(v_buf.dtype))
+        scores = torch.matmul(xq.transpose(1, 2), k_buf.transpose(2, 3)).float()         # [B, H, 1, chunk]
+        hidden = torch.arange(k_buf.size(2), device=pos.device) > pos
+        probs = torch.softmax(scores.masked_fill(hidden, float("-inf")), dim=-1).to(xq.dtype)
+        out = torch.matmul(probs, v_buf)                                                 # [B, H, 1, dv]
+        return out.transpose(1, 2).reshape(bs, 1, -1), cache
 
     def extra_repr(self) -> str:
         return (f"heads={self.n_heads}, z_head_dim={self.z_head_dim}, "

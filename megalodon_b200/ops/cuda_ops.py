@@ -116,6 +116,13 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
                 out.copy_(res)
             res = out
         return res.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
+    if (a.dim() == 2 and a.shape[0] <= 16 and not a_mn and not b_mn and mode == 0 and out is None
+            and not want_preact and not accumulate):
+        # a few rows (decoding): one pass over the weights on the CUDA cores beats a 128-row MMA tile
+        _bump()
+        res = _C().gemv_small_m(a, b, bias, 1 if act == "silu" else 0, _DT[out_dtype], alpha)
+        if res is not None:
+            return res, None
     _bump()
     res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
                              _DT[out_dtype], mode, alpha, _err_flag(a.device),

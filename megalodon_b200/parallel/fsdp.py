@@ -280,11 +280,13 @@ class FullyShardedDataParallel(nn.Module):
         if self._is_root is not None:
             return
         self._is_root = True
+        # plain attributes, not sub-modules: registering the root as a child of its units would make
+        # the module tree cyclic (train() / eval() would never return)
         for u in self._units():
             if u is not self:
                 u._is_root = False
-                u._root = self
-        self._root = self
+                object.__setattr__(u, "_root", self)
+        object.__setattr__(self, "_root", self)
         if self.compute_device.type == "cuda" and self.world_size > 1:
             self._comm_stream = torch.cuda.Stream(self.compute_device)
 

@@ -426,3 +426,57 @@ def test_ema_parameters_hidden_and_dropout():
     assert torch.allclose(y[kept], t.detach()[kept] / 0.75, rtol=1e-5)
     y.backward(torch.ones_like(y))
     assert torch.equal(t.grad != 0, kept)
+
+
+def test_decode_session_cuda_graph_matches_cache_path():
+    """Graph-replayed decoding gives the logits of the regular cache path (bf16, chunk boundary crossed)."""
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.decoding import DecodeSession
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.utils import init_cache, set_random_seed
+    from megalodon_b200.ops import cuda_ops
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    set_random_seed(0)
+    model = build_model(cfg, "bf16", False, False)
+    model.eval()
+    inner = model._wrapped
+    B = 2
+    g = torch.Generator().manual_seed(1)
+    prompt = torch.randint(0, 512, (B, 128 + 120), generator=g).cuda()
+    with torch.no_grad():
+        cache = init_cache(B, inner, torch.bfloat16, device=prompt.device)
+        _, cache = model(prompt[:, :128], cache=cache)
+        logits, cache = model(prompt[:, 128:], cache=cache)
+        sess = DecodeSession(model, B, torch.bfloat16)
+        sess.load_cache(cache)
+        tok = logits[:, -1].argmax(-1)
+        worst = 0.0
+        for i in range(20):                       # position 120 -> 140: crosses the chunk boundary at 128
+            ref, cache = model(tok.view(B, 1), cache=cache)
+            got = sess.step(tok)
+            worst = max(worst, (ref[:, -1] - got).abs().max().item())
+            tok = ref[:, -1].argmax(-1)           # both paths follow the reference tokens
+        assert sess._graph is not None, "the step was never captured"
+        cuda_ops.check_kernel_errors()
+    assert worst < 0.15, worst
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 272, 136), (3, 1024, 4096), (16, 530, 264)])
+@pytest.mark.parametrize("act", [None, "silu"])
+def test_small_m_linear(M, N, K, act):
+    """Few-row linear (decode path) against an fp32 reference."""
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(11)
+    dev = _dev()
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.05).bfloat16()
+    b = torch.randn(N, device=dev).bfloat16()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        y, _ = cuda_ops.gemm(x, w, b, act, out_dtype=out_dtype)
+        ref = x.float() @ w.float().t() + b.float()
+        if act:
+            ref = torch.nn.functional.silu(ref)
+        assert y.dtype == out_dtype and y.shape == (M, N)
+        _close(y, ref, 3e-2, 2e-2, f"small-m linear {M}x{N}x{K} {act} {out_dtype}")

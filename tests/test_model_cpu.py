@@ -195,3 +195,42 @@ def test_checkpoint_roundtrips(tmp_path):
         assert torch.equal(st2[k], v), k
     rc = reloading.reload_config(tmp_path / "cons2")
     assert not rc.is_fsdp and rc.mp_world_size == 1 and rc.dtype == "fp32"
+
+
+def test_decode_session_matches_cache_path():
+    """The fixed-shape decode state reproduces the regular cache path token for token, from a prefilled
+    cache and from an empty one, across a chunk boundary."""
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.decoding import DecodeSession
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.utils import init_cache, set_random_seed
+    cfg = ModelConf(num_layers=2, model_dim=64, num_heads=2, z_dim=32, value_dim=64, ffn_hidden_dim=64,
+                    cema_ndim=4, chunk_size=8, vocab_size=50, swiglu=True, norm_num_groups=8)
+    set_random_seed(0)
+    model = build_model(cfg, "fp32", device=torch.device("cpu"))
+    model.eval()
+    inner = model._wrapped
+    B = 2
+    prompt = torch.randint(0, 50, (B, 11))
+    with torch.no_grad():
+        cache = init_cache(B, inner, torch.float32, device=torch.device("cpu"))
+        _, cache = model(prompt[:, :8], cache=cache)
+        logits, cache = model(prompt[:, 8:], cache=cache)
+        sess = DecodeSession(model, B, torch.float32, use_graph=False)
+        sess.load_cache(cache)
+        t_ref = t_ses = logits[:, -1].argmax(-1)
+        for _ in range(14):
+            ref, cache = model(t_ref.view(B, 1), cache=cache)
+            got = sess.step(t_ses)
+            assert torch.allclose(ref[:, -1], got, atol=1e-5, rtol=1e-5)
+            t_ref, t_ses = ref[:, -1].argmax(-1), got.argmax(-1)
+        cache = init_cache(B, inner, torch.float32, device=torch.device("cpu"))
+        sess = DecodeSession(model, B, torch.float32, use_graph=False)
+        tok = torch.randint(0, 50, (B,))
+        for _ in range(10):
+            ref, cache = model(tok.view(B, 1), cache=cache)
+            got = sess.step(tok)
+            assert torch.allclose(ref[:, -1], got, atol=1e-5, rtol=1e-5)
+            tok = ref[:, -1].argmax(-1)
+    model.train()        # the module tree must stay acyclic after forwards
+    model.eval()
