@@ -153,8 +153,10 @@ def main():
         cfg.num_layers = args.layers
     local_len = args.seq_len // world
     chunks_local = local_len // cfg.chunk_size
-    # one GPU holds the whole 32K sequence only with layer checkpointing; a 1/8 slice fits without
-    cfg.layerwise_ckpt = (not args.no_ckpt) and chunks_local > 1
+    # One GPU holds the whole 32K sequence only with layer checkpointing.  Activations cost about 1 GB
+    # per layer and 4096-token chunk, optimiser state 137 GB / N: from two chunks per GPU down (N >= 4)
+    # everything fits in 180 GB without recomputation.
+    cfg.layerwise_ckpt = (not args.no_ckpt) and chunks_local > 2
     set_random_seed(1234)
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)

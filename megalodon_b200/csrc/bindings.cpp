@@ -430,6 +430,52 @@ OptTensor gemv_small_m(const Tensor& x, const Tensor& w, const OptTensor& bias, 
   return y;
 }
 
+// ------------------------------------------------------------------ FFT long convolution
+// x [..., L] contiguous -> half spectrum [..., N2/2 + 1, 2] (fp32 pairs) of the zero-padded row
+Tensor rfft_rows(const Tensor& x, bool flip) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int L = x.size(-1);
+  TORCH_CHECK(mb::fftconv_supported(L), "rfft: length > 8192 is not supported by the native kernel");
+  const long long rows = x.numel() / L;
+  const int bins = (1 << mb::fftconv_logn(L)) / 2 + 1;
+  auto shape = x.sizes().vec();
+  shape.back() = bins;
+  shape.push_back(2);
+  Tensor out = torch::empty(shape, x.options().dtype(at::kFloat));
+  mb::rfft_rows(x.data_ptr(), out.data_ptr<float>(), rows, L, flip, dtype_code(x), stream());
+  return out;
+}
+
+// x [B, D, L], kf [D, N2/2 + 1, 2] -> y [B, D, L] = irfft(rfft(x) * kf (or conj kf))[:L]
+Tensor fftconv_apply(const Tensor& x, const Tensor& kf, bool conj_k) {
+  check_cuda_contig(x, "x");
+  check_cuda_contig(kf, "kf");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int L = x.size(-1), D = x.size(-2);
+  const int bins = (1 << mb::fftconv_logn(L)) / 2 + 1;
+  TORCH_CHECK(mb::fftconv_supported(L) && kf.scalar_type() == at::kFloat && kf.numel() == (long long)D * bins * 2);
+  Tensor y = torch::empty_like(x);
+  mb::fftconv_rows(x.data_ptr(), kf.data_ptr<float>(), y.data_ptr(), x.numel() / L, L, D, conj_k, dtype_code(x),
+                   stream());
+  return y;
+}
+
+// dk [D, L] fp32 = sum over batch of the correlation of dy with x
+Tensor fftconv_dk(const Tensor& dy, const Tensor& x) {
+  check_cuda_contig(dy, "dy");
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int L = x.size(-1), D = x.size(-2);
+  TORCH_CHECK(mb::fftconv_supported(L) && dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type());
+  const int bins = (1 << mb::fftconv_logn(L)) / 2 + 1;
+  Tensor acc = torch::zeros({D, bins, 2}, x.options().dtype(at::kFloat));
+  Tensor dk = torch::empty({D, L}, x.options().dtype(at::kFloat));
+  mb::fftconv_dk(dy.data_ptr(), x.data_ptr(), acc.data_ptr<float>(), dk.data_ptr<float>(), x.numel() / L, L, D,
+                 dtype_code(x), stream());
+  return dk;
+}
+
 // ------------------------------------------------------------------ attention softmax (in place)
 // s [..., L1, L2] with contiguous last dim and uniform row stride; returns lse [rows] (fp32)
 Tensor attn_softmax_fwd(Tensor& s, int64_t L1, int64_t L2, bool causal, double drop_p, int64_t seed,
@@ -623,6 +669,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false);
   m.def("gemv_small_m", &gemv_small_m);
+  m.def("rfft_rows", &rfft_rows);
+  m.def("fftconv_apply", &fftconv_apply);
+  m.def("fftconv_dk", &fftconv_dk);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
   m.def("time_sums", &time_sums);

@@ -85,6 +85,14 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
                       const GemmPeerSpec* peers = nullptr, bool accumulate = false);
+// ---- FFT long convolution (fftconv_kernels.cu); spectra are [rows, N2/2 + 1] complex, N2 = 1 << fftconv_logn(L)
+int fftconv_logn(int L);
+bool fftconv_supported(int L);          // L <= 8192
+void rfft_rows(const void* x, float* out_spec, long long rows, int L, bool flip, int dtype, cudaStream_t st);
+void fftconv_rows(const void* x, const float* kf, void* y, long long rows, int L, int D, bool conj_k, int dtype,
+                  cudaStream_t st);
+void fftconv_dk(const void* dy, const void* x, float* acc_spec, float* dk, long long rows, int L, int D, int dtype,
+                cudaStream_t st);
 // y = act(alpha x w^T + bias) for M <= 16 rows of x (gemv_kernels.cu); false if the shapes do not qualify
 bool gemv_small_m(const void* x, const void* w, const void* bias, int bias_dtype, void* y, int M, int N, int K,
                   long long ldx, long long ldw, long long ldy, float alpha, int act, int in_dtype, int out_dtype,

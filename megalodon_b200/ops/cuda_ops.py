@@ -491,12 +491,53 @@ def ema_hidden(x, p, q, hx):
     return h
 
 
+class _FFTConv(torch.autograd.Function):
+    """Causal long convolution x [B, D, L] * k [D, L] through the shared-memory FFT kernels.  The
+    input spectrum is not kept: the backward pass recomputes it inside the kernels that need it."""
+
+    @staticmethod
+    def forward(ctx, x, k):
+        xc = x.contiguous()
+        kf = _C().rfft_rows(k.float().contiguous(), False)          # [D, bins, 2]
+        _bump(2)
+        y = _C().fftconv_apply(xc, kf, False)
+        ctx.save_for_backward(xc, kf)
+        ctx.k_dtype = k.dtype
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, kf = ctx.saved_tensors
+        dyc = dy.contiguous()
+        dx = dk = None
+        if ctx.needs_input_grad[0]:
+            _bump()
+            dx = _C().fftconv_apply(dyc, kf, True)
+        if ctx.needs_input_grad[1]:
+            _bump(2)
+            dk = _C().fftconv_dk(dyc, xc).to(ctx.k_dtype)
+        return dx, dk
+
+
+def _fft_native_ok(x, L) -> bool:
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and 1 <= L <= 8192
+
+
 def fftconv(x, k):
-    return reference.fftconv(x, k)
+    """x [B, D, L] (or [D, L]), k [D, L] -> causal convolution along L."""
+    if not _fft_native_ok(x, x.shape[-1]) or x.dim() not in (2, 3) or k.dim() != 2:
+        return reference.fftconv(x, k)
+    x3 = x if x.dim() == 3 else x.unsqueeze(0)
+    y = _FFTConv.apply(x3, k)
+    return y if x.dim() == 3 else y.squeeze(0)
 
 
 def rfft(x, flip=False):
-    return reference.rfft(x, flip)
+    """Real FFT of the zero-padded rows (length 2 * max(32, next_pow2(L))) as a complex tensor."""
+    if not _fft_native_ok(x, x.shape[-1]) or x.requires_grad:
+        return reference.rfft(x, flip)
+    _bump()
+    return torch.view_as_complex(_C().rfft_rows(x.contiguous(), bool(flip)))
 
 
 # ----------------------------------------------------------------------------- attention

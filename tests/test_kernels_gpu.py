@@ -480,3 +480,31 @@ def test_small_m_linear(M, N, K, act):
             ref = torch.nn.functional.silu(ref)
         assert y.dtype == out_dtype and y.shape == (M, N)
         _close(y, ref, 3e-2, 2e-2, f"small-m linear {M}x{N}x{K} {act} {out_dtype}")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("B,D,L", [(2, 8, 37), (1, 16, 300), (2, 4, 4096)])
+def test_fftconv_native(dtype, B, D, L):
+    """Shared-memory FFT convolution (forward and both gradients) and rfft against torch.fft."""
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(12)
+    dev = _dev()
+    x = torch.randn(B, D, L, device=dev).to(dtype)
+    k = torch.randn(D, L, device=dev) * torch.exp(-torch.arange(L, device=dev) / 50.0)
+    g = torch.randn(B, D, L, device=dev).to(dtype)
+    outs = []
+    for mod in (ops, reference):
+        xs, ks = x.clone().requires_grad_(), k.clone().requires_grad_()
+        y = mod.fftconv(xs, ks)
+        y.backward(g)
+        outs.append((y, xs.grad, ks.grad))
+    (y0, dx0, dk0), (y1, dx1, dk1) = outs
+    atol, rtol = (2e-3, 2e-3) if dtype == torch.float32 else (8e-2, 5e-2)
+    _close(y0, y1, atol, rtol, "fftconv y")
+    _close(dx0, dx1, atol, rtol, "fftconv dx")
+    _close(dk0, dk1, atol * (10 if dtype != torch.float32 else 1) * max(1.0, dk1.abs().max().item()), rtol, "fftconv dk")
+    for flip in (False, True):
+        f0 = torch.view_as_real(ops.rfft(x, flip))
+        f1 = torch.view_as_real(reference.rfft(x, flip))
+        _close(f0, f1, 5e-3 * max(1.0, f1.abs().max().item()), 2e-3, f"rfft flip={flip}")
