@@ -41,6 +41,8 @@ def parse():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--ckpt-layers", type=int, default=None,
+                    help="checkpoint only the first K layers (default: all at N=1, 20 at N=2, none from N=4)")
     ap.add_argument("--kernel-profile", default=None,
                     help="after the timed regions, run one more step under torch.profiler and write a per-kernel "
                          "summary to this path (rank number appended); never part of a reported number")
@@ -157,6 +159,11 @@ def main():
     # per layer and 4096-token chunk, optimiser state 137 GB / N: from two chunks per GPU down (N >= 4)
     # everything fits in 180 GB without recomputation.
     cfg.layerwise_ckpt = (not args.no_ckpt) and chunks_local > 2
+    if args.ckpt_layers is not None:
+        cfg.ckpt_layers = args.ckpt_layers
+    elif chunks_local == 4:
+        # four chunks per GPU (N = 2): state 86 GB + 4 GB of activations per un-checkpointed layer
+        cfg.ckpt_layers = 20
     set_random_seed(1234)
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)
@@ -316,7 +323,8 @@ def main():
                          f"V{cfg.vocab_size}), {n_params / 1e9:.2f}B params",
                 "global_batch": 1, "seq_len": args.seq_len,
                 "parallelism": f"cp{world}" + ("+zero3_over_cp+p2p_handoff" if world > 1 else ""),
-                "activation_checkpointing": bool(cfg.layerwise_ckpt),
+                "activation_checkpointing": (False if not cfg.layerwise_ckpt else
+                                             ("all layers" if cfg.ckpt_layers is None else f"first {cfg.ckpt_layers} layers")),
                 "optimizer": "AdamW fp32 master+moments, clip 1.0",
                 "gemm_backend": cuda_ops.gemm_backend(),
                 "l2": "working set (17 GB bf16 weights + activations) streams through L2 every step; no flush needed",
@@ -327,6 +335,8 @@ def main():
                     "wall_ms_per_step": wall_ms / args.steps,
                     "h2d_bytes_per_step": 2 * args.seq_len * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches,
+            "peak_mem_gb_rank0": {"allocated": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1),
+                                  "reserved": round(torch.cuda.max_memory_reserved() / 2 ** 30, 1)},
             "phases_ms_rank0": {k: round(v, 1) for k, v in phases.items()},
             "steps_ms_rank0": [round(v, 1) for v in steps_ms],
         }

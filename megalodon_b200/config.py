@@ -69,6 +69,9 @@ class ModelConf:
     scale_emb: bool = False
     share_emb: bool = False
     layerwise_ckpt: bool = False
+    # with layerwise_ckpt: checkpoint only the first `ckpt_layers` blocks (None = all of them); the
+    # rest keep their activations, which trades spare memory for less recomputation
+    ckpt_layers: Optional[int] = None
 
     def __post_init__(self):
         # The reference checks `z_dim % z_dim` (always true, config.py:73); the

@@ -154,7 +154,8 @@ class Mega(nn.Module):
         self.layers = nn.ModuleList()
         for layer_id in range(self.num_layers):
             block = MegaBlock(cfg, layer_id)
-            layer = checkpoint_wrapper(block) if cfg.layerwise_ckpt else block
+            n_ckpt = self.num_layers if getattr(cfg, "ckpt_layers", None) is None else cfg.ckpt_layers
+            layer = checkpoint_wrapper(block) if (cfg.layerwise_ckpt and layer_id < n_ckpt) else block
             self.layers.append(wrap(layer))
         self.output = MegaOutputLayer(cfg, self.embed.weight)
 
