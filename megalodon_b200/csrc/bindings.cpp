@@ -646,7 +646,10 @@ void reduce_slots(const Tensor& slots, Tensor& out, int64_t world) {
 
 }  // namespace
 
+void register_cpu_ops(pybind11::module& m);      // cpu_ops.cpp
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
+  register_cpu_ops(m);
   m.def("rms_norm_fwd", &rms_norm_fwd);
   m.def("rms_norm_bwd", &rms_norm_bwd);
   m.def("layer_norm_fwd", &layer_norm_fwd);

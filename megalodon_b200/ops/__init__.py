@@ -28,6 +28,15 @@ def _cuda():
     return cuda_ops
 
 
+def _cpu_native_ok(x: Tensor, *others) -> bool:
+    """The C++ host implementations (csrc/cpu_ops.cpp) cover fp32 forward passes without autograd."""
+    if x.is_cuda or x.dtype != torch.float32 or not have_ext():
+        return False
+    if torch.is_grad_enabled() and any(t is not None and torch.is_tensor(t) and t.requires_grad for t in (x,) + others):
+        return False
+    return True
+
+
 # ------------------------------------------------------------------ GEMM-shaped
 def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: Optional[str] = None) -> Tensor:
     """y = act(x @ w^T + b); `act` is None or "silu"."""
@@ -63,6 +72,10 @@ def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=
     if native_for(x):
         return _cuda().timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
                                      padding_mask, num_groups, eps, gamma_offset)
+    if _cpu_native_ok(x, prev_mean, prev_var, gamma, beta) and prev_count is not None:
+        G = x.shape[-1] if num_groups is None else num_groups
+        return require_ext().cpu_timestep_norm_fwd(x, prev_count, prev_mean, prev_var, gamma, float(gamma_offset),
+                                                   beta, padding_mask, G, float(eps))
     return reference.timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
                                    padding_mask, num_groups, eps, gamma_offset)
 
@@ -103,6 +116,9 @@ def cema(x, p, q, gamma, omega, hx, compute_last_state: bool):
     """Fused complex-EMA layer on channels-last x [B, L, D] -> (y, h_last)."""
     if native_for(x):
         return _cuda().cema(x, p, q, gamma, omega, hx, compute_last_state)
+    if _cpu_native_ok(x, p, q, gamma, omega, hx):
+        y, h = require_ext().cpu_cema_fwd(x, p, q, gamma, omega, hx)
+        return y, (h if compute_last_state else None)
     return reference.cema(x, p, q, gamma, omega, hx, compute_last_state)
 
 

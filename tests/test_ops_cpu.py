@@ -1,0 +1,57 @@
+"""C++ host implementations (csrc/cpu_ops.cpp) against the PyTorch statements of the same operators."""
+import pytest
+import torch
+
+from megalodon_b200 import ops
+from megalodon_b200.ops import _ext, reference
+
+needs_ext = pytest.mark.skipif(not _ext.have_ext(), reason="extension not built")
+
+
+@needs_ext
+@pytest.mark.parametrize("B,L,H,G,masked", [(2, 70, 64, 8, True), (1, 1, 32, 32, False), (3, 33, 48, 4, False)])
+def test_cpu_timestep_norm_forward(B, L, H, G, masked):
+    torch.manual_seed(0)
+    x = torch.randn(B, L, H)
+    cnt = torch.randint(0, 5, (B,))
+    cnt[0] = 0
+    pm, pv = torch.randn(B, G) * 0.1, torch.rand(B, G) + 0.5
+    gm, bt = torch.randn(H) * 0.1, torch.randn(H) * 0.1
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool)
+        mask[-1, L - 7:] = True
+    with torch.no_grad():
+        got = ops.timestep_norm(x, cnt, pm, pv, gm, bt, mask, G, 1e-5, 1.0)
+        ref = reference.timestep_norm(x, cnt, pm, pv, gm, bt, mask, G, 1e-5, 1.0)
+    for a, b in zip(got, ref):
+        assert a.dtype == b.dtype and a.shape == b.shape
+        assert torch.allclose(a.double(), b.double(), atol=1e-5, rtol=1e-5)
+
+
+@needs_ext
+@pytest.mark.parametrize("with_h", [True, False])
+def test_cpu_cema_forward(with_h):
+    torch.manual_seed(1)
+    B, L, D, N = 2, 37, 24, 16
+    x = torch.randn(B, L, D)
+    alpha, delta = torch.rand(D, N) * 0.5 + 0.1, torch.rand(D, N) * 0.5 + 0.1
+    q = torch.polar(1 - alpha * delta, torch.rand(D, N) * 3)
+    gamma = torch.view_as_complex(torch.randn(D, N, 2)) * 0.25
+    omega = torch.randn(D)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2)) if with_h else None
+    with torch.no_grad():
+        y0, h0 = ops.cema(x, alpha, q, gamma, omega, hx, True)
+        y1, h1 = reference.cema_scan(x, alpha, q, gamma, omega, hx)
+    assert torch.allclose(y0, y1, atol=1e-4, rtol=1e-4)
+    assert torch.allclose(torch.view_as_real(h0), torch.view_as_real(h1), atol=1e-4, rtol=1e-4)
+
+
+@needs_ext
+def test_cpu_ops_leave_autograd_to_pytorch():
+    """With gradients required the dispatcher must not take the forward-only C++ path."""
+    x = torch.randn(1, 5, 8, requires_grad=True)
+    cnt, pm, pv = torch.zeros(1, dtype=torch.long), torch.zeros(1, 2), torch.ones(1, 2)
+    y = ops.timestep_norm(x, cnt, pm, pv, torch.zeros(8), torch.zeros(8), None, 2, 1e-5, 1.0)[0]
+    y.sum().backward()
+    assert x.grad is not None
