@@ -55,13 +55,27 @@ class SymmetricRegion:
         self.ptr_table = torch.tensor(self.ptrs, dtype=torch.int64, device=self.device)
         dist.barrier(group=self.group)          # every rank has zeroed its copy
 
+    def check_range(self, offset: int, nbytes: int = 0, rank: Optional[int] = None, align: int = 4) -> None:
+        """Host-side validation of every address handed to a kernel: inside the region, aligned
+        (4 bytes for flags, 16 for payload), existing rank.  A bad offset is an exception here,
+        never a fault on a peer GPU."""
+        if rank is not None and not 0 <= rank < self.world:
+            raise ValueError(f"rank {rank} outside the region's group of {self.world}")
+        if offset < 0 or nbytes < 0 or offset + nbytes > self.nbytes:
+            raise ValueError(f"range [{offset}, {offset + nbytes}) outside the {self.nbytes}-byte region")
+        if offset % align != 0:
+            raise ValueError(f"offset {offset} is not {align}-byte aligned")
+
     def view(self, offset: int, nbytes: int, dtype: torch.dtype) -> torch.Tensor:
+        self.check_range(offset, nbytes, align=16)
         return self.local[offset:offset + nbytes].view(dtype)
 
-    def peer_ptr(self, rank: int, offset: int = 0) -> int:
+    def peer_ptr(self, rank: int, offset: int = 0, nbytes: int = 0) -> int:
+        self.check_range(offset, nbytes, rank)
         return self.ptrs[rank] + offset
 
-    def ptr_table_at(self, offset: int) -> torch.Tensor:
+    def ptr_table_at(self, offset: int, nbytes: int = 0) -> torch.Tensor:
+        self.check_range(offset, nbytes)
         return self.ptr_table + offset
 
 

@@ -58,3 +58,17 @@ def test_oversized_message_is_rejected():
     _, a, _ = _pair(slot_bytes=64)
     with pytest.raises(AssertionError):
         a.send(torch.zeros(1000), "fwd")
+
+
+def test_region_rejects_bad_ranges():
+    """Offsets handed to kernels are validated on the host (no GPU needed for the check itself)."""
+    import pytest
+    from megalodon_b200.parallel.symm import SymmetricRegion
+    r = SymmetricRegion.__new__(SymmetricRegion)
+    r.nbytes, r.world = 4096, 2
+    r.check_range(0, 4096)
+    r.check_range(4092, 4, rank=1)
+    for bad in [dict(offset=-4), dict(offset=4096, nbytes=4), dict(offset=2, nbytes=4),
+                dict(offset=0, nbytes=16, rank=2), dict(offset=8, nbytes=16, align=16)]:
+        with pytest.raises(ValueError):
+            r.check_range(**bad)
