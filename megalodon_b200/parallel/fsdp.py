@@ -404,9 +404,13 @@ class FullyShardedDataParallel(nn.Module):
         """Backward of `_FlatViews`: add the gradients autograd produced (everything except weights
         whose GEMM already accumulated into the buffer), then see whether the unit is complete."""
         buf = self._grad_buffer()
+        dsts, srcs = [], []
         for info, g in zip(self._infos, grads):
             if g is not None:
-                buf[info.offset:info.offset + info.numel].add_(g.reshape(-1).to(buf.dtype))
+                dsts.append(buf[info.offset:info.offset + info.numel])
+                srcs.append(g.reshape(-1) if g.dtype == buf.dtype else g.reshape(-1).to(buf.dtype))
+        if dsts:
+            torch._foreach_add_(dsts, srcs)      # a couple of multi-tensor launches instead of one per parameter
         self._post_backward()
 
     # ------------------------------------------------------------------ forward / backward
