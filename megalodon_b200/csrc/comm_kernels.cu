@@ -222,15 +222,59 @@ __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, i
                                             long long shard_n, float scale, O* __restrict__ out,
                                             double* __restrict__ sumsq, bool accumulate) {
   __shared__ float scratch[32];
+  constexpr int kMaxWorld = 8;
+  constexpr int kPer = 16 / sizeof(T);           // elements per 16-byte load
   const long long lo = (long long)rank * shard_n;
+  const T* src[kMaxWorld];
+#pragma unroll
+  for (int p = 0; p < kMaxWorld; ++p) src[p] = p < world ? bufs[(rank + p) % world] + lo : nullptr;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long nvec = (world <= kMaxWorld) ? shard_n / kPer : 0;
   float ss = 0.f;
-  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < shard_n;
-       i += (long long)gridDim.x * blockDim.x) {
+  // every peer's 16 bytes are requested before any is used: up to 8 remote loads in flight per thread,
+  // 512-byte requests per warp on the link
+  for (long long v = tid; v < nvec; v += stride) {
+    uint4 raw[kMaxWorld];
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p)
+      if (p < world) raw[p] = __ldcv(reinterpret_cast<const uint4*>(src[p] + v * kPer));
+    float acc[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int p = 0; p < kMaxWorld; ++p) {
+      if (p < world) {
+        const T* e = reinterpret_cast<const T*>(&raw[p]);
+#pragma unroll
+        for (int j = 0; j < kPer; ++j) acc[j] += to_f(e[j]);
+      }
+    }
+    if constexpr (kPer == 8) {
+      float prev[8];
+      if (accumulate) load8(out + v * 8, prev);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        acc[j] = accumulate ? fmaf(acc[j], scale, prev[j]) : acc[j] * scale;
+        ss = fmaf(acc[j], acc[j], ss);
+      }
+      store8(out + v * 8, acc);
+    } else {
+#pragma unroll
+      for (int j = 0; j < kPer; ++j) {
+        acc[j] *= scale;
+        if (accumulate) acc[j] += to_f(out[v * kPer + j]);
+        ss = fmaf(acc[j], acc[j], ss);
+        out[v * kPer + j] = from_f<O>(acc[j]);
+      }
+    }
+  }
+  for (long long i = nvec * kPer + tid; i < shard_n; i += stride) {     // tail (and world > 8)
     float acc = 0.f;
     for (int p = 0; p < world; ++p) acc += to_f(bufs[(rank + p) % world][lo + i]);
     acc *= scale;
     if (accumulate) acc += to_f(out[i]);
-    ss += acc * acc;
+    ss = fmaf(acc, acc, ss);
     out[i] = from_f<O>(acc);
   }
   ss = block_sum(ss, scratch);
@@ -269,7 +313,7 @@ void reduce_slots(const void* slots, void* out, long long n, int world, int dtyp
 void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
                           double* sumsq, bool accumulate, int in_dtype, int out_dtype, cudaStream_t st) {
   if (shard_n == 0) return;
-  const int grid = (int)std::min<long long>(div_up(shard_n, 256), 148LL * 8);
+  const int grid = (int)std::min<long long>(div_up(shard_n / 8 + 1, 256), 148LL * 4);
   MB_DISPATCH_DTYPE(in_dtype, {
     using T = scalar_t;
     if (out_dtype == kF32 && in_dtype != kF32) {
