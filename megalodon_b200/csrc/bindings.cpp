@@ -635,6 +635,28 @@ void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, do
                            dtype_code(out), stream());
 }
 
+// bufs: int64 device tensor of every rank's staging address; p / m / v fp32 shards updated in place
+void reduce_scatter_adamw(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& p, Tensor& m,
+                          Tensor& v, const OptTensor& low, const OptTensor& sumsq, double lr, double beta1,
+                          double beta2, double eps, double wd, int64_t step) {
+  check_cuda_contig(bufs, "bufs");
+  check_cuda_contig(p, "p");
+  check_cuda_contig(m, "m");
+  check_cuda_contig(v, "v");
+  c10::cuda::CUDAGuard guard(p.device());
+  TORCH_CHECK(bufs.scalar_type() == at::kLong && p.scalar_type() == at::kFloat && m.scalar_type() == at::kFloat &&
+              v.scalar_type() == at::kFloat && m.numel() == p.numel() && v.numel() == p.numel());
+  if (low.has_value()) TORCH_CHECK(low->is_contiguous() && low->numel() == p.numel());
+  if (sumsq.has_value()) TORCH_CHECK(sumsq->scalar_type() == at::kDouble && sumsq->numel() == 1);
+  const bool ok = mb::reduce_scatter_adamw(
+      reinterpret_cast<const void* const*>(bufs.data_ptr<int64_t>()), (int)rank, (int)bufs.numel(), p.numel(),
+      (float)scale, p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
+      low.has_value() ? low->data_ptr() : nullptr, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (float)lr,
+      (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, (int)in_dtype,
+      low.has_value() ? dtype_code(*low) : (int)in_dtype, stream());
+  TORCH_CHECK(ok, "reduce_scatter_adamw: shard must be a multiple of 8 elements, 16-bit gradients, at most 8 ranks");
+}
+
 // out = sum of `world` consecutive slots of out.numel() elements each
 void reduce_slots(const Tensor& slots, Tensor& out, int64_t world) {
   check_cuda_contig(slots, "slots");
@@ -677,6 +699,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fftconv_dk", &fftconv_dk);
   m.def("reduce_slots", &reduce_slots);
   m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
+  m.def("reduce_scatter_adamw", &reduce_scatter_adamw);
   m.def("time_sums", &time_sums);
   m.def("affine_apply", &affine_apply);
   m.def("dropout", &dropout);

@@ -23,6 +23,8 @@
 // `*err`, skips its remaining work and returns, so a missing peer shows up as a
 // Python exception instead of a hung GPU.  Only plain (non-multimem) peer
 // accesses are used here.
+#include <cmath>
+
 #include "common.cuh"
 #include "kernels.h"
 
@@ -281,6 +283,66 @@ __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, i
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
 }
 
+// Reduce-scatter fused with the sharded AdamW update (for runs without global-norm clipping, where the
+// update of a shard needs nothing but its own reduced gradient): pull this rank's slice of every peer's
+// staged gradient, sum in fp32, apply the 1/dp scale, then update the fp32 master weights and both
+// moments in place and write the compute-dtype copy that the next forward's all-gather reads.  The
+// reduced gradient is never written to memory; `sumsq` still receives its squared norm for logging.
+template <typename T, typename Lo>
+__global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, int rank, int world, long long shard_n,
+                                            float scale, float* __restrict__ p, float* __restrict__ m,
+                                            float* __restrict__ v, Lo* __restrict__ low, double* __restrict__ sumsq,
+                                            float lr, float beta1, float beta2, float eps, float wd, float bc1,
+                                            float bc2_sqrt) {
+  __shared__ float scratch[32];
+  constexpr int kMaxWorld = 8;
+  static_assert(sizeof(T) == 2, "gradients are staged in a 16-bit type");
+  const long long lo = (long long)rank * shard_n;
+  const T* src[kMaxWorld];
+#pragma unroll
+  for (int q = 0; q < kMaxWorld; ++q) src[q] = q < world ? bufs[(rank + q) % world] + lo : nullptr;
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  const long long nvec = shard_n / 8;
+  const float step = lr / bc1;
+  const float decay = 1.f - lr * wd;
+  float ss = 0.f;
+  for (long long i = tid; i < nvec; i += stride) {
+    uint4 raw[kMaxWorld];
+#pragma unroll
+    for (int q = 0; q < kMaxWorld; ++q)
+      if (q < world) raw[q] = __ldcv(reinterpret_cast<const uint4*>(src[q] + i * 8));
+    float g[8], pv[8], mv[8], vv[8];
+    load8(p + i * 8, pv);
+    load8(m + i * 8, mv);
+    load8(v + i * 8, vv);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) g[j] = 0.f;
+#pragma unroll
+    for (int q = 0; q < kMaxWorld; ++q) {
+      if (q < world) {
+        const T* e = reinterpret_cast<const T*>(&raw[q]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) g[j] += to_f(e[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const float gj = g[j] * scale;
+      ss = fmaf(gj, gj, ss);
+      mv[j] = beta1 * mv[j] + (1.f - beta1) * gj;
+      vv[j] = beta2 * vv[j] + (1.f - beta2) * gj * gj;
+      pv[j] = pv[j] * decay - step * mv[j] / (sqrtf(vv[j]) / bc2_sqrt + eps);
+    }
+    store8(m + i * 8, mv);
+    store8(v + i * 8, vv);
+    store8(p + i * 8, pv);
+    if (low != nullptr) store8(low + i * 8, pv);
+  }
+  ss = block_sum(ss, scratch);
+  if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
+}
+
 template <typename T>
 __global__ void reduce_slots_kernel(const T* __restrict__ slots, T* __restrict__ out, long long n, int world) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
@@ -326,6 +388,29 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
                                                              (T*)out, sumsq, accumulate);
     }
   });
+}
+
+// shard_n must be a multiple of 8 and world <= 8; `low` may be null.  Returns false otherwise.
+bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
+                          float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
+                          float wd, int step, int in_dtype, int low_dtype, cudaStream_t st) {
+  if (shard_n == 0) return true;
+  if (shard_n % 8 != 0 || world > 8 || in_dtype == kF32 || (low != nullptr && low_dtype != in_dtype)) return false;
+  const float bc1 = 1.f - powf(beta1, (float)step);
+  const float bc2s = sqrtf(1.f - powf(beta2, (float)step));
+  const int grid = (int)std::min<long long>(div_up(shard_n / 8, 256), 148LL * 4);
+  if (in_dtype == kBF16) {
+    prefer_max_shared(reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16>);
+    reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(
+        (const __nv_bfloat16* const*)bufs, rank, world, shard_n, scale, p, m, v, (__nv_bfloat16*)low, sumsq, lr, beta1,
+        beta2, eps, wd, bc1, bc2s);
+  } else {
+    prefer_max_shared(reduce_scatter_adamw_kernel<__half, __half>);
+    reduce_scatter_adamw_kernel<__half, __half><<<grid, 256, 0, st>>>(
+        (const __half* const*)bufs, rank, world, shard_n, scale, p, m, v, (__half*)low, sumsq, lr, beta1, beta2, eps, wd,
+        bc1, bc2s);
+  }
+  return true;
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,

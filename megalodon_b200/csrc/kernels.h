@@ -97,6 +97,10 @@ void fftconv_dk(const void* dy, const void* x, float* acc_spec, float* dk, long 
 bool gemv_small_m(const void* x, const void* w, const void* bias, int bias_dtype, void* y, int M, int N, int K,
                   long long ldx, long long ldw, long long ldy, float alpha, int act, int in_dtype, int out_dtype,
                   cudaStream_t st);
+// reduce-scatter fused with the sharded AdamW update (comm_kernels.cu); false if the shapes do not qualify
+bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
+                          float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
+                          float wd, int step, int in_dtype, int low_dtype, cudaStream_t st);
 // Whether GEMMs with more than 128 rows run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); on by default.
 void gemm_set_cta_pairs(bool on);
 int gemm_pair_max_active_clusters();

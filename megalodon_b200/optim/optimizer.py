@@ -11,6 +11,7 @@ with `.grad` (then it is a plain AdamW).
 """
 from __future__ import annotations
 
+import functools
 import logging
 from typing import Iterable
 
@@ -46,6 +47,43 @@ class FusedAdamW(Optimizer):
         defaults = dict(lr=lr, betas=betas, eps=eps, weight_decay=weight_decay)
         super().__init__(params, defaults)
 
+    def _state_of(self, p):
+        st = self.state[p]
+        if not st:
+            st["step"] = 0
+            st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
+            st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+        return st
+
+    def fuse_with_reduce_scatter(self, enabled: bool = True) -> int:
+        """Run the update of every FSDP shard inside the peer-memory reduce-scatter kernel of its unit
+        (`SymmetricReduceScatter.reduce_scatter_adamw`), during backward, instead of in `step()`.
+        Only meaningful without global-norm gradient clipping - the update of a shard then depends
+        on nothing but its own reduced gradient - and without gradient accumulation over several
+        backward passes (an accumulating pass falls back to the separate kernels).  `step()` still
+        has to be called: it advances the step counters.  Returns the number of shards switched."""
+        n = 0
+        for group in self.param_groups:
+            for p in group["params"]:
+                unit = getattr(p, "_fsdp_unit", None)
+                if unit is None or not unit.mixed_precision or unit.world_size == 1:
+                    continue
+                p._update_in_backward = functools.partial(self._update_in_backward, p, group) if enabled else None
+                n += 1
+        return n
+
+    @torch.no_grad()
+    def _update_in_backward(self, p, group, reducer, flat_grad, scale, sumsq) -> None:
+        unit = p._fsdp_unit
+        st = self._state_of(p)
+        if p._lowp_shard is None:
+            p._lowp_shard = torch.empty(p.numel(), dtype=unit.compute_dtype, device=p.device)
+        b1, b2 = group["betas"]
+        reducer.reduce_scatter_adamw(flat_grad, p.data, st["exp_avg"], st["exp_avg_sq"], p._lowp_shard, scale, sumsq,
+                                     lr=group["lr"], beta1=b1, beta2=b2, eps=group["eps"],
+                                     weight_decay=group["weight_decay"], step=st["step"] + 1)
+        p._updated_in_backward = True
+
     @torch.no_grad()
     def step(self, closure=None):
         loss = None
@@ -63,14 +101,17 @@ class FusedAdamW(Optimizer):
                     root = getattr(unit, "_root", unit)
                     scale_ptr = root._clip_coef
                     roots.add(root)
+                if getattr(p, "_updated_in_backward", False):
+                    # the reduce-scatter kernel already applied this step's update
+                    p._updated_in_backward = False
+                    self._state_of(p)["step"] += 1
+                    p._master_version = getattr(p, "_master_version", 0) + 1
+                    p._lowp_version = (p._version, p._master_version)
+                    continue
                 grad = p.grad if p.grad is not None else getattr(p, "_grad_shard", None)
                 if grad is None:
                     continue
-                st = self.state[p]
-                if not st:
-                    st["step"] = 0
-                    st["exp_avg"] = torch.zeros_like(p, dtype=torch.float32)
-                    st["exp_avg_sq"] = torch.zeros_like(p, dtype=torch.float32)
+                st = self._state_of(p)
                 st["step"] += 1
                 low = None
                 if unit is not None and unit.mixed_precision:

@@ -496,6 +496,17 @@ class FullyShardedDataParallel(nn.Module):
             stream = root._comm_stream
             if stream is not None:
                 stream.wait_stream(torch.cuda.current_stream())
+            update = getattr(p, "_update_in_backward", None)
+            if update is not None and not accumulate:
+                # no clipping in this run: the optimiser's update of the shard rides in the same kernel
+                with (torch.cuda.stream(stream) if stream is not None else _nullcontext()):
+                    update(fused_rs, flat_grad, 1.0 / self.gradient_divide_factor, root._fused_sumsq)
+                if stream is not None:
+                    flat_grad.record_stream(stream)
+                    root._pending.append(True)
+                if self.reshard_after_forward and not self._is_root:
+                    self._free_full()
+                return None
             with (torch.cuda.stream(stream) if stream is not None else _nullcontext()):
                 fused_rs.reduce_scatter(flat_grad, shard, 1.0 / self.gradient_divide_factor,
                                         root._fused_sumsq, accumulate)

@@ -345,6 +345,30 @@ class SymmetricReduceScatter:
         ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
         ext.reduce_scatter_sumsq(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, out_shard, sumsq, accumulate)
 
+    @torch.no_grad()
+    def reduce_scatter_adamw(self, flat_grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor,
+                             exp_avg_sq: torch.Tensor, low: Optional[torch.Tensor], scale: float,
+                             sumsq: Optional[torch.Tensor], *, lr: float, beta1: float, beta2: float, eps: float,
+                             weight_decay: float, step: int) -> None:
+        """Reduce-scatter fused with the AdamW update of this rank's shard (see
+        `reduce_scatter_adamw_kernel`): the reduced gradient is consumed in registers, `master`,
+        `exp_avg`, `exp_avg_sq` (fp32 shards) are updated in place and `low` receives the
+        compute-dtype copy of the new weights."""
+        from ..ops._ext import require
+        from ..ops.cuda_ops import _DT
+        ext = require()
+        n = flat_grad.numel()
+        assert n * flat_grad.element_size() <= self.stage_bytes and flat_grad.dtype == self.dtype
+        assert n == master.numel() * self.world
+        t = self._toggle
+        self._toggle ^= 1
+        stage = self.region.view(t * self.stage_bytes, n * flat_grad.element_size(), flat_grad.dtype)
+        stage.copy_(flat_grad.view(-1))
+        self.epoch += 1
+        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
+        ext.reduce_scatter_adamw(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, master, exp_avg, exp_avg_sq,
+                                 low, sumsq, lr, beta1, beta2, eps, weight_decay, step)
+
     def check(self) -> None:
         code = int(self._err.item())
         if code:

@@ -508,3 +508,34 @@ def test_fftconv_native(dtype, B, D, L):
         f0 = torch.view_as_real(ops.rfft(x, flip))
         f1 = torch.view_as_real(reference.rfft(x, flip))
         _close(f0, f1, 5e-3 * max(1.0, f1.abs().max().item()), 2e-3, f"rfft flip={flip}")
+
+
+def test_reduce_scatter_adamw_kernel_two_local_ranks():
+    """The fused reduce-scatter + AdamW kernel on one GPU: the two 'ranks' are two staging buffers
+    in local memory, each rank's shard is checked against the AdamW formula on the summed gradient."""
+    from megalodon_b200.ops._ext import require
+    from megalodon_b200.ops.cuda_ops import _DT
+    ext = require()
+    torch.manual_seed(13)
+    dev = _dev()
+    world, shard_n = 2, 4096 + 64
+    stage = [torch.randn(world * shard_n, device=dev).bfloat16() for _ in range(world)]
+    bufs = torch.tensor([t.data_ptr() for t in stage], dtype=torch.int64, device=dev)
+    lr, b1, b2, eps, wd, step, scale = 3e-3, 0.9, 0.95, 1e-8, 0.1, 3, 0.5
+    for rank in range(world):
+        p = torch.randn(shard_n, device=dev)
+        m = torch.randn(shard_n, device=dev) * 0.1
+        v = torch.rand(shard_n, device=dev) * 0.1
+        low = torch.empty(shard_n, device=dev, dtype=torch.bfloat16)
+        sumsq = torch.zeros((), device=dev, dtype=torch.float64)
+        g = scale * sum(t.float()[rank * shard_n:(rank + 1) * shard_n] for t in stage)
+        m_ref = b1 * m + (1 - b1) * g
+        v_ref = b2 * v + (1 - b2) * g * g
+        p_ref = p * (1 - lr * wd) - (lr / (1 - b1 ** step)) * m_ref / (v_ref.sqrt() / (1 - b2 ** step) ** 0.5 + eps)
+        ext.reduce_scatter_adamw(bufs, rank, _DT[torch.bfloat16], scale, p, m, v, low, sumsq, lr, b1, b2, eps, wd, step)
+        torch.cuda.synchronize()
+        _close(p, p_ref, 1e-5, 1e-5, "p")
+        _close(m, m_ref, 1e-6, 1e-5, "m")
+        _close(v, v_ref, 1e-6, 1e-5, "v")
+        _close(low, p_ref, 2e-2, 1e-2, "low")
+        assert abs(sumsq.item() - (g.double() ** 2).sum().item()) < 1e-3 * (g.double() ** 2).sum().item()

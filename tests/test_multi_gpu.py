@@ -306,3 +306,56 @@ def test_fsdp_with_peer_memory_reduce_scatter_matches_nccl():
         for (l0, n0), (l1, n1) in zip(r[False], r[True]):
             assert abs(l0 - l1) < 5e-2, r
             assert abs(n0 - n1) < 0.1 * max(1.0, n0), r
+
+
+def _fsdp_rs_adamw_case(rank, world):
+    """No clipping: NCCL reduce-scatter + separate AdamW kernel vs the update fused into the
+    peer-memory reduce-scatter kernel."""
+    from megalodon_b200.config import ModelConf, OptimConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.optim import build_optimizer
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.parallel.symm import enable_peer_reduce_scatter
+    from megalodon_b200.utils import set_random_seed
+    initialize_model_parallel(1, 1)
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    toks = torch.randint(0, 512, (4, 257), generator=torch.Generator().manual_seed(0))
+    toks = toks[rank * 2:(rank + 1) * 2].cuda()
+    x, y = toks[:, :-1], toks[:, 1:]
+    out = {}
+    for fused in (False, True):
+        set_random_seed(0)
+        model = build_model(cfg, "bf16", False, True)
+        opt, sched = build_optimizer(model, OptimConf(lr=3e-3, warmup=2, clip=0.0), 20, "bf16")
+        rs = None
+        if fused:
+            rs = enable_peer_reduce_scatter(model, timeout_s=20.0)
+            assert opt.fuse_with_reduce_scatter() > 0
+        curve = []
+        for _ in range(4):
+            loss = model(x, targets=y)[0].mean()
+            loss.backward()
+            model.grad_all_reduce()
+            model.finish_backward()
+            opt.step(); sched.step(); opt.zero_grad()
+            curve.append(loss.item())
+        if fused:
+            torch.cuda.synchronize()
+            rs.check()
+        cuda_ops.check_kernel_errors()
+        shard = torch.cat([p.detach().float().reshape(-1)[:4096] for p in model.parameters()])
+        out[fused] = (curve, shard.cpu())
+    return out
+
+
+def test_fsdp_reduce_scatter_fused_with_adamw_matches_separate_kernels():
+    _need_gpus(2)
+    for r in _run(_fsdp_rs_adamw_case):
+        (c0, s0), (c1, s1) = r[False], r[True]
+        for l0, l1 in zip(c0, c1):
+            assert abs(l0 - l1) < 5e-2, (c0, c1)
+        assert c1[-1] < c1[0], c1                       # it actually trains
+        assert (s0 - s1).abs().max().item() < 2e-2, (s0 - s1).abs().max().item()
