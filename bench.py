@@ -42,7 +42,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ckpt-layers", type=int, default=None,
-                    help="checkpoint only the first K layers (default: all at N=1, 20 at N=2, none from N=4)")
+                    help="checkpoint only the first K layers (default: 28 at N=1, 16 at N=2, none from N=4)")
     ap.add_argument("--kernel-profile", default=None,
                     help="after the timed regions, run one more step under torch.profiler and write a per-kernel "
                          "summary to this path (rank number appended); never part of a reported number")
@@ -161,9 +161,15 @@ def main():
     cfg.layerwise_ckpt = (not args.no_ckpt) and chunks_local > 2
     if args.ckpt_layers is not None:
         cfg.ckpt_layers = args.ckpt_layers
+    elif chunks_local == 8:
+        # N = 1: 138 GB of optimiser state; four un-checkpointed layers bring the peak to 154 GB allocated
+        # (170 GB reserved) and save their recomputation
+        cfg.ckpt_layers = 28
     elif chunks_local == 4:
-        # four chunks per GPU (N = 2): state 86 GB + 4 GB of activations per un-checkpointed layer
-        cfg.ckpt_layers = 20
+        # N = 2: state 86 GB + about 3 GB of activations per un-checkpointed layer; 16 of 32 checkpointed
+        # peaks at 139 GB allocated (148 GB reserved).  Ten checkpointed layers (170 GB reserved) ran into
+        # allocator retries and was slower.
+        cfg.ckpt_layers = 16
     set_random_seed(1234)
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)
