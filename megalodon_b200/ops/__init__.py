@@ -84,6 +84,9 @@ def sequence_norm(x, gamma, beta, padding_mask=None, num_groups=None, eps: float
                   length_last: bool = False):
     if native_for(x):
         return _cuda().sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
+    if _cpu_native_ok(x, gamma, beta):
+        return require_ext().cpu_sequence_norm_fwd(x, gamma, beta, padding_mask, int(num_groups or 0), float(eps),
+                                                   bool(length_last))
     return reference.sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
 
 
@@ -91,12 +94,18 @@ def sequence_norm(x, gamma, beta, padding_mask=None, num_groups=None, eps: float
 def ema_parameters(p, q, gamma, hx, length: int):
     if native_for(p):
         return _cuda().ema_parameters(p, q, gamma, hx, length)
+    if (not p.is_cuda and have_ext() and not (torch.is_grad_enabled() and any(
+            t is not None and t.requires_grad for t in (p, q, gamma, hx)))):
+        k, b = require_ext().cpu_ema_parameters_fwd(p, q, gamma, hx, int(length))
+        return k, b
     return reference.ema_parameters(p, q, gamma, hx, length)
 
 
 def ema_hidden(x, p, q, hx):
     if native_for(x):
         return _cuda().ema_hidden(x, p, q, hx)
+    if _cpu_native_ok(x, p, q, hx):
+        return require_ext().cpu_ema_hidden_fwd(x, p, q, hx)
     return reference.ema_hidden(x, p, q, hx)
 
 

@@ -55,3 +55,43 @@ def test_cpu_ops_leave_autograd_to_pytorch():
     y = ops.timestep_norm(x, cnt, pm, pv, torch.zeros(8), torch.zeros(8), None, 2, 1e-5, 1.0)[0]
     y.sum().backward()
     assert x.grad is not None
+
+
+@needs_ext
+@pytest.mark.parametrize("groups,length_last,masked", [(None, False, False), (None, True, True), (4, False, True),
+                                                       (4, True, False)])
+def test_cpu_sequence_norm_forward(groups, length_last, masked):
+    torch.manual_seed(2)
+    B, L, H = 2, 19, 16
+    x = torch.randn(B, H, L) if length_last else torch.randn(B, L, H)
+    gamma, beta = torch.randn(H), torch.randn(H)
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool)
+        mask[0, 15:] = True
+    with torch.no_grad():
+        got = ops.sequence_norm(x, gamma, beta, mask, groups, 1e-5, length_last)
+        ref = reference.sequence_norm(x, gamma, beta, mask, groups, 1e-5, length_last)
+    assert got.shape == ref.shape and torch.allclose(got, ref, atol=1e-5, rtol=1e-5)
+
+
+@needs_ext
+@pytest.mark.parametrize("with_h", [True, False])
+def test_cpu_ema_parameters_and_hidden_forward(with_h):
+    torch.manual_seed(3)
+    B, L, D, N = 2, 23, 6, 4
+    alpha, delta = torch.rand(D, N) * 0.5 + 0.1, torch.rand(D, N) * 0.5 + 0.1
+    q = torch.polar(1 - alpha * delta, torch.rand(D, N) * 3)
+    gamma = torch.view_as_complex(torch.randn(D, N, 2)) * 0.25
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2)) if with_h else None
+    x = torch.randn(B, D, L)
+    with torch.no_grad():
+        k0, b0 = ops.ema_parameters(alpha, q, gamma, hx, L)
+        k1, b1 = reference.ema_parameters(alpha, q, gamma, hx, L)
+        h0 = ops.ema_hidden(x, alpha, q, hx)
+        h1 = reference.ema_hidden(x, alpha, q, hx)
+    assert torch.allclose(k0, k1, atol=1e-5, rtol=1e-5)
+    assert (b0 is None) == (b1 is None)
+    if b0 is not None:
+        assert torch.allclose(b0, b1, atol=1e-5, rtol=1e-5)
+    assert torch.allclose(torch.view_as_real(h0), torch.view_as_real(h1), atol=1e-5, rtol=1e-5)
