@@ -30,7 +30,7 @@ NVCC_FLAGS = [
 setup(
     name="megalodon_b200",
     version="0.1.0",
-    packages=find_packages(include=["megalodon_b200", "megalodon_b200.*"]),
+    packages=find_packages(include=["megalodon_b200", "megalodon_b200.*", "megalodon"]),
     ext_modules=[
         CUDAExtension(
             "megalodon_b200._C",

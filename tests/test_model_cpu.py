@@ -234,3 +234,32 @@ def test_decode_session_matches_cache_path():
             tok = ref[:, -1].argmax(-1)
     model.train()        # the module tree must stay acyclic after forwards
     model.eval()
+
+
+def test_reference_import_paths_resolve_to_this_package():
+    """`megalodon.*` module paths of the reference are the same module objects as `megalodon_b200.*`."""
+    import megalodon.model.mega as a
+    import megalodon_b200.model.mega as b
+    assert a is b
+    from megalodon.distributed import initialize_model_parallel, get_chunk_parallel_world_size  # noqa: F401
+    from megalodon.model.mega import build_model as bm
+    from megalodon.modules import FusedLayerNorm, FusedRMSNorm, MovingAverageGatedAttention, TimestepNorm  # noqa: F401
+    from megalodon.modules.fused_ops import (ema_hidden, ema_parameters, fftconv, fused_fftconv_bwd,  # noqa: F401
+                                             fused_fftconv_fwd, memory_efficient_dropout, swift_efficient_attention,
+                                             swift_efficient_attention_bwd, swift_efficient_attention_fwd)
+    from megalodon.optim import build_optimizer, rescale_grads  # noqa: F401
+    from megalodon.utils import clip_grad_norm_, init_cache, set_random_seed  # noqa: F401
+    from megalodon.reloading import reload_model  # noqa: F401
+    from megalodon.inference import inference  # noqa: F401
+    from megalodon.generation import generate  # noqa: F401
+    import megalodon_b200.models.mega as c
+    assert bm is c.build_model
+    x = torch.randn(2, 3, 9)
+    k = torch.randn(3, 9)
+    g = torch.randn(2, 3, 9)
+    dx, dk = fused_fftconv_bwd(g, x, k)
+    assert dx.shape == x.shape and dk.shape == k.shape
+    q = torch.randn(1, 5, 2, 4)
+    v = torch.randn(1, 5, 2, 6)
+    dq, dk2, dv = swift_efficient_attention_bwd(torch.randn(1, 5, 2, 6), q, q.clone(), v)
+    assert dq.shape == q.shape and dv.shape == v.shape
