@@ -30,45 +30,52 @@ class TokenizerConf:
 
 @dataclass
 class OptimConf:
-    lr: float = 1e-3
-    warmup: int = 2000
-    weight_decay: float = 0.1
+    # AdamW on the fp32 master shards
+    lr: float = 1e-3                 # peak learning rate, reached after `warmup` steps
+    warmup: int = 2000               # linear warm-up steps starting from lr * lr_init_ratio
+    weight_decay: float = 0.1        # decoupled
     epsilon: float = 1e-8
     beta1: float = 0.9
     beta2: float = 0.98
-    clip: float = 1.0
+    clip: float = 1.0                # global-norm clipping threshold; 0 disables clipping
+    # schedule after warm-up: "linear" | "cosine" | "constant"
     scheduler: str = "linear"
     lr_init_ratio: float = 1e-4
-    lr_end_ratio: float = 0.01
-    cycles: float = 1.0
+    lr_end_ratio: float = 0.01       # final lr as a fraction of the peak
+    cycles: float = 1.0              # cosine cycles over the decay phase
 
 
 @dataclass
 class ModelConf:
+    # ---- sizes
     num_layers: int = 8
-    model_dim: int = 1024
-    z_dim: int = 256
-    value_dim: int = 2048
+    model_dim: int = 1024            # residual stream D
+    z_dim: int = 256                 # shared query/key width S (all heads together)
+    value_dim: int = 2048            # value / gate width E (all heads together)
     num_heads: int = 1
     ffn_hidden_dim: int = 2048
-    cema_ndim: int = 16
-    chunk_size: int = 2048
+    cema_ndim: int = 16              # complex EMA states per feature
+    chunk_size: int = 2048           # attention never crosses a chunk
+    vocab_size: int = -1             # -1: filled in from the tokenizer
+    output_size: int = -1            # -1: same as vocab_size
+    # ---- attention implementation: None = unfused (post-softmax dropout), "swift" / "fused" = kernels (DropKey)
     efficient_attn: Optional[str] = None
-    init_mode: str = "he"
-    vocab_size: int = -1
-    output_size: int = -1
-    norm_num_groups: int = 32
+    init_mode: str = "he"            # none | bert | he | gaussian | xavier
+    # ---- normalisation
+    norm_num_groups: int = 32        # TimestepNorm groups
     norm_affine: bool = True
     norm_eps: float = 1e-5
     rope_base: Optional[float] = None
+    # ---- regularisation
     dropout: float = 0.0
     hidden_dropout: float = 0.0
     attention_dropout: float = 0.0
-    swiglu: bool = False
-    rescale_nffn: bool = False
-    scale_emb: bool = False
-    share_emb: bool = False
-    layerwise_ckpt: bool = False
+    # ---- variants
+    swiglu: bool = False             # SiLU(fc1 x) * fc3 x instead of SiLU(fc1 x)
+    rescale_nffn: bool = False       # learnable per-layer scale 0.1 * 0.5^layer on the FFN branch
+    scale_emb: bool = False          # multiply embeddings by sqrt(D)
+    share_emb: bool = False          # tie output projection and embedding
+    layerwise_ckpt: bool = False     # activation checkpointing per block
     # with layerwise_ckpt: checkpoint only the first `ckpt_layers` blocks (None = all of them); the
     # rest keep their activations, which trades spare memory for less recomputation
     ckpt_layers: Optional[int] = None
