@@ -3,7 +3,10 @@
 // `megalodon_b200._C`.
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAException.h>
 #include <torch/extension.h>
+
+#include <type_traits>
 
 #include <optional>
 #include <tuple>
@@ -668,49 +671,66 @@ void reduce_slots(const Tensor& slots, Tensor& out, int64_t world) {
 
 }  // namespace
 
+// Every operator below launches kernels on the current stream.  `checked(fn)` wraps a binding so that
+// a failed launch (bad configuration, a sticky error of an earlier kernel) surfaces as a Python
+// exception at the call that hit it instead of at some later synchronisation point.
+template <typename R, typename... A>
+auto checked(R (*fn)(A...)) {
+  return [fn](A... args) -> R {
+    if constexpr (std::is_void_v<R>) {
+      fn(args...);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+    } else {
+      R out = fn(args...);
+      C10_CUDA_KERNEL_LAUNCH_CHECK();
+      return out;
+    }
+  };
+}
+
 void register_cpu_ops(pybind11::module& m);      // cpu_ops.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_cpu_ops(m);
-  m.def("rms_norm_fwd", &rms_norm_fwd);
-  m.def("rms_norm_bwd", &rms_norm_bwd);
-  m.def("layer_norm_fwd", &layer_norm_fwd);
-  m.def("layer_norm_bwd", &layer_norm_bwd);
-  m.def("timestep_norm_fwd", &timestep_norm_fwd);
-  m.def("timestep_norm_bwd", &timestep_norm_bwd);
-  m.def("cema_fwd", &cema_fwd);
-  m.def("cema_bwd", &cema_bwd);
-  m.def("swiglu_fwd", &swiglu_fwd);
-  m.def("swiglu_bwd", &swiglu_bwd);
-  m.def("rotary", &rotary);
-  m.def("cross_entropy_fwd", &cross_entropy_fwd);
-  m.def("cross_entropy_bwd", &cross_entropy_bwd);
-  m.def("adamw_step", &adamw_step);
-  m.def("sum_squares", &sum_squares);
-  m.def("scale_by_ptr", &scale_by_ptr);
-  m.def("clip_coef", &clip_coef);
-  m.def("gemm", &gemm, py::arg("A"), py::arg("B"), py::arg("out"), py::arg("bias"), py::arg("act"), py::arg("a_mn"),
+  m.def("rms_norm_fwd", checked(&rms_norm_fwd));
+  m.def("rms_norm_bwd", checked(&rms_norm_bwd));
+  m.def("layer_norm_fwd", checked(&layer_norm_fwd));
+  m.def("layer_norm_bwd", checked(&layer_norm_bwd));
+  m.def("timestep_norm_fwd", checked(&timestep_norm_fwd));
+  m.def("timestep_norm_bwd", checked(&timestep_norm_bwd));
+  m.def("cema_fwd", checked(&cema_fwd));
+  m.def("cema_bwd", checked(&cema_bwd));
+  m.def("swiglu_fwd", checked(&swiglu_fwd));
+  m.def("swiglu_bwd", checked(&swiglu_bwd));
+  m.def("rotary", checked(&rotary));
+  m.def("cross_entropy_fwd", checked(&cross_entropy_fwd));
+  m.def("cross_entropy_bwd", checked(&cross_entropy_bwd));
+  m.def("adamw_step", checked(&adamw_step));
+  m.def("sum_squares", checked(&sum_squares));
+  m.def("scale_by_ptr", checked(&scale_by_ptr));
+  m.def("clip_coef", checked(&clip_coef));
+  m.def("gemm", checked(&gemm), py::arg("A"), py::arg("B"), py::arg("out"), py::arg("bias"), py::arg("act"), py::arg("a_mn"),
         py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false);
-  m.def("gemv_small_m", &gemv_small_m);
-  m.def("rfft_rows", &rfft_rows);
-  m.def("fftconv_apply", &fftconv_apply);
-  m.def("fftconv_dk", &fftconv_dk);
-  m.def("reduce_slots", &reduce_slots);
-  m.def("reduce_scatter_sumsq", &reduce_scatter_sumsq);
-  m.def("reduce_scatter_adamw", &reduce_scatter_adamw);
-  m.def("time_sums", &time_sums);
-  m.def("affine_apply", &affine_apply);
-  m.def("dropout", &dropout);
-  m.def("ema_parameters_fwd", &ema_parameters_fwd);
-  m.def("ema_parameters_bwd", &ema_parameters_bwd);
-  m.def("attn_softmax_fwd", &attn_softmax_fwd);
-  m.def("attn_softmax_bwd", &attn_softmax_bwd);
-  m.def("p2p_send", &p2p_send);
-  m.def("p2p_recv", &p2p_recv);
-  m.def("peer_barrier", &peer_barrier);
+  m.def("gemv_small_m", checked(&gemv_small_m));
+  m.def("rfft_rows", checked(&rfft_rows));
+  m.def("fftconv_apply", checked(&fftconv_apply));
+  m.def("fftconv_dk", checked(&fftconv_dk));
+  m.def("reduce_slots", checked(&reduce_slots));
+  m.def("reduce_scatter_sumsq", checked(&reduce_scatter_sumsq));
+  m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw));
+  m.def("time_sums", checked(&time_sums));
+  m.def("affine_apply", checked(&affine_apply));
+  m.def("dropout", checked(&dropout));
+  m.def("ema_parameters_fwd", checked(&ema_parameters_fwd));
+  m.def("ema_parameters_bwd", checked(&ema_parameters_bwd));
+  m.def("attn_softmax_fwd", checked(&attn_softmax_fwd));
+  m.def("attn_softmax_bwd", checked(&attn_softmax_bwd));
+  m.def("p2p_send", checked(&p2p_send));
+  m.def("p2p_recv", checked(&p2p_recv));
+  m.def("peer_barrier", checked(&peer_barrier));
   m.def("gemm_set_cta_pairs", [](bool on) { mb::gemm_set_cta_pairs(on); });
   m.def("gemm_pair_max_active_clusters", []() { return mb::gemm_pair_max_active_clusters(); });
-  m.def("allreduce_sumsq", &allreduce_sumsq);
+  m.def("allreduce_sumsq", checked(&allreduce_sumsq));
 }
