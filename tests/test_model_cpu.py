@@ -263,3 +263,28 @@ def test_reference_import_paths_resolve_to_this_package():
     v = torch.randn(1, 5, 2, 6)
     dq, dk2, dv = swift_efficient_attention_bwd(torch.randn(1, 5, 2, 6), q, q.clone(), v)
     assert dq.shape == q.shape and dv.shape == v.shape
+
+
+def test_partial_checkpointing_gives_the_same_gradients():
+    """Checkpointing only the first k blocks (ModelConf.ckpt_layers) changes memory, not numbers."""
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.utils import set_random_seed
+    base = dict(num_layers=3, model_dim=64, num_heads=2, z_dim=32, value_dim=64, ffn_hidden_dim=64, cema_ndim=4,
+                chunk_size=8, vocab_size=50, swiglu=True, norm_num_groups=8)
+    toks = torch.randint(0, 50, (2, 17))
+    x, y = toks[:, :-1], toks[:, 1:]
+    grads = []
+    for kw in (dict(layerwise_ckpt=False), dict(layerwise_ckpt=True, ckpt_layers=1), dict(layerwise_ckpt=True)):
+        set_random_seed(0)
+        model = build_model(ModelConf(**base, **kw), "fp32", device=torch.device("cpu"))
+        model._wrapped.seq_microbatch_chunks = 1
+        from megalodon_b200.parallel.checkpoint import CheckpointWrapper
+        n_wrapped = sum(isinstance(m, CheckpointWrapper) for m in model.modules())
+        assert n_wrapped == (0 if not kw["layerwise_ckpt"] else kw.get("ckpt_layers", 3))
+        loss = model(x, targets=y)[0].mean()
+        loss.backward()
+        model.finish_backward()
+        grads.append(torch.cat([p._grad_shard.float().reshape(-1) for p in model.parameters()]))
+    assert torch.allclose(grads[0], grads[1], atol=1e-6, rtol=1e-5)
+    assert torch.allclose(grads[0], grads[2], atol=1e-6, rtol=1e-5)
