@@ -53,6 +53,8 @@ def parse() -> TrainerConf:
     ap.add_argument("--tokenizer_path", default=None)
     ap.add_argument("--vocab_size", type=int, default=32000)
     ap.add_argument("--layerwise_ckpt", type=lambda s: s.lower() == "true", default=True)
+    ap.add_argument("--ckpt_layers", type=int, default=None,
+                    help="with --layerwise_ckpt: checkpoint only the first K blocks (default: all)")
     ap.add_argument("--seq_microbatch_chunks", type=int, default=1)
     ap.add_argument("--shard_over_chunk_group", type=lambda s: s.lower() == "true", default=True)
     ap.add_argument("--peer_transport", type=lambda s: s.lower() == "true", default=True)
@@ -62,6 +64,7 @@ def parse() -> TrainerConf:
     if model.vocab_size <= 0:
         model.vocab_size = a.vocab_size
     model.layerwise_ckpt = a.layerwise_ckpt
+    model.ckpt_layers = a.ckpt_layers
     model.efficient_attn = model.efficient_attn or "fused"
     optim = OptimConf(**{f.name: getattr(a, f.name) for f in dataclasses.fields(OptimConf)})
     cfg = TrainerConf(model=model, optim=optim, tokenizer=TokenizerConf(path=a.tokenizer_path))
