@@ -58,7 +58,11 @@ def sample_top_p(probs: torch.Tensor, p: float) -> torch.Tensor:
 def generate(model, dtype: str, tokenizer, prompt: Optional[List[str]] = None, max_prompt_len: int = 256,
              max_gen_len: int = 256, use_sampling: bool = False, temp: float = 1.0, top_k: int = 0,
              top_p: float = 0.0, remove_prompts: bool = True,
-             truncate_chunks: Optional[int] = None) -> List[List[int]]:
+             truncate_chunks: Optional[int] = None,
+             use_decode_session: Optional[bool] = None) -> List[List[int]]:
+    """`use_decode_session`: run the one-token steps through `decoding.DecodeSession` (fixed-shape
+    state, replayed from a CUDA graph on a single GPU) instead of the growing-cache path; same tokens,
+    a fraction of the per-token cost.  Default: on for CUDA models without tensor parallelism."""
     model.eval()
     device = next(model.parameters()).device
     if prompt is not None:
@@ -110,9 +114,22 @@ def generate(model, dtype: str, tokenizer, prompt: Optional[List[str]] = None, m
             cache = truncate_cache(cache, stats_only)
 
     logger.debug(f"prev_pos={prev_pos}, start_pos={start_pos}, end_pos={end_pos}")
+    if use_decode_session is None:
+        tensor_parallel = model_parallel_is_initialized() and \
+            torch.distributed.get_world_size(get_model_parallel_group()) > 1
+        use_decode_session = device.type == "cuda" and not tensor_parallel
+    session = None
     for cur in range(start_pos, end_pos):
-        logits, cache = model(tokens[:, prev_pos:cur], cache=cache)
-        logits = logits[:, -1]
+        if session is not None:
+            logits = session.step(tokens[:, prev_pos])
+        else:
+            logits, cache = model(tokens[:, prev_pos:cur], cache=cache)
+            logits = logits[:, -1]
+            if use_decode_session:
+                # from here on every call feeds exactly one token: switch to the fixed-shape state
+                from .decoding import DecodeSession
+                session = DecodeSession(model, bsz, compute_dtype)
+                session.load_cache(cache)
         if use_sampling:
             probs = torch.softmax(logits / temp, dim=-1)
             if top_p > 0.0:

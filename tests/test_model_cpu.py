@@ -128,6 +128,13 @@ def test_inference_scoring_and_generation():
     assert len(out) == 2 and all(len(o) == 6 for o in out)
     out2 = generate(model, "fp32", Tok(), prompt=["hello world, this is a prompt", "short"], max_gen_len=6)
     assert out == out2          # greedy decoding is deterministic
+    # the fixed-shape decode session (what CUDA models use by default) produces the same tokens
+    out3 = generate(model, "fp32", Tok(), prompt=["hello world, this is a prompt", "short"], max_gen_len=6,
+                    use_decode_session=True)
+    assert out3 == out
+    long_a = generate(model, "fp32", Tok(), prompt=["ab"], max_gen_len=40)
+    long_b = generate(model, "fp32", Tok(), prompt=["ab"], max_gen_len=40, use_decode_session=True)
+    assert long_a == long_b     # 40 tokens cross several chunk boundaries
     probs = torch.softmax(torch.randn(3, 50), -1)
     assert sample_top_k(probs.clone(), 5).shape == (3, 1)
     assert sample_top_p(probs.clone(), 0.8).shape == (3, 1)
