@@ -539,3 +539,29 @@ def test_reduce_scatter_adamw_kernel_two_local_ranks():
         _close(v, v_ref, 1e-6, 1e-5, "v")
         _close(low, p_ref, 2e-2, 1e-2, "low")
         assert abs(sumsq.item() - (g.double() ** 2).sum().item()) < 1e-3 * (g.double() ** 2).sum().item()
+
+
+def test_generate_with_decode_session_on_gpu():
+    """`generate()` on a CUDA model takes the graph-replayed session after the prompt; it must run and
+    agree with the growing-cache path on the first tokens (bf16 ties can diverge later)."""
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.generation import generate
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.utils import set_random_seed
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    set_random_seed(0)
+    model = build_model(cfg, "bf16", False, False)
+
+    class Tok:
+        bos_id, eos_id, pad_id, n_words = 1, 2, 0, 512
+
+        def encode(self, s, bos, eos):
+            return ([self.bos_id] if bos else []) + [3 + (ord(ch) % 200) for ch in s]
+
+    prompt = ["the quick brown fox jumps over the lazy dog " * 3]
+    a = generate(model, "bf16", Tok(), prompt=prompt, max_gen_len=24, use_decode_session=False)
+    b = generate(model, "bf16", Tok(), prompt=prompt, max_gen_len=24)
+    assert len(a) == len(b) == 1 and len(a[0]) == len(b[0]) == 24
+    assert a[0][:2] == b[0][:2], (a, b)
