@@ -113,3 +113,39 @@ def test_checkpointing_and_bf16_run():
     res16 = run_ranks(_train_steps, 2, 1, 1, {}, False, 2, "bf16")
     assert all(torch.isfinite(torch.tensor(l)) for l, _ in res16[0][0])
     assert abs(res16[0][0][0][0] - base[0][0][0][0]) < 0.1
+
+
+def _decode_case(rank, world, mp):
+    """Prefill through the regular cache path, then decode through the fixed-shape session."""
+    from megalodon_b200.decoding import DecodeSession
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.utils import init_cache, set_random_seed
+    if world > 1:
+        initialize_model_parallel(mp, 1)
+    set_random_seed(1234)
+    cfg = _tiny_cfg()
+    model = build_model(cfg, "fp32", False, False)
+    model.eval()
+    inner = model._wrapped
+    B = 2
+    prompt = torch.randint(0, cfg.vocab_size, (B, 16 + 5), generator=torch.Generator().manual_seed(3))
+    outs = []
+    with torch.no_grad():
+        cache = init_cache(B, inner, torch.float32, device=torch.device("cpu"))
+        _, cache = model(prompt[:, :16], cache=cache)
+        logits, cache = model(prompt[:, 16:], cache=cache)
+        sess = DecodeSession(model, B, torch.float32, use_graph=False)
+        sess.load_cache(cache)
+        tok = logits[:, -1].argmax(-1)
+        for _ in range(14):                      # positions 5 .. 18 of the chunk: crosses the boundary at 16
+            lg = sess.step(tok)
+            outs.append(lg.clone())
+            tok = lg.argmax(-1)
+    return torch.stack(outs)
+
+
+def test_decode_session_under_tensor_parallelism_matches_single_rank():
+    single = run_ranks(_decode_case, 1, 1)[0]
+    for got in run_ranks(_decode_case, 2, 2):
+        assert torch.allclose(got, single, atol=2e-4, rtol=2e-4), (got - single).abs().max()
