@@ -95,6 +95,7 @@ class MegaOutputLayer(nn.Module):
         streaming = piece is not None
         first_piece = piece is None or piece[0] == 0
         last_piece = piece is None or piece[0] == piece[1] - 1
+        emit = piece is not None and len(piece) > 3 and bool(piece[3])
         if cache is not None:
             prev_count, prev_mean, prev_var = cache
         elif carry is not None:
@@ -119,6 +120,8 @@ class MegaOutputLayer(nn.Module):
             x = attach_to_graph(x, packed)
         if streaming and not last_piece:
             return x, (prev_count, prev_mean, prev_var)
+        if emit:
+            return x, (prev_count.detach(), prev_mean.detach(), prev_var.detach())
         return x, None
 
     def forward(self, x: Tensor, cache: Optional[Tuple[Tensor, Tensor, Tensor]] = None, carry=None,
@@ -159,8 +162,12 @@ class Mega(nn.Module):
             self.layers.append(wrap(layer))
         self.output = MegaOutputLayer(cfg, self.embed.weight)
 
-    def forward(self, tokens: Tensor, cache=None, targets: Optional[Tensor] = None):
+    def forward(self, tokens: Tensor, cache=None, targets: Optional[Tensor] = None, prefill: bool = False):
         """tokens [B, L].  Returns `(logits fp32 [B, L/cp, V], cache)`.
+
+        `prefill=True` runs `self.prefill(tokens)` instead (chunk-parallel prefill that returns the
+        last position's logits and a cache); it goes through `forward` so that a wrapping FSDP unit
+        has gathered the parameters.
 
         With `targets` [B, L] (training only) the vocabulary projection and the
         cross-entropy are evaluated piece by piece and the first return value is
@@ -171,6 +178,9 @@ class Mega(nn.Module):
         `self.seq_microbatch_chunks = k` feeds the local sequence through every
         layer in pieces of k chunks, carrying the TimestepNorm statistics and
         CEMA state from piece to piece: same math, bounded activation memory."""
+        if prefill:
+            assert cache is None and targets is None
+            return self.prefill(tokens)
         bsz, seq_len = tokens.shape
         c = self.chunk_size
         if cache is None:
@@ -187,7 +197,9 @@ class Mega(nn.Module):
             cache_layers, cache_output = cache
             first_kv = cache_layers[0][0]
             cache_len = 0 if first_kv is None else first_kv[-1]
-            assert self.chunk_parallel_size == 1, "inference mode does not support chunk parallel."
+            # With a cache the tokens are not split and nothing is handed between ranks: on a
+            # chunk-parallel group every rank runs the same step on the same state (replicated decode,
+            # e.g. after `prefill`), which keeps the sharded parameters' collectives in lockstep.
             if cache_len > 0:
                 assert cache_len + seq_len <= c
         assert seq_len < c or seq_len % c == 0, f"{seq_len}/{c}"
@@ -238,6 +250,62 @@ class Mega(nn.Module):
         if targets is not None:
             return self._gather_losses(outs), None
         return torch.cat(outs, dim=1), None
+
+    @torch.no_grad()
+    def prefill(self, tokens: Tensor):
+        """Chunk-parallel prefill: tokens [B, L] with L a multiple of chunk_size x chunk-parallel size.
+        Every rank runs its slice (the CEMA / TimestepNorm state is handed from rank to rank as in
+        training), the last rank's final state is broadcast, and every rank returns
+        `(logits of the last position [B, V] fp32, cache)` where `cache` has the structure of
+        `utils.init_cache` with an empty key/value tail - ready for `forward(tokens, cache)` or
+        `decoding.DecodeSession.load_cache`.  The reference cannot combine a cache with chunk
+        parallelism (model/mega.py:210)."""
+        import torch.distributed as dist
+        from ..parallel import get_chunk_parallel_group, get_chunk_parallel_ranks
+        bsz, total = tokens.shape
+        c, cp = self.chunk_size, self.chunk_parallel_size
+        assert total % (c * cp) == 0, "prefill length must be a multiple of chunk_size x chunk-parallel size"
+        seq_len = total // cp
+        lo = self.chunk_parallel_rank * seq_len
+        x = self.embed(tokens[:, lo:lo + seq_len])
+        if self.emb_scale is not None:
+            x = x * self.emb_scale
+        k = getattr(self, "seq_microbatch_chunks", None) or (seq_len // c)
+        piece_len = min(seq_len, k * c)
+        n = seq_len // piece_len
+        mask = None
+        if not self.efficient_attn:
+            mask = torch.triu(torch.full((1, 1, c, c), float("-inf"), device=tokens.device), diagonal=1).to(x.dtype)
+        freqs_cis = self.rope.get_freqs_cis(0, c)
+        pieces = list(torch.split(x, piece_len, dim=1))
+        layer_states = []
+        for layer in self.layers:
+            carry = None
+            for i in range(n):
+                pieces[i], carry = layer(pieces[i], freqs_cis, mask, None, carry, (i, n, seq_len, True))
+            layer_states.append(carry)
+        carry = None
+        for i in range(n):
+            xn, carry = self.output.normalize(pieces[i], None, carry, (i, n, seq_len, True))
+        logits = self.output.output(xn[:, -1:]).float()[:, 0]
+        out_state = carry
+        if cp > 1:
+            src = get_chunk_parallel_ranks()[-1]
+            group = get_chunk_parallel_group()
+            flat = [logits] + [t for st in layer_states for t in (st[0], st[1], st[2], torch.view_as_real(st[3]))] \
+                + list(out_state)
+            for t in flat:
+                dist.broadcast(t, src=src, group=group)
+        first = self.layers[0]
+        while hasattr(first, "_wrapped"):
+            first = first._wrapped
+        dt = x.dtype
+        cache_layers = []
+        for count, mean, var, hx in layer_states:
+            kv = (torch.empty((bsz, 0, self.local_heads, self.z_head_dim), dtype=dt, device=x.device),
+                  torch.empty((bsz, 0, self.local_heads, self.v_head_dim), dtype=dt, device=x.device), 0)
+            cache_layers.append((kv, (count, mean, var), hx))
+        return logits, (cache_layers, tuple(out_state))
 
     def _piece_loss(self, xn: Tensor, targets: Tensor) -> Tensor:
         logits = self.output.output(xn)

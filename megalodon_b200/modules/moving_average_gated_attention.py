@@ -210,6 +210,8 @@ class MovingAverageGatedAttention(nn.Module):
         first_piece = piece is None or piece[0] == 0
         last_piece = piece is None or piece[0] == piece[1] - 1
         local_len = seq_len if piece is None else piece[2]
+        # prefill: the last piece also returns the final (count, mean, var, h) of this rank
+        emit = piece is not None and len(piece) > 3 and bool(piece[3])
         cache_attn = cache_norm = hx = None
         prev_count = prev_mean = prev_var = None
         if cache is not None:
@@ -224,7 +226,7 @@ class MovingAverageGatedAttention(nn.Module):
 
         out_tsn, prev_count, prev_mean, prev_var = self.timenorm(x, prev_count, prev_mean, prev_var)
         send_now = cache is None and last_piece and should_send_to_next()
-        need_state = cache_attn is not None or send_now or (streaming and not last_piece)
+        need_state = cache_attn is not None or send_now or (streaming and not last_piece) or emit
         out_cema, hx = self.cema.forward_channels_last(out_tsn, hx, need_state)
 
         new_carry = None
@@ -236,6 +238,8 @@ class MovingAverageGatedAttention(nn.Module):
             out_cema = attach_to_graph(out_cema, packed)
         elif streaming and not last_piece:
             new_carry = (prev_count, prev_mean, prev_var, hx)
+        if emit and last_piece and cache is None:
+            new_carry = (prev_count.detach(), prev_mean.detach(), prev_var.detach(), hx.detach())
 
         out_cema = gather_from_model_parallel_region(out_cema)
         mx = self.rmsnorm(out_cema)

@@ -161,6 +161,27 @@ def init_cache(bsz: int, model, compute_dtype: torch.dtype, truncate: bool = Fal
     return layers, (None, None, None)
 
 
+def reshard_cache(cache, mp_rank: int, mp_size: int):
+    """Slice a cache produced without tensor parallelism (e.g. by a chunk-parallel prefill) down to
+    what model-parallel rank `mp_rank` of `mp_size` holds: its heads of the key/value tail, its
+    TimestepNorm groups, its features of the CEMA state.  Counts are shared."""
+    if mp_size == 1:
+        return cache
+
+    def part(t, dim):
+        n = t.size(dim) // mp_size
+        return t.narrow(dim, mp_rank * n, n).contiguous()
+
+    layers, out_norm = cache
+    new_layers = []
+    for kv, (count, mean, var), hx in layers:
+        if kv is not None:
+            kv = (part(kv[0], 2), part(kv[1], 2), kv[2])
+        new_layers.append((kv, (count, part(mean, 1), part(var, 1)), None if hx is None else part(hx, 1)))
+    count, mean, var = out_norm
+    return new_layers, (count, part(mean, 1), part(var, 1))
+
+
 def truncate_cache(cache, truncated_cache):
     """Keep KV and CEMA state of `cache` but take the normalisation statistics
     from `truncated_cache` (statistics re-derived over a recent window)."""

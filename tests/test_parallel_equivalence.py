@@ -149,3 +149,77 @@ def test_decode_session_under_tensor_parallelism_matches_single_rank():
     single = run_ranks(_decode_case, 1, 1)[0]
     for got in run_ranks(_decode_case, 2, 2):
         assert torch.allclose(got, single, atol=2e-4, rtol=2e-4), (got - single).abs().max()
+
+
+def _prefill_decode_case(rank, world, cp):
+    """Chunk-parallel prefill that emits a cache, then replicated decode through the cache path."""
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.utils import init_cache, set_random_seed
+    if world > 1:
+        initialize_model_parallel(1, cp)
+    set_random_seed(1234)
+    cfg = _tiny_cfg()
+    model = build_model(cfg, "fp32", False, False, shard_over_chunk_group=cp > 1)
+    model.eval()
+    inner = model._wrapped
+    B, c = 2, cfg.chunk_size
+    prompt = torch.randint(0, cfg.vocab_size, (B, 4 * c), generator=torch.Generator().manual_seed(5))
+    outs = []
+    with torch.no_grad():
+        if cp > 1:
+            inner.seq_microbatch_chunks = 1          # two pieces per rank: exercises the carry as well
+            logits, cache = model(prompt, prefill=True)
+        else:
+            cache = init_cache(B, inner, torch.float32, device=torch.device("cpu"))
+            for s in range(0, 4 * c, 2 * c):
+                full, cache = model(prompt[:, s:s + 2 * c], cache=cache)
+            logits = full[:, -1]
+        outs.append(logits.clone())
+        tok = logits.argmax(-1)
+        for _ in range(6):
+            lg, cache = model(tok.view(B, 1), cache=cache)
+            outs.append(lg[:, -1].clone())
+            tok = lg[:, -1].argmax(-1)
+    return torch.stack(outs)
+
+
+def test_chunk_parallel_prefill_hands_its_state_to_decode():
+    single = run_ranks(_prefill_decode_case, 1, 1)[0]
+    for got in run_ranks(_prefill_decode_case, 2, 2):
+        assert torch.allclose(got, single, atol=2e-4, rtol=2e-4), (got - single).abs().max()
+
+
+def _cache_case(rank, world, mp):
+    """Cache after prefilling one and a half chunks through the regular cache path."""
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.utils import init_cache, set_random_seed
+    if world > 1:
+        initialize_model_parallel(mp, 1)
+    set_random_seed(1234)
+    cfg = _tiny_cfg()
+    model = build_model(cfg, "fp32", False, False)
+    model.eval()
+    B, c = 2, cfg.chunk_size
+    prompt = torch.randint(0, cfg.vocab_size, (B, c + c // 2), generator=torch.Generator().manual_seed(9))
+    with torch.no_grad():
+        cache = init_cache(B, model._wrapped, torch.float32, device=torch.device("cpu"))
+        _, cache = model(prompt[:, :c], cache=cache)
+        _, cache = model(prompt[:, c:], cache=cache)
+    return cache
+
+
+def test_reshard_cache_matches_a_tensor_parallel_cache():
+    from megalodon_b200.utils import reshard_cache
+    full = run_ranks(_cache_case, 1, 1)[0]
+    per_rank = run_ranks(_cache_case, 2, 2)
+    for r, (layers, out_norm) in enumerate(per_rank):
+        exp_layers, exp_out = reshard_cache(full, r, 2)
+        for (kv, norm, hx), (ekv, enorm, ehx) in zip(layers, exp_layers):
+            assert kv[2] == ekv[2]
+            for a, b in list(zip(kv[:2], ekv[:2])) + list(zip(norm, enorm)):
+                assert a.shape == b.shape and torch.allclose(a.float(), b.float(), atol=1e-4, rtol=1e-4)
+            assert torch.allclose(torch.view_as_real(hx), torch.view_as_real(ehx), atol=1e-4, rtol=1e-4)
+        for a, b in zip(out_norm, exp_out):
+            assert torch.allclose(a.float(), b.float(), atol=1e-4, rtol=1e-4)
