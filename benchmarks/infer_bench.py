@@ -82,15 +82,15 @@ def main():
         toks = torch.randint(0, cfg.vocab_size, (1, P), generator=g).cuda()
         with torch.no_grad():
             for _ in range(2):
-                logits, _ = model(toks)
-            del logits
+                logits, cache = model(toks, prefill=True)
+            del logits, cache
             barrier()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             e0.record()
             for _ in range(args.reps):
-                logits, _ = model(toks)
-                nxt = logits[:, -1].argmax(-1)          # what a generation loop would read
-                del logits
+                logits, cache = model(toks, prefill=True)     # last-position logits + the cache a decoder takes over
+                nxt = logits.argmax(-1)
+                del logits, cache
             e1.record()
             barrier()
         ms = maxed(e0.elapsed_time(e1) / args.reps)
