@@ -565,3 +565,30 @@ def test_generate_with_decode_session_on_gpu():
     b = generate(model, "bf16", Tok(), prompt=prompt, max_gen_len=24)
     assert len(a) == len(b) == 1 and len(a[0]) == len(b[0]) == 24
     assert a[0][:2] == b[0][:2], (a, b)
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_reduce_scatter_sumsq_kernel_local_ranks(world, out_dtype):
+    """The peer-memory reduce-scatter kernel with every 'rank' a local buffer: sum, scale, cast, squared
+    norm and the accumulate mode for 2, 4 and 8 ranks."""
+    from megalodon_b200.ops._ext import require
+    from megalodon_b200.ops.cuda_ops import _DT
+    ext = require()
+    torch.manual_seed(14)
+    dev = _dev()
+    shard_n = 2048 + 64
+    stage = [torch.randn(world * shard_n, device=dev).bfloat16() for _ in range(world)]
+    bufs = torch.tensor([t.data_ptr() for t in stage], dtype=torch.int64, device=dev)
+    scale = 1.0 / world
+    for rank in (0, world - 1):
+        ref = scale * sum(t.float()[rank * shard_n:(rank + 1) * shard_n] for t in stage)
+        out = torch.empty(shard_n, device=dev, dtype=out_dtype)
+        sumsq = torch.zeros((), device=dev, dtype=torch.float64)
+        ext.reduce_scatter_sumsq(bufs, rank, _DT[torch.bfloat16], scale, out, sumsq, False)
+        _close(out, ref, 2e-2 if out_dtype == torch.bfloat16 else 1e-5, 1e-2, f"reduce-scatter world={world}")
+        want = (out.double() ** 2).sum().item() if out_dtype == torch.float32 else (ref.double() ** 2).sum().item()
+        assert abs(sumsq.item() - want) < 2e-2 * want
+        prev = out.clone()
+        ext.reduce_scatter_sumsq(bufs, rank, _DT[torch.bfloat16], scale, out, None, True)     # out += ...
+        _close(out, prev.float() + ref, 4e-2 if out_dtype == torch.bfloat16 else 1e-5, 2e-2, "accumulate")
