@@ -118,7 +118,8 @@ def reference_arm(args):
             why = "reference imports but no driver for it is wired up"
         except Exception as e:  # noqa: BLE001
             why = f"reference import fails: {type(e).__name__}: {e}"[:300]
-    print(json.dumps({"impl": "reference", "unavailable": why}))
+    if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also when launched as N ranks
+        print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
 def main():
