@@ -32,6 +32,9 @@ def main():
     ap.add_argument("--batches", default="1,4,16")
     ap.add_argument("--gen-len", type=int, default=256)
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--kernel-profile", default=None,
+                    help="decode: also run one eager fixed-shape step per batch size under torch.profiler and write "
+                         "the per-kernel summary to this path (never part of a reported number)")
     ap.add_argument("--eager", action="store_true", help="decode through the regular cache path instead of the "
                                                          "graph-replayed fixed-shape session")
     args = ap.parse_args()
@@ -144,6 +147,28 @@ def main():
                 e1.record()
                 barrier()
                 results[B] = maxed(e0.elapsed_time(e1) / args.gen_len)
+                if args.kernel_profile and rank == 0:
+                    import collections
+                    from torch.profiler import ProfilerActivity, profile
+                    from megalodon_b200.decoding import DecodeSession
+                    eager = DecodeSession(model, B, torch.bfloat16, use_graph=False)
+                    eager.load_cache(cache)          # the state right after the prompt is as good as any for a profile
+                    for _ in range(3):
+                        tok = eager.step(tok).argmax(-1, keepdim=True)
+                    torch.cuda.synchronize()
+                    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+                        tok = eager.step(tok).argmax(-1, keepdim=True)
+                        torch.cuda.synchronize()
+                    agg = collections.defaultdict(lambda: [0.0, 0])
+                    for e in prof.events():
+                        if e.device_type == torch.autograd.DeviceType.CUDA:
+                            agg[e.name][0] += e.device_time
+                            agg[e.name][1] += 1
+                    tot = sum(v[0] for v in agg.values())
+                    with open(f"{args.kernel_profile}.batch{B}", "w") as f:
+                        f.write(f"batch {B}: kernel time {tot / 1e3:.2f} ms, {sum(v[1] for v in agg.values())} launches\n")
+                        for name, (t, n) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:25]:
+                            f.write(f"{t / 1e3:8.3f} ms {100 * t / tot:5.1f}% {n:5d}x {t / n:8.1f} us  {name[:110]}\n")
         cuda_ops.check_kernel_errors()
         if rank == 0:
             out = {"metric": "decode ms/token", "value": results, "unit": "ms", "n_gpus": world,
