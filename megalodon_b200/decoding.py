@@ -137,8 +137,18 @@ class DecodeSession:
             # capture: the step reads and writes only the session's buffers
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
+            try:
+                with torch.cuda.graph(graph):
+                    captured = self._step_body()
+            except Exception as e:  # noqa: BLE001 - an op that cannot be captured: stay on the eager step
+                import logging
+                logging.getLogger().warning(f"decode step could not be captured in a CUDA graph ({e}); "
+                                            "continuing with eager fixed-shape steps")
+                torch.cuda.synchronize()
+                self.use_graph = False
                 self.logits = self._step_body()
+                return self.logits
+            self.logits = captured
             self._graph = graph
             # capturing does not execute: run this token now (the state was not advanced yet)
             graph.replay()
