@@ -137,8 +137,12 @@ class DecodeSession:
             # capture: the step reads and writes only the session's buffers
             torch.cuda.synchronize()
             graph = torch.cuda.CUDAGraph()
+            # with a process group alive its watchdog thread makes CUDA calls of its own; in the default
+            # (global) capture mode those would invalidate the capture, so other threads are exempted
+            dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
+            mode = {"capture_error_mode": "thread_local"} if dist_on else {}
             try:
-                with torch.cuda.graph(graph):
+                with torch.cuda.graph(graph, **mode):
                     captured = self._step_body()
             except Exception as e:  # noqa: BLE001 - an op that cannot be captured: stay on the eager step
                 import logging
