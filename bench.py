@@ -122,6 +122,24 @@ def reference_arm(args):
         print(json.dumps({"impl": "reference", "unavailable": why}))
 
 
+def step_roofline(cfg, seq_len: int, world: int, ms_per_step: float) -> dict:
+    """Matrix-product arithmetic of one step against the measured cuBLAS throughput: forward + backward
+    of every layer and the vocabulary projection, plus the recomputed forward of the checkpointed layers."""
+    from megalodon_b200.utils.profiling import measured_peaks, model_flops_per_token
+    base = model_flops_per_token(cfg, with_recompute=False)            # forward + backward per token
+    n_ckpt = 0 if not cfg.layerwise_ckpt else (cfg.num_layers if cfg.ckpt_layers is None else cfg.ckpt_layers)
+    vocab = cfg.vocab_size if cfg.output_size == -1 else cfg.output_size
+    layer_fwd = (base - 6.0 * cfg.model_dim * vocab) / 3.0 / cfg.num_layers   # one layer's forward per token
+    flops_step = (base + n_ckpt * layer_fwd) * seq_len
+    pk = measured_peaks()
+    per_gpu = flops_step / world / (ms_per_step / 1e3)
+    return {"pflop_per_step": round(flops_step / 1e15, 3),
+            "achieved_tflops_per_gpu": round(per_gpu / 1e12, 1),
+            "fraction_of_sustained_cublas": round(per_gpu / (pk["bf16_tflops_sustained"] * 1e12), 3),
+            "fraction_of_burst_cublas": round(per_gpu / (pk["bf16_tflops"] * 1e12), 3),
+            "peaks": pk["source"]}
+
+
 def main():
     args = parse()
     if args.impl == "reference":
@@ -347,6 +365,10 @@ def main():
             "phases_ms_rank0": {k: round(v, 1) for k, v in phases.items()},
             "steps_ms_rank0": [round(v, 1) for v in steps_ms],
         }
+        try:
+            out["roofline"] = step_roofline(cfg, args.seq_len, world, dev_ms / args.steps)
+        except Exception as e:  # noqa: BLE001 - never lose the result line over the derived figures
+            out["roofline"] = {"error": repr(e)[:200]}
         if args.layers is not None:
             out["invalid"] = "reduced depth (debug run)"
         print(json.dumps(out))
