@@ -28,6 +28,7 @@ import time
 
 # before CUDA initialises: peer-waiting kernels must never be held up by a lazy kernel load
 os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")    # one hardware queue per stream in use
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
@@ -52,7 +53,52 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="override depth (debugging only; marks the run invalid)")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_1cta", "cublas"])
     ap.add_argument("--no-ckpt", action="store_true")
+    ap.add_argument("--step-timeout-s", type=float, default=150.0,
+                    help="a rank whose host makes no step progress for this long dumps its Python stacks and the "
+                         "device's abort record to stderr and exits non-zero (the launcher then stops the others)")
     return ap.parse_args()
+
+
+class StepWatchdog:
+    """Host-side guard of the benchmark loop.  A daemon thread looks at two things once a second:
+    the time since the main thread last finished enqueuing a step, and the pinned mirror of the
+    device's abort record (set by the first kernel whose bounded wait on a peer ran out).  Either one
+    ends the process with a report instead of leaving N GPUs waiting for the collective timeout."""
+
+    def __init__(self, rank: int, timeout_s: float, abort_record=None):
+        self.rank, self.timeout_s, self.abort = rank, timeout_s, abort_record
+        self.last = time.time()
+        self.where = "start"
+        self._stop = False
+        threading.Thread(target=self._run, daemon=True).start()
+
+    def progress(self, where: str) -> None:
+        self.last = time.time()
+        self.where = where
+        if os.environ.get("MEGALODON_B200_BENCH_VERBOSE"):
+            print(f"[rank {self.rank}] {time.strftime('%H:%M:%S')} {where}", file=sys.stderr, flush=True)
+
+    def stop(self) -> None:
+        self._stop = True
+
+    def _run(self):
+        import faulthandler
+        tripped_at = None
+        while not self._stop:
+            time.sleep(1.0)
+            if self.abort is not None and self.abort.tripped():
+                if tripped_at is None:
+                    tripped_at = time.time()
+                    from megalodon_b200.parallel.symm import describe_abort
+                    print(f"[rank {self.rank}] peer wait failed after '{self.where}': "
+                          f"{describe_abort(self.abort.host.tolist())}", file=sys.stderr, flush=True)
+                elif time.time() - tripped_at > 20.0:      # the main thread had its chance to raise
+                    os._exit(4)
+            if time.time() - self.last > self.timeout_s:
+                print(f"[rank {self.rank}] no progress for {self.timeout_s:.0f} s after '{self.where}'; stacks:",
+                      file=sys.stderr, flush=True)
+                faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
+                os._exit(3)
 
 
 class ClockSampler:
@@ -163,7 +209,8 @@ def main():
     torch.cuda.set_device(local_rank)
     rank = 0
     if world > 1:
-        info = init_torch_distributed()
+        # a collective that takes minutes is a failure here: end the job rather than occupy N GPUs
+        info = init_torch_distributed(timeout=300)
         rank = info.global_rank
         initialize_model_parallel(1, world)
     if args.gemm:
@@ -197,8 +244,13 @@ def main():
     if world > 1:
         # CEMA / TimestepNorm state goes from rank to rank through peer memory, not NCCL send/recv
         from megalodon_b200.parallel.symm import enable_peer_transport
-        peer_timeout = float(os.environ.get("MEGALODON_B200_PEER_TIMEOUT_S", "60"))
+        from megalodon_b200.parallel.symm import AbortRecord
+        peer_timeout = float(os.environ.get("MEGALODON_B200_PEER_TIMEOUT_S", "10"))
         mailbox, _ = enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=peer_timeout)
+        abort_record = AbortRecord.get(torch.device("cuda", local_rank))
+    else:
+        abort_record = None
+    dog = StepWatchdog(rank, args.step_timeout_s, abort_record)
     opt, sched = build_optimizer(model, OptimConf(lr=1e-4, warmup=10, clip=1.0), 1000, "bf16")
     data = SyntheticTokens(cfg.vocab_size, 1, args.seq_len, seed=0)
     n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)
@@ -225,18 +277,20 @@ def main():
         # a bounded device-side wait that ran out shows up here instead of slowing every later step
         cuda_ops.check_kernel_errors()
         if world > 1:
-            mailbox.check()
-            rs = getattr(model, "_symm_rs", None)
-            if rs is not None:
-                rs.check()
+            abort_record.check()
+
+    def peers_ok_so_far():
+        # host-only look at the pinned mirror of the abort record: costs nothing inside a timed region
+        if abort_record is not None and abort_record.tripped():
+            torch.cuda.synchronize()
+            abort_record.check()
 
     for i in range(args.warmup):
         x, y = next(data)
         last = step(x, y, True)
         torch.cuda.synchronize()
         check_peers()
-        if os.environ.get("MEGALODON_B200_BENCH_VERBOSE"):
-            print(f"[rank {rank}] warmup step {i} loss {last:.4f}", file=sys.stderr, flush=True)
+        dog.progress(f"warm-up step {i} done, loss {last:.4f}")
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -255,7 +309,9 @@ def main():
         return ev
 
     e0.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        peers_ok_so_far()
+        dog.progress(f"timed step {i} being enqueued")
         m = [mark()]
         tok_loss, _ = model(xd, targets=yd)
         loss = tok_loss.mean()
@@ -283,17 +339,18 @@ def main():
     e2, e3 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t_wall = time.perf_counter()
     e2.record()
-    for _ in range(args.steps):
+    for i in range(args.steps):
         x, y = next(data)
         last = step(x, y, True)
+        peers_ok_so_far()
+        dog.progress(f"end-to-end step {i} done")
     e3.record()
     barrier()
     e2e_ms = e2.elapsed_time(e3)
     wall_ms = (time.perf_counter() - t_wall) * 1e3
     clocks = sampler.stop()
-    cuda_ops.check_kernel_errors()
-    if world > 1:
-        mailbox.check()
+    check_peers()
+    dog.progress("timed regions done")
 
     if args.kernel_profile:
         import collections
@@ -372,9 +429,12 @@ def main():
         if args.layers is not None:
             out["invalid"] = "reduced depth (debug run)"
         print(json.dumps(out))
+    dog.progress("result printed")
     if world > 1:
         dist.barrier()
+        dog.progress("final barrier passed")
         dist.destroy_process_group()
+    dog.stop()
 
 
 if __name__ == "__main__":

@@ -12,5 +12,11 @@ import os as _os
 # is read when CUDA initialises, so it is set at import time, before the first
 # CUDA call; an explicit setting by the user is left alone.
 _os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
+# For the same reason no two streams of this package may share a hardware work queue: work queued
+# behind a waiting kernel of ANOTHER stream in the same queue cannot start, although nothing orders
+# the two.  The default of 8 queues is fewer than the streams in use (compute, parameter gather,
+# gradient reduction, one internal stream per NCCL communicator); 32 gives each its own.  Also read
+# when CUDA initialises.
+_os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
 
 __version__ = "0.1.0"

@@ -582,8 +582,28 @@ std::vector<OptTensor> ema_parameters_bwd(const OptTensor& dk, const OptTensor& 
 // ------------------------------------------------------------------ peer-memory communication
 // Peer addresses are passed as integers (they come from the symmetric-memory rendezvous and are not
 // tensors of this process).  `counter` / `err` are small device tensors owned by the caller.
+// Device-side address of a pinned host tensor (what a kernel must use to write to it); 0 if the
+// memory is not mapped into the device's address space.
+int64_t pinned_device_ptr(const Tensor& t) {
+  TORCH_CHECK(!t.is_cuda() && t.is_pinned(), "expects a pinned host tensor");
+  void* dptr = nullptr;
+  if (cudaHostGetDevicePointer(&dptr, t.data_ptr(), 0) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return 0;
+  }
+  return reinterpret_cast<int64_t>(dptr);
+}
+
+// `abort`: the device's abort record (int32[kCommAbortWords], see comm_kernels.cu)
+int* abort_ptr(Tensor& abort) {
+  TORCH_CHECK(abort.is_cuda() && abort.scalar_type() == at::kInt && abort.is_contiguous() &&
+              abort.numel() >= mb::kCommAbortWords, "abort record must be a CUDA int32 tensor of 16 words");
+  return abort.data_ptr<int>();
+}
+
 void p2p_send(const Tensor& src, int64_t remote_dst, int64_t nbytes, int64_t remote_flag, int64_t seq,
-              int64_t local_ack, int64_t need_ack, Tensor& counter, int64_t timeout_ns, Tensor& err) {
+              int64_t local_ack, int64_t need_ack, Tensor& counter, int64_t timeout_ns, Tensor& abort, int64_t rank,
+              int64_t dir) {
   check_cuda_contig(src, "src");
   c10::cuda::CUDAGuard guard(src.device());
   TORCH_CHECK(nbytes % 16 == 0 && nbytes <= (int64_t)(src.numel() * src.element_size()), "payload must be whole 16-byte words");
@@ -591,11 +611,11 @@ void p2p_send(const Tensor& src, int64_t remote_dst, int64_t nbytes, int64_t rem
   mb::p2p_send(src.data_ptr(), reinterpret_cast<void*>(remote_dst), nbytes, reinterpret_cast<unsigned int*>(remote_flag),
                (unsigned int)seq, reinterpret_cast<const unsigned int*>(local_ack), (unsigned int)need_ack,
                reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), (unsigned long long)timeout_ns,
-               err.data_ptr<int>(), stream());
+               abort_ptr(abort), (int)rank, (int)dir, stream());
 }
 
 void p2p_recv(Tensor& dst, int64_t local_slot, int64_t nbytes, int64_t local_flag, int64_t seq, int64_t remote_ack,
-              Tensor& counter, int64_t timeout_ns, Tensor& err) {
+              Tensor& counter, int64_t timeout_ns, Tensor& abort, int64_t rank, int64_t dir) {
   check_cuda_contig(dst, "dst");
   c10::cuda::CUDAGuard guard(dst.device());
   TORCH_CHECK(nbytes % 16 == 0 && nbytes <= (int64_t)(dst.numel() * dst.element_size()));
@@ -603,31 +623,38 @@ void p2p_recv(Tensor& dst, int64_t local_slot, int64_t nbytes, int64_t local_fla
   mb::p2p_recv(dst.data_ptr(), reinterpret_cast<const void*>(local_slot), nbytes,
                reinterpret_cast<const unsigned int*>(local_flag), (unsigned int)seq,
                reinterpret_cast<unsigned int*>(remote_ack), reinterpret_cast<unsigned int*>(counter.data_ptr<int>()),
-               (unsigned long long)timeout_ns, err.data_ptr<int>(), stream());
+               (unsigned long long)timeout_ns, abort_ptr(abort), (int)rank, (int)dir, stream());
 }
 
 // pads: int64 device tensor with the address of every rank's signal pad
-void peer_barrier(const Tensor& pads, int64_t rank, int64_t epoch, int64_t timeout_ns, Tensor& err) {
+void peer_barrier(const Tensor& pads, int64_t rank, int64_t epoch, int64_t timeout_ns, Tensor& abort, int64_t tag) {
   check_cuda_contig(pads, "pads");
   c10::cuda::CUDAGuard guard(pads.device());
   TORCH_CHECK(pads.scalar_type() == at::kLong && pads.numel() <= 32);
   mb::peer_barrier(reinterpret_cast<unsigned int* const*>(pads.data_ptr<int64_t>()), (int)rank, (int)pads.numel(),
-                   (unsigned int)epoch, (unsigned long long)timeout_ns, err.data_ptr<int>(), stream());
+                   (unsigned int)epoch, (unsigned long long)timeout_ns, abort_ptr(abort), (int)tag, stream());
 }
 
 // bufs: int64 device tensor with the address of every rank's copy of the buffer (same byte offset everywhere)
+const int* opt_abort(const OptTensor& abort) {
+  if (!abort.has_value()) return nullptr;
+  TORCH_CHECK(abort->is_cuda() && abort->scalar_type() == at::kInt && abort->numel() >= 1);
+  return abort->data_ptr<int>();
+}
+
 void allreduce_sumsq(const Tensor& bufs, int64_t rank, int64_t nbytes, double scale, const OptTensor& sumsq,
-                     int64_t dtype) {
+                     int64_t dtype, const OptTensor& abort) {
   check_cuda_contig(bufs, "bufs");
   c10::cuda::CUDAGuard guard(bufs.device());
   TORCH_CHECK(bufs.scalar_type() == at::kLong && nbytes % 16 == 0);
   if (sumsq.has_value()) TORCH_CHECK(sumsq->scalar_type() == at::kDouble && sumsq->numel() == 1);
   mb::allreduce_sumsq(reinterpret_cast<void* const*>(bufs.data_ptr<int64_t>()), (int)rank, (int)bufs.numel(), nbytes,
-                      (float)scale, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (int)dtype, stream());
+                      (float)scale, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (int)dtype, opt_abort(abort),
+                      stream());
 }
 
 void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& out,
-                          const OptTensor& sumsq, bool accumulate) {
+                          const OptTensor& sumsq, bool accumulate, const OptTensor& abort) {
   check_cuda_contig(bufs, "bufs");
   check_cuda_contig(out, "out");
   c10::cuda::CUDAGuard guard(out.device());
@@ -635,13 +662,13 @@ void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, do
   mb::reduce_scatter_sumsq(reinterpret_cast<const void* const*>(bufs.data_ptr<int64_t>()), (int)rank,
                            (int)bufs.numel(), out.numel(), (float)scale, out.data_ptr(),
                            sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, accumulate, (int)in_dtype,
-                           dtype_code(out), stream());
+                           dtype_code(out), opt_abort(abort), stream());
 }
 
 // bufs: int64 device tensor of every rank's staging address; p / m / v fp32 shards updated in place
 void reduce_scatter_adamw(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& p, Tensor& m,
                           Tensor& v, const OptTensor& low, const OptTensor& sumsq, double lr, double beta1,
-                          double beta2, double eps, double wd, int64_t step) {
+                          double beta2, double eps, double wd, int64_t step, const OptTensor& abort) {
   check_cuda_contig(bufs, "bufs");
   check_cuda_contig(p, "p");
   check_cuda_contig(m, "m");
@@ -656,7 +683,7 @@ void reduce_scatter_adamw(const Tensor& bufs, int64_t rank, int64_t in_dtype, do
       (float)scale, p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
       low.has_value() ? low->data_ptr() : nullptr, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (float)lr,
       (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, (int)in_dtype,
-      low.has_value() ? dtype_code(*low) : (int)in_dtype, stream());
+      low.has_value() ? dtype_code(*low) : (int)in_dtype, opt_abort(abort), stream());
   TORCH_CHECK(ok, "reduce_scatter_adamw: shard must be a multiple of 8 elements, 16-bit gradients, at most 8 ranks");
 }
 
@@ -718,8 +745,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fftconv_apply", checked(&fftconv_apply));
   m.def("fftconv_dk", checked(&fftconv_dk));
   m.def("reduce_slots", checked(&reduce_slots));
-  m.def("reduce_scatter_sumsq", checked(&reduce_scatter_sumsq));
-  m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw));
+  m.def("reduce_scatter_sumsq", checked(&reduce_scatter_sumsq), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
+        py::arg("scale"), py::arg("out"), py::arg("sumsq"), py::arg("accumulate"), py::arg("abort") = py::none());
+  m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
+        py::arg("scale"), py::arg("p"), py::arg("m"), py::arg("v"), py::arg("low"), py::arg("sumsq"), py::arg("lr"),
+        py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
+        py::arg("abort") = py::none());
   m.def("time_sums", checked(&time_sums));
   m.def("affine_apply", checked(&affine_apply));
   m.def("dropout", checked(&dropout));
@@ -732,5 +763,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("peer_barrier", checked(&peer_barrier));
   m.def("gemm_set_cta_pairs", [](bool on) { mb::gemm_set_cta_pairs(on); });
   m.def("gemm_pair_max_active_clusters", []() { return mb::gemm_pair_max_active_clusters(); });
-  m.def("allreduce_sumsq", checked(&allreduce_sumsq));
+  m.def("allreduce_sumsq", checked(&allreduce_sumsq), py::arg("bufs"), py::arg("rank"), py::arg("nbytes"),
+        py::arg("scale"), py::arg("sumsq"), py::arg("dtype"), py::arg("abort") = py::none());
+  m.attr("COMM_ABORT_WORDS") = (int)mb::kCommAbortWords;
+  m.def("pinned_device_ptr", &pinned_device_ptr);
 }

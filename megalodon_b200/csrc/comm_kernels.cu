@@ -19,10 +19,21 @@
 //                         Replaces the bucketed all_reduce of grad_all_reduce
 //                         plus the separate norm pass (fairscale_fsdp.py:89-219).
 //
-// Every wait is bounded by a caller-supplied timeout; on expiry the kernel sets
-// `*err`, skips its remaining work and returns, so a missing peer shows up as a
-// Python exception instead of a hung GPU.  Only plain (non-multimem) peer
-// accesses are used here.
+// Failure handling.  Every wait is bounded by a caller-supplied timeout, and all
+// communication objects of a device share one "abort record" (kAbortWords ints,
+// see `record_abort`).  The first wait that runs out writes its identity there
+// (which rank, which kind of wait, direction, sequence number wanted and seen).
+// From then on the failure spreads without further timeouts:
+//   * every later wait on this GPU polls word 0 of the record and returns at
+//     once when it is set;
+//   * a kernel that gives up still signals its peer, but with the poison value
+//     kPoison instead of a sequence number / epoch, so the peer's wait returns
+//     immediately, records "peer gave up" and poisons its own neighbours in
+//     turn.
+// One lost signal therefore costs ONE timeout for the whole job, and the host
+// reads who waited for what.  The record is also copied to a pinned host word
+// (if one is registered) so the host can notice a failure without synchronising
+// the device.  Only plain (non-multimem) peer accesses are used here.
 #include <cmath>
 
 #include "common.cuh"
@@ -47,33 +58,83 @@ __device__ __forceinline__ void st_release_sys(unsigned int* p, unsigned int v) 
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Wait until *flag >= want (unsigned, epochs only grow).  Returns false on timeout.
-__device__ __forceinline__ bool wait_flag_ge(const unsigned int* flag, unsigned int want,
-                                             unsigned long long timeout_ns) {
-  if (ld_acquire_sys(flag) >= want) return true;
+constexpr unsigned int kPoison = 0xffffffffu;     // flag value meaning "the writer gave up"
+
+// Abort record: [0] code (0 = healthy), [1] kind of wait, [2] direction / peer index, [3] value wanted,
+// [4] value seen, [5] rank of the waiting GPU in its group, [6] tag (caller's choice, e.g. unit number),
+// [7] 1 when the cause was a peer's poison rather than a timeout, [8..9] address of the pinned host mirror.
+constexpr int kAbortWords = 16;
+enum WaitKind : int { kWaitSendAck = 1, kWaitRecv = 2, kWaitBarrier = 3, kWaitStaged = 4 };
+enum WaitResult : int { kWaitOk = 0, kWaitTimedOut = 1, kWaitAborted = 2, kWaitPoisoned = 3 };
+
+__device__ __forceinline__ int ld_volatile(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
+
+// Wait until *flag >= want (unsigned, sequence numbers and epochs only grow and never reach kPoison).
+__device__ __forceinline__ WaitResult wait_flag_ge(const unsigned int* flag, unsigned int want,
+                                                   unsigned long long timeout_ns, const int* abort,
+                                                   unsigned int* seen) {
+  unsigned int v = ld_acquire_sys(flag);
   const unsigned long long t0 = now_ns();
   // Exponential back-off up to 2 us per poll: a waiting warp shares its SM with whatever compute
   // kernel runs on the other streams, and a tight poll loop steals issue slots from it.
   unsigned int spins = 0, pause_ns = 32;
-  while (ld_acquire_sys(flag) < want) {
-    if ((++spins & 0x3f) == 0 && now_ns() - t0 > timeout_ns) return false;
+  while (true) {
+    *seen = v;
+    if (v == kPoison) return kWaitPoisoned;
+    if (v >= want) return kWaitOk;
+    if ((++spins & 0x7) == 0) {
+      if (ld_volatile(abort) != 0) return kWaitAborted;
+      if (now_ns() - t0 > timeout_ns) return kWaitTimedOut;
+    }
     __nanosleep(pause_ns);
     if (pause_ns < 2048) pause_ns <<= 1;
+    v = ld_acquire_sys(flag);
   }
-  return true;
+}
+
+// First failure wins.  `res` is what wait_flag_ge returned (a wait that ended because the record was
+// already set has nothing to add).
+__device__ __forceinline__ void record_abort(int* abort, WaitResult res, int kind, int dir_or_peer,
+                                             unsigned int want, unsigned int seen, int rank, int tag) {
+  if (res != kWaitTimedOut && res != kWaitPoisoned) return;
+  if (atomicCAS(abort, 0, 10 + kind) != 0) return;
+  abort[1] = kind; abort[2] = dir_or_peer; abort[3] = (int)want; abort[4] = (int)seen; abort[5] = rank;
+  abort[6] = tag; abort[7] = res == kWaitPoisoned ? 1 : 0;
+  __threadfence();
+  const unsigned long long host = ((unsigned long long)(unsigned int)abort[9] << 32) | (unsigned int)abort[8];
+  if (host != 0) {
+    volatile int* h = reinterpret_cast<volatile int*>(host);
+    for (int i = 1; i < 8; ++i) h[i] = abort[i];
+    __threadfence_system();
+    h[0] = 10 + kind;
+  }
+}
+
+// True (for every thread of the CTA alike) when the device's abort record is set: data kernels then
+// return without touching peer memory, so a failed step drains quickly.
+__device__ __forceinline__ bool block_sees_abort(const int* abort) {
+  __shared__ int dead;
+  if (threadIdx.x == 0) dead = abort != nullptr && ld_volatile(abort) != 0;
+  __syncthreads();
+  return dead != 0;
 }
 
 // Counts CTAs that have finished; returns true in exactly one thread of the last CTA to arrive.
-__device__ __forceinline__ bool last_block_done(unsigned int* counter) {
+// `failed` CTAs leave a mark, and `*any_failed` tells the last CTA whether any did.
+__device__ __forceinline__ bool last_block_done(unsigned int* counter, bool failed, bool* any_failed) {
   __shared__ bool is_last;
+  __shared__ bool some_failed;
   __threadfence_system();           // this CTA's (possibly remote) stores are ordered before the count
   __syncthreads();
   if (threadIdx.x == 0) {
+    if (failed) atomicOr(counter, 0x40000000u);
     const unsigned int prev = atomicAdd(counter, 1u);
-    is_last = prev == gridDim.x - 1;
+    is_last = (prev & 0xffffu) == gridDim.x - 1;
+    some_failed = (prev & 0x40000000u) != 0;
     if (is_last) *counter = 0;      // ready for the next launch
   }
   __syncthreads();
+  *any_failed = some_failed;
   return is_last && threadIdx.x == 0;
 }
 
@@ -81,46 +142,64 @@ __device__ __forceinline__ bool last_block_done(unsigned int* counter) {
 __global__ void p2p_send_kernel(const uint4* __restrict__ src, uint4* __restrict__ remote_dst, long long n16,
                                 unsigned int* remote_flag, unsigned int seq, const unsigned int* local_ack,
                                 unsigned int need_ack, unsigned int* counter, unsigned long long timeout_ns,
-                                int* err) {
+                                int* abort, int rank, int dir) {
   __shared__ int ok;
-  if (threadIdx.x == 0) ok = (need_ack == 0 || wait_flag_ge(local_ack, need_ack, timeout_ns)) ? 1 : 0;
+  if (threadIdx.x == 0) {
+    WaitResult res = ld_volatile(abort) != 0 ? kWaitAborted : kWaitOk;
+    unsigned int seen = 0;
+    if (res == kWaitOk && need_ack != 0) res = wait_flag_ge(local_ack, need_ack, timeout_ns, abort, &seen);
+    // a timeout here means: slot still unacknowledged, the receiver is gone or too far behind
+    record_abort(abort, res, kWaitSendAck, dir, need_ack, seen, rank, (int)seq);
+    ok = res == kWaitOk ? 1 : 0;
+  }
   __syncthreads();
   if (ok) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
          i += (long long)gridDim.x * blockDim.x)
       remote_dst[i] = src[i];
-  } else if (threadIdx.x == 0) {
-    atomicExch(err, 11);            // slot still unacknowledged: receiver is gone or too far behind
   }
-  const bool flagger = last_block_done(counter);
-  if (flagger && ok) st_release_sys(remote_flag, seq);
+  bool any_failed;
+  const bool flagger = last_block_done(counter, !ok, &any_failed);
+  if (flagger) st_release_sys(remote_flag, any_failed ? kPoison : seq);     // a poisoned flag releases the receiver
 }
 
 __global__ void p2p_recv_kernel(uint4* __restrict__ dst, const uint4* __restrict__ local_slot, long long n16,
                                 const unsigned int* local_flag, unsigned int seq, unsigned int* remote_ack,
-                                unsigned int* counter, unsigned long long timeout_ns, int* err) {
+                                unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
+                                int dir) {
   __shared__ int ok;
-  if (threadIdx.x == 0) ok = wait_flag_ge(local_flag, seq, timeout_ns) ? 1 : 0;
+  if (threadIdx.x == 0) {
+    WaitResult res = ld_volatile(abort) != 0 ? kWaitAborted : kWaitOk;
+    unsigned int seen = 0;
+    if (res == kWaitOk) res = wait_flag_ge(local_flag, seq, timeout_ns, abort, &seen);
+    record_abort(abort, res, kWaitRecv, dir, seq, seen, rank, (int)seq);    // timeout: the message never arrived
+    ok = res == kWaitOk ? 1 : 0;
+  }
   __syncthreads();
   if (ok) {
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
          i += (long long)gridDim.x * blockDim.x)
       dst[i] = local_slot[i];
-  } else if (threadIdx.x == 0) {
-    atomicExch(err, 12);            // the message never arrived
   }
-  const bool acker = last_block_done(counter);
-  if (acker && ok && remote_ack != nullptr) st_release_sys(remote_ack, seq);
+  bool any_failed;
+  const bool acker = last_block_done(counter, !ok, &any_failed);
+  if (acker && remote_ack != nullptr) st_release_sys(remote_ack, any_failed ? kPoison : seq);
 }
 
 // Each rank writes `epoch` into slot [rank] of every peer's pad and waits until all slots of its own
-// pad reach `epoch`.  pads[p] is the address of rank p's pad (an array of `world` uint32).
+// pad reach `epoch`.  pads[p] is the address of rank p's pad (an array of `world` uint32).  One warp.
 __global__ void peer_barrier_kernel(unsigned int* const* __restrict__ pads, int rank, int world, unsigned int epoch,
-                                    unsigned long long timeout_ns, int* err) {
+                                    unsigned long long timeout_ns, int* abort, int tag) {
   const int p = threadIdx.x;
+  const bool dead = ld_volatile(abort) != 0;
   __threadfence_system();
-  if (p < world) st_release_sys(pads[p] + rank, epoch);
-  if (p < world && !wait_flag_ge(pads[rank] + p, epoch, timeout_ns)) atomicExch(err, 13);
+  if (p < world && !dead) st_release_sys(pads[p] + rank, epoch);
+  WaitResult res = dead ? kWaitAborted : kWaitOk;
+  unsigned int seen = 0;
+  if (p < world && !dead) res = wait_flag_ge(pads[rank] + p, epoch, timeout_ns, abort, &seen);
+  record_abort(abort, res, kWaitBarrier, p, epoch, seen, rank, tag);
+  // one failed wait poisons this rank's slot on every peer, so their barriers return at once
+  if (__any_sync(0xffffffffu, res != kWaitOk) && p < world) st_release_sys(pads[p] + rank, kPoison);
 }
 
 template <typename T>
@@ -166,8 +245,10 @@ struct Vec8<__half> {
 // Rank r owns words [r * slice16, (r + 1) * slice16) of the n16-word buffer.
 template <typename T>
 __global__ void allreduce_sumsq_16bit_kernel(uint4* const* __restrict__ bufs, int rank, int world, long long n16,
-                                             long long slice16, float scale, double* __restrict__ sumsq) {
+                                             long long slice16, float scale, double* __restrict__ sumsq,
+                                             const int* abort) {
   __shared__ float scratch[32];
+  if (block_sees_abort(abort)) return;
   const long long lo = (long long)rank * slice16;
   const long long hi = min(n16, lo + slice16);
   float ss = 0.f;
@@ -196,8 +277,10 @@ __global__ void allreduce_sumsq_16bit_kernel(uint4* const* __restrict__ bufs, in
 }
 
 __global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int rank, int world, long long n16,
-                                           long long slice16, float scale, double* __restrict__ sumsq) {
+                                           long long slice16, float scale, double* __restrict__ sumsq,
+                                           const int* abort) {
   __shared__ float scratch[32];
+  if (block_sees_abort(abort)) return;
   const long long lo = (long long)rank * slice16;
   const long long hi = min(n16, lo + slice16);
   float ss = 0.f;
@@ -222,8 +305,9 @@ __global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int
 template <typename T, typename O>
 __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, int rank, int world,
                                             long long shard_n, float scale, O* __restrict__ out,
-                                            double* __restrict__ sumsq, bool accumulate) {
+                                            double* __restrict__ sumsq, bool accumulate, const int* abort) {
   __shared__ float scratch[32];
+  if (block_sees_abort(abort)) return;
   constexpr int kMaxWorld = 8;
   constexpr int kPer = 16 / sizeof(T);           // elements per 16-byte load
   const long long lo = (long long)rank * shard_n;
@@ -293,8 +377,9 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
                                             float scale, float* __restrict__ p, float* __restrict__ m,
                                             float* __restrict__ v, Lo* __restrict__ low, double* __restrict__ sumsq,
                                             float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                                            float bc2_sqrt) {
+                                            float bc2_sqrt, const int* abort) {
   __shared__ float scratch[32];
+  if (block_sees_abort(abort)) return;
   constexpr int kMaxWorld = 8;
   static_assert(sizeof(T) == 2, "gradients are staged in a 16-bit type");
   const long long lo = (long long)rank * shard_n;
@@ -373,7 +458,8 @@ void reduce_slots(const void* slots, void* out, long long n, int world, int dtyp
 }
 
 void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
-                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, cudaStream_t st) {
+                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, const int* abort,
+                          cudaStream_t st) {
   if (shard_n == 0) return;
   const int grid = (int)std::min<long long>(div_up(shard_n / 8 + 1, 256), 148LL * 4);
   MB_DISPATCH_DTYPE(in_dtype, {
@@ -381,11 +467,11 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
     if (out_dtype == kF32 && in_dtype != kF32) {
       prefer_max_shared(reduce_scatter_sumsq_kernel<T, float>);
       reduce_scatter_sumsq_kernel<T, float><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
-                                                                 (float*)out, sumsq, accumulate);
+                                                                 (float*)out, sumsq, accumulate, abort);
     } else {
       prefer_max_shared(reduce_scatter_sumsq_kernel<T, T>);
       reduce_scatter_sumsq_kernel<T, T><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
-                                                             (T*)out, sumsq, accumulate);
+                                                             (T*)out, sumsq, accumulate, abort);
     }
   });
 }
@@ -393,7 +479,7 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
 // shard_n must be a multiple of 8 and world <= 8; `low` may be null.  Returns false otherwise.
 bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
                           float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
-                          float wd, int step, int in_dtype, int low_dtype, cudaStream_t st) {
+                          float wd, int step, int in_dtype, int low_dtype, const int* abort, cudaStream_t st) {
   if (shard_n == 0) return true;
   if (shard_n % 8 != 0 || world > 8 || in_dtype == kF32 || (low != nullptr && low_dtype != in_dtype)) return false;
   const float bc1 = 1.f - powf(beta1, (float)step);
@@ -403,58 +489,59 @@ bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long lon
     prefer_max_shared(reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16>);
     reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(
         (const __nv_bfloat16* const*)bufs, rank, world, shard_n, scale, p, m, v, (__nv_bfloat16*)low, sumsq, lr, beta1,
-        beta2, eps, wd, bc1, bc2s);
+        beta2, eps, wd, bc1, bc2s, abort);
   } else {
     prefer_max_shared(reduce_scatter_adamw_kernel<__half, __half>);
     reduce_scatter_adamw_kernel<__half, __half><<<grid, 256, 0, st>>>(
         (const __half* const*)bufs, rank, world, shard_n, scale, p, m, v, (__half*)low, sumsq, lr, beta1, beta2, eps, wd,
-        bc1, bc2s);
+        bc1, bc2s, abort);
   }
   return true;
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
               const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,
-              unsigned long long timeout_ns, int* err, cudaStream_t st) {
+              unsigned long long timeout_ns, int* abort, int rank, int dir, cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
   prefer_max_shared(p2p_send_kernel);
   p2p_send_kernel<<<grid, 256, 0, st>>>((const uint4*)src, (uint4*)remote_dst, n16, remote_flag, seq, local_ack,
-                                        need_ack, counter, timeout_ns, err);
+                                        need_ack, counter, timeout_ns, abort, rank, dir);
 }
 
 void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
-              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* err,
-              cudaStream_t st) {
+              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
+              int dir, cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
   prefer_max_shared(p2p_recv_kernel);
   p2p_recv_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (const uint4*)local_slot, n16, local_flag, seq, remote_ack,
-                                        counter, timeout_ns, err);
+                                        counter, timeout_ns, abort, rank, dir);
 }
 
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
-                  int* err, cudaStream_t st) {
+                  int* abort, int tag, cudaStream_t st) {
   prefer_max_shared(peer_barrier_kernel);
-  peer_barrier_kernel<<<1, 32, 0, st>>>(pads, rank, world, epoch, timeout_ns, err);
+  peer_barrier_kernel<<<1, 32, 0, st>>>(pads, rank, world, epoch, timeout_ns, abort, tag);
 }
 
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
-                     int dtype, cudaStream_t st) {
+                     int dtype, const int* abort, cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const long long slice16 = (n16 + world - 1) / world;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(slice16, 256), 148LL * 4));
   if (dtype == kBF16) {
     prefer_max_shared(allreduce_sumsq_16bit_kernel<__nv_bfloat16>);
     allreduce_sumsq_16bit_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16,
-                                                                    scale, sumsq);
+                                                                    scale, sumsq, abort);
   } else if (dtype == kF16) {
     prefer_max_shared(allreduce_sumsq_16bit_kernel<__half>);
     allreduce_sumsq_16bit_kernel<__half><<<grid, 256, 0, st>>>((uint4* const*)bufs, rank, world, n16, slice16, scale,
-                                                             sumsq);
+                                                             sumsq, abort);
   } else {
     prefer_max_shared(allreduce_sumsq_f32_kernel);
-    allreduce_sumsq_f32_kernel<<<grid, 256, 0, st>>>((float4* const*)bufs, rank, world, n16, slice16, scale, sumsq);
+    allreduce_sumsq_f32_kernel<<<grid, 256, 0, st>>>((float4* const*)bufs, rank, world, n16, slice16, scale, sumsq,
+                                                     abort);
   }
 }
 

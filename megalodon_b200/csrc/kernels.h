@@ -100,7 +100,7 @@ bool gemv_small_m(const void* x, const void* w, const void* bias, int bias_dtype
 // reduce-scatter fused with the sharded AdamW update (comm_kernels.cu); false if the shapes do not qualify
 bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
                           float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
-                          float wd, int step, int in_dtype, int low_dtype, cudaStream_t st);
+                          float wd, int step, int in_dtype, int low_dtype, const int* abort, cudaStream_t st);
 // Whether GEMMs with more than 128 rows run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); on by default.
 void gemm_set_cta_pairs(bool on);
 int gemm_pair_max_active_clusters();
@@ -129,19 +129,24 @@ void ema_parameters_bwd(const float* dk, const float* dbias, const float* p, con
                         const float* h, float* dp, float* dq, float* dgamma, float* dh, int B, int D, int N, int L,
                         cudaStream_t st);
 
-// ---- peer-memory communication (comm_kernels.cu); pointers may address a peer GPU's memory
+// ---- peer-memory communication (comm_kernels.cu); pointers may address a peer GPU's memory.
+// `abort` is the device's abort record (kCommAbortWords ints, zero = healthy): the first bounded wait
+// that runs out describes itself there, later waits return at once, and peers are released with
+// poisoned flags.  `rank` / `dir` / `tag` only label the record.
+constexpr int kCommAbortWords = 16;
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
               const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,
-              unsigned long long timeout_ns, int* err, cudaStream_t st);
+              unsigned long long timeout_ns, int* abort, int rank, int dir, cudaStream_t st);
 void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
-              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* err,
-              cudaStream_t st);
+              unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
+              int dir, cudaStream_t st);
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
-                  int* err, cudaStream_t st);
+                  int* abort, int tag, cudaStream_t st);
 // out[i] (+)= scale * sum_p bufs[p][rank * shard_n + i]; out dtype = in dtype or fp32; sumsq += |out|^2
 void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
-                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, cudaStream_t st);
+                          double* sumsq, bool accumulate, int in_dtype, int out_dtype, const int* abort,
+                          cudaStream_t st);
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
-                     int dtype, cudaStream_t st);
+                     int dtype, const int* abort, cudaStream_t st);
 
 }  // namespace mb

@@ -288,7 +288,9 @@ class FullyShardedDataParallel(nn.Module):
                 object.__setattr__(u, "_root", self)
         object.__setattr__(self, "_root", self)
         if self.compute_device.type == "cuda" and self.world_size > 1:
-            self._comm_stream = torch.cuda.Stream(self.compute_device)
+            # high priority: the flag barriers and reductions on this stream are what peers wait for;
+            # their few CTAs should be placed ahead of the compute stream's pending ones
+            self._comm_stream = torch.cuda.Stream(self.compute_device, priority=-1)
 
     @property
     def children_share_process_group(self) -> bool:
@@ -362,7 +364,7 @@ class FullyShardedDataParallel(nn.Module):
             if u._full is None:
                 u._full = torch.empty(u._numel_padded, dtype=shard.dtype, device=shard.device)
         if self._gather_stream is None:
-            self._gather_stream = torch.cuda.Stream(self.compute_device)
+            self._gather_stream = torch.cuda.Stream(self.compute_device, priority=-1)
         gs = self._gather_stream
         gs.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(gs):

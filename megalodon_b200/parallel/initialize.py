@@ -52,7 +52,11 @@ def initialize_model_parallel(
     model_parallel_backend: Optional[str] = None,
     chunk_parallel_backend: Optional[str] = None,
     ddp_backend: Optional[str] = None,
+    timeout: Optional[float] = None,
 ) -> None:
+    """`timeout` (seconds) applies to every group created here; by default the groups inherit the
+    timeout `init_torch_distributed` was given (a group created without one gets the backend's own
+    default - 10 minutes for NCCL - whatever the default group was told)."""
     global _TOPO
     if not dist.is_initialized():
         raise RuntimeError("torch.distributed must be initialised first")
@@ -69,6 +73,11 @@ def initialize_model_parallel(
         logger.info(f"> initializing chunk parallel with size {cp}")
         logger.info(f"> initializing model parallel with size {mp}")
 
+    import datetime
+    from .setup import process_group_timeout
+    seconds = timeout if timeout is not None else process_group_timeout()
+    tkw = {} if seconds is None else {"timeout": datetime.timedelta(seconds=float(seconds))}
+
     grid = torch.arange(world).reshape(dp, cp, mp)
     my_dp, my_cp, my_mp = (int(v[0]) for v in torch.where(grid == rank))
     topo = _Topology(mp_rank=my_mp, dp_rank=my_dp, cp_rank=my_cp)
@@ -77,19 +86,19 @@ def initialize_model_parallel(
     for j in range(cp):
         for k in range(mp):
             ranks = grid[:, j, k].tolist()
-            g = dist.new_group(ranks, backend=ddp_backend)
+            g = dist.new_group(ranks, backend=ddp_backend, **tkw)
             if (j, k) == (my_cp, my_mp):
                 topo.dp_group, topo.dp_ranks = g, ranks
     for i in range(dp):
         for j in range(cp):
             ranks = grid[i, j, :].tolist()
-            g = dist.new_group(ranks, backend=model_parallel_backend)
+            g = dist.new_group(ranks, backend=model_parallel_backend, **tkw)
             if (i, j) == (my_dp, my_cp):
                 topo.mp_group, topo.mp_ranks = g, ranks
     for i in range(dp):
         for k in range(mp):
             ranks = grid[i, :, k].tolist()
-            g = dist.new_group(ranks, backend=chunk_parallel_backend)
+            g = dist.new_group(ranks, backend=chunk_parallel_backend, **tkw)
             if (i, k) == (my_dp, my_mp):
                 topo.cp_group, topo.cp_ranks = g, ranks
                 topo.prev_chunk_rank = ranks[my_cp - 1] if my_cp > 0 else None
@@ -99,7 +108,7 @@ def initialize_model_parallel(
     if cp > 1 and dp > 1:
         for k in range(mp):
             ranks = grid[:, :, k].reshape(-1).tolist()
-            g = dist.new_group(ranks, backend=ddp_backend)
+            g = dist.new_group(ranks, backend=ddp_backend, **tkw)
             if k == my_mp:
                 topo.shard_group, topo.shard_ranks = g, ranks
     elif cp > 1:

@@ -109,8 +109,18 @@ def default_backend() -> str:
     return "nccl" if torch.cuda.is_available() else "gloo"
 
 
+_PG_TIMEOUT_S = [None]
+
+
+def process_group_timeout():
+    """Seconds given to `init_torch_distributed` (None before it ran): the timeout that
+    `initialize_model_parallel` passes on to the groups it creates."""
+    return _PG_TIMEOUT_S[0]
+
+
 def init_distributed_process_group(timeout: int, backend: str | None = None) -> None:
     kwargs = {}
+    _PG_TIMEOUT_S[0] = int(timeout)
     backend = backend or default_backend()
     if backend == "nccl":
         kwargs["device_id"] = torch.device("cuda", torch.cuda.current_device())

@@ -17,8 +17,26 @@ On top of it:
 
 Both also run over `HostFabric`, an in-process emulation of the peer memory of
 all ranks, which is how the slot / sequence / acknowledgement protocol and the
-timeout paths are tested without GPUs.  Waiting never blocks forever: a wait
-that is not satisfied within `timeout_s` raises `PeerTimeout`.
+timeout paths are tested without GPUs.
+
+Failure handling
+----------------
+Waiting never blocks forever, and one lost signal costs one timeout for the
+whole job, not one per wait:
+
+* every wait is bounded by `timeout_s`;
+* all communication objects of a device share one `AbortRecord`.  The first
+  wait that runs out writes who it was there (rank, kind of wait, direction,
+  sequence number wanted and seen); every later wait on that GPU returns at
+  once;
+* a kernel that gave up still signals its peers, with a poison value instead
+  of a sequence number, so their waits return at once too and they poison
+  their own neighbours in turn;
+* the record is mirrored into pinned host memory: `AbortRecord.tripped()` is a
+  plain host read (no device synchronisation) that a training loop can poll
+  between steps; `check()` raises `PeerTimeout` with the recorded details.
+
+After a failure the flags stay poisoned; `reset()` (collective) clears them.
 """
 from __future__ import annotations
 
@@ -29,7 +47,70 @@ import torch.distributed as dist
 
 
 class PeerTimeout(RuntimeError):
-    """A bounded wait on a peer's flag ran out."""
+    """A bounded wait on a peer's flag ran out (or a peer that gave up released it)."""
+
+
+POISON = 0xFFFFFFFF          # flag value written by a kernel that gave up
+_WAIT_KINDS = {1: "send (waiting for the receiver to acknowledge the slot)", 2: "receive (waiting for the message)",
+               3: "flag barrier", 4: "staged-buffer wait"}
+_DIRS = {0: "forward", 1: "backward"}
+
+
+def describe_abort(words) -> str:
+    """Readable form of an abort record (sequence of >= 8 ints, word 0 = code)."""
+    code, kind, where, want, seen, rank, tag, poisoned = (int(w) for w in list(words)[:8])
+    want &= 0xFFFFFFFF
+    seen &= 0xFFFFFFFF
+    what = _WAIT_KINDS.get(kind, f"wait of kind {kind}")
+    loc = f"direction {_DIRS.get(where, where)}" if kind in (1, 2) else f"peer {where}"
+    why = ("released by a poisoned flag: a peer gave up first" if poisoned
+           else f"timed out: wanted {want}, flag shows {'POISON' if seen == POISON else seen}")
+    return f"rank {rank}: {what}, {loc}, message/epoch {tag}: {why} (code {code})"
+
+
+class AbortRecord:
+    """The failure record shared by every communication object of one device (see the module docstring).
+    `dev` is the int32[16] device tensor handed to the kernels, `host` its pinned mirror."""
+
+    WORDS = 16
+    _by_device: Dict[int, "AbortRecord"] = {}
+
+    @classmethod
+    def get(cls, device) -> "AbortRecord":
+        device = torch.device(device)
+        idx = device.index if device.index is not None else torch.cuda.current_device()
+        rec = cls._by_device.get(idx)
+        if rec is None:
+            rec = cls._by_device[idx] = cls(torch.device("cuda", idx))
+        return rec
+
+    def __init__(self, device: torch.device):
+        from ..ops._ext import require
+        self.device = device
+        self.host = torch.zeros(self.WORDS, dtype=torch.int32).pin_memory()
+        words = [0] * self.WORDS
+        addr = int(require().pinned_device_ptr(self.host))      # 0 if the mirror cannot be mapped
+        for i, w in ((8, addr & 0xFFFFFFFF), (9, addr >> 32)):
+            words[i] = w - (1 << 32) if w >= (1 << 31) else w
+        self.dev = torch.tensor(words, dtype=torch.int32, device=device)
+
+    def tripped(self) -> bool:
+        """Host-only look at the pinned mirror: True once a kernel on this device gave up."""
+        return int(self.host[0]) != 0
+
+    def read(self) -> Optional[List[int]]:
+        """The record (synchronises the device), or None when healthy."""
+        words = self.dev.tolist()
+        return words if words[0] != 0 else None
+
+    def clear(self) -> None:
+        self.dev[:8].zero_()
+        self.host[:8].zero_()
+
+    def check(self) -> None:
+        words = self.read()
+        if words is not None:
+            raise PeerTimeout(describe_abort(words))
 
 
 def _round_up(x: int, m: int) -> int:
@@ -88,6 +169,8 @@ class HostFabric:
         self.nbytes = _round_up(nbytes, 256)
         self.mem = [torch.zeros(self.nbytes, dtype=torch.uint8) for _ in range(world)]
         self.dropped_flags = 0        # fault injection: number of upcoming flag writes to lose
+        self.abort: List[Optional[str]] = [None] * world     # per rank: why its "device" gave up
+        self.timeouts = 0             # waits that ran their full time (a poisoned flag does not count)
 
     def region(self, rank: int) -> "HostRegion":
         return HostRegion(self, rank)
@@ -101,6 +184,12 @@ class HostRegion:
 
     def u32(self, rank: int, offset: int) -> torch.Tensor:
         return self.fabric.mem[rank][offset:offset + 4].view(torch.int32)
+
+    def read_u32(self, rank: int, offset: int) -> int:
+        return int(self.u32(rank, offset).item()) & 0xFFFFFFFF
+
+    def write_u32(self, rank: int, offset: int, value: int) -> None:
+        self.u32(rank, offset).fill_(value - (1 << 32) if value >= (1 << 31) else value)
 
     def bytes_of(self, rank: int, offset: int, nbytes: int) -> torch.Tensor:
         return self.fabric.mem[rank][offset:offset + nbytes]
@@ -135,7 +224,7 @@ class PeerMailbox:
         if not self._is_host:
             dev = region.device
             self._counters = torch.zeros(4, dtype=torch.int32, device=dev)
-            self._err = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._abort = AbortRecord.get(dev)
             self._stage: Dict[int, torch.Tensor] = {}
 
     @staticmethod
@@ -175,7 +264,7 @@ class PeerMailbox:
             require().p2p_send(src, self.region.peer_ptr(peer, self._slot_off(d, slot)), padded,
                                self.region.peer_ptr(peer, self._flag_off(d, slot)), seq,
                                self.region.peer_ptr(self.region.rank, self._ack_off(d, slot)), need_ack,
-                               self._counters[d:d + 1], self.timeout_ns, self._err)
+                               self._counters[d:d + 1], self.timeout_ns, self._abort.dev, self.region.rank, d)
 
     def recv(self, buf: torch.Tensor, direction) -> torch.Tensor:
         d = self._dir(direction)
@@ -195,20 +284,37 @@ class PeerMailbox:
             require().p2p_recv(dst, self.region.peer_ptr(me, self._slot_off(d, slot)), padded,
                                self.region.peer_ptr(me, self._flag_off(d, slot)), seq,
                                self.region.peer_ptr(peer, self._ack_off(d, slot)), self._counters[2 + d:3 + d],
-                               self.timeout_ns, self._err)
+                               self.timeout_ns, self._abort.dev, self.region.rank, d)
             if dst.data_ptr() != buf.data_ptr():
                 buf.view(-1).view(torch.uint8).copy_(dst.view(torch.uint8)[:nbytes])
         return buf
 
     def check(self) -> None:
-        """Raise `PeerTimeout` if one of the kernels gave up waiting (synchronises the device)."""
+        """Raise `PeerTimeout` if a kernel on this device gave up waiting (synchronises the device)."""
         if self._is_host:
+            why = self.region.fabric.abort[self.region.rank]
+            if why:
+                raise PeerTimeout(why)
             return
-        code = int(self._err.item())
-        if code:
-            self._err.zero_()
-            what = {11: "send: slot not acknowledged by the receiver", 12: "recv: message never arrived"}
-            raise PeerTimeout(what.get(code, f"peer wait timed out (code {code})"))
+        self._abort.check()
+
+    def reset(self, group: Optional[dist.ProcessGroup] = None) -> None:
+        """Back to the initial state after a failure: flags, acknowledgements, sequence numbers and the
+        abort record are cleared.  Collective over the mailbox's group (every rank must call it with
+        nothing in flight); on the host fabric it clears this rank's side only."""
+        lo = self._flag_off(0, 0)
+        n = 2 * 2 * self.n_slots * 4
+        self.send_seq, self.recv_seq = [0, 0], [0, 0]
+        if self._is_host:
+            self.region.local[lo:lo + n].zero_()
+            self.region.fabric.abort[self.region.rank] = None
+            return
+        torch.cuda.synchronize(self.region.device)
+        self.region.local[lo:lo + n].zero_()
+        self._counters.zero_()
+        self._abort.clear()
+        torch.cuda.synchronize(self.region.device)
+        dist.barrier(group=group if group is not None else self.region.group)
 
     # ---- CUDA helpers
     def _padded(self, t: torch.Tensor, nbytes: int, for_write: bool = False):
@@ -225,24 +331,48 @@ class PeerMailbox:
             stage[:nbytes].copy_(tc.view(-1).view(torch.uint8))
         return stage, padded
 
-    # ---- host emulation (same protocol, CPU tensors, no blocking)
+    # ---- host emulation (same protocol as the kernels, CPU tensors; a wait that is not already
+    # satisfied counts as one that ran its full time)
+    def _host_wait(self, rank_of_flag: int, off: int, want: int, what: str) -> None:
+        r = self.region
+        fab = r.fabric
+        if fab.abort[r.rank]:
+            raise PeerTimeout(f"rank {r.rank}: gave up earlier ({fab.abort[r.rank]})")
+        seen = r.read_u32(rank_of_flag, off)
+        if seen == POISON:
+            fab.abort[r.rank] = f"rank {r.rank}: {what}: released by a poisoned flag: a peer gave up first"
+        elif seen < want:
+            fab.timeouts += 1
+            fab.abort[r.rank] = f"rank {r.rank}: {what}: timed out: wanted {want}, flag shows {seen}"
+        else:
+            return
+        raise PeerTimeout(fab.abort[r.rank])
+
     def _host_send(self, t, d, peer, slot, seq, need_ack, nbytes):
         r = self.region
-        if need_ack and int(r.u32(r.rank, self._ack_off(d, slot)).item()) < need_ack:
-            raise PeerTimeout("send: slot not acknowledged by the receiver")
+        try:
+            if r.fabric.abort[r.rank] or need_ack:
+                self._host_wait(r.rank, self._ack_off(d, slot), need_ack,
+                                f"send (waiting for the receiver to acknowledge the slot), direction {_DIRS[d]}")
+        except PeerTimeout:
+            r.write_u32(peer, self._flag_off(d, slot), POISON)       # releases the receiver at once
+            raise
         r.bytes_of(peer, self._slot_off(d, slot), nbytes).copy_(t.detach().contiguous().view(-1).view(torch.uint8))
         if r.fabric.dropped_flags > 0:
             r.fabric.dropped_flags -= 1          # injected fault: the flag write is lost
             return
-        r.u32(peer, self._flag_off(d, slot)).fill_(seq)
+        r.write_u32(peer, self._flag_off(d, slot), seq)
 
     def _host_recv(self, buf, d, peer, slot, seq, nbytes):
         r = self.region
-        if int(r.u32(r.rank, self._flag_off(d, slot)).item()) < seq:
-            self.recv_seq[d] -= 1
-            raise PeerTimeout("recv: message never arrived")
+        try:
+            self._host_wait(r.rank, self._flag_off(d, slot), seq,
+                            f"receive (waiting for the message), direction {_DIRS[d]}")
+        except PeerTimeout:
+            r.write_u32(peer, self._ack_off(d, slot), POISON)        # releases a sender waiting for this slot
+            raise
         buf.view(-1).view(torch.uint8).copy_(r.bytes_of(r.rank, self._slot_off(d, slot), nbytes))
-        r.u32(peer, self._ack_off(d, slot)).fill_(seq)
+        r.write_u32(peer, self._ack_off(d, slot), seq)
 
 
 # ----------------------------------------------------------------------------- all-reduce + grad norm
@@ -259,7 +389,7 @@ class SymmetricAllReduce:
         self.timeout_ns = int(timeout_s * 1e9)
         self.epoch = 0
         dev = region.device
-        self._err = torch.zeros(1, dtype=torch.int32, device=dev)
+        self._abort = AbortRecord.get(dev)
         self._bufs = region.ptr_table_at(0).contiguous()
         self._pads = region.ptr_table_at(self.pad_off).contiguous()
 
@@ -270,7 +400,7 @@ class SymmetricAllReduce:
     def _barrier(self) -> None:
         from ..ops._ext import require
         self.epoch += 1
-        require().peer_barrier(self._pads, self.region.rank, self.epoch, self.timeout_ns, self._err)
+        require().peer_barrier(self._pads, self.region.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
 
     @torch.no_grad()
     def all_reduce_(self, tensors: List[torch.Tensor], sumsq: Optional[torch.Tensor] = None,
@@ -293,15 +423,16 @@ class SymmetricAllReduce:
                 if padded != nbytes:
                     stage[part.numel():].zero_()
                 self._barrier()                      # every rank has staged its bucket
-                ext.allreduce_sumsq(self._bufs, self.region.rank, padded, scale, sumsq, _DT[t.dtype])
+                ext.allreduce_sumsq(self._bufs, self.region.rank, padded, scale, sumsq, _DT[t.dtype], self._abort.dev)
                 self._barrier()                      # every rank has pushed its reduced slice
                 part.copy_(stage[:part.numel()])
 
     def check(self) -> None:
-        code = int(self._err.item())
-        if code:
-            self._err.zero_()
-            raise PeerTimeout(f"peer barrier timed out (code {code})")
+        self._abort.check()
+
+    def reset(self) -> None:
+        """Collective: clear the signal pad, the epoch and the abort record after a failure."""
+        _reset_pads(self, self.region, self.pad_off)
 
 
 class SymmetricReduceScatter:
@@ -319,7 +450,7 @@ class SymmetricReduceScatter:
         self.region = SymmetricRegion(self.pad_off + _round_up(4 * self.world, 256), group, device)
         self._pads = self.region.ptr_table_at(self.pad_off).contiguous()
         self._bufs = [self.region.ptr_table_at(0).contiguous(), self.region.ptr_table_at(self.stage_bytes).contiguous()]
-        self._err = torch.zeros(1, dtype=torch.int32, device=device)
+        self._abort = AbortRecord.get(device)
         self.timeout_ns = int(timeout_s * 1e9)
         self.epoch = 0
         self._toggle = 0
@@ -342,8 +473,9 @@ class SymmetricReduceScatter:
         stage = self.region.view(t * self.stage_bytes, n * flat_grad.element_size(), flat_grad.dtype)
         stage.copy_(flat_grad.view(-1))
         self.epoch += 1
-        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
-        ext.reduce_scatter_sumsq(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, out_shard, sumsq, accumulate)
+        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
+        ext.reduce_scatter_sumsq(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, out_shard, sumsq, accumulate,
+                                 self._abort.dev)
 
     @torch.no_grad()
     def reduce_scatter_adamw(self, flat_grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor,
@@ -365,15 +497,26 @@ class SymmetricReduceScatter:
         stage = self.region.view(t * self.stage_bytes, n * flat_grad.element_size(), flat_grad.dtype)
         stage.copy_(flat_grad.view(-1))
         self.epoch += 1
-        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
+        ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
         ext.reduce_scatter_adamw(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, master, exp_avg, exp_avg_sq,
-                                 low, sumsq, lr, beta1, beta2, eps, weight_decay, step)
+                                 low, sumsq, lr, beta1, beta2, eps, weight_decay, step, self._abort.dev)
 
     def check(self) -> None:
-        code = int(self._err.item())
-        if code:
-            self._err.zero_()
-            raise PeerTimeout(f"reduce-scatter peer barrier timed out (code {code})")
+        self._abort.check()
+
+    def reset(self) -> None:
+        """Collective: clear the signal pad, the epoch and the abort record after a failure."""
+        _reset_pads(self, self.region, self.pad_off)
+        self._toggle = 0
+
+
+def _reset_pads(obj, region: SymmetricRegion, pad_off: int) -> None:
+    torch.cuda.synchronize(region.device)
+    region.local[pad_off:pad_off + _round_up(4 * region.world, 256)].zero_()
+    obj.epoch = 0
+    obj._abort.clear()
+    torch.cuda.synchronize(region.device)
+    dist.barrier(group=region.group)
 
 
 # ----------------------------------------------------------------------------- wiring

@@ -22,7 +22,7 @@ from typing import Optional
 import torch
 import torch.distributed as dist
 
-from .symm import PeerTimeout, SymmetricRegion, _round_up
+from .symm import AbortRecord, SymmetricRegion, _round_up
 
 _WORKSPACE = [None]
 
@@ -47,7 +47,7 @@ class TensorParallelWorkspace:
         self.pad_off = (2 + 2 * self.world) * self.part_bytes
         self.region = SymmetricRegion(self.pad_off + _round_up(4 * self.world, 256), group, device)
         self.timeout_ns = int(timeout_s * 1e9)
-        self._err = torch.zeros(1, dtype=torch.int32, device=device)
+        self._abort = AbortRecord.get(device)
         self._pads = self.region.ptr_table_at(self.pad_off).contiguous()
         self.epoch = 0
         self._stage_toggle = 0
@@ -56,13 +56,10 @@ class TensorParallelWorkspace:
     def _barrier(self) -> None:
         from ..ops._ext import require
         self.epoch += 1
-        require().peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._err)
+        require().peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
 
     def check(self) -> None:
-        code = int(self._err.item())
-        if code:
-            self._err.zero_()
-            raise PeerTimeout(f"tensor-parallel peer barrier timed out (code {code})")
+        self._abort.check()
 
     # y[M, N] = act([x_0 | x_1 | ...] w^T + bias), x_r = this rank's [M, K / world] shard
     def ag_gemm(self, x_part: torch.Tensor, w: torch.Tensor, bias=None, act=None, b_mn: bool = False,

@@ -1,5 +1,6 @@
-"""Peer-memory communication on 2 GPUs of one box (child processes, NCCL for the
-bootstrap, NVLS off, plain peer loads/stores in the kernels)."""
+"""Peer-memory communication on 2, 4 and 8 GPUs of one box (child processes, NCCL for the
+bootstrap, NVLS off, plain peer loads/stores in the kernels).  Cases that depend on the number of
+ranks (a rank with two neighbours exists only from 3 ranks up) run at every size the box offers."""
 import os
 import socket
 import tempfile
@@ -15,6 +16,9 @@ pytestmark = pytest.mark.gpu
 def _need_gpus(n):
     if not torch.cuda.is_available() or torch.cuda.device_count() < n:
         pytest.skip(f"needs {n} GPUs")
+
+
+WORLDS = [2, 4, 8]
 
 
 def _free_port():
@@ -78,10 +82,9 @@ def _mailbox_case(rank, world):
         torch.cuda.synchronize()
         try:
             box.check()
-        except PeerTimeout:
-            timed_out = True
-        box.recv_seq[0] -= 1                 # that message was never consumed
-    dist.barrier()
+        except PeerTimeout as e:
+            timed_out = "receive" in str(e) and "timed out" in str(e)
+    box.reset()                              # collective: flags, sequence numbers and the abort record start over
     if rank == 0:
         box.send(torch.arange(16.0, device=dev), "fwd")
     else:
@@ -99,6 +102,82 @@ def test_peer_mailbox_two_gpus():
     res = _run(_mailbox_case)
     assert all(r[0] for r in res)
     assert res[1][1], "the unanswered receive should have reported a timeout"
+
+
+def _line_case(rank, world):
+    """A line of `world` ranks: every layer's state goes rank to rank forward, every gradient back,
+    more rounds than slots.  Then rank 0 withholds one message: the whole line must be out after ONE
+    wait ran its time, and `reset()` must bring it back."""
+    import time
+    import torch.distributed as dist
+    from megalodon_b200.parallel.symm import AbortRecord, PeerMailbox, PeerTimeout, SymmetricRegion
+    dev = torch.device("cuda", rank)
+    slot, n_slots, timeout_s = 8192, 2, 1.0
+    region = SymmetricRegion(PeerMailbox.bytes_needed(slot, n_slots), None, dev)
+    box = PeerMailbox(region, rank - 1 if rank > 0 else None, rank + 1 if rank + 1 < world else None, slot,
+                      n_slots=n_slots, timeout_s=timeout_s)
+    ok = True
+
+    def forward(k, withhold=False):
+        val = torch.full((2000,), float(k), device=dev)
+        if rank > 0:
+            box.recv(val, "fwd")
+            val = val + 1
+        if rank + 1 < world and not withhold:
+            box.send(val, "fwd")
+        return val
+
+    def backward(k):
+        g = torch.full((37,), -float(k), device=dev, dtype=torch.bfloat16)
+        if rank + 1 < world:
+            box.recv(g, "bwd")
+            g = g - 1
+        if rank > 0:
+            box.send(g, "bwd")
+        return g
+
+    for k in range(9):
+        v = forward(k)
+        g = backward(k)
+        ok = ok and bool((v == k + rank).all()) and bool((g.float() == -k - (world - 1 - rank)).all())
+    torch.cuda.synchronize()
+    box.check()
+    dist.barrier()
+    # fault made on the host: rank 0 does not launch one send
+    t0 = time.time()
+    forward(100, withhold=(rank == 0))
+    backward(100)
+    torch.cuda.synchronize()
+    waited = time.time() - t0
+    report = ""
+    try:
+        box.check()
+    except PeerTimeout as e:
+        report = str(e)
+    tripped = AbortRecord.get(dev).tripped()             # host-only look at the pinned mirror
+    box.reset()
+    v = forward(7)
+    g = backward(7)
+    torch.cuda.synchronize()
+    box.check()
+    ok = ok and bool((v == 7 + rank).all()) and bool((g.float() == -7 - (world - 1 - rank)).all())
+    return ok, waited, report, tripped, timeout_s
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_mailbox_line_with_middle_ranks_and_one_timeout_for_the_whole_line(world):
+    _need_gpus(world)
+    res = _run(_line_case, world)
+    timeout_s = res[0][4]
+    for r, (ok, waited, report, tripped, _) in enumerate(res):
+        assert ok, f"rank {r}: wrong payload"
+        assert report, f"rank {r} did not learn of the failure"
+        assert tripped, f"rank {r}: pinned mirror of the abort record not set"
+        # one wait ran its time (rank 1's); nobody may have waited for two
+        assert waited < 1.9 * timeout_s + 1.0, f"rank {r} waited {waited:.2f} s"
+    assert "timed out" in res[1][2] and "receive" in res[1][2] and "forward" in res[1][2], res[1][2]
+    for r in range(2, world):
+        assert "poisoned" in res[r][2], res[r][2]
 
 
 def _allreduce_case(rank, world):
@@ -126,9 +205,10 @@ def _allreduce_case(rank, world):
     return out
 
 
-def test_symmetric_allreduce_two_gpus():
-    _need_gpus(2)
-    res = _run(_allreduce_case)
+@pytest.mark.parametrize("world", WORLDS)
+def test_symmetric_allreduce(world):
+    _need_gpus(world)
+    res = _run(_allreduce_case, world)
     for r in res:
         assert r["torch.bfloat16"][0] < 5e-2 and r["torch.bfloat16"][1] < 1e-3, r
         assert r["torch.float32"][0] < 1e-5 and r["torch.float32"][1] < 1e-5, r
@@ -147,7 +227,7 @@ def _train_case(rank, world):
     cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
                     cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
                     efficient_attn="fused", layerwise_ckpt=True)
-    toks = torch.randint(0, 512, (2, 513), generator=torch.Generator().manual_seed(0)).cuda()
+    toks = torch.randint(0, 512, (2, 128 * max(4, world) + 1), generator=torch.Generator().manual_seed(0)).cuda()
     x, y = toks[:, :-1], toks[:, 1:]
     curves = {}
     for transport in ("nccl", "p2p"):
@@ -174,9 +254,10 @@ def _train_case(rank, world):
     return curves
 
 
-def test_chunk_parallel_training_over_peer_memory_matches_nccl():
-    _need_gpus(2)
-    res = _run(_train_case)
+@pytest.mark.parametrize("world", WORLDS)
+def test_chunk_parallel_training_over_peer_memory_matches_nccl(world):
+    _need_gpus(world)
+    res = _run(_train_case, world)
     for r in res:
         for (l0, n0), (l1, n1) in zip(r["nccl"], r["p2p"]):
             assert abs(l0 - l1) < 5e-2, r
@@ -274,7 +355,7 @@ def _fsdp_rs_case(rank, world):
     cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
                     cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
                     efficient_attn="fused")
-    toks = torch.randint(0, 512, (4, 257), generator=torch.Generator().manual_seed(0))
+    toks = torch.randint(0, 512, (2 * world, 257), generator=torch.Generator().manual_seed(0))
     toks = toks[rank * 2:(rank + 1) * 2].cuda()
     x, y = toks[:, :-1], toks[:, 1:]
     curves = {}
@@ -300,9 +381,10 @@ def _fsdp_rs_case(rank, world):
     return curves
 
 
-def test_fsdp_with_peer_memory_reduce_scatter_matches_nccl():
-    _need_gpus(2)
-    for r in _run(_fsdp_rs_case):
+@pytest.mark.parametrize("world", WORLDS)
+def test_fsdp_with_peer_memory_reduce_scatter_matches_nccl(world):
+    _need_gpus(world)
+    for r in _run(_fsdp_rs_case, world):
         for (l0, n0), (l1, n1) in zip(r[False], r[True]):
             assert abs(l0 - l1) < 5e-2, r
             assert abs(n0 - n1) < 0.1 * max(1.0, n0), r

@@ -28,14 +28,23 @@ def test_messages_arrive_in_order_and_slots_are_reused():
         assert torch.equal(back, grad)
 
 
-def test_receive_without_send_times_out_and_can_be_retried():
-    _, a, b = _pair()
+def test_receive_without_send_times_out_and_reset_recovers():
+    fabric, a, b = _pair()
     out = torch.empty(4)
     with pytest.raises(PeerTimeout):
         b.recv(out, "fwd")
-    a.send(torch.arange(4.0), "fwd")         # the late message is still delivered
+    assert fabric.timeouts == 1
+    with pytest.raises(PeerTimeout):         # the failure is sticky: no second full-length wait
+        b.recv(out, "fwd")
+    assert fabric.timeouts == 1
+    with pytest.raises(PeerTimeout):
+        b.check()
+    a.reset()
+    b.reset()
+    a.send(torch.arange(4.0), "fwd")
     b.recv(out, "fwd")
     assert torch.equal(out, torch.arange(4.0))
+    b.check()
 
 
 def test_sender_may_not_lap_the_receiver():
@@ -52,6 +61,100 @@ def test_dropped_flag_is_detected_by_the_receiver():
     a.send(torch.ones(4), "fwd")
     with pytest.raises(PeerTimeout):
         b.recv(torch.empty(4), "fwd")
+
+
+def _line(world, n_slots=2, slot_bytes=64):
+    fabric = HostFabric(world, PeerMailbox.bytes_needed(slot_bytes, n_slots))
+    boxes = [PeerMailbox(fabric.region(r), r - 1 if r > 0 else None, r + 1 if r + 1 < world else None, slot_bytes,
+                         n_slots=n_slots) for r in range(world)]
+    return fabric, boxes
+
+
+def _try(fn, *args):
+    """On the GPU a kernel that gave up does not stop the host: the next operation is still launched
+    (and, under the abort record, releases its peer with a poisoned flag)."""
+    try:
+        fn(*args)
+        return True
+    except PeerTimeout:
+        return False
+
+
+def _forward(boxes, k, log=None):
+    """One layer's handoff along the line: rank r receives from r - 1, then sends to r + 1."""
+    world = len(boxes)
+    for r in range(world):
+        val, ok = float(k), True
+        if r > 0:
+            got = torch.zeros(3)
+            ok = _try(boxes[r].recv, got, "fwd")
+            val = float(got[0]) + 1.0
+        if r + 1 < world:
+            ok = _try(boxes[r].send, torch.full((3,), val), "fwd") and ok
+        if log is not None and ok:
+            log[r].append(val)
+
+
+def _backward(boxes, k, log=None):
+    world = len(boxes)
+    for r in reversed(range(world)):
+        val, ok = -float(k), True
+        if r + 1 < world:
+            got = torch.zeros(5)
+            ok = _try(boxes[r].recv, got, "bwd")
+            val = float(got[0]) - 1.0
+        if r > 0:
+            ok = _try(boxes[r].send, torch.full((5,), val), "bwd") and ok
+        if log is not None and ok:
+            log[r].append(val)
+
+
+def test_four_rank_line_middle_ranks_both_directions_beyond_the_slot_count():
+    """Ranks 1 and 2 have both neighbours: they receive and send in both directions, and with two
+    slots and seven rounds every slot, flag and acknowledgement is reused several times."""
+    fabric, boxes = _line(4, n_slots=2)
+    for k in range(7):
+        log = [[] for _ in range(4)]
+        _forward(boxes, k, log)
+        assert [v[0] for v in log] == [k, k + 1, k + 2, k + 3]
+        log = [[] for _ in range(4)]
+        _backward(boxes, k, log)
+        assert [v[0] for v in log] == [-k - 3, -k - 2, -k - 1, -k]
+    assert fabric.timeouts == 0
+    for b in boxes:
+        b.check()
+
+
+def test_one_dropped_flag_takes_all_four_ranks_out_within_one_timeout():
+    fabric, boxes = _line(4, n_slots=2)
+    _forward(boxes, 0)
+    _backward(boxes, 0)
+    fabric.dropped_flags = 1                 # rank 0's next announcement to rank 1 is lost
+    _forward(boxes, 1)                       # rank 1 times out; ranks 2 and 3 are released by poison
+    assert fabric.timeouts == 1
+    assert [a is not None for a in fabric.abort] == [False, True, True, True]
+    _backward(boxes, 1)                      # rank 0 learns of it from rank 1's poisoned gradient flag
+    assert fabric.timeouts == 1, "only the first wait may run its full time"
+    assert all(a is not None for a in fabric.abort)
+    assert "timed out" in fabric.abort[1] and "direction forward" in fabric.abort[1]
+    assert "wanted 2" in fabric.abort[1] and "flag shows 0" in fabric.abort[1]     # slot 1 was never written
+    for r in (0, 2, 3):
+        assert "poisoned" in fabric.abort[r]
+    for b in boxes:
+        with pytest.raises(PeerTimeout):
+            b.check()
+    for b in boxes:
+        b.reset()
+    log = [[] for _ in range(4)]
+    _forward(boxes, 5, log)
+    assert [v[0] for v in log] == [5, 6, 7, 8]
+
+
+def test_abort_record_is_readable():
+    from megalodon_b200.parallel.symm import POISON, describe_abort
+    msg = describe_abort([12, 2, 1, 133, 132, 5, 133, 0])
+    assert "rank 5" in msg and "receive" in msg and "backward" in msg and "wanted 133" in msg and "132" in msg
+    assert "poisoned" in describe_abort([13, 3, 2, 7, POISON - (1 << 32), 1, 7, 1])
 
 
 def test_oversized_message_is_rejected():
