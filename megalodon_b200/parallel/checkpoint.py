@@ -103,6 +103,11 @@ class CheckpointWrapper(nn.Module):
     def __init__(self, module: nn.Module):
         super().__init__()
         self._wrapped = module
+        # The wrapper is invisible in state dicts (like fairscale's checkpoint_wrapper, which the
+        # reference uses): keys are those of the wrapped block, so a checkpoint written with
+        # checkpointing loads into a model built without it and the other way round.
+        self._register_state_dict_hook(_strip_wrapper_prefix)
+        self._register_load_state_dict_pre_hook(_insert_wrapper_prefix)
 
     def __getattr__(self, name: str) -> Any:
         try:
@@ -121,6 +126,19 @@ class CheckpointWrapper(nn.Module):
         out = checkpoint(run, x, freqs_cis, mask, piece, *(carry or ()))
         y, state = out[0], out[1:]
         return y, (tuple(state) if state else None)
+
+
+def _strip_wrapper_prefix(module, state_dict, prefix, local_metadata):
+    inner = prefix + "_wrapped."
+    for key in [k for k in state_dict if k.startswith(inner)]:
+        state_dict[prefix + key[len(inner):]] = state_dict.pop(key)
+    return state_dict
+
+
+def _insert_wrapper_prefix(state_dict, prefix, local_metadata, strict, missing_keys, unexpected_keys, error_msgs):
+    inner = prefix + "_wrapped."
+    for key in [k for k in state_dict if k.startswith(prefix) and not k.startswith(inner)]:
+        state_dict[inner + key[len(prefix):]] = state_dict.pop(key)
 
 
 def checkpoint_wrapper(module: nn.Module) -> CheckpointWrapper:

@@ -488,6 +488,10 @@ class FullyShardedDataParallel(nn.Module):
         if self.world_size > 1 and fused_rs is not None and flat_grad.dtype == fused_rs.dtype:
             # peer-memory reduce-scatter: sum + 1/dp scale + cast + |g|^2 partial in one kernel
             accumulate = p._grad_shard is not None
+            if accumulate and p._grad_shard.dtype != torch.float32:
+                # second backward pass before an optimiser step: the running sum moves to fp32
+                self._sync_comm()
+                p._grad_shard = p._grad_shard.float()
             shard = p._grad_shard if accumulate else torch.empty(self._shard_numel, dtype=red_dtype, device=g.device)
             if getattr(root, "_fused_sumsq", None) is None:
                 root._fused_sumsq = torch.zeros((), dtype=torch.float64, device=g.device)
@@ -540,8 +544,10 @@ class FullyShardedDataParallel(nn.Module):
         if p._grad_shard is None:
             p._grad_shard = shard
         else:
+            # several backward passes before one optimiser step: accumulate in fp32 like the
+            # reference's FSDP (a bf16 running sum loses the small micro-batch contributions)
             self._sync_comm()
-            p._grad_shard = p._grad_shard + shard
+            p._grad_shard = p._grad_shard.float().add_(shard)
         if self.reshard_after_forward and not self._is_root:
             self._free_full()
         return None
@@ -606,6 +612,8 @@ class FullyShardedDataParallel(nn.Module):
             return
         for g in self._grad_tensors():
             dist.all_reduce(g, group=self.chunk_parallel_process_group)
+        # the squared norm a fused reduce-scatter accumulated describes the gradients BEFORE this sum
+        self._fused_sumsq = None
 
     @torch.no_grad()
     def clip_grad_norm_(self, max_norm: Union[float, int], norm_type: Union[float, int] = 2.0) -> torch.Tensor:

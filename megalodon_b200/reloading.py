@@ -113,6 +113,9 @@ def reload_config_and_tokenizer(ckpt_dir: Path, tokenizer_path: Optional[str] = 
     known = {f for f in ModelConf.__dataclass_fields__}
     model_cfg = ModelConf(**{k: v for k, v in cfg["model"].items() if k in known})
     model_cfg.init_mode = "none"
+    # training-time memory settings have no place in the evaluation model
+    model_cfg.layerwise_ckpt = False
+    model_cfg.ckpt_layers = None
     if model_cfg.vocab_size == -1:          # old checkpoints do not record it
         model_cfg.vocab_size = tokenizer.n_words
     assert model_cfg.vocab_size == tokenizer.n_words, (tokenizer.n_words, model_cfg.vocab_size)
@@ -142,11 +145,19 @@ def build_consolidated_model(model_cfg: ModelConf, dtype: str) -> Mega:
 
 
 def load_state_dict(model: Mega, state_dict: Dict, strict: bool) -> None:
+    """Missing or unexpected *buffers* are logged (older checkpoints lack some); a missing
+    *parameter* is an error even with `strict=False` - the model is built with `init_mode='none'`,
+    so a weight that is not in the file would stay uninitialised memory."""
     missing, unexpected = model.load_state_dict(state_dict, strict=strict)
     if missing:
         logger.warning(f"Missing keys when reloading: {missing}")
     if unexpected:
         logger.warning(f"Unexpected keys when reloading: {unexpected}")
+    params = {name for name, _ in model.named_parameters()}
+    lost = [k for k in missing if k in params]
+    if lost:
+        raise RuntimeError(f"checkpoint has no value for {len(lost)} parameter(s), e.g. {lost[:4]}; "
+                           f"keys it has that the model does not: {list(unexpected)[:4]}")
 
 
 def load_consolidated_weights(ckpt_dir: Path, model: Mega, reloaded: ReloadedConf, dtype: str) -> None:

@@ -204,6 +204,45 @@ def test_checkpoint_roundtrips(tmp_path):
     assert not rc.is_fsdp and rc.mp_world_size == 1 and rc.dtype == "fp32"
 
 
+def test_checkpointed_model_saves_and_reloads_under_the_plain_key_names(tmp_path):
+    """A model trained with activation checkpointing writes the same key names as one without
+    (fairscale's checkpoint_wrapper, which the reference uses, does not rename keys); reloading builds
+    the evaluation model without checkpointing, every tensor equals the file's, and a file that
+    lacks a parameter is refused instead of leaving uninitialised weights."""
+    from megalodon_b200 import reloading
+    from megalodon_b200.config import TokenizerConf
+    from megalodon_b200.models.mega import Mega
+    cfg = _cfg(layerwise_ckpt=True, ckpt_layers=1)
+    model = _build(cfg, seed=3)
+    plain_keys = set(_build(_cfg(), seed=3).state_dict().keys())
+    assert set(model.state_dict().keys()) == plain_keys
+    reloading.save_consolidated(model, str(tmp_path / "cons"), cfg, dtype="fp32")
+    state = torch.load(tmp_path / "cons" / "consolidated.pth")
+    assert set(state.keys()) == plain_keys
+
+    import json
+    saved = json.load(open(tmp_path / "cons" / "config.json"))
+    assert saved["model"]["layerwise_ckpt"] is True
+    known = set(type(cfg).__dataclass_fields__)
+    mcfg = type(cfg)(**{k: v for k, v in saved["model"].items() if k in known})
+    mcfg.init_mode = "none"
+    for wrapped_too in (False, True):              # the file loads into either kind of model
+        mcfg.layerwise_ckpt, mcfg.ckpt_layers = wrapped_too, None
+        ev = Mega(mcfg)
+        reloading.load_state_dict(ev, dict(state), strict=False)
+        got = ev.state_dict()
+        for k, v in state.items():
+            assert torch.equal(got[k], v), k
+    # same outputs as the trained model
+    toks = torch.randint(0, 96, (2, 32), generator=torch.Generator().manual_seed(5))
+    ev.eval(); model.eval()
+    with torch.no_grad():
+        assert torch.allclose(ev(toks)[0], model(toks)[0], atol=1e-5)
+    broken = {k: v for k, v in state.items() if k != "layers.1.mega.wz.weight"}
+    with pytest.raises(RuntimeError, match="no value for 1 parameter"):
+        reloading.load_state_dict(Mega(mcfg), broken, strict=False)
+
+
 def test_decode_session_matches_cache_path():
     """The fixed-shape decode state reproduces the regular cache path token for token, from a prefilled
     cache and from an empty one, across a chunk boundary."""

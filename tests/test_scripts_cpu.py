@@ -68,5 +68,6 @@ def test_train_consolidate_eval_roundtrip(tmp_path, sp_model):
                 "--dtype", "fp32", "--ppl_files_str", str(ppl_file), "--prompt_path", str(prompts),
                 "--gen_seq_len", "8", "--batch_size", "2"])
     assert "PPL on" in out and "Finished all evaluations" in out
+    assert "Missing keys when reloading" not in out and "Unexpected keys when reloading" not in out
     gens = [json.loads(l) for l in open(dump / "generations" / "0.jsonl")]
     assert [g["prompt"] for g in gens] == ["alpha beta gamma", "ocean shark"]
