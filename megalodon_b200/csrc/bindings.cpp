@@ -653,22 +653,52 @@ void allreduce_sumsq(const Tensor& bufs, int64_t rank, int64_t nbytes, double sc
                       stream());
 }
 
+// piece table of per-parameter sharding: int64 [P, 3] on the device (see comm_kernels.cu)
+const long long* table_ptr(const OptTensor& table, int* npieces) {
+  *npieces = 0;
+  if (!table.has_value()) return nullptr;
+  TORCH_CHECK(table->is_cuda() && table->scalar_type() == at::kLong && table->is_contiguous() && table->dim() == 2 &&
+              table->size(1) == 3, "piece table must be a contiguous CUDA int64 [P, 3] tensor");
+  TORCH_CHECK(table->size(0) <= mb::piece_table_limit(), "more parameters in one unit than the kernels' piece table holds");
+  *npieces = (int)table->size(0);
+  return reinterpret_cast<const long long*>(table->data_ptr<int64_t>());
+}
+
+// full (natural order) <- piece r of every parameter from peer_shards[r], for every rank r
+void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, const OptTensor& abort) {
+  check_cuda_contig(full, "full");
+  check_cuda_contig(peer_shards, "peer_shards");
+  c10::cuda::CUDAGuard guard(full.device());
+  TORCH_CHECK(peer_shards.scalar_type() == at::kLong && peer_shards.numel() <= 32);
+  int npieces = 0;
+  const long long* tab = table_ptr(table, &npieces);
+  TORCH_CHECK(reinterpret_cast<uintptr_t>(full.data_ptr()) % 16 == 0);
+  mb::gather_pull(full.data_ptr(), reinterpret_cast<const void* const*>(peer_shards.data_ptr<int64_t>()),
+                  (int)peer_shards.numel(), tab, npieces, full.numel(), (int)full.element_size(), opt_abort(abort),
+                  stream());
+}
+
 void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& out,
-                          const OptTensor& sumsq, bool accumulate, const OptTensor& abort) {
+                          const OptTensor& sumsq, bool accumulate, const OptTensor& abort, const OptTensor& table) {
   check_cuda_contig(bufs, "bufs");
   check_cuda_contig(out, "out");
   c10::cuda::CUDAGuard guard(out.device());
   TORCH_CHECK(bufs.scalar_type() == at::kLong);
+  int npieces = 0;
+  const long long* tab = table_ptr(table, &npieces);
   mb::reduce_scatter_sumsq(reinterpret_cast<const void* const*>(bufs.data_ptr<int64_t>()), (int)rank,
                            (int)bufs.numel(), out.numel(), (float)scale, out.data_ptr(),
                            sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, accumulate, (int)in_dtype,
-                           dtype_code(out), opt_abort(abort), stream());
+                           dtype_code(out), opt_abort(abort), tab, npieces, stream());
 }
 
 // bufs: int64 device tensor of every rank's staging address; p / m / v fp32 shards updated in place
 void reduce_scatter_adamw(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& p, Tensor& m,
                           Tensor& v, const OptTensor& low, const OptTensor& sumsq, double lr, double beta1,
-                          double beta2, double eps, double wd, int64_t step, const OptTensor& abort) {
+                          double beta2, double eps, double wd, int64_t step, const OptTensor& abort,
+                          const OptTensor& table) {
+  int npieces = 0;
+  const long long* tab = table_ptr(table, &npieces);
   check_cuda_contig(bufs, "bufs");
   check_cuda_contig(p, "p");
   check_cuda_contig(m, "m");
@@ -683,7 +713,7 @@ void reduce_scatter_adamw(const Tensor& bufs, int64_t rank, int64_t in_dtype, do
       (float)scale, p.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(),
       low.has_value() ? low->data_ptr() : nullptr, sumsq.has_value() ? sumsq->data_ptr<double>() : nullptr, (float)lr,
       (float)beta1, (float)beta2, (float)eps, (float)wd, (int)step, (int)in_dtype,
-      low.has_value() ? dtype_code(*low) : (int)in_dtype, opt_abort(abort), stream());
+      low.has_value() ? dtype_code(*low) : (int)in_dtype, opt_abort(abort), tab, npieces, stream());
   TORCH_CHECK(ok, "reduce_scatter_adamw: shard must be a multiple of 8 elements, 16-bit gradients, at most 8 ranks");
 }
 
@@ -746,11 +776,14 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("fftconv_dk", checked(&fftconv_dk));
   m.def("reduce_slots", checked(&reduce_slots));
   m.def("reduce_scatter_sumsq", checked(&reduce_scatter_sumsq), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
-        py::arg("scale"), py::arg("out"), py::arg("sumsq"), py::arg("accumulate"), py::arg("abort") = py::none());
+        py::arg("scale"), py::arg("out"), py::arg("sumsq"), py::arg("accumulate"), py::arg("abort") = py::none(),
+        py::arg("table") = py::none());
+  m.def("gather_pull", checked(&gather_pull), py::arg("full"), py::arg("peer_shards"), py::arg("table"),
+        py::arg("abort") = py::none());
   m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
         py::arg("scale"), py::arg("p"), py::arg("m"), py::arg("v"), py::arg("low"), py::arg("sumsq"), py::arg("lr"),
         py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
-        py::arg("abort") = py::none());
+        py::arg("abort") = py::none(), py::arg("table") = py::none());
   m.def("time_sums", checked(&time_sums));
   m.def("affine_apply", checked(&affine_apply));
   m.def("dropout", checked(&dropout));
@@ -767,4 +800,5 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale"), py::arg("sumsq"), py::arg("dtype"), py::arg("abort") = py::none());
   m.attr("COMM_ABORT_WORDS") = (int)mb::kCommAbortWords;
   m.def("pinned_device_ptr", &pinned_device_ptr);
+  m.def("piece_table_limit", []() { return mb::piece_table_limit(); });
 }

@@ -299,18 +299,49 @@ __global__ void allreduce_sumsq_f32_kernel(float4* const* __restrict__ bufs, int
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
 }
 
+// Per-parameter sharding (parallel/fsdp.py): rank r's shard is the concatenation of piece r of every
+// parameter, while gradients and gathered parameters are laid out in natural order.  `table` holds one
+// row (shard_offset, piece, offset) per parameter; all three are multiples of 64 elements, so a
+// 16-byte vector never straddles two pieces.  Returns the natural-order index of shard element `i`
+// of rank `rank`.
+constexpr int kMaxPieces = 96;
+struct PieceMap {
+  long long shard_end[kMaxPieces];     // shard_offset + piece
+  long long delta[kMaxPieces];         // offset + rank * piece - shard_offset
+};
+__device__ __forceinline__ void load_piece_map(PieceMap* pm, const long long* __restrict__ table, int npieces,
+                                               int rank) {
+  for (int i = threadIdx.x; i < npieces; i += blockDim.x) {
+    const long long so = table[3 * i], piece = table[3 * i + 1], off = table[3 * i + 2];
+    pm->shard_end[i] = so + piece;
+    pm->delta[i] = off + (long long)rank * piece - so;
+  }
+  __syncthreads();
+}
+__device__ __forceinline__ long long shard_to_natural(const PieceMap* pm, int npieces, long long i) {
+  int lo = 0, hi = npieces - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (i < pm->shard_end[mid]) hi = mid; else lo = mid + 1;
+  }
+  return i + pm->delta[lo];
+}
+
 // Reduce-scatter by pull: this rank sums ITS slice of every peer's staged buffer in fp32, scales it
 // (gradient averaging), stores it to a local shard in the output dtype and accumulates the squared
 // norm of what it stored.  One pass replaces reduce-scatter + cast/scale + the gradient-norm pass.
 template <typename T, typename O>
 __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, int rank, int world,
                                             long long shard_n, float scale, O* __restrict__ out,
-                                            double* __restrict__ sumsq, bool accumulate, const int* abort) {
+                                            double* __restrict__ sumsq, bool accumulate, const int* abort,
+                                            const long long* __restrict__ table, int npieces) {
   __shared__ float scratch[32];
+  __shared__ PieceMap pm;
   if (block_sees_abort(abort)) return;
+  if (table != nullptr) load_piece_map(&pm, table, npieces, rank);
   constexpr int kMaxWorld = 8;
   constexpr int kPer = 16 / sizeof(T);           // elements per 16-byte load
-  const long long lo = (long long)rank * shard_n;
+  const long long lo = table != nullptr ? 0 : (long long)rank * shard_n;
   const T* src[kMaxWorld];
 #pragma unroll
   for (int p = 0; p < kMaxWorld; ++p) src[p] = p < world ? bufs[(rank + p) % world] + lo : nullptr;
@@ -322,9 +353,10 @@ __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, i
   // 512-byte requests per warp on the link
   for (long long v = tid; v < nvec; v += stride) {
     uint4 raw[kMaxWorld];
+    const long long at = table != nullptr ? shard_to_natural(&pm, npieces, v * kPer) : v * kPer;
 #pragma unroll
     for (int p = 0; p < kMaxWorld; ++p)
-      if (p < world) raw[p] = __ldcv(reinterpret_cast<const uint4*>(src[p] + v * kPer));
+      if (p < world) raw[p] = __ldcv(reinterpret_cast<const uint4*>(src[p] + at));
     float acc[kPer];
 #pragma unroll
     for (int j = 0; j < kPer; ++j) acc[j] = 0.f;
@@ -357,7 +389,8 @@ __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, i
   }
   for (long long i = nvec * kPer + tid; i < shard_n; i += stride) {     // tail (and world > 8)
     float acc = 0.f;
-    for (int p = 0; p < world; ++p) acc += to_f(bufs[(rank + p) % world][lo + i]);
+    const long long at = table != nullptr ? shard_to_natural(&pm, npieces, i) : i;
+    for (int p = 0; p < world; ++p) acc += to_f(bufs[(rank + p) % world][lo + at]);
     acc *= scale;
     if (accumulate) acc += to_f(out[i]);
     ss = fmaf(acc, acc, ss);
@@ -377,12 +410,15 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
                                             float scale, float* __restrict__ p, float* __restrict__ m,
                                             float* __restrict__ v, Lo* __restrict__ low, double* __restrict__ sumsq,
                                             float lr, float beta1, float beta2, float eps, float wd, float bc1,
-                                            float bc2_sqrt, const int* abort) {
+                                            float bc2_sqrt, const int* abort, const long long* __restrict__ table,
+                                            int npieces) {
   __shared__ float scratch[32];
+  __shared__ PieceMap pm;
   if (block_sees_abort(abort)) return;
+  if (table != nullptr) load_piece_map(&pm, table, npieces, rank);
   constexpr int kMaxWorld = 8;
   static_assert(sizeof(T) == 2, "gradients are staged in a 16-bit type");
-  const long long lo = (long long)rank * shard_n;
+  const long long lo = table != nullptr ? 0 : (long long)rank * shard_n;
   const T* src[kMaxWorld];
 #pragma unroll
   for (int q = 0; q < kMaxWorld; ++q) src[q] = q < world ? bufs[(rank + q) % world] + lo : nullptr;
@@ -394,9 +430,10 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
   float ss = 0.f;
   for (long long i = tid; i < nvec; i += stride) {
     uint4 raw[kMaxWorld];
+    const long long at = table != nullptr ? shard_to_natural(&pm, npieces, i * 8) : i * 8;
 #pragma unroll
     for (int q = 0; q < kMaxWorld; ++q)
-      if (q < world) raw[q] = __ldcv(reinterpret_cast<const uint4*>(src[q] + i * 8));
+      if (q < world) raw[q] = __ldcv(reinterpret_cast<const uint4*>(src[q] + at));
     float g[8], pv[8], mv[8], vv[8];
     load8(p + i * 8, pv);
     load8(m + i * 8, mv);
@@ -426,6 +463,52 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
   }
   ss = block_sum(ss, scratch);
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
+}
+
+// Parameter all-gather by pull into the natural layout.  Every 16-byte word of `full` comes from the
+// shard of the rank that owns it: word at natural element index n of parameter p (offset <= n <
+// offset + world * piece) lives on rank (n - offset) / piece at shard index shard_offset + (n - offset) % piece.
+// Four loads per thread are in flight before the first store.
+struct NaturalMap {
+  long long nat_end[kMaxPieces];       // offset + world * piece
+  long long off[kMaxPieces], piece[kMaxPieces], soff[kMaxPieces];
+};
+__global__ void gather_pull_kernel(uint4* __restrict__ full, const uint4* const* __restrict__ peer_shards, int world,
+                                   const long long* __restrict__ table, int npieces, long long nwords, int per,
+                                   const int* abort) {
+  __shared__ NaturalMap nm;
+  if (block_sees_abort(abort)) return;
+  for (int i = threadIdx.x; i < npieces; i += blockDim.x) {
+    nm.soff[i] = table[3 * i]; nm.piece[i] = table[3 * i + 1]; nm.off[i] = table[3 * i + 2];
+    nm.nat_end[i] = nm.off[i] + (long long)world * nm.piece[i];
+  }
+  __syncthreads();
+  constexpr int kUnroll = 4;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long w0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; w0 < nwords; w0 += stride * kUnroll) {
+    uint4 v[kUnroll];
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long w = w0 + u * stride;
+      if (w < nwords) {
+        const long long n = w * per;                      // natural element index of this word
+        int lo = 0, hi = npieces - 1;
+        while (lo < hi) {
+          const int mid = (lo + hi) >> 1;
+          if (n < nm.nat_end[mid]) hi = mid; else lo = mid + 1;
+        }
+        const long long rel = n - nm.off[lo];
+        const long long r = rel / nm.piece[lo];
+        const long long j = rel - r * nm.piece[lo];
+        v[u] = __ldcv(peer_shards[r] + (nm.soff[lo] + j) / per);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      const long long w = w0 + u * stride;
+      if (w < nwords) full[w] = v[u];
+    }
+  }
 }
 
 template <typename T>
@@ -459,19 +542,20 @@ void reduce_slots(const void* slots, void* out, long long n, int world, int dtyp
 
 void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
                           double* sumsq, bool accumulate, int in_dtype, int out_dtype, const int* abort,
-                          cudaStream_t st) {
+                          const long long* table, int npieces, cudaStream_t st) {
   if (shard_n == 0) return;
+  if (npieces > kMaxPieces) table = nullptr, npieces = -1;          // caller checks piece_table_limit()
   const int grid = (int)std::min<long long>(div_up(shard_n / 8 + 1, 256), 148LL * 4);
   MB_DISPATCH_DTYPE(in_dtype, {
     using T = scalar_t;
     if (out_dtype == kF32 && in_dtype != kF32) {
       prefer_max_shared(reduce_scatter_sumsq_kernel<T, float>);
       reduce_scatter_sumsq_kernel<T, float><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
-                                                                 (float*)out, sumsq, accumulate, abort);
+                                                                 (float*)out, sumsq, accumulate, abort, table, npieces);
     } else {
       prefer_max_shared(reduce_scatter_sumsq_kernel<T, T>);
       reduce_scatter_sumsq_kernel<T, T><<<grid, 256, 0, st>>>((const T* const*)bufs, rank, world, shard_n, scale,
-                                                             (T*)out, sumsq, accumulate, abort);
+                                                             (T*)out, sumsq, accumulate, abort, table, npieces);
     }
   });
 }
@@ -479,8 +563,10 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
 // shard_n must be a multiple of 8 and world <= 8; `low` may be null.  Returns false otherwise.
 bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
                           float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
-                          float wd, int step, int in_dtype, int low_dtype, const int* abort, cudaStream_t st) {
+                          float wd, int step, int in_dtype, int low_dtype, const int* abort, const long long* table,
+                          int npieces, cudaStream_t st) {
   if (shard_n == 0) return true;
+  if (npieces > kMaxPieces) return false;
   if (shard_n % 8 != 0 || world > 8 || in_dtype == kF32 || (low != nullptr && low_dtype != in_dtype)) return false;
   const float bc1 = 1.f - powf(beta1, (float)step);
   const float bc2s = sqrtf(1.f - powf(beta2, (float)step));
@@ -489,14 +575,27 @@ bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long lon
     prefer_max_shared(reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16>);
     reduce_scatter_adamw_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, st>>>(
         (const __nv_bfloat16* const*)bufs, rank, world, shard_n, scale, p, m, v, (__nv_bfloat16*)low, sumsq, lr, beta1,
-        beta2, eps, wd, bc1, bc2s, abort);
+        beta2, eps, wd, bc1, bc2s, abort, table, npieces);
   } else {
     prefer_max_shared(reduce_scatter_adamw_kernel<__half, __half>);
     reduce_scatter_adamw_kernel<__half, __half><<<grid, 256, 0, st>>>(
         (const __half* const*)bufs, rank, world, shard_n, scale, p, m, v, (__half*)low, sumsq, lr, beta1, beta2, eps, wd,
-        bc1, bc2s, abort);
+        bc1, bc2s, abort, table, npieces);
   }
   return true;
+}
+
+int piece_table_limit() { return kMaxPieces; }
+
+void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
+                 long long numel_padded, int esize, const int* abort, cudaStream_t st) {
+  if (numel_padded == 0 || npieces > kMaxPieces) return;
+  const int per = 16 / esize;
+  const long long nwords = numel_padded / per;
+  const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(nwords, 256 * 4), 148LL * 4));
+  prefer_max_shared(gather_pull_kernel);
+  gather_pull_kernel<<<grid, 256, 0, st>>>((uint4*)full, (const uint4* const*)peer_shards, world, table, npieces, nwords,
+                                           per, abort);
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,

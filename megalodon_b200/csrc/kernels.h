@@ -100,7 +100,8 @@ bool gemv_small_m(const void* x, const void* w, const void* bias, int bias_dtype
 // reduce-scatter fused with the sharded AdamW update (comm_kernels.cu); false if the shapes do not qualify
 bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long long shard_n, float scale, float* p,
                           float* m, float* v, void* low, double* sumsq, float lr, float beta1, float beta2, float eps,
-                          float wd, int step, int in_dtype, int low_dtype, const int* abort, cudaStream_t st);
+                          float wd, int step, int in_dtype, int low_dtype, const int* abort, const long long* table,
+                          int npieces, cudaStream_t st);
 // Whether GEMMs with more than 128 rows run on CTA pairs (tcgen05 cta_group::2, 256 x 256 tiles); on by default.
 void gemm_set_cta_pairs(bool on);
 int gemm_pair_max_active_clusters();
@@ -145,7 +146,15 @@ void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int e
 // out[i] (+)= scale * sum_p bufs[p][rank * shard_n + i]; out dtype = in dtype or fp32; sumsq += |out|^2
 void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long long shard_n, float scale, void* out,
                           double* sumsq, bool accumulate, int in_dtype, int out_dtype, const int* abort,
-                          cudaStream_t st);
+                          const long long* table, int npieces, cudaStream_t st);
+// `table` (optional, device int64 [npieces, 3] rows (shard_offset, piece, offset)): the staged buffers are in
+// natural parameter order and rank r owns piece r of every parameter (per-parameter sharding); without it
+// rank r owns the contiguous range [r * shard_n, (r + 1) * shard_n).  At most piece_table_limit() rows.
+int piece_table_limit();
+// Parameter all-gather by pull: full (natural order) <- piece r of every parameter from rank r's shard
+// (peer_shards[r], possibly peer memory), for all r.  Element size `esize` bytes (2 or 4).
+void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
+                 long long numel_padded, int esize, const int* abort, cudaStream_t st);
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
                      int dtype, const int* abort, cudaStream_t st);
 

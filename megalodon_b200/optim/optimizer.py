@@ -73,7 +73,7 @@ class FusedAdamW(Optimizer):
         return n
 
     @torch.no_grad()
-    def _update_in_backward(self, p, group, reducer, flat_grad, scale, sumsq) -> None:
+    def _update_in_backward(self, p, group, reducer, flat_grad, scale, sumsq, table=None) -> None:
         unit = p._fsdp_unit
         st = self._state_of(p)
         if p._lowp_shard is None:
@@ -81,7 +81,7 @@ class FusedAdamW(Optimizer):
         b1, b2 = group["betas"]
         reducer.reduce_scatter_adamw(flat_grad, p.data, st["exp_avg"], st["exp_avg_sq"], p._lowp_shard, scale, sumsq,
                                      lr=group["lr"], beta1=b1, beta2=b2, eps=group["eps"],
-                                     weight_decay=group["weight_decay"], step=st["step"] + 1)
+                                     weight_decay=group["weight_decay"], step=st["step"] + 1, table=table)
         p._updated_in_backward = True
 
     @torch.no_grad()

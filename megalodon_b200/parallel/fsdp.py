@@ -8,10 +8,20 @@ updates, `clip_grad_norm_`, `grad_all_reduce`, and full / local state dicts.
 
 Design of one unit
 ------------------
-* All parameters of the unit live in ONE flat buffer.  Each parameter starts
-  at a multiple of 64 elements (128 B in bf16) so TMA tiles and vector loads
-  of any parameter are aligned; the buffer is padded to a multiple of
-  `world * 64` and cut into `world` equal shards.
+* All parameters of the unit live in ONE flat buffer in their natural order.
+  Sharding is PER PARAMETER: every parameter is padded to `world` pieces of
+  the same length (a multiple of 64 elements = 128 B in bf16, so TMA tiles and
+  vector loads stay aligned) and rank r holds piece r of every parameter; a
+  rank's shard is the concatenation of its pieces.  For a weight matrix
+  [N, K] with N divisible by `world`, piece r is the row block
+  [r N / world, (r + 1) N / world): every rank owns an equal slice of every
+  matrix, which is what lets a kernel pull the rows it needs from their owner
+  with balanced traffic (`symm.SymmetricParamGather`, the gathering GEMM).
+  Mapping (element j of parameter p, piece length `piece`, natural offset
+  `offset`, `shard_offset = offset / world`):
+      full[offset + j]  <->  shard of rank j // piece, index shard_offset + j % piece
+  A cut of the flat buffer into `world` contiguous ranges (fairscale's layout)
+  would put a whole matrix on one or two ranks.
 * The fp32 shard is an `nn.Parameter` (`flat_param`): the master weights.
   A compute-dtype copy of the shard (`flat_param._lowp_shard`) feeds the
   all-gather; the fused AdamW kernel refreshes it in the same pass that
@@ -71,10 +81,13 @@ class TrainingState(Enum):
 
 
 class _ParamInfo:
-    __slots__ = ("name", "shape", "numel", "offset", "owners")
+    """`offset`: start in the natural-order buffer; `piece`: elements of this parameter held by each
+    rank (world * piece >= numel); `shard_offset`: start of the piece inside every rank's shard."""
+    __slots__ = ("name", "shape", "numel", "offset", "owners", "piece", "shard_offset")
 
-    def __init__(self, name, shape, numel, offset, owners):
+    def __init__(self, name, shape, numel, offset, owners, piece=0, shard_offset=0):
         self.name, self.shape, self.numel, self.offset, self.owners = name, shape, numel, offset, owners
+        self.piece, self.shard_offset = piece, shard_offset
 
 
 def _group_size(group) -> int:
@@ -216,25 +229,23 @@ class FullyShardedDataParallel(nn.Module):
                 if id(p) in by_id:
                     by_id[id(p)].owners.append((mod, pname, full_name))
                     continue
-                info = _ParamInfo(full_name, tuple(p.shape), p.numel(), offset, [(mod, pname, full_name)])
+                piece = -(-p.numel() // (self.world_size * ALIGN)) * ALIGN
+                info = _ParamInfo(full_name, tuple(p.shape), p.numel(), offset, [(mod, pname, full_name)],
+                                  piece, offset // self.world_size)
                 by_id[id(p)] = info
                 infos.append(info)
                 datas.append(p.detach())
-                offset += -(-p.numel() // ALIGN) * ALIGN
+                offset += piece * self.world_size
         self._infos = infos
         world = self.world_size
-        quantum = world * ALIGN
-        self._numel_padded = max(quantum, -(-offset // quantum) * quantum)
+        self._numel_padded = max(world * ALIGN, offset)
         self._shard_numel = self._numel_padded // world
+        self._piece_tables: Dict[Any, torch.Tensor] = {}
         if device is None:
             device = datas[0].device if datas else torch.device("cpu")
-        lo = self.rank * self._shard_numel
-        hi = lo + self._shard_numel
         shard = torch.zeros(self._shard_numel, dtype=torch.float32, device=device)
         for info, d in zip(infos, datas):
-            a, b = max(info.offset, lo), min(info.offset + info.numel, hi)
-            if a < b:
-                shard[a - lo:b - lo].copy_(d.reshape(-1)[a - info.offset:b - info.offset])
+            self._write_piece(shard, info, d.reshape(-1))
         self.flat_param = nn.Parameter(shard)
         self.flat_param._fsdp_unit = self
         self.flat_param._grad_shard = None
@@ -261,6 +272,56 @@ class FullyShardedDataParallel(nn.Module):
             if isinstance(cur, FullyShardedDataParallel):
                 return True
         return False
+
+    # ------------------------------------------------------------------ layout (see the module docstring)
+    def _write_piece(self, shard: torch.Tensor, info: _ParamInfo, flat_param: torch.Tensor) -> None:
+        """Copy this rank's piece of one (unpadded, flattened) parameter into `shard`."""
+        a = self.rank * info.piece
+        b = min(a + info.piece, info.numel)
+        if a < b:
+            shard[info.shard_offset:info.shard_offset + (b - a)].copy_(flat_param[a:b])
+
+    def piece_table(self, device) -> torch.Tensor:
+        """int64 [P, 3] rows (shard_offset, piece, offset) on `device`: what the native kernels that
+        move data between the shard and the natural layouts need."""
+        key = str(device)
+        t = self._piece_tables.get(key)
+        if t is None:
+            rows = [[i.shard_offset, i.piece, i.offset] for i in self._infos] or [[0, self._shard_numel, 0]]
+            t = self._piece_tables[key] = torch.tensor(rows, dtype=torch.int64, device=device)
+        return t
+
+    def _unshard(self, rank_major: torch.Tensor, full: torch.Tensor) -> None:
+        """[shard of rank 0 | shard of rank 1 | ...] -> natural order."""
+        W, S = self.world_size, self._shard_numel
+        src = rank_major.view(W, S)
+        for i in self._infos:
+            full[i.offset:i.offset + W * i.piece].view(W, i.piece).copy_(src[:, i.shard_offset:i.shard_offset + i.piece])
+
+    def _to_rank_major(self, full: torch.Tensor, rank_major: torch.Tensor) -> None:
+        """natural order -> [what rank 0 owns | what rank 1 owns | ...] (input of a reduce-scatter)."""
+        W, S = self.world_size, self._shard_numel
+        dst = rank_major.view(W, S)
+        for i in self._infos:
+            dst[:, i.shard_offset:i.shard_offset + i.piece].copy_(full[i.offset:i.offset + W * i.piece].view(W, i.piece))
+
+    def _scratch(self, numel: int, dtype: torch.dtype, device) -> torch.Tensor:
+        """Root-owned scratch for the rank-major side of a collective, one per (stream, dtype): uses on
+        one stream are ordered, so one buffer per stream is enough however many units are in flight."""
+        root = getattr(self, "_root", self)
+        pool = root.__dict__.setdefault("_scratch_pool", {})
+        sid = torch.cuda.current_stream(device).cuda_stream if torch.device(device).type == "cuda" else 0
+        key = (sid, dtype)
+        buf = pool.get(key)
+        if buf is None or buf.numel() < numel:
+            buf = pool[key] = torch.empty(numel, dtype=dtype, device=device)
+        return buf[:numel]
+
+    def _all_gather_natural(self, full: torch.Tensor, shard: torch.Tensor) -> None:
+        """full (natural order) <- every rank's shard."""
+        tmp = self._scratch(self._numel_padded, shard.dtype, shard.device)
+        all_gather_flat(tmp, shard, self.process_group)
+        self._unshard(tmp, full)
 
     def __getattr__(self, name: str) -> Any:
         try:
@@ -340,7 +401,12 @@ class FullyShardedDataParallel(nn.Module):
             self._full.untyped_storage().resize_(self._numel_padded * self._full.element_size())
         # write through `.data`: the re-gather before backward must not bump the
         # autograd version counter shared with the views handed to the module
-        all_gather_flat(self._full.data, shard, self.process_group)
+        puller = getattr(getattr(self, "_root", self), "_symm_gather", None)
+        if puller is not None and shard.is_cuda:
+            puller.shards_written()
+            puller.pull(self, self._full.data)
+        else:
+            self._all_gather_natural(self._full.data, shard)
         self._full_version = _ver(self.flat_param)
 
     def _prefetch_gathers(self) -> None:
@@ -367,9 +433,15 @@ class FullyShardedDataParallel(nn.Module):
             self._gather_stream = torch.cuda.Stream(self.compute_device, priority=-1)
         gs = self._gather_stream
         gs.wait_stream(torch.cuda.current_stream())
+        puller = getattr(self, "_symm_gather", None)
         with torch.cuda.stream(gs):
+            if puller is not None:
+                puller.shards_written()        # flag barrier: every rank's shards of this step are in place
             for u, shard in zip(stale, shards):
-                all_gather_flat(u._full.data, shard, u.process_group)
+                if puller is not None:
+                    puller.pull(u, u._full.data)
+                else:
+                    u._all_gather_natural(u._full.data, shard)
                 u._full_version = _ver(u.flat_param)
                 ev = torch.cuda.Event()
                 ev.record(gs)
@@ -506,7 +578,8 @@ class FullyShardedDataParallel(nn.Module):
             if update is not None and not accumulate:
                 # no clipping in this run: the optimiser's update of the shard rides in the same kernel
                 with (torch.cuda.stream(stream) if stream is not None else _nullcontext()):
-                    update(fused_rs, flat_grad, 1.0 / self.gradient_divide_factor, root._fused_sumsq)
+                    update(fused_rs, flat_grad, 1.0 / self.gradient_divide_factor, root._fused_sumsq,
+                           self.piece_table(flat_grad.device))
                 if stream is not None:
                     flat_grad.record_stream(stream)
                     root._pending.append(True)
@@ -515,7 +588,7 @@ class FullyShardedDataParallel(nn.Module):
                 return None
             with (torch.cuda.stream(stream) if stream is not None else _nullcontext()):
                 fused_rs.reduce_scatter(flat_grad, shard, 1.0 / self.gradient_divide_factor,
-                                        root._fused_sumsq, accumulate)
+                                        root._fused_sumsq, accumulate, table=self.piece_table(flat_grad.device))
             if stream is not None:
                 flat_grad.record_stream(stream)
                 shard.record_stream(stream)
@@ -528,15 +601,22 @@ class FullyShardedDataParallel(nn.Module):
             if self.gradient_divide_factor != 1.0:
                 g = g / self.gradient_divide_factor
             shard = torch.empty(self._shard_numel, dtype=red_dtype, device=g.device)
+
+            def scatter():
+                # the collective wants [what rank 0 owns | what rank 1 owns | ...]
+                ordered = self._scratch(self._numel_padded, g.dtype, g.device)
+                self._to_rank_major(g, ordered)
+                reduce_scatter_flat(shard, ordered, self.process_group_reduce_scatter)
+
             if root._comm_stream is not None:
                 root._comm_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(root._comm_stream):
-                    reduce_scatter_flat(shard, g, self.process_group_reduce_scatter)
+                    scatter()
                 g.record_stream(root._comm_stream)
                 shard.record_stream(root._comm_stream)
                 root._pending.append(True)
             else:
-                reduce_scatter_flat(shard, g, self.process_group_reduce_scatter)
+                scatter()
         else:
             shard = g
             if self.gradient_divide_factor != 1.0:
@@ -704,7 +784,9 @@ class FullyShardedDataParallel(nn.Module):
         if self.world_size == 1:
             return shard
         full = torch.empty(self._numel_padded, dtype=shard.dtype, device=shard.device)
-        all_gather_flat(full, shard.contiguous(), self.process_group)
+        tmp = torch.empty_like(full)
+        all_gather_flat(tmp, shard.contiguous(), self.process_group)
+        self._unshard(tmp, full)
         return full
 
     @torch.no_grad()
@@ -738,8 +820,6 @@ class FullyShardedDataParallel(nn.Module):
         self._lazy_init()
         missing, used = [], set()
         for prefix, unit in self._unit_prefixes():
-            lo = unit.rank * unit._shard_numel
-            hi = lo + unit._shard_numel
             for info in unit._infos:
                 src = None
                 for _, _, name in info.owners:
@@ -751,10 +831,7 @@ class FullyShardedDataParallel(nn.Module):
                     missing.append(f"{prefix}.{info.name}" if prefix else info.name)
                     continue
                 assert tuple(src.shape) == info.shape, (info.name, tuple(src.shape), info.shape)
-                a, b = max(info.offset, lo), min(info.offset + info.numel, hi)
-                if a < b:
-                    unit.flat_param.data[a - lo:b - lo].copy_(
-                        src.reshape(-1)[a - info.offset:b - info.offset].to(unit.flat_param.device))
+                unit._write_piece(unit.flat_param.data, info, src.reshape(-1).to(unit.flat_param.device))
             unit.flat_param._master_version = getattr(unit.flat_param, "_master_version", 0) + 1
         bufs = dict(self._wrapped.named_buffers())
         for name, buf in bufs.items():
@@ -777,7 +854,8 @@ class FullyShardedDataParallel(nn.Module):
             out["shards"][key] = unit.flat_param.detach().cpu().clone()
             out["meta"][key] = {
                 "world_size": unit.world_size, "rank": unit.rank, "numel_padded": unit._numel_padded,
-                "params": [(i.name, list(i.shape), i.offset) for i in unit._infos],
+                "layout": "per_parameter",      # rank r holds piece r of every parameter (see the module docstring)
+                "params": [(i.name, list(i.shape), i.offset, i.piece, i.shard_offset) for i in unit._infos],
             }
         for name, buf in self._wrapped.named_buffers():
             out["buffers"][_clean_name(name)] = buf.detach().cpu().clone()
@@ -789,7 +867,8 @@ class FullyShardedDataParallel(nn.Module):
         for prefix, unit in self._unit_prefixes():
             key = prefix or "_root"
             meta = payload["meta"][key]
-            assert meta["world_size"] == unit.world_size and meta["rank"] == unit.rank, \
+            assert (meta["world_size"] == unit.world_size and meta["rank"] == unit.rank
+                    and meta.get("layout", "flat_cut" if unit.world_size > 1 else "per_parameter") == "per_parameter"), \
                 "sharded checkpoint was written with a different sharding layout"
             unit.flat_param.data.copy_(payload["shards"][key].to(unit.flat_param.device))
             unit.flat_param._master_version = getattr(unit.flat_param, "_master_version", 0) + 1

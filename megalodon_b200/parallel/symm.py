@@ -457,8 +457,11 @@ class SymmetricReduceScatter:
 
     @torch.no_grad()
     def reduce_scatter(self, flat_grad: torch.Tensor, out_shard: torch.Tensor, scale: float,
-                       sumsq: Optional[torch.Tensor], accumulate: bool = False) -> None:
-        """out_shard (+)= scale * (this rank's slice of the sum over ranks of flat_grad).
+                       sumsq: Optional[torch.Tensor], accumulate: bool = False,
+                       table: Optional[torch.Tensor] = None) -> None:
+        """out_shard (+)= scale * (this rank's slice of the sum over ranks of flat_grad).  With `table`
+        (the unit's `piece_table`) `flat_grad` is in natural parameter order and the slice of rank r is
+        piece r of every parameter; without it the slice is the contiguous range r.
 
         Staging buffer t is rewritten two calls later; by then every peer has passed the barrier of
         the call in between, which its stream reaches only after its own read of buffer t finished."""
@@ -475,13 +478,13 @@ class SymmetricReduceScatter:
         self.epoch += 1
         ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
         ext.reduce_scatter_sumsq(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, out_shard, sumsq, accumulate,
-                                 self._abort.dev)
+                                 self._abort.dev, table)
 
     @torch.no_grad()
     def reduce_scatter_adamw(self, flat_grad: torch.Tensor, master: torch.Tensor, exp_avg: torch.Tensor,
                              exp_avg_sq: torch.Tensor, low: Optional[torch.Tensor], scale: float,
                              sumsq: Optional[torch.Tensor], *, lr: float, beta1: float, beta2: float, eps: float,
-                             weight_decay: float, step: int) -> None:
+                             weight_decay: float, step: int, table: Optional[torch.Tensor] = None) -> None:
         """Reduce-scatter fused with the AdamW update of this rank's shard (see
         `reduce_scatter_adamw_kernel`): the reduced gradient is consumed in registers, `master`,
         `exp_avg`, `exp_avg_sq` (fp32 shards) are updated in place and `low` receives the
@@ -499,7 +502,7 @@ class SymmetricReduceScatter:
         self.epoch += 1
         ext.peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
         ext.reduce_scatter_adamw(self._bufs[t], self.rank, _DT[flat_grad.dtype], scale, master, exp_avg, exp_avg_sq,
-                                 low, sumsq, lr, beta1, beta2, eps, weight_decay, step, self._abort.dev)
+                                 low, sumsq, lr, beta1, beta2, eps, weight_decay, step, self._abort.dev, table)
 
     def check(self) -> None:
         self._abort.check()
@@ -508,6 +511,86 @@ class SymmetricReduceScatter:
         """Collective: clear the signal pad, the epoch and the abort record after a failure."""
         _reset_pads(self, self.region, self.pad_off)
         self._toggle = 0
+
+
+class SymmetricParamGather:
+    """Parameter all-gather of FSDP units by pulling from peer memory (replaces the NCCL all-gather
+    that fairscale issues before every block, reference model/mega.py:251-262).
+
+    The compute-dtype shard of every unit lives in one peer-mapped region.  `pull(unit, full)` runs
+    one kernel that reads piece r of every parameter from rank r's shard and writes it to its place
+    in the natural-order buffer `full` - no rank-major staging copy, no reordering pass.  Before the
+    first pull after an optimiser step, `shards_written()` runs a flag barrier: every rank has
+    finished writing its shards (the fused AdamW kernel writes them).  Overwriting a shard that a
+    slower rank is still reading cannot happen: a rank updates its shards only after the gradient
+    reductions of the step, which need every rank's backward pass and therefore every rank's pulls."""
+
+    def __init__(self, model, timeout_s: float = 30.0):
+        from ..ops._ext import require
+        self.model = model
+        units = model._units()
+        self.group = model.process_group
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        device = next(model.parameters()).device
+        esize = torch.empty(0, dtype=model.compute_dtype).element_size()
+        offs, total = [], 0
+        for u in units:
+            assert u.process_group is self.group, "all units must share the sharding group"
+            assert len(u._infos) <= require().piece_table_limit(), "too many parameters in one unit"
+            offs.append(total)
+            total += _round_up(u._shard_numel * esize, 256)
+        self.pad_off = total
+        self.region = SymmetricRegion(total + _round_up(4 * self.world, 256), self.group, device)
+        self._pads = self.region.ptr_table_at(self.pad_off).contiguous()
+        self._abort = AbortRecord.get(device)
+        self.timeout_ns = int(timeout_s * 1e9)
+        self.epoch = 0
+        self._token = None
+        self._peer_ptrs: Dict[int, torch.Tensor] = {}
+        for u, off in zip(units, offs):
+            shard = self.region.view(off, u._shard_numel * esize, model.compute_dtype)
+            p = u.flat_param
+            shard.copy_(p.data)
+            p._lowp_shard = shard
+            p._lowp_version = (p._version, getattr(p, "_master_version", 0))
+            self._peer_ptrs[id(u)] = self.region.ptr_table_at(off).contiguous()
+        torch.cuda.synchronize(device)
+        dist.barrier(group=self.group)
+
+    def shards_written(self) -> None:
+        """Flag barrier on the current stream, once per version of the master weights."""
+        from ..ops._ext import require
+        root = self.model
+        token = tuple((u.flat_param._version, getattr(u.flat_param, "_master_version", 0)) for u in root._units())
+        if token == self._token:
+            return
+        self._token = token
+        for u in root._units():
+            u._lowp_shard()                  # a no-op unless the master weights changed behind the optimiser
+        self.epoch += 1
+        require().peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
+
+    def pull(self, unit, full: torch.Tensor) -> None:
+        from ..ops._ext import require
+        require().gather_pull(full, self._peer_ptrs[id(unit)], unit.piece_table(full.device), self._abort.dev)
+
+    def check(self) -> None:
+        self._abort.check()
+
+    def reset(self) -> None:
+        _reset_pads(self, self.region, self.pad_off)
+        self._token = None
+
+
+def enable_peer_gather(model, timeout_s: float = 30.0) -> Optional[SymmetricParamGather]:
+    """Replace the NCCL parameter all-gather of every FSDP unit of `model` by pulls from peer memory."""
+    if getattr(model, "world_size", 1) <= 1 or not getattr(model, "mixed_precision", False):
+        return None
+    model._lazy_init()
+    sg = SymmetricParamGather(model, timeout_s=timeout_s)
+    model._symm_gather = sg
+    return sg
 
 
 def _reset_pads(obj, region: SymmetricRegion, pad_off: int) -> None:
@@ -556,6 +639,8 @@ def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_
     if (getattr(model, "world_size", 1) > 1 and getattr(model, "mixed_precision", False)
             and os.environ.get("MEGALODON_B200_PEER_RS", "1") == "1"):
         enable_peer_reduce_scatter(model, timeout_s=timeout_s)
+    if os.environ.get("MEGALODON_B200_PEER_AG", "1") == "1":
+        enable_peer_gather(model, timeout_s=timeout_s)
     reducer = None
     if not getattr(model, "chunk_group_is_sharded", False):
         bucket = allreduce_bucket_mb << 20

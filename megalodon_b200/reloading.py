@@ -301,13 +301,14 @@ def consolidate(sharded_dir: str, out_dir: str, dtype: str = "bf16") -> None:
         for unit, meta in first["meta"].items():
             shard_world = meta["world_size"]
             by_rank = {payloads[r]["meta"][unit]["rank"]: payloads[r]["shards"][unit] for r in members}
-            full = torch.cat([by_rank[i] for i in range(shard_world)])
             prefix = "" if unit == "_root" else unit + "."
-            for name, shape, offset in meta["params"]:
+            # rank r's shard holds piece r of every parameter at the same shard offset
+            for name, shape, _offset, piece, shard_offset in meta["params"]:
                 n = 1
                 for s in shape:
                     n *= s
-                state[prefix + name] = full[offset:offset + n].view(shape).to(tdtype).clone()
+                whole = torch.cat([by_rank[i][shard_offset:shard_offset + piece] for i in range(shard_world)])
+                state[prefix + name] = whole[:n].view(shape).to(tdtype).clone()
         for name, buf in first["buffers"].items():
             state[name] = buf.to(tdtype) if buf.is_floating_point() else buf
         # tied embedding: expose the shared tensor under both names

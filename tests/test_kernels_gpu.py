@@ -595,3 +595,55 @@ def test_reduce_scatter_sumsq_kernel_local_ranks(world, out_dtype):
         prev = out.clone()
         ext.reduce_scatter_sumsq(bufs, rank, _DT[torch.bfloat16], scale, out, None, True)     # out += ...
         _close(out, prev.float() + ref, 4e-2 if out_dtype == torch.bfloat16 else 1e-5, 2e-2, "accumulate")
+
+
+def _pieces(world, numels):
+    """Piece table of per-parameter sharding for parameters of the given sizes (fsdp.py layout)."""
+    rows, off = [], 0
+    for n in numels:
+        piece = -(-n // (world * 64)) * 64
+        rows.append([off // world, piece, off])
+        off += piece * world
+    return rows, off
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_per_parameter_sharding_kernels_local_ranks(world):
+    """Gather-by-pull into the natural layout and the reduce-scatter with a piece table, every 'rank' a
+    local buffer, against index arithmetic in PyTorch."""
+    from megalodon_b200.ops._ext import require
+    from megalodon_b200.ops.cuda_ops import _DT
+    ext = require()
+    torch.manual_seed(15)
+    dev = _dev()
+    rows, total = _pieces(world, [4096 * 24, 130, 64 * world, 7000, 8 * 1024 * 3])
+    table = torch.tensor(rows, dtype=torch.int64, device=dev)
+    S = total // world
+    # all-gather: shard r holds piece r of every parameter
+    full_ref = torch.randn(total, device=dev).bfloat16()
+    shards = [torch.empty(S, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    for so, piece, off in rows:
+        for r in range(world):
+            shards[r][so:so + piece] = full_ref[off + r * piece:off + (r + 1) * piece]
+    ptrs = torch.tensor([t.data_ptr() for t in shards], dtype=torch.int64, device=dev)
+    full = torch.zeros(total, device=dev, dtype=torch.bfloat16)
+    ext.gather_pull(full, ptrs, table)
+    assert torch.equal(full, full_ref)
+    full32 = torch.zeros(total, device=dev, dtype=torch.float32)
+    shards32 = [s.float() for s in shards]
+    ptrs32 = torch.tensor([t.data_ptr() for t in shards32], dtype=torch.int64, device=dev)
+    ext.gather_pull(full32, ptrs32, table)
+    assert torch.equal(full32, full_ref.float())
+    # reduce-scatter: staged gradients in natural order, rank r receives piece r of every parameter
+    stage = [torch.randn(total, device=dev).bfloat16() for _ in range(world)]
+    bufs = torch.tensor([t.data_ptr() for t in stage], dtype=torch.int64, device=dev)
+    summed = sum(t.float() for t in stage) / world
+    for rank in (0, world // 2, world - 1):
+        ref = torch.empty(S, device=dev)
+        for so, piece, off in rows:
+            ref[so:so + piece] = summed[off + rank * piece:off + (rank + 1) * piece]
+        out = torch.empty(S, device=dev, dtype=torch.float32)
+        sumsq = torch.zeros((), device=dev, dtype=torch.float64)
+        ext.reduce_scatter_sumsq(bufs, rank, _DT[torch.bfloat16], 1.0 / world, out, sumsq, False, None, table)
+        _close(out, ref, 1e-5, 1e-5, f"reduce-scatter with piece table, world={world} rank={rank}")
+        assert abs(sumsq.item() - (ref.double() ** 2).sum().item()) < 1e-3 * (ref.double() ** 2).sum().item()
