@@ -348,7 +348,8 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
                                             const OptTensor& bias, int64_t act, bool a_mn, bool b_mn,
                                             bool want_preact, int64_t out_dtype_code, int64_t mode, double alpha,
                                             Tensor& err, const std::vector<int64_t>& a_part_ptrs, int64_t a_first,
-                                            const std::vector<int64_t>& c_part_ptrs, bool accumulate) {
+                                            const std::vector<int64_t>& c_part_ptrs, bool accumulate,
+                                            const std::vector<int64_t>& b_gather_ptrs, int64_t b_gather_rank) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "operands must be CUDA tensors");
   c10::cuda::CUDAGuard guard(A.device());
   TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && A.dim() == B.dim(), "operands must both be 2-D or both 3-D");
@@ -400,13 +401,28 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
     peers.c_nparts = (int)c_part_ptrs.size();
     for (size_t i = 0; i < c_part_ptrs.size(); ++i) peers.c_ptrs[i] = reinterpret_cast<void*>(c_part_ptrs[i]);
   }
+  // gathered weight operand: b_gather_ptrs[r] = rank r's row block, B = the local full matrix it lands in
+  mb::GemmGatherSpec gather;
+  if (!b_gather_ptrs.empty()) {
+    TORCH_CHECK(b_gather_ptrs.size() <= 8 && B.dim() == 2 && B.is_contiguous(), "gathered B must be a contiguous matrix");
+    TORCH_CHECK(mb::gemm_gather_supported(M, N, K, (int)b_gather_ptrs.size()), "shape not supported by the gathering GEMM");
+    gather.world = (int)b_gather_ptrs.size();
+    gather.rank = (int)b_gather_rank;
+    for (size_t i = 0; i < b_gather_ptrs.size(); ++i) gather.src[i] = reinterpret_cast<const void*>(b_gather_ptrs[i]);
+    gather.dst = B.data_ptr();
+    static thread_local Tensor flags;          // one scratch per device is enough: uses are ordered on the stream
+    if (!flags.defined() || flags.device() != A.device())
+      flags = torch::zeros({512}, A.options().dtype(at::kInt));
+    TORCH_CHECK(mb::gemm_gather_flag_words(N) <= flags.numel());
+    gather.flags = reinterpret_cast<unsigned int*>(flags.data_ptr<int>());
+  }
   const int rc = mb::gemm_bf16_tcgen05(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                        pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
                                        (int)act, M, N, K, A.stride(-2), B.stride(-2), C.stride(-2), a_mn, b_mn,
                                        (int)mode, (float)alpha, batch, a_bs, b_bs, c_bs, dtype_code(A),
                                        (int)out_dtype_code, err.data_ptr<int>(), sms, stream(),
                                        (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr,
-                                       accumulate && out.has_value());
+                                       accumulate && out.has_value(), gather.world > 0 ? &gather : nullptr);
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
 }
@@ -665,7 +681,8 @@ const long long* table_ptr(const OptTensor& table, int* npieces) {
 }
 
 // full (natural order) <- piece r of every parameter from peer_shards[r], for every rank r
-void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, const OptTensor& abort) {
+void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, int64_t listed_numel,
+                 const OptTensor& abort) {
   check_cuda_contig(full, "full");
   check_cuda_contig(peer_shards, "peer_shards");
   c10::cuda::CUDAGuard guard(full.device());
@@ -673,8 +690,9 @@ void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, c
   int npieces = 0;
   const long long* tab = table_ptr(table, &npieces);
   TORCH_CHECK(reinterpret_cast<uintptr_t>(full.data_ptr()) % 16 == 0);
+  const int64_t listed = listed_numel;          // world * sum of the listed pieces, known to the caller
   mb::gather_pull(full.data_ptr(), reinterpret_cast<const void* const*>(peer_shards.data_ptr<int64_t>()),
-                  (int)peer_shards.numel(), tab, npieces, full.numel(), (int)full.element_size(), opt_abort(abort),
+                  (int)peer_shards.numel(), tab, npieces, listed, (int)full.element_size(), opt_abort(abort),
                   stream());
 }
 
@@ -769,7 +787,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("gemm", checked(&gemm), py::arg("A"), py::arg("B"), py::arg("out"), py::arg("bias"), py::arg("act"), py::arg("a_mn"),
         py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
-        py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false);
+        py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false,
+        py::arg("b_gather_ptrs") = std::vector<int64_t>(), py::arg("b_gather_rank") = 0);
+  m.def("gemm_gather_supported", [](int64_t M, int64_t N, int64_t K, int64_t world) {
+    return mb::gemm_gather_supported((int)M, (int)N, (int)K, (int)world);
+  });
   m.def("gemv_small_m", checked(&gemv_small_m));
   m.def("rfft_rows", checked(&rfft_rows));
   m.def("fftconv_apply", checked(&fftconv_apply));
@@ -779,7 +801,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale"), py::arg("out"), py::arg("sumsq"), py::arg("accumulate"), py::arg("abort") = py::none(),
         py::arg("table") = py::none());
   m.def("gather_pull", checked(&gather_pull), py::arg("full"), py::arg("peer_shards"), py::arg("table"),
-        py::arg("abort") = py::none());
+        py::arg("listed_numel"), py::arg("abort") = py::none());
   m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
         py::arg("scale"), py::arg("p"), py::arg("m"), py::arg("v"), py::arg("low"), py::arg("sumsq"), py::arg("lr"),
         py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("step"),

@@ -465,49 +465,57 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
   if (threadIdx.x == 0 && sumsq != nullptr) atomicAdd(sumsq, (double)ss);
 }
 
-// Parameter all-gather by pull into the natural layout.  Every 16-byte word of `full` comes from the
-// shard of the rank that owns it: word at natural element index n of parameter p (offset <= n <
-// offset + world * piece) lives on rank (n - offset) / piece at shard index shard_offset + (n - offset) % piece.
-// Four loads per thread are in flight before the first store.
+// Parameter all-gather by pull into the natural layout.  The table may list all parameters of a unit
+// or a subset (the rest being gathered by the GEMMs that consume them); the kernel walks the listed
+// parameters back to back.  Word k of parameter p (0 <= k < world * piece) lives on rank k / piece at
+// shard index shard_offset + k % piece and goes to natural index offset + k.  Four loads per thread
+// are in flight before the first store.
 struct NaturalMap {
-  long long nat_end[kMaxPieces];       // offset + world * piece
+  long long cum_end[kMaxPieces];       // elements of the listed parameters up to and including this one
   long long off[kMaxPieces], piece[kMaxPieces], soff[kMaxPieces];
 };
 __global__ void gather_pull_kernel(uint4* __restrict__ full, const uint4* const* __restrict__ peer_shards, int world,
-                                   const long long* __restrict__ table, int npieces, long long nwords, int per,
-                                   const int* abort) {
+                                   const long long* __restrict__ table, int npieces, int per, const int* abort) {
   __shared__ NaturalMap nm;
+  __shared__ long long total;
   if (block_sees_abort(abort)) return;
-  for (int i = threadIdx.x; i < npieces; i += blockDim.x) {
-    nm.soff[i] = table[3 * i]; nm.piece[i] = table[3 * i + 1]; nm.off[i] = table[3 * i + 2];
-    nm.nat_end[i] = nm.off[i] + (long long)world * nm.piece[i];
+  if (threadIdx.x == 0) {
+    long long cum = 0;
+    for (int i = 0; i < npieces; ++i) {
+      nm.soff[i] = table[3 * i]; nm.piece[i] = table[3 * i + 1]; nm.off[i] = table[3 * i + 2];
+      cum += (long long)world * nm.piece[i];
+      nm.cum_end[i] = cum;
+    }
+    total = cum;
   }
   __syncthreads();
+  const long long nwords = total / per;
   constexpr int kUnroll = 4;
   const long long stride = (long long)gridDim.x * blockDim.x;
   for (long long w0 = (long long)blockIdx.x * blockDim.x + threadIdx.x; w0 < nwords; w0 += stride * kUnroll) {
     uint4 v[kUnroll];
+    long long dst[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       const long long w = w0 + u * stride;
+      dst[u] = -1;
       if (w < nwords) {
-        const long long n = w * per;                      // natural element index of this word
+        const long long n = w * per;                      // element index within the listed parameters
         int lo = 0, hi = npieces - 1;
         while (lo < hi) {
           const int mid = (lo + hi) >> 1;
-          if (n < nm.nat_end[mid]) hi = mid; else lo = mid + 1;
+          if (n < nm.cum_end[mid]) hi = mid; else lo = mid + 1;
         }
-        const long long rel = n - nm.off[lo];
+        const long long rel = n - (nm.cum_end[lo] - (long long)world * nm.piece[lo]);
         const long long r = rel / nm.piece[lo];
         const long long j = rel - r * nm.piece[lo];
         v[u] = __ldcv(peer_shards[r] + (nm.soff[lo] + j) / per);
+        dst[u] = (nm.off[lo] + rel) / per;
       }
     }
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const long long w = w0 + u * stride;
-      if (w < nwords) full[w] = v[u];
-    }
+    for (int u = 0; u < kUnroll; ++u)
+      if (dst[u] >= 0) full[dst[u]] = v[u];
   }
 }
 
@@ -588,14 +596,14 @@ bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long lon
 int piece_table_limit() { return kMaxPieces; }
 
 void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
-                 long long numel_padded, int esize, const int* abort, cudaStream_t st) {
-  if (numel_padded == 0 || npieces > kMaxPieces) return;
+                 long long listed_numel, int esize, const int* abort, cudaStream_t st) {
+  if (listed_numel == 0 || npieces == 0 || npieces > kMaxPieces) return;
   const int per = 16 / esize;
-  const long long nwords = numel_padded / per;
+  const long long nwords = listed_numel / per;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(nwords, 256 * 4), 148LL * 4));
   prefer_max_shared(gather_pull_kernel);
-  gather_pull_kernel<<<grid, 256, 0, st>>>((uint4*)full, (const uint4* const*)peer_shards, world, table, npieces, nwords,
-                                           per, abort);
+  gather_pull_kernel<<<grid, 256, 0, st>>>((uint4*)full, (const uint4* const*)peer_shards, world, table, npieces, per,
+                                           abort);
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,

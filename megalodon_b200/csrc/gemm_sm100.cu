@@ -80,6 +80,16 @@ struct GemmParams {
   // c_part_cols), a slot in the memory of the rank that owns those columns
   int c_nparts, c_part_cols;
   void* c_parts[kMaxPeers];
+  // all-gather -> GEMM on the weight operand (B, K-major [N, K], rows sharded over `g_world` ranks in
+  // blocks of N / g_world rows; pair kernel only).  g_src[r] is rank r's block (peer memory for r !=
+  // g_rank), g_dst the local full matrix that tmap_b reads.  The copy warps of all CTAs move the matrix
+  // in 128-row chunks (claimed 8 KiB at a time through g_flags[0], starting with this rank's own rows);
+  // g_flags[1 + c] counts the finished 8 KiB units of chunk c, and a producer loads B rows of chunk c
+  // only once all K / 32 of them are in.  The n-tile walk starts at this rank's own rows too.
+  int g_world, g_rank;
+  const void* g_src[kMaxPeers];
+  void* g_dst;
+  unsigned int* g_flags;
 };
 
 struct TmapArray {
@@ -422,8 +432,85 @@ __device__ __forceinline__ void pair_k_range(const GemmParams& p, int m0, int nu
   if (p.mode == 3) kb0 = min(num_k - 1, m0 / BK);
 }
 
-template <bool A_MN, bool B_MN, typename OutT>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads, 1)
+constexpr int kGatherWarps = 4;                 // copy warps of the gathering variant
+constexpr int kGatherUnitBytes = 8192;          // one claim: 32 lanes x 16 loads of 16 bytes
+
+// Tile -> (m0, n0, batch).  With a gathered B the n-tiles are walked starting at this rank's own rows,
+// whose chunks are copied first.
+__device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int num_m, int num_n,
+                                                 int tiles_per_batch, int& m0, int& n0, int& bz) {
+  bz = tile / tiles_per_batch;
+  const int t = tile - bz * tiles_per_batch;
+  int nt = t / num_m;
+  if (p.g_world > 0) {
+    nt += (int)(((long long)p.g_rank * (p.N / p.g_world)) / kPairBN);
+    if (nt >= num_n) nt -= num_n;
+  }
+  m0 = (t % num_m) * kPairBM;
+  n0 = nt * kPairBN;
+}
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu_u32(const unsigned int* p) {
+  unsigned int v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void fence_proxy_async_all() { asm volatile("fence.proxy.async;" ::: "memory"); }
+
+// Bounded wait until chunk `chunk` of the gathered matrix is complete in local memory.
+__device__ __forceinline__ bool wait_chunk(const GemmParams& p, int chunk, volatile int* abort_flag) {
+  const unsigned int need = (unsigned int)(p.K / 32);
+  const unsigned int* flag = p.g_flags + 1 + chunk;
+  if (ld_acquire_gpu_u32(flag) < need) {
+    const unsigned long long t0 = globaltimer_ns();
+    uint32_t spins = 0;
+    while (ld_acquire_gpu_u32(flag) < need) {
+      if ((++spins & 0x3f) == 0) {
+        if (*abort_flag) return false;
+        if (globaltimer_ns() - t0 > kWaitTimeoutNs) return false;
+      }
+      __nanosleep(64);
+    }
+  }
+  fence_proxy_async_all();        // the copy warps wrote through the generic proxy, TMA reads through the async one
+  return true;
+}
+
+// Body of one copy warp: claim 8 KiB units until none is left.  Never waits for anything.
+__device__ __forceinline__ void gather_copy_warp(const GemmParams& p, int lane) {
+  const int nchunks = p.N / 128;
+  const int upc = p.K / 32;                              // 8 KiB units per 128-row chunk (K * 256 B / 8192)
+  const int total = nchunks * upc;
+  const int rows_per_rank = p.N / p.g_world;
+  const int first_chunk = (int)(((long long)p.g_rank * rows_per_rank) / 128);
+  while (true) {
+    unsigned int u = 0;
+    if (lane == 0) u = atomicAdd(p.g_flags, 1u);
+    u = __shfl_sync(0xffffffffu, u, 0);
+    if (u >= (unsigned int)total) break;
+    const int oc = (int)u / upc, sub = (int)u - oc * upc;
+    int chunk = oc + first_chunk;
+    if (chunk >= nchunks) chunk -= nchunks;
+    const int row0 = chunk * 128;
+    const int owner = row0 / rows_per_rank;
+    const long long src_byte = (long long)(row0 - owner * rows_per_rank) * p.K * 2 + (long long)sub * kGatherUnitBytes;
+    const long long dst_byte = (long long)row0 * p.K * 2 + (long long)sub * kGatherUnitBytes;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(p.g_src[owner]) + src_byte);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(p.g_dst) + dst_byte);
+    uint4 v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __ldcv(src + lane + 32 * i);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) dst[lane + 32 * i] = v[i];
+    fence_proxy_async_all();
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) atomicAdd(p.g_flags + 1 + chunk, 1u);
+  }
+}
+
+template <bool A_MN, bool B_MN, typename OutT, bool GATHER = false>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b,
                          const __grid_constant__ GemmParams p, int in_fmt) {
   using L = PairSmem;
@@ -480,14 +567,17 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int bz = tile / tiles_per_batch;
-        const int t = tile - bz * tiles_per_batch;
-        const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+        int m0, n0, bz;
+        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
         if (pair_tile_skipped(p, m0, n0)) continue;
         const int my_m = m0 + (int)rank * BM;
         const int my_n = n0 + (int)rank * (kPairBN / 2);
         int kb0, kb1;
         pair_k_range(p, m0, num_k, kb0, kb1);
+        if constexpr (GATHER) {
+          // this CTA's 128 rows of B are exactly one chunk of the gathered matrix
+          if (my_n < p.N && !wait_chunk(p, my_n / 128, abort_flag)) { ok = false; break; }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!wait_or_abort(empty_bar + stage, phase ^ 1, abort_flag)) { ok = false; break; }
           uint8_t* sa = smem + stage * L::stage_bytes;
@@ -527,9 +617,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-        const int bz = tile / tiles_per_batch;
-        const int t = tile - bz * tiles_per_batch;
-        const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+        int m0, n0, bz;
+        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
         if (pair_tile_skipped(p, m0, n0)) continue;
         int kb0, kb1;
         pair_k_range(p, m0, num_k, kb0, kb1);
@@ -563,6 +652,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       }
       if (!ok) { *abort_flag = 1; atomicExch(p.err, 2); }
     }
+  } else if (GATHER && warp >= kGemmThreads / 32) {
+    // ------------------------------------------------------------ copy warps (gathering variant)
+    gather_copy_warp(p, lane);
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
@@ -572,9 +664,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
     OutT* C = reinterpret_cast<OutT*>(p.C);
     OutT* P = reinterpret_cast<OutT*>(p.preact);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
-      const int bz = tile / tiles_per_batch;
-      const int t = tile - bz * tiles_per_batch;
-      const int m0 = (t % num_m) * kPairBM, n0 = (t / num_m) * kPairBN;
+      int m0, n0, bz;
+      pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
       if (pair_tile_skipped(p, m0, n0)) continue;
       if (!wait_or_abort(tmem_full + acc, acc_phase, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
@@ -706,6 +797,26 @@ static int launch_gemm(const TmapArray& ta, const CUtensorMap& tb, const GemmPar
   return cudaGetLastError() == cudaSuccess ? 0 : -3;
 }
 
+// Pair kernel with copy warps that gather the K-major weight operand from its owners while the tensor
+// cores work (see GemmParams::g_*).  The claim counter and the chunk flags are cleared on the stream first.
+template <typename OutT>
+static int launch_gemm_pair_gather(const TmapArray& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt,
+                                   int sms, cudaStream_t st) {
+  using L = PairSmem;
+  auto kern = gemm_tcgen05_pair_kernel<false, false, OutT, true>;
+  static bool configured = false;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::total) != cudaSuccess) return -2;
+    configured = true;
+  }
+  if (cudaMemsetAsync(p.g_flags, 0, sizeof(unsigned int) * (1 + p.N / 128), st) != cudaSuccess) return -8;
+  const int tiles = ((p.M + kPairBM - 1) / kPairBM) * ((p.N + kPairBN - 1) / kPairBN) * p.batch;
+  const int pairs = sms / 2;
+  const int grid = 2 * (tiles < pairs ? tiles : pairs);
+  kern<<<grid, kGemmThreads + kGatherWarps * 32, L::total, st>>>(ta, tb, p, in_fmt);
+  return cudaGetLastError() == cudaSuccess ? 0 : -3;
+}
+
 template <bool A_MN, bool B_MN, typename OutT>
 static int launch_gemm_pair(const TmapArray& ta, const CUtensorMap& tb, const GemmParams& p, int in_fmt, int sms,
                             cudaStream_t st) {
@@ -731,7 +842,7 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
-                      const GemmPeerSpec* peers, bool accumulate) {
+                      const GemmPeerSpec* peers, bool accumulate, const GemmGatherSpec* gather) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA wants 16-byte strides; the vectorised epilogue wants 16-byte aligned rows of C
   if (lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return -1;
@@ -767,10 +878,23 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
   }
   const bool pair = g_use_pair && M > BM && num_sms >= 2;
   if (!ok) return -41;
+  if (gather != nullptr && gather->world > 0) {
+    // B must be the whole K-major weight, contiguous, its row blocks whole 128-row chunks
+    if (!gemm_gather_supported(M, N, K, gather->world) || !pair || a_mn || b_mn || batch != 1 || mode != 0 ||
+        p.a_parts != 1 || ldb != K || gather->world > kMaxPeers || gather->flags == nullptr || B != gather->dst)
+      return -9;
+    p.g_world = gather->world; p.g_rank = gather->rank; p.g_dst = gather->dst; p.g_flags = gather->flags;
+    for (int i = 0; i < gather->world; ++i) p.g_src[i] = gather->src[i];
+  }
   ok = ok && (b_mn ? make_tmap_3d(&tb, B, N, K, batch, ldb, b_bs, 64, 64, in_dtype)
                    : make_tmap_3d(&tb, B, K, N, batch, ldb, b_bs, BK, pair ? kPairBN / 2 : BN, in_dtype));
   if (!ok) return -4;
   const int fmt = in_dtype == kBF16 ? 1 : 0;
+  if (p.g_world > 0) {
+    if (out_dtype == kBF16) return launch_gemm_pair_gather<__nv_bfloat16>(ta, tb, p, fmt, num_sms, st);
+    if (out_dtype == kF16) return launch_gemm_pair_gather<__half>(ta, tb, p, fmt, num_sms, st);
+    return launch_gemm_pair_gather<float>(ta, tb, p, fmt, num_sms, st);
+  }
   if (pair) {
 #define GEMM_PAIR_CASE(AMN, BMN)                                                                        \
   if (a_mn == AMN && b_mn == BMN) {                                                                     \
@@ -800,6 +924,11 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
 }
 
 void gemm_set_cta_pairs(bool on) { g_use_pair = on; }
+
+bool gemm_gather_supported(int M, int N, int K, int world) {
+  return g_use_pair && M > BM && world > 1 && world <= kMaxPeers && N % (world * 128) == 0 && K % 64 == 0;
+}
+int gemm_gather_flag_words(int N) { return 1 + N / 128; }
 
 // How many CTA pairs of the pair kernel the device can hold at once (diagnostic).
 int gemm_pair_max_active_clusters() {

@@ -80,11 +80,27 @@ struct GemmPeerSpec {
   int c_nparts = 1;
   void* c_ptrs[8] = {};
 };
+// Parameter all-gather fused into the GEMM that first consumes the weight (forward of a linear layer,
+// B = w [N, K] K-major).  The weight's rows are sharded over `world` ranks in blocks of N / world rows
+// (per-parameter FSDP sharding); src[r] is rank r's block - peer memory for r != rank - and dst the local
+// full matrix, which must also be the GEMM's B pointer.  Copy warps inside the GEMM kernel pull the blocks
+// over NVLink into dst 128 rows at a time while the tensor cores already work on the rows that have
+// arrived, starting with the rank's own; every byte crosses the link once, and dst is complete when
+// the kernel ends.  `flags`: gemm_gather_flag_words(N) uint32 of device scratch.
+struct GemmGatherSpec {
+  int world = 0, rank = 0;
+  const void* src[8] = {};
+  void* dst = nullptr;
+  unsigned int* flags = nullptr;
+};
+bool gemm_gather_supported(int M, int N, int K, int world);
+int gemm_gather_flag_words(int N);
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
-                      const GemmPeerSpec* peers = nullptr, bool accumulate = false);
+                      const GemmPeerSpec* peers = nullptr, bool accumulate = false,
+                      const GemmGatherSpec* gather = nullptr);
 // ---- FFT long convolution (fftconv_kernels.cu); spectra are [rows, N2/2 + 1] complex, N2 = 1 << fftconv_logn(L)
 int fftconv_logn(int L);
 bool fftconv_supported(int L);          // L <= 8192
@@ -151,10 +167,11 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
 // natural parameter order and rank r owns piece r of every parameter (per-parameter sharding); without it
 // rank r owns the contiguous range [r * shard_n, (r + 1) * shard_n).  At most piece_table_limit() rows.
 int piece_table_limit();
-// Parameter all-gather by pull: full (natural order) <- piece r of every parameter from rank r's shard
-// (peer_shards[r], possibly peer memory), for all r.  Element size `esize` bytes (2 or 4).
+// Parameter all-gather by pull: full (natural order) <- piece r of every parameter listed in `table` from
+// rank r's shard (peer_shards[r], possibly peer memory), for all r.  `listed_numel` = world * sum of the
+// listed pieces (only sizes the grid).  Element size `esize` bytes (2 or 4).
 void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
-                 long long numel_padded, int esize, const int* abort, cudaStream_t st);
+                 long long listed_numel, int esize, const int* abort, cudaStream_t st);
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
                      int dtype, const int* abort, cudaStream_t st);
 

@@ -77,9 +77,12 @@ def _tma_ok(t: Tensor) -> bool:
 def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str] = None, *,
          a_mn: bool = False, b_mn: bool = False, want_preact: bool = False,
          out_dtype: Optional[torch.dtype] = None, out: Optional[Tensor] = None, mode: int = 0,
-         alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None, accumulate: bool = False):
+         alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None, accumulate: bool = False,
+         b_gather=None):
     """C = act(alpha * A B^T + bias), or with `accumulate` (needs `out`) C += alpha * A B^T + bias.
-    `a_mn` / `b_mn`: operand is stored [K, rows].
+    `a_mn` / `b_mn`: operand is stored [K, rows].  `b_gather = (addresses of every rank's row block of
+    B, this rank)`: B (a contiguous [N, K] matrix) is filled from those blocks by the kernel itself
+    while it computes (FSDP all-gather fused into the consuming GEMM).
     Operands may be 2-D or 3-D (batched) strided views with a contiguous last
     dim.  `mode` 1..3 exploits causal structure (see gemm_sm100.cu).  Returns
     (C, preact | None)."""
@@ -87,14 +90,16 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
     native = (_GEMM_BACKEND[0] == "tcgen05" and a.dtype in (torch.bfloat16, torch.float16)
               and _tma_ok(a) and _tma_ok(b) and (out is None or _tma_ok(out))
               and (b.shape[-1] if b_mn else b.shape[-2]) % 8 == 0)
-    if a_part_ptrs or c_part_ptrs:
+    if a_part_ptrs or c_part_ptrs or b_gather:
         if not native:
             raise RuntimeError("peer-memory GEMM needs the tcgen05 backend and TMA-compatible operands")
         _bump()
         res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
                                  _DT[out_dtype], mode, alpha, _err_flag(a.device),
                                  a_part_ptrs=list(a_part_ptrs or []), a_first=a_first,
-                                 c_part_ptrs=list(c_part_ptrs or []))
+                                 c_part_ptrs=list(c_part_ptrs or []),
+                                 b_gather_ptrs=list(b_gather[0]) if b_gather else [],
+                                 b_gather_rank=int(b_gather[1]) if b_gather else 0)
         if rc != 0:
             raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
         return res, pre
@@ -132,12 +137,32 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
     return res, pre
 
 
+def ensure_gathered(w: Tensor) -> Tensor:
+    """A weight whose all-gather was left to its first consuming GEMM (`_gather_spec`) but is about to
+    be read by something else: gather it now."""
+    spec = getattr(w, "_gather_spec", None)
+    if spec is not None and spec.pending:
+        spec.pull_now()
+    return w
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, b, act):
         x2 = x.reshape(-1, x.shape[-1])
         need_pre = act is not None and any(ctx.needs_input_grad[:3])
-        y, pre = gemm(x2, w, b, act, want_preact=need_pre)
+        spec = getattr(w, "_gather_spec", None)
+        if spec is not None and spec.pending:
+            # first use of a sharded weight since the last optimiser step: this GEMM gathers it
+            if (_GEMM_BACKEND[0] == "tcgen05" and w.is_contiguous() and _tma_ok(x2)
+                    and _C().gemm_gather_supported(x2.shape[0], w.shape[0], w.shape[1], len(spec.sources()[0]))):
+                y, pre = gemm(x2, w, b, act, want_preact=need_pre, b_gather=spec.sources())
+                spec.done()
+            else:
+                spec.pull_now()
+                y, pre = gemm(x2, w, b, act, want_preact=need_pre)
+        else:
+            y, pre = gemm(x2, w, b, act, want_preact=need_pre)
         ctx.save_for_backward(x2, w, pre if pre is not None else torch.empty(0, device=x.device))
         ctx.wgrad_sink = getattr(w, "_wgrad_sink", None)
         ctx.has_bias = b is not None

@@ -281,14 +281,17 @@ class FullyShardedDataParallel(nn.Module):
         if a < b:
             shard[info.shard_offset:info.shard_offset + (b - a)].copy_(flat_param[a:b])
 
-    def piece_table(self, device) -> torch.Tensor:
+    def piece_table(self, device, infos=None, key=None) -> torch.Tensor:
         """int64 [P, 3] rows (shard_offset, piece, offset) on `device`: what the native kernels that
-        move data between the shard and the natural layouts need."""
-        key = str(device)
+        move data between the shard and the natural layouts need.  `infos` restricts the table to
+        some parameters (cached under `key`)."""
+        key = (str(device), key)
         t = self._piece_tables.get(key)
         if t is None:
-            rows = [[i.shard_offset, i.piece, i.offset] for i in self._infos] or [[0, self._shard_numel, 0]]
-            t = self._piece_tables[key] = torch.tensor(rows, dtype=torch.int64, device=device)
+            rows = [[i.shard_offset, i.piece, i.offset] for i in (self._infos if infos is None else infos)]
+            if infos is None and not rows:
+                rows = [[0, self._shard_numel, 0]]
+            t = self._piece_tables[key] = torch.tensor(rows, dtype=torch.int64, device=device).reshape(-1, 3)
         return t
 
     def _unshard(self, rank_major: torch.Tensor, full: torch.Tensor) -> None:
@@ -447,6 +450,12 @@ class FullyShardedDataParallel(nn.Module):
                 ev.record(gs)
                 u._gather_event = ev
 
+    def _pull_pending(self) -> None:
+        puller = getattr(getattr(self, "_root", self), "_symm_gather", None)
+        for info in list(self._fused_infos):
+            if info.name in self._fused_pending:
+                puller.pull_one(self, info, self._full.data)
+
     def _free_full(self) -> None:
         if self.world_size > 1 and self._full is not None:
             self._full.untyped_storage().resize_(0)
@@ -459,9 +468,12 @@ class FullyShardedDataParallel(nn.Module):
         else:
             views = [leaf[info.offset:info.offset + info.numel].view(info.shape) for info in self._infos]
         direct = track and leaf.is_cuda and leaf.dtype in (torch.bfloat16, torch.float16)
+        fused = {i.name for i in getattr(self, "_fused_infos", ())}
         for info, v in zip(self._infos, views):
             if direct and len(info.shape) == 2:
                 v._wgrad_sink = functools.partial(self._grad_view, info)
+            if info.name in fused:
+                v._gather_spec = _GatherSpec(self, info)
             for mod, pname, _ in info.owners:
                 mod.__dict__[pname] = v
 
@@ -515,6 +527,8 @@ class FullyShardedDataParallel(nn.Module):
         self.training_state = TrainingState.FORWARD
         out = self._wrapped(*args, **kwargs)
         self.training_state = TrainingState.IDLE
+        if getattr(self, "_fused_pending", None):
+            self._pull_pending()           # matrices that no gathering GEMM consumed in this call
         if self.reshard_after_forward and not self._is_root:
             self._free_full()
             if want_grad:
@@ -884,6 +898,32 @@ class FullyShardedDataParallel(nn.Module):
                 f"mixed_precision={self.mixed_precision}, compute_dtype={self.compute_dtype}, "
                 f"fp32_reduce_scatter={self.fp32_reduce_scatter}, "
                 f"reshard_after_forward={self.reshard_after_forward}")
+
+
+class _GatherSpec:
+    """Carried by the view of a weight matrix whose all-gather is left to the first GEMM that consumes
+    it (`ops.cuda_ops._Linear`): where every rank's row block lives, and whether it is still missing
+    from the unit's gathered buffer."""
+    __slots__ = ("unit", "info")
+
+    def __init__(self, unit: "FullyShardedDataParallel", info: _ParamInfo):
+        self.unit, self.info = unit, info
+
+    @property
+    def pending(self) -> bool:
+        return self.info.name in self.unit._fused_pending
+
+    def sources(self):
+        """(address of every rank's row block, this rank)."""
+        esize = self.unit._full.element_size()
+        return [a + self.info.shard_offset * esize for a in self.unit._shard_peer_addr], self.unit.rank
+
+    def done(self) -> None:
+        self.unit._fused_pending.discard(self.info.name)
+
+    def pull_now(self) -> None:
+        root = getattr(self.unit, "_root", self.unit)
+        root._symm_gather.pull_one(self.unit, self.info, self.unit._full.data)
 
 
 def _ver(p: torch.Tensor):

@@ -525,9 +525,14 @@ class SymmetricParamGather:
     slower rank is still reading cannot happen: a rank updates its shards only after the gradient
     reductions of the step, which need every rank's backward pass and therefore every rank's pulls."""
 
-    def __init__(self, model, timeout_s: float = 30.0):
+    def __init__(self, model, timeout_s: float = 30.0, fuse_into_gemm: bool = True):
         from ..ops._ext import require
         self.model = model
+        # With `fuse_into_gemm` the weight matrices of the blocks are not pulled by `pull` at all: the
+        # forward GEMM that first consumes a weight gathers it itself, its copy warps pulling the row
+        # blocks from their owners while the tensor cores work on the rows already there
+        # (`GemmGatherSpec` in csrc/kernels.h).  `pull` then moves only the small parameters.
+        self.fuse_into_gemm = fuse_into_gemm
         units = model._units()
         self.group = model.process_group
         self.world = dist.get_world_size(self.group)
@@ -555,8 +560,21 @@ class SymmetricParamGather:
             p._lowp_shard = shard
             p._lowp_version = (p._version, getattr(p, "_master_version", 0))
             self._peer_ptrs[id(u)] = self.region.ptr_table_at(off).contiguous()
+            u._shard_peer_addr = [self.region.peer_ptr(r, off) for r in range(self.world)]
+            u._fused_infos = self._fusable(u) if fuse_into_gemm and not u._is_root else []
+            u._fused_pending = set()
         torch.cuda.synchronize(device)
         dist.barrier(group=self.group)
+
+    def _fusable(self, unit) -> list:
+        """Parameters of `unit` that the gathering GEMM can take: matrices [N, K] whose row blocks are
+        whole 128-row chunks without padding."""
+        out = []
+        for i in unit._infos:
+            if (len(i.shape) == 2 and i.shape[0] % (self.world * 128) == 0 and i.shape[1] % 64 == 0
+                    and i.piece * self.world == i.numel):
+                out.append(i)
+        return out
 
     def shards_written(self) -> None:
         """Flag barrier on the current stream, once per version of the master weights."""
@@ -572,8 +590,28 @@ class SymmetricParamGather:
         require().peer_barrier(self._pads, self.rank, self.epoch, self.timeout_ns, self._abort.dev, self.epoch)
 
     def pull(self, unit, full: torch.Tensor) -> None:
+        """Gather `unit` into `full`, except the matrices left to the gathering GEMMs (they are marked
+        pending on the unit; `FullyShardedDataParallel.forward` pulls whatever no GEMM took)."""
         from ..ops._ext import require
-        require().gather_pull(full, self._peer_ptrs[id(unit)], unit.piece_table(full.device), self._abort.dev)
+        skip = unit._fused_infos
+        if skip:
+            names = {i.name for i in skip}
+            rest = [i for i in unit._infos if i.name not in names]
+            table = unit.piece_table(full.device, rest, key="unfused")
+            listed = self.world * sum(i.piece for i in rest)
+            unit._fused_pending = set(names)
+        else:
+            table = unit.piece_table(full.device)
+            listed = unit._numel_padded
+        if listed:
+            require().gather_pull(full, self._peer_ptrs[id(unit)], table, listed, self._abort.dev)
+
+    def pull_one(self, unit, info, full: torch.Tensor) -> None:
+        """Gather a single parameter (a matrix whose first use was not a gathering GEMM)."""
+        from ..ops._ext import require
+        table = unit.piece_table(full.device, [info], key=("one", info.name))
+        require().gather_pull(full, self._peer_ptrs[id(unit)], table, self.world * info.piece, self._abort.dev)
+        unit._fused_pending.discard(info.name)
 
     def check(self) -> None:
         self._abort.check()
@@ -583,12 +621,18 @@ class SymmetricParamGather:
         self._token = None
 
 
-def enable_peer_gather(model, timeout_s: float = 30.0) -> Optional[SymmetricParamGather]:
-    """Replace the NCCL parameter all-gather of every FSDP unit of `model` by pulls from peer memory."""
+def enable_peer_gather(model, timeout_s: float = 30.0,
+                       fuse_into_gemm: Optional[bool] = None) -> Optional[SymmetricParamGather]:
+    """Replace the NCCL parameter all-gather of every FSDP unit of `model` by pulls from peer memory;
+    with `fuse_into_gemm` (default on, MEGALODON_B200_FUSED_AG=0 turns it off) the weight matrices are
+    gathered inside the GEMM that first consumes them."""
+    import os
     if getattr(model, "world_size", 1) <= 1 or not getattr(model, "mixed_precision", False):
         return None
+    if fuse_into_gemm is None:
+        fuse_into_gemm = os.environ.get("MEGALODON_B200_FUSED_AG", "1") == "1"
     model._lazy_init()
-    sg = SymmetricParamGather(model, timeout_s=timeout_s)
+    sg = SymmetricParamGather(model, timeout_s=timeout_s, fuse_into_gemm=fuse_into_gemm)
     model._symm_gather = sg
     return sg
 

@@ -115,7 +115,9 @@ class AGLinear(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x_part, w, bias, act):
+        from ..ops import cuda_ops
         ws = workspace()
+        cuda_ops.ensure_gathered(w)
         x2 = x_part.reshape(-1, x_part.shape[-1])
         need_pre = act is not None and any(ctx.needs_input_grad[:3])
         y, pre = ws.ag_gemm(x2, w, bias, act, want_preact=need_pre)
@@ -148,7 +150,9 @@ class LinearRS(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, w):
+        from ..ops import cuda_ops
         ws = workspace()
+        cuda_ops.ensure_gathered(w)
         x2 = x.reshape(-1, x.shape[-1])
         y = ws.gemm_rs(x2, w)
         ctx.save_for_backward(x2, w)

@@ -627,12 +627,20 @@ def test_per_parameter_sharding_kernels_local_ranks(world):
             shards[r][so:so + piece] = full_ref[off + r * piece:off + (r + 1) * piece]
     ptrs = torch.tensor([t.data_ptr() for t in shards], dtype=torch.int64, device=dev)
     full = torch.zeros(total, device=dev, dtype=torch.bfloat16)
-    ext.gather_pull(full, ptrs, table)
+    ext.gather_pull(full, ptrs, table, total)
     assert torch.equal(full, full_ref)
     full32 = torch.zeros(total, device=dev, dtype=torch.float32)
     shards32 = [s.float() for s in shards]
     ptrs32 = torch.tensor([t.data_ptr() for t in shards32], dtype=torch.int64, device=dev)
-    ext.gather_pull(full32, ptrs32, table)
+    ext.gather_pull(full32, ptrs32, table, total)
+    # a subset of the parameters (the others are gathered elsewhere) leaves the rest of the buffer alone
+    some = torch.tensor([rows[1], rows[3]], dtype=torch.int64, device=dev)
+    part = torch.full((total,), -7.0, device=dev, dtype=torch.bfloat16)
+    ext.gather_pull(part, ptrs, some, world * (rows[1][1] + rows[3][1]))
+    want = torch.full((total,), -7.0, device=dev, dtype=torch.bfloat16)
+    for so, piece, off in (rows[1], rows[3]):
+        want[off:off + world * piece] = full_ref[off:off + world * piece]
+    assert torch.equal(part, want)
     assert torch.equal(full32, full_ref.float())
     # reduce-scatter: staged gradients in natural order, rank r receives piece r of every parameter
     stage = [torch.randn(total, device=dev).bfloat16() for _ in range(world)]
@@ -647,3 +655,32 @@ def test_per_parameter_sharding_kernels_local_ranks(world):
         ext.reduce_scatter_sumsq(bufs, rank, _DT[torch.bfloat16], 1.0 / world, out, sumsq, False, None, table)
         _close(out, ref, 1e-5, 1e-5, f"reduce-scatter with piece table, world={world} rank={rank}")
         assert abs(sumsq.item() - (ref.double() ** 2).sum().item()) < 1e-3 * (ref.double() ** 2).sum().item()
+
+
+@pytest.mark.parametrize("world,M,N,K", [(2, 512, 512, 256), (4, 384, 1024, 512), (8, 1024, 2048, 1024),
+                                         (8, 4096, 1024, 4096)])
+def test_gemm_that_gathers_its_weight_local_ranks(world, M, N, K):
+    """The GEMM whose copy warps gather the row-sharded weight while it runs: every 'rank' is a local
+    buffer here.  The product must equal x w^T and the full weight must be complete afterwards."""
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(16)
+    dev = _dev()
+    x = torch.randn(M, K, device=dev).bfloat16()
+    w = (torch.randn(N, K, device=dev) / K ** 0.5).bfloat16()
+    bias = torch.randn(N, device=dev).bfloat16()
+    rows = N // world
+    blocks = [w[r * rows:(r + 1) * rows].clone() for r in range(world)]
+    ref = x.float() @ w.float().t() + bias.float()
+    for rank in (0, world - 1):
+        full = torch.full((N, K), float("nan"), device=dev, dtype=torch.bfloat16)
+        y, _ = cuda_ops.gemm(x, full, bias, None, b_gather=([b.data_ptr() for b in blocks], rank))
+        torch.cuda.synchronize()
+        assert torch.equal(full, w), "gathered weight incomplete"
+        _close(y, ref, 3e-2, 2e-2, f"gathering GEMM world={world} rank={rank}")
+        cuda_ops.check_kernel_errors()
+    # second use of the same scratch flags, SiLU epilogue with pre-activation
+    full = torch.zeros(N, K, device=dev, dtype=torch.bfloat16)
+    y, pre = cuda_ops.gemm(x, full, bias, "silu", want_preact=True, b_gather=([b.data_ptr() for b in blocks], 1))
+    _close(pre, ref, 3e-2, 2e-2, "pre-activation")
+    _close(y, torch.nn.functional.silu(ref), 3e-2, 2e-2, "silu")
+    cuda_ops.check_kernel_errors()
