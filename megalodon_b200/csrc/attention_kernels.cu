@@ -230,7 +230,55 @@ inline bool softmax_vec_ok(const void* base, int L2, long long ld, int dtype) {
   return L2 % 8 == 0 && ld % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 31) == 0;
 }
 
+// Backward preparation of the fused-softmax attention: for every (batch, position, head) row of d_v values
+//   delta = dO . O          (equals sum_j P_ij dP_ij, the softmax Jacobian's row term)
+//   dO'   = dO / rowsum     (so that P~^T dO' = P^T dO with the un-normalised P~ that the forward kept)
+// dO, O, dO' are [B, L, H, dv] contiguous; rowsum and delta are [B, H, L] fp32.  One warp per row.
+template <typename T>
+__global__ void attn_bwd_prep_kernel(const T* __restrict__ dout, const T* __restrict__ out,
+                                     const float* __restrict__ rowsum, T* __restrict__ dos,
+                                     float* __restrict__ delta, long long rows, int L, int H, int dv) {
+  const int lane = threadIdx.x & 31;
+  const long long r = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (r >= rows) return;
+  const int h = (int)(r % H);
+  const long long bl = r / H;
+  const int l = (int)(bl % L);
+  const long long b = bl / L;
+  const long long vidx = (b * H + h) * L + l;
+  const float s = rowsum[vidx];
+  const float inv = s > 0.f ? 1.f / s : 0.f;
+  const T* g = dout + r * dv;
+  const T* o = out + r * dv;
+  T* d = dos + r * dv;
+  float acc = 0.f;
+  for (int c = lane * 8; c < dv; c += 256) {
+    float gv[8], ov[8];
+    load8(g + c, gv);
+    load8(o + c, ov);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      acc = fmaf(gv[i], ov[i], acc);
+      gv[i] *= inv;
+    }
+    store8(d + c, gv);
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) delta[vidx] = acc;
+}
+
 }  // namespace
+
+void attn_bwd_prep(const void* dout, const void* out, const float* rowsum, void* dos, float* delta, int B, int L,
+                   int H, int dv, int dtype, cudaStream_t st) {
+  const long long rows = (long long)B * L * H;
+  if (rows == 0) return;
+  const int warps = 8;
+  MB_DISPATCH_16BIT(dtype, (attn_bwd_prep_kernel<scalar_t><<<(unsigned)div_up(rows, warps), warps * 32, 0, st>>>(
+                               (const scalar_t*)dout, (const scalar_t*)out, rowsum, (scalar_t*)dos, delta, rows, L, H,
+                               dv)));
+}
 
 void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2, long long ld, bool causal,
                       float dropkey_p, unsigned long long seed, unsigned long long offset, int dtype,

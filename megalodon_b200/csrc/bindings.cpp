@@ -349,7 +349,9 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
                                             bool want_preact, int64_t out_dtype_code, int64_t mode, double alpha,
                                             Tensor& err, const std::vector<int64_t>& a_part_ptrs, int64_t a_first,
                                             const std::vector<int64_t>& c_part_ptrs, bool accumulate,
-                                            const std::vector<int64_t>& b_gather_ptrs, int64_t b_gather_rank) {
+                                            const std::vector<int64_t>& b_gather_ptrs, int64_t b_gather_rank,
+                                            int64_t epi_kind, const OptTensor& row_in, const OptTensor& row_in2,
+                                            const OptTensor& row_out, const OptTensor& aux, int64_t causal_off) {
   TORCH_CHECK(A.is_cuda() && B.is_cuda(), "operands must be CUDA tensors");
   c10::cuda::CUDAGuard guard(A.device());
   TORCH_CHECK((A.dim() == 2 || A.dim() == 3) && A.dim() == B.dim(), "operands must both be 2-D or both 3-D");
@@ -416,13 +418,35 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
     TORCH_CHECK(mb::gemm_gather_flag_words(N) <= flags.numel());
     gather.flags = reinterpret_cast<unsigned int*>(flags.data_ptr<int>());
   }
+  // softmax fused into the epilogue (attention products): fp32 row vectors [batch, M]
+  mb::GemmSoftmaxSpec sm;
+  if (epi_kind != 0) {
+    auto rowvec = [&](const OptTensor& t, const char* what) -> float* {
+      TORCH_CHECK(t.has_value() && t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() &&
+                  t->numel() == (int64_t)batch * M, what, ": expected a contiguous fp32 [batch, M] CUDA tensor");
+      return t->data_ptr<float>();
+    };
+    sm.kind = (int)epi_kind;
+    sm.causal_off = (int)causal_off;
+    if (epi_kind == 1) sm.row_out = rowvec(row_out, "row_out");
+    if (epi_kind == 2) { sm.row_in = rowvec(row_in, "row_in"); sm.row_out = rowvec(row_out, "row_out"); }
+    if (epi_kind == 3) sm.row_in = rowvec(row_in, "row_in");
+    if (epi_kind == 4) {
+      sm.row_in = rowvec(row_in, "row_in");
+      sm.row_in2 = rowvec(row_in2, "row_in2");
+      TORCH_CHECK(aux.has_value() && aux->scalar_type() == C.scalar_type() && aux->sizes() == C.sizes() &&
+                  aux->strides() == C.strides(), "aux must have the dtype and layout of the output");
+      sm.aux = aux->data_ptr();
+    }
+  }
   const int rc = mb::gemm_bf16_tcgen05(A.data_ptr(), B.data_ptr(), C.data_ptr(),
                                        pre.has_value() ? pre->data_ptr() : nullptr, opt_ptr(bias), bias_code,
                                        (int)act, M, N, K, A.stride(-2), B.stride(-2), C.stride(-2), a_mn, b_mn,
                                        (int)mode, (float)alpha, batch, a_bs, b_bs, c_bs, dtype_code(A),
                                        (int)out_dtype_code, err.data_ptr<int>(), sms, stream(),
                                        (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr,
-                                       accumulate && out.has_value(), gather.world > 0 ? &gather : nullptr);
+                                       accumulate && out.has_value(), gather.world > 0 ? &gather : nullptr,
+                                       sm.kind != 0 ? &sm : nullptr);
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
 }
@@ -517,6 +541,23 @@ void attn_softmax_bwd(const Tensor& p, Tensor& dp, int64_t L1, int64_t L2, bool 
   const long long rows = p.numel() / p.size(-1);
   mb::attn_softmax_bwd(p.data_ptr(), dp.data_ptr(), rows, (int)L1, (int)L2, p.stride(-2), causal, dtype_code(p),
                        stream());
+}
+
+// dout, out [B, L, H, dv] (16-bit), rowsum [B, H, L] fp32 -> (dout / rowsum, delta [B, H, L] = dout . out)
+std::tuple<Tensor, Tensor> attn_bwd_prep(const Tensor& dout, const Tensor& out, const Tensor& rowsum) {
+  check_cuda_contig(dout, "dout");
+  check_cuda_contig(out, "out");
+  check_cuda_contig(rowsum, "rowsum");
+  c10::cuda::CUDAGuard guard(dout.device());
+  TORCH_CHECK(dout.dim() == 4 && dout.sizes() == out.sizes() && dout.scalar_type() == out.scalar_type());
+  TORCH_CHECK(dout.scalar_type() == at::kBFloat16 || dout.scalar_type() == at::kHalf);
+  const int B = dout.size(0), L = dout.size(1), H = dout.size(2), dv = dout.size(3);
+  TORCH_CHECK(dv % 8 == 0 && rowsum.scalar_type() == at::kFloat && rowsum.numel() == (int64_t)B * H * L);
+  Tensor dos = torch::empty_like(dout);
+  Tensor delta = torch::empty({B, H, L}, rowsum.options());
+  mb::attn_bwd_prep(dout.data_ptr(), out.data_ptr(), rowsum.data_ptr<float>(), dos.data_ptr(), delta.data_ptr<float>(),
+                    B, L, H, dv, dtype_code(dout), stream());
+  return {dos, delta};
 }
 
 // ------------------------------------------------------------------ SequenceNorm pieces, dropout, CEMA coefficients
@@ -788,7 +829,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("b_mn"), py::arg("want_preact"), py::arg("out_dtype"), py::arg("mode"), py::arg("alpha"), py::arg("err"),
         py::arg("a_part_ptrs") = std::vector<int64_t>(), py::arg("a_first") = 0,
         py::arg("c_part_ptrs") = std::vector<int64_t>(), py::arg("accumulate") = false,
-        py::arg("b_gather_ptrs") = std::vector<int64_t>(), py::arg("b_gather_rank") = 0);
+        py::arg("b_gather_ptrs") = std::vector<int64_t>(), py::arg("b_gather_rank") = 0, py::arg("epi_kind") = 0,
+        py::arg("row_in") = py::none(), py::arg("row_in2") = py::none(), py::arg("row_out") = py::none(),
+        py::arg("aux") = py::none(), py::arg("causal_off") = 0);
   m.def("gemm_gather_supported", [](int64_t M, int64_t N, int64_t K, int64_t world) {
     return mb::gemm_gather_supported((int)M, (int)N, (int)K, (int)world);
   });
@@ -813,6 +856,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("ema_parameters_bwd", checked(&ema_parameters_bwd));
   m.def("attn_softmax_fwd", checked(&attn_softmax_fwd));
   m.def("attn_softmax_bwd", checked(&attn_softmax_bwd));
+  m.def("attn_bwd_prep", checked(&attn_bwd_prep));
   m.def("p2p_send", checked(&p2p_send));
   m.def("p2p_recv", checked(&p2p_recv));
   m.def("peer_barrier", checked(&peer_barrier));

@@ -883,16 +883,6 @@ void pick_split(int N, int& npt, int& nsplit) {
   } while (0)
 
 
-#define MB_DISPATCH_16BIT(dtype, ...)                         \
-  do {                                                        \
-    if ((dtype) == mb::kBF16) {                               \
-      using scalar_t = __nv_bfloat16;                         \
-      __VA_ARGS__;                                            \
-    } else {                                                  \
-      using scalar_t = __half;                                \
-      __VA_ARGS__;                                            \
-    }                                                         \
-  } while (0)
 
 #define CEMA_TILED_SWITCH(N, ...)                                      \
   do {                                                                 \

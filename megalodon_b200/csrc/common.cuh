@@ -161,6 +161,17 @@ __device__ __forceinline__ cfloat cadd(cfloat a, cfloat b) { return {a.re + b.re
     }                                                         \
   } while (0)
 
+#define MB_DISPATCH_16BIT(dtype, ...)                         \
+  do {                                                        \
+    if ((dtype) == mb::kBF16) {                               \
+      using scalar_t = __nv_bfloat16;                         \
+      __VA_ARGS__;                                            \
+    } else {                                                  \
+      using scalar_t = __half;                                \
+      __VA_ARGS__;                                            \
+    }                                                         \
+  } while (0)
+
 inline int div_up(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 }  // namespace mb

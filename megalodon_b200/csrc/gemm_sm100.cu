@@ -90,6 +90,19 @@ struct GemmParams {
   const void* g_src[kMaxPeers];
   void* g_dst;
   unsigned int* g_flags;
+  // Softmax of chunk-local attention fused into the epilogues of its products (fp32 row vectors indexed
+  // [batch, row]; column j of row i takes part iff j <= i + causal_off when mode == 1, always otherwise):
+  //   1 row max     nothing is stored; row_out[i] = max(row_out[i], alpha * acc[i, j])        (S = Q K^T, pass 1)
+  //   2 exp         C = exp(alpha * acc - row_in[i]) (0 where masked), row_out[i] += sum_j C  (S = Q K^T, pass 2)
+  //   3 row scale   C = alpha * acc / row_in[i]  (0 for an empty row)                         (O = P V)
+  //   4 dS          C = aux[i, j] / row_in[i] * (alpha * acc - row_in2[i])                    (dP = dO V^T -> dS)
+  // `aux` has the layout of C and may be C itself.
+  int epi;
+  const float* row_in;
+  const float* row_in2;
+  float* row_out;
+  const void* aux;
+  int causal_off;
 };
 
 struct TmapArray {
@@ -201,6 +214,73 @@ __device__ __forceinline__ void add_row32(const OutT* src, float (&v)[32], int n
   } else {
     for (int i = 0; i < nvalid; ++i) v[i] += to_f(src[i]);
   }
+}
+
+enum EpiMode : int { kEpiStd = 0, kEpiRowMax = 1, kEpiExp = 2, kEpiRowScale = 3, kEpiDS = 4 };
+
+__device__ __forceinline__ void atomic_max_float(float* addr, float v) {
+  if (v >= 0.f) atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+  else atomicMin(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+// Per-row state of the fused-softmax epilogues: one thread owns one output row of the tile.
+struct EpiRow {
+  float a, b, acc;       // a, b: row scalars read once per tile; acc: running max / sum over the tile
+};
+__device__ __forceinline__ void epi_row_begin(const GemmParams& p, long long ridx, bool row_ok, EpiRow& r) {
+  r.a = r.b = 0.f;
+  r.acc = p.epi == kEpiRowMax ? -INFINITY : 0.f;
+  if (!row_ok) return;
+  if (p.epi == kEpiExp) r.a = p.row_in[ridx];
+  else if (p.epi == kEpiRowScale || p.epi == kEpiDS) {
+    const float s = p.row_in[ridx];
+    r.a = s > 0.f ? 1.f / s : 0.f;
+    if (p.epi == kEpiDS) r.b = p.row_in2[ridx];
+  }
+}
+__device__ __forceinline__ void epi_row_end(const GemmParams& p, long long ridx, bool row_ok, const EpiRow& r) {
+  if (!row_ok) return;
+  if (p.epi == kEpiRowMax) { if (r.acc > -INFINITY) atomic_max_float(p.row_out + ridx, r.acc); }
+  else if (p.epi == kEpiExp) atomicAdd(p.row_out + ridx, r.acc);
+}
+// One 32-column chunk of row `row` (v = alpha * acc).  Returns false when the standard epilogue should run.
+template <typename OutT>
+__device__ __forceinline__ bool epi_chunk(const GemmParams& p, float (&v)[32], int row, int col0, int nvalid,
+                                          long long off, OutT* C, EpiRow& r) {
+  if (p.epi == kEpiStd) return false;
+  const int last = p.mode == 1 ? row + p.causal_off : 0x7fffffff;      // last column that takes part
+  if (p.epi == kEpiRowMax) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (i < nvalid && col0 + i <= last) r.acc = fmaxf(r.acc, v[i]);
+    return true;
+  }
+  if (p.epi == kEpiExp) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float e = (i < nvalid && col0 + i <= last) ? __expf(v[i] - r.a) : 0.f;
+      e = to_f(from_f<OutT>(e));                 // the sum is taken over the values as they are stored
+      r.acc += e;
+      v[i] = e;
+    }
+    store_row32<OutT>(C + off, v, nvalid);
+    return true;
+  }
+  if (p.epi == kEpiRowScale) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] *= r.a;
+    store_row32<OutT>(C + off, v, nvalid);
+    return true;
+  }
+  // kEpiDS
+  float pt[32];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) pt[i] = 0.f;
+  add_row32<OutT>(reinterpret_cast<const OutT*>(p.aux) + off, pt, nvalid);
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = (i < nvalid && col0 + i <= last) ? pt[i] * r.a * (v[i] - r.b) : 0.f;
+  store_row32<OutT>(C + off, v, nvalid);
+  return true;
 }
 
 template <int BN, bool A_MN, bool B_MN, typename OutT>
@@ -346,6 +426,9 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
       tcgen05_fence_after();
       const int row = m0 + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quarter * 32) << 16);
+      const long long ridx = (long long)tc.bz * p.M + row;
+      EpiRow er;
+      if (p.epi != kEpiStd) epi_row_begin(p, ridx, row < p.M, er);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -357,6 +440,12 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
         const int nvalid = min(32, p.N - col0);
+        if (p.epi != kEpiStd) {
+          if (row < p.M)
+            epi_chunk<OutT>(p, v, row, col0, nvalid, (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0,
+                            C, er);
+          continue;
+        }
         if (p.bias != nullptr) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -387,6 +476,7 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
           }
         }
       }
+      if (p.epi != kEpiStd) epi_row_end(p, ridx, row < p.M, er);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(tmem_empty + acc);
@@ -671,6 +761,9 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       tcgen05_fence_after();
       const int row = m0 + (int)rank * BM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * kPairBN + ((uint32_t)(quarter * 32) << 16);
+      const long long ridx = (long long)bz * p.M + row;
+      EpiRow er;
+      if (p.epi != kEpiStd) epi_row_begin(p, ridx, row < p.M, er);
 #pragma unroll 1
       for (int c = 0; c < kPairBN / 32; ++c) {
         uint32_t r[32];
@@ -682,6 +775,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
         const int nvalid = min(32, p.N - col0);
+        if (p.epi != kEpiStd) {
+          if (row < p.M)
+            epi_chunk<OutT>(p, v, row, col0, nvalid, (long long)bz * p.c_batch_stride + (long long)row * p.ldc + col0,
+                            C, er);
+          continue;
+        }
         if (p.bias != nullptr) {
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
@@ -711,6 +810,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
           }
         }
       }
+      if (p.epi != kEpiStd) epi_row_end(p, ridx, row < p.M, er);
       tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(tmem_empty + acc), 0));
@@ -842,7 +942,8 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       int act, int M, int N, int K, long long lda, long long ldb, long long ldc, bool a_mn,
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
-                      const GemmPeerSpec* peers, bool accumulate, const GemmGatherSpec* gather) {
+                      const GemmPeerSpec* peers, bool accumulate, const GemmGatherSpec* gather,
+                      const GemmSoftmaxSpec* softmax) {
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return 0;
   // TMA wants 16-byte strides; the vectorised epilogue wants 16-byte aligned rows of C
   if (lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return -1;
@@ -855,6 +956,13 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
   p.err = err; p.ldc = ldc; p.mode = mode; p.alpha = alpha; p.batch = batch; p.c_batch_stride = c_bs;
   p.a_parts = 1; p.a_part_k = K; p.a_first = 0; p.c_nparts = 1; p.c_part_cols = N;
   p.accumulate = accumulate ? 1 : 0;
+  if (softmax != nullptr && softmax->kind != 0) {
+    if (softmax->kind < 1 || softmax->kind > 4 || bias != nullptr || act != 0 || preact != nullptr || accumulate ||
+        peers != nullptr)
+      return -10;
+    p.epi = softmax->kind; p.row_in = softmax->row_in; p.row_in2 = softmax->row_in2; p.row_out = softmax->row_out;
+    p.aux = softmax->aux; p.causal_off = softmax->causal_off;
+  }
   bool ok = true;
   if (peers != nullptr && peers->a_parts > 1) {
     // gathered A: K-major pieces [M, K / parts] living on different GPUs

@@ -93,6 +93,21 @@ struct GemmGatherSpec {
   void* dst = nullptr;
   unsigned int* flags = nullptr;
 };
+// Softmax of chunk-local attention fused into the epilogues of its matrix products (no softmax kernel, the
+// logits never leave tensor memory in fp32).  Row vectors are fp32 [batch, M].  With mode == 1, column j of
+// row i takes part iff j <= i + causal_off.
+//   kind 1: row_out[i] = max(row_out[i], alpha acc[i, :])               nothing stored        (Q K^T, pass 1)
+//   kind 2: C = exp(alpha acc - row_in[i]), row_out[i] += sum_j C[i, j]                        (Q K^T, pass 2)
+//   kind 3: C = alpha acc / row_in[i]                                                         (P V)
+//   kind 4: C = aux / row_in[i] * (alpha acc - row_in2[i]); aux laid out like C, may be C      (dO V^T -> dS)
+struct GemmSoftmaxSpec {
+  int kind = 0;
+  const float* row_in = nullptr;
+  const float* row_in2 = nullptr;
+  float* row_out = nullptr;
+  const void* aux = nullptr;
+  int causal_off = 0;
+};
 bool gemm_gather_supported(int M, int N, int K, int world);
 int gemm_gather_flag_words(int N);
 int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const void* bias, int bias_dtype,
@@ -100,7 +115,7 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       bool b_mn, int mode, float alpha, int batch, long long a_bs, long long b_bs, long long c_bs,
                       int in_dtype, int out_dtype, int* err, int num_sms, cudaStream_t st,
                       const GemmPeerSpec* peers = nullptr, bool accumulate = false,
-                      const GemmGatherSpec* gather = nullptr);
+                      const GemmGatherSpec* gather = nullptr, const GemmSoftmaxSpec* softmax = nullptr);
 // ---- FFT long convolution (fftconv_kernels.cu); spectra are [rows, N2/2 + 1] complex, N2 = 1 << fftconv_logn(L)
 int fftconv_logn(int L);
 bool fftconv_supported(int L);          // L <= 8192
@@ -130,6 +145,9 @@ void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2,
                       cudaStream_t st);
 void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
                       int dtype, cudaStream_t st);
+// delta[b, h, l] = dO . O and dO' = dO / rowsum[b, h, l] over rows of dv values (dv a multiple of 8, 16-bit types)
+void attn_bwd_prep(const void* dout, const void* out, const float* rowsum, void* dos, float* delta, int B, int L,
+                   int H, int dv, int dtype, cudaStream_t st);
 
 // ---- SequenceNorm pieces and dropout (sequence_norm_kernels.cu)
 void time_sums(const void* u, const void* v, const bool* mask, float* s1, float* s2, int B, int L, int H,

@@ -78,11 +78,13 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
          a_mn: bool = False, b_mn: bool = False, want_preact: bool = False,
          out_dtype: Optional[torch.dtype] = None, out: Optional[Tensor] = None, mode: int = 0,
          alpha: float = 1.0, a_part_ptrs=None, a_first: int = 0, c_part_ptrs=None, accumulate: bool = False,
-         b_gather=None):
+         b_gather=None, softmax=None):
     """C = act(alpha * A B^T + bias), or with `accumulate` (needs `out`) C += alpha * A B^T + bias.
     `a_mn` / `b_mn`: operand is stored [K, rows].  `b_gather = (addresses of every rank's row block of
     B, this rank)`: B (a contiguous [N, K] matrix) is filled from those blocks by the kernel itself
-    while it computes (FSDP all-gather fused into the consuming GEMM).
+    while it computes (FSDP all-gather fused into the consuming GEMM).  `softmax = dict(epi_kind=..,
+    row_in=.., row_in2=.., row_out=.., aux=.., causal_off=..)`: one of the fused-softmax epilogues of the
+    attention products (csrc/kernels.h, GemmSoftmaxSpec); native path only.
     Operands may be 2-D or 3-D (batched) strided views with a contiguous last
     dim.  `mode` 1..3 exploits causal structure (see gemm_sm100.cu).  Returns
     (C, preact | None)."""
@@ -103,6 +105,8 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
         if rc != 0:
             raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
         return res, pre
+    if softmax and not native:
+        raise RuntimeError("fused-softmax epilogues need the tcgen05 backend and TMA-compatible operands")
     if not native:
         A = a.transpose(-1, -2) if a_mn else a
         Bm = b if b_mn else b.transpose(-1, -2)
@@ -122,7 +126,7 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
             res = out
         return res.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
     if (a.dim() == 2 and a.shape[0] <= 16 and not a_mn and not b_mn and mode == 0 and out is None
-            and not want_preact and not accumulate):
+            and not want_preact and not accumulate and not softmax):
         # a few rows (decoding): one pass over the weights on the CUDA cores beats a 128-row MMA tile
         _bump()
         res = _C().gemv_small_m(a, b, bias, 1 if act == "silu" else 0, _DT[out_dtype], alpha)
@@ -131,7 +135,7 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
     _bump()
     res, pre, rc = _C().gemm(a, b, out, bias, 1 if act == "silu" else 0, a_mn, b_mn, want_preact,
                              _DT[out_dtype], mode, alpha, _err_flag(a.device),
-                             accumulate=bool(accumulate and out is not None))
+                             accumulate=bool(accumulate and out is not None), **(softmax or {}))
     if rc != 0:
         raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
     return res, pre
@@ -583,51 +587,99 @@ def _attention_native_ok(q, k, v) -> bool:
 
 
 class _Attention(torch.autograd.Function):
+    """Chunk-local attention as matrix products on the tcgen05 GEMM (batched over heads).
+
+    Without DropKey and with square causal (or unmasked) scores the softmax lives in the GEMM
+    epilogues: Q K^T runs twice - the first pass keeps only the row maxima, the second writes
+    exp(s - max) in the activation dtype and accumulates the row sums - so the logits are never
+    rounded to 16 bits or written out in fp32, and P V divides by the row sum in its epilogue.
+    Backward: dV = P^T dO', dS comes out of the epilogue of dO V^T, then dQ and dK.  What is kept for
+    backward is the un-normalised P (16-bit), the row sums and the output.  With DropKey (or a key
+    cache longer than the query block) the scores go through the stand-alone softmax kernels."""
+
     @staticmethod
     def forward(ctx, q, k, v, scale, drop_p, causal):
         q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
         B, L1, H, dk = q.shape
         L2, dv = k.shape[1], v.shape[-1]
         square = causal and L1 == L2
+        fused = drop_p == 0.0 and (square or not causal) and _FUSED_SOFTMAX[0]
         ld = -(-L2 // 128) * 128                     # padded row length of the score buffer
         P = torch.empty(B, H, L1, ld, dtype=q.dtype, device=q.device)
         out = torch.empty(B, L1, H, dv, dtype=q.dtype, device=q.device)
-        seed = offset = 0
-        if drop_p > 0.0:
-            seed = int(torch.randint(0, 2 ** 62, (1,)).item())
-        for b in range(B):
-            Pb = P[b][:, :, :L2]
-            gemm(_heads_view(q, b), _heads_view(k, b), out=Pb, mode=1 if square else 0, alpha=scale)
-            _bump()
-            _C().attn_softmax_fwd(Pb, L1, L2, causal, drop_p, seed, offset + b)
-            gemm(Pb, _heads_view(v, b), b_mn=True, out=_heads_view(out, b), mode=2 if square else 0)
-        ctx.save_for_backward(q, k, v, P)
-        ctx.meta = (scale, causal, square, L2)
+        mode_s, mode_o = (1, 2) if square else (0, 0)
+        if fused:
+            rmax = torch.full((B, H, L1), float("-inf"), dtype=torch.float32, device=q.device)
+            rsum = torch.zeros((B, H, L1), dtype=torch.float32, device=q.device)
+            for b in range(B):
+                Pb, qb, kb = P[b][:, :, :L2], _heads_view(q, b), _heads_view(k, b)
+                gemm(qb, kb, out=Pb, mode=mode_s, alpha=scale, softmax=dict(epi_kind=1, row_out=rmax[b]))
+                gemm(qb, kb, out=Pb, mode=mode_s, alpha=scale,
+                     softmax=dict(epi_kind=2, row_in=rmax[b], row_out=rsum[b]))
+                gemm(Pb, _heads_view(v, b), b_mn=True, out=_heads_view(out, b), mode=mode_o,
+                     softmax=dict(epi_kind=3, row_in=rsum[b]))
+            ctx.save_for_backward(q, k, v, P, rsum, out)
+        else:
+            seed = offset = 0
+            if drop_p > 0.0:
+                seed = int(torch.randint(0, 2 ** 62, (1,)).item())
+            for b in range(B):
+                Pb = P[b][:, :, :L2]
+                gemm(_heads_view(q, b), _heads_view(k, b), out=Pb, mode=mode_s, alpha=scale)
+                _bump()
+                _C().attn_softmax_fwd(Pb, L1, L2, causal, drop_p, seed, offset + b)
+                gemm(Pb, _heads_view(v, b), b_mn=True, out=_heads_view(out, b), mode=mode_o)
+            ctx.save_for_backward(q, k, v, P)
+        ctx.meta = (scale, causal, square, L2, fused)
         return out
 
     @staticmethod
     def backward(ctx, dout):
-        q, k, v, P = ctx.saved_tensors
-        scale, causal, square, L2 = ctx.meta
+        scale, causal, square, L2, fused = ctx.meta
+        if fused:
+            q, k, v, P, rsum, out = ctx.saved_tensors
+        else:
+            q, k, v, P = ctx.saved_tensors
         dout = dout.contiguous()
         B, L1, H, dk = q.shape
         dq, dk_, dv_ = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        dP = torch.empty_like(P[0])
+        m1, m2, m3 = (1, 2, 3) if square else (0, 0, 0)
+        if fused:
+            # delta_i = dO_i . O_i (what sum_j P_ij dP_ij equals) and dO' = dO / rowsum, in one pass
+            _bump()
+            dos, delta = _C().attn_bwd_prep(dout, out, rsum)                                      # delta [B, H, L1]
+        else:
+            dP = torch.empty_like(P[0])
         for b in range(B):
             Pb = P[b][:, :, :L2]
-            dPb = dP[:, :, :L2]
-            dOb = _heads_view(dout, b)
-            # dV = P^T dO   (A = P stored [q, key] = [K, M]; B = dO stored [q, dv] = [K, N])
-            gemm(Pb, dOb, a_mn=True, b_mn=True, out=_heads_view(dv_, b), mode=3 if square else 0)
-            # dP = dO V^T
-            gemm(dOb, _heads_view(v, b), out=dPb, mode=1 if square else 0)
-            _bump()
-            _C().attn_softmax_bwd(Pb, dPb, L1, L2, causal)      # dP <- dS in place
+            if fused:
+                # dV = P~^T (dO / l); dS = P~ / l * (dO V^T - delta) written over P~; dQ, dK from dS
+                gemm(Pb, _heads_view(dos, b), a_mn=True, b_mn=True, out=_heads_view(dv_, b), mode=m3)
+                gemm(_heads_view(dout, b), _heads_view(v, b), out=Pb, mode=m1,
+                     softmax=dict(epi_kind=4, row_in=rsum[b], row_in2=delta[b], aux=Pb))
+                dSb = Pb
+            else:
+                dPb = dP[:, :, :L2]
+                dOb = _heads_view(dout, b)
+                # dV = P^T dO   (A = P stored [q, key] = [K, M]; B = dO stored [q, dv] = [K, N])
+                gemm(Pb, dOb, a_mn=True, b_mn=True, out=_heads_view(dv_, b), mode=m3)
+                # dP = dO V^T
+                gemm(dOb, _heads_view(v, b), out=dPb, mode=m1)
+                _bump()
+                _C().attn_softmax_bwd(Pb, dPb, L1, L2, causal)      # dP <- dS in place
+                dSb = dPb
             # dQ = scale dS K ; dK = scale dS^T Q
-            gemm(dPb, _heads_view(k, b), b_mn=True, out=_heads_view(dq, b), mode=2 if square else 0, alpha=scale)
-            gemm(dPb, _heads_view(q, b), a_mn=True, b_mn=True, out=_heads_view(dk_, b),
-                 mode=3 if square else 0, alpha=scale)
+            gemm(dSb, _heads_view(k, b), b_mn=True, out=_heads_view(dq, b), mode=m2, alpha=scale)
+            gemm(dSb, _heads_view(q, b), a_mn=True, b_mn=True, out=_heads_view(dk_, b), mode=m3, alpha=scale)
         return dq, dk_, dv_, None, None, None
+
+
+_FUSED_SOFTMAX = [True]
+
+
+def set_fused_attention_softmax(on: bool) -> None:
+    """Softmax inside the epilogues of the attention products (default) or the stand-alone kernels."""
+    _FUSED_SOFTMAX[0] = bool(on)
 
 
 def attention(q, k, v, scale, dropout, use_causal_mask, training):

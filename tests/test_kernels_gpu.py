@@ -308,6 +308,15 @@ def test_tiny_model_trains_on_gpu():
 def test_attention_matches_reference(B, L1, L2, H, dk, dv, causal):
     from megalodon_b200 import ops
     from megalodon_b200.ops import cuda_ops, reference
+    _attention_case(ops, cuda_ops, reference, B, L1, L2, H, dk, dv, causal)
+    cuda_ops.set_fused_attention_softmax(False)          # the stand-alone softmax kernels
+    try:
+        _attention_case(ops, cuda_ops, reference, B, L1, L2, H, dk, dv, causal)
+    finally:
+        cuda_ops.set_fused_attention_softmax(True)
+
+
+def _attention_case(ops, cuda_ops, reference, B, L1, L2, H, dk, dv, causal):
     torch.manual_seed(8)
     dev = _dev()
     q = (torch.randn(B, L1, H, dk, device=dev) * 0.3).bfloat16()
@@ -684,3 +693,33 @@ def test_gemm_that_gathers_its_weight_local_ranks(world, M, N, K):
     _close(pre, ref, 3e-2, 2e-2, "pre-activation")
     _close(y, torch.nn.functional.silu(ref), 3e-2, 2e-2, "silu")
     cuda_ops.check_kernel_errors()
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_attention_at_the_7b_shape(fused):
+    """One 4096-token chunk with the 7B head geometry (4 heads, d_qk 256, d_v 2048), causal: the fused
+    softmax epilogues (and the stand-alone softmax kernels) against fp32 PyTorch, forward and backward.
+    Logits are made large enough (|s| up to ~15) that a wrong row maximum would overflow or flush rows."""
+    from megalodon_b200.ops import cuda_ops, reference
+    torch.manual_seed(17)
+    dev = _dev()
+    B, L, H, dk, dv = 1, 4096, 4, 256, 2048
+    q = (torch.randn(B, L, H, dk, device=dev) * 0.25).bfloat16()
+    k = (torch.randn(B, L, H, dk, device=dev) * 0.25).bfloat16()
+    v = torch.randn(B, L, H, dv, device=dev).bfloat16()
+    g = torch.randn(B, L, H, dv, device=dev).bfloat16()
+    cuda_ops.set_fused_attention_softmax(fused)
+    try:
+        qq, kk, vv = (t.clone().requires_grad_() for t in (q, k, v))
+        o = cuda_ops.attention(qq, kk, vv, 1.0, 0.0, True, True)
+        o.backward(g)
+    finally:
+        cuda_ops.set_fused_attention_softmax(True)
+    cuda_ops.check_kernel_errors()
+    qr, kr, vr = (t.float().requires_grad_() for t in (q, k, v))
+    oref = reference.attention(qr, kr, vr, 1.0, 0.0, True, True)
+    oref.backward(g.float())
+    for name, a, b in (("o", o, oref), ("dq", qq.grad, qr.grad), ("dk", kk.grad, kr.grad), ("dv", vv.grad, vr.grad)):
+        rel = (a.float() - b).norm() / b.norm()
+        assert rel < 2e-2, f"{name}: relative error {rel:.4f}"
+        assert torch.isfinite(a.float()).all(), name
