@@ -7,8 +7,15 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         benchmarks/infer_bench.py --phase decode [--batches 1,4,16] [--gen-len 256]
 
-The two phases use different process-group layouts, so they are separate launches; the decode phase
-fills its cache by prefilling a short prompt (one full chunk plus a remainder) through the cache path.
+    # both: prefill with chunk parallelism over all N GPUs, hand weights and state over to a
+    # tensor-parallel layout over the same N GPUs (N may exceed the number of heads), decode there
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        benchmarks/infer_bench.py --phase both [--prompt-len 131072] [--batches 1,4,16] [--gen-len 256]
+
+`prefill` and `decode` alone use one process-group layout each; the decode phase then fills its cache by
+prefilling a short prompt (one full chunk plus a remainder) through the cache path.  `both` switches
+layouts inside the process: the tensor-parallel model receives the prefill model's weights (sliced on
+the GPU from its gathered buffers) and the prefill's final state re-sharded by features and heads.
 Random-init bf16 weights, uniform random prompt.  Timing: CUDA events after warm-up, max over ranks.
 Rank 0 prints one JSON line per phase.
 """
@@ -26,7 +33,7 @@ sys.path.insert(0, ROOT)
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--phase", choices=["prefill", "decode"], required=True)
+    ap.add_argument("--phase", choices=["prefill", "decode", "both"], required=True)
     ap.add_argument("--model", default="mega7B_32k")
     ap.add_argument("--layers", type=int, default=None, help="debug: fewer layers (not a valid result)")
     ap.add_argument("--prompt-len", type=int, default=None, help="prefill: total prompt tokens (default 16384 per GPU)")
@@ -71,7 +78,84 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
-    if args.phase == "prefill":
+    if args.phase == "both":
+        from megalodon_b200.decoding import DecodeSession
+        from megalodon_b200.parallel import destroy_model_parallel, get_model_parallel_rank
+        from megalodon_b200.parallel.chunk_parallel import set_handoff_transport
+        from megalodon_b200.reloading import shard_state_dict_for_model_parallel
+        from megalodon_b200.utils import expand_cache, reshard_cache
+        assert world > 1, "--phase both needs several GPUs"
+        # ---- phase 1: chunk-parallel prefill
+        initialize_model_parallel(1, world)
+        model = build_model(cfg, "bf16", reshard_after_forward=False, shard_over_chunk_group=True)
+        model.eval()
+        model._wrapped.seq_microbatch_chunks = 1
+        from megalodon_b200.parallel.symm import enable_peer_transport
+        enable_peer_transport(model, max_batch=1, n_slots=8, timeout_s=10.0)
+        P = args.prompt_len or 16384 * world
+        assert P % (world * cfg.chunk_size) == 0
+        toks = torch.randint(0, cfg.vocab_size, (1, P), generator=torch.Generator().manual_seed(0)).cuda()
+        with torch.no_grad():
+            logits, cache = model(toks, prefill=True)            # warm-up
+            del logits, cache
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            logits, cache = model(toks, prefill=True)
+            e1.record()
+            barrier()
+        prefill_ms = maxed(e0.elapsed_time(e1))
+        cuda_ops.check_kernel_errors()
+        first_tok = logits.argmax(-1, keepdim=True)               # [1, 1]
+        # ---- hand-over: weights sliced on the GPU, state re-sharded, process groups re-made
+        full_sd = model.gathered_state_dict()
+        destroy_model_parallel()
+        set_handoff_transport("nccl")
+        initialize_model_parallel(world, 1)
+        mp_rank = get_model_parallel_rank()
+        barrier()
+        t_switch = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t_switch[0].record()
+        decoder = build_model(cfg, "bf16", reshard_after_forward=False)
+        decoder.eval()
+        decoder.load_state_dict(shard_state_dict_for_model_parallel(full_sd, cfg.num_heads, mp_rank, world), strict=False)
+        state = reshard_cache(cache, mp_rank, world)
+        del model, full_sd, cache
+        torch.cuda.empty_cache()
+        t_switch[1].record()
+        barrier()
+        switch_ms = maxed(t_switch[0].elapsed_time(t_switch[1]))
+        # ---- phase 2: tensor-parallel decode from the prefilled state
+        results = {}
+        with torch.inference_mode():
+            for B in [int(b) for b in args.batches.split(",")]:
+                sess = DecodeSession(decoder, B, torch.bfloat16)
+                sess.load_cache(expand_cache(state, B))
+                tok = first_tok.expand(B, 1).contiguous()
+                for _ in range(8):
+                    tok = sess.step(tok).argmax(-1, keepdim=True)
+                barrier()
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                for _ in range(args.gen_len):
+                    tok = sess.step(tok).argmax(-1, keepdim=True)
+                e1.record()
+                barrier()
+                results[B] = maxed(e0.elapsed_time(e1) / args.gen_len)
+                del sess
+        cuda_ops.check_kernel_errors()
+        if rank == 0:
+            out = {"metric": "prefill tokens/s and decode ms/token", "value": P / (prefill_ms / 1e3), "unit": "tokens/s",
+                   "decode_ms_per_token": results, "layout_switch_ms": switch_ms, "n_gpus": world, "dtype": "bf16",
+                   "data": "synthetic",
+                   "config": {"model": f"{args.model} L{cfg.num_layers}", "prompt_len": P,
+                              "prefill": f"cp{world}, peer-memory hand-off", "decode": f"mp{world}"
+                              + (f" ({world // cfg.num_heads} ranks per head)" if world > cfg.num_heads else ""),
+                              "gen_len": args.gen_len, "sampling": "greedy", "chunk": cfg.chunk_size}}
+            if args.layers is not None:
+                out["invalid"] = "reduced depth (debug run)"
+            print(json.dumps(out))
+    elif args.phase == "prefill":
         if world > 1:
             initialize_model_parallel(1, world)
         model = build_model(cfg, "bf16", reshard_after_forward=False, shard_over_chunk_group=True)

@@ -37,6 +37,8 @@ class DecodeSession:
         self.model = model
         self.mega = _unwrap(model)
         m = self.mega
+        if hasattr(model, "materialize_views"):
+            model.materialize_views()         # the step calls sub-modules directly, not the FSDP wrapper
         self.B = batch_size
         self.dtype = dtype
         self.device = next(model.parameters()).device
@@ -47,7 +49,7 @@ class DecodeSession:
         self.use_graph = (self.device.type == "cuda" and not multi) if use_graph is None else use_graph
         c = m.chunk_size
         first = _unwrap(m.layers[0]).mega
-        H, dk, dv = first.local_heads, first.z_head_dim, first.v_head_dim
+        H, dk, dv = first.local_heads, first.z_head_dim, first.local_v_head_dim
         G = first.timenorm.groups_per_partition
         D, N = first.local_mdim, first.cema.ndim
         dev = self.device

@@ -152,7 +152,10 @@ class Mega(nn.Module):
                                        init_method=get_init_fn("gaussian", dim=self.model_dim))
         self.z_head_dim = cfg.z_dim // cfg.num_heads
         self.v_head_dim = cfg.value_dim // cfg.num_heads
-        self.local_heads = self.num_heads // get_model_parallel_world_size()
+        mp = get_model_parallel_world_size()
+        # more ranks than heads: one head per rank, its value columns split over mp / num_heads ranks
+        self.local_heads = max(1, self.num_heads // mp)
+        self.local_v_head_dim = self.v_head_dim // max(1, mp // self.num_heads)
         self.rope = RotaryEmbedding(self.z_head_dim, cfg.chunk_size, base=cfg.rope_base)
         self.layers = nn.ModuleList()
         for layer_id in range(self.num_layers):
@@ -303,7 +306,7 @@ class Mega(nn.Module):
         cache_layers = []
         for count, mean, var, hx in layer_states:
             kv = (torch.empty((bsz, 0, self.local_heads, self.z_head_dim), dtype=dt, device=x.device),
-                  torch.empty((bsz, 0, self.local_heads, self.v_head_dim), dtype=dt, device=x.device), 0)
+                  torch.empty((bsz, 0, self.local_heads, self.local_v_head_dim), dtype=dt, device=x.device), 0)
             cache_layers.append((kv, (count, mean, var), hx))
         return logits, (cache_layers, tuple(out_state))
 

@@ -145,7 +145,22 @@ class MovingAverageGatedAttention(nn.Module):
         self.z_head_dim = zdim // num_heads
         self.v_head_dim = hdim // num_heads
         world = get_model_parallel_world_size()
-        self.local_heads = divide_and_check_no_remainder(num_heads, world)
+        # Heads are the unit of tensor parallelism (reference: moving_average_gated_attention.py:181).
+        # With more ranks than heads (e.g. 8 ranks, 4 heads) one head is split over `head_split`
+        # consecutive ranks along d_v: each of them projects that head's shared q/k (replicated
+        # slice of wz, gamma, beta), its own slice of v and r, and attends with the full scores over
+        # its d_v / head_split value columns; wh2 sums the partial outputs as usual.  The reference
+        # cannot shard below one head per rank.  Inference only (see ColumnParallelLinear.partition).
+        self.head_split = 1
+        z_partition = None
+        if world > num_heads:
+            self.head_split = divide_and_check_no_remainder(world, num_heads)
+            self.local_heads = 1
+            from ..parallel.initialize import get_model_parallel_rank
+            z_partition = (get_model_parallel_rank() // self.head_split, num_heads)
+        else:
+            self.local_heads = divide_and_check_no_remainder(num_heads, world)
+        self.local_v_head_dim = divide_and_check_no_remainder(self.v_head_dim, self.head_split)
         self.local_mdim = divide_and_check_no_remainder(mdim, world)
         self.chunk_size = chunk_size
         self.efficient_attn = efficient_attn
@@ -163,14 +178,14 @@ class MovingAverageGatedAttention(nn.Module):
         self.wv = ColumnParallelLinear(mdim, hdim, bias=True, input_is_parallel=True,
                                        gather_output=False, init_method=init_fn, activation="silu")
         self.wz = ColumnParallelLinear(mdim, zdim, bias=True, input_is_parallel=False,
-                                       gather_output=False, init_method=init_fn)
+                                       gather_output=False, init_method=init_fn, partition=z_partition)
         self.wr = ColumnParallelLinear(mdim, hdim, bias=True, input_is_parallel=False,
                                        gather_output=False, init_method=init_fn, activation="silu")
         self.wh1 = ColumnParallelLinear(mdim, mdim, bias=True, input_is_parallel=False,
                                         gather_output=False, init_method=init_fn)
         self.wh2 = RowParallelLinear(hdim, mdim, bias=False, input_is_parallel=True,
                                      parallel_output=True, init_method=init_fn)
-        self.inner_attention = _InnerAttention(self.z_head_dim, self.v_head_dim, self.local_heads,
+        self.inner_attention = _InnerAttention(self.z_head_dim, self.local_v_head_dim, self.local_heads,
                                                chunk_size, attention_dropout, efficient_attn)
         self.gamma = Parameter(torch.zeros(2, self.z_head_dim * self.local_heads))
         self.beta = Parameter(torch.zeros(2, self.z_head_dim * self.local_heads))

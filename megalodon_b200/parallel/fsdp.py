@@ -829,6 +829,47 @@ class FullyShardedDataParallel(nn.Module):
         return sd
 
     @torch.no_grad()
+    def materialize_views(self) -> None:
+        """Gather every unit (if it is not current) and hand the wrapped modules plain views of the
+        parameters, without running a forward pass.  For code that calls sub-modules of the wrapped
+        model directly (the fixed-shape decode session) right after construction or loading."""
+        self._lazy_init()
+        for unit in self._units():
+            if unit._gather_event is not None:
+                torch.cuda.current_stream().wait_event(unit._gather_event)
+                unit._gather_event = None
+            if not unit._full_is_valid():
+                unit._gather_full()
+            if getattr(unit, "_fused_pending", None):
+                unit._pull_pending()
+            unit._set_views(unit._full)
+
+    @torch.no_grad()
+    def gathered_state_dict(self) -> "OrderedDict[str, torch.Tensor]":
+        """The compute-dtype parameters as they sit in the units' gathered buffers, under the wrapped
+        model's names (views, no copy, no communication).  Needs every unit's buffer to be resident
+        and current - i.e. a forward pass since the last optimiser step with
+        `reshard_after_forward=False`.  Used to hand the weights of one parallel layout to another
+        inside one process (chunk-parallel prefill, then tensor-parallel decode)."""
+        self._lazy_init()
+        sd: "OrderedDict[str, torch.Tensor]" = OrderedDict()
+        for prefix, unit in self._unit_prefixes():
+            if not unit._full_is_valid():
+                raise RuntimeError(f"unit {prefix or '<root>'} holds no current gathered parameters")
+            for info in unit._infos:
+                t = unit._full[info.offset:info.offset + info.numel].view(info.shape)
+                for _, _, name in info.owners:
+                    sd[f"{prefix}.{name}" if prefix else name] = t
+        for name, buf in self._wrapped.named_buffers():
+            owner = self._wrapped
+            parts = name.split(".")
+            for part in parts[:-1]:
+                owner = owner._modules[part]
+            if parts[-1] not in owner._non_persistent_buffers_set:
+                sd[_clean_name(name)] = buf.detach()
+        return sd
+
+    @torch.no_grad()
     def load_state_dict(self, state_dict: Dict[str, torch.Tensor], strict: bool = True):
         """Load a full state dict (every rank passes the same dict)."""
         self._lazy_init()

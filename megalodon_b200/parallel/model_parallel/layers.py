@@ -36,16 +36,22 @@ InitFn = Callable[[torch.Tensor], torch.Tensor]
 
 def _initialize_affine_weight(weight: torch.Tensor, out_features: int, in_features: int,
                               per_partition_size: int, partition_dim: int, init_method: InitFn,
-                              stride: int = 1, return_master_weight: bool = False) -> Optional[torch.Tensor]:
+                              stride: int = 1, return_master_weight: bool = False,
+                              partition: Optional[tuple] = None) -> Optional[torch.Tensor]:
+    """`partition = (index, count)`: slice number `index` of `count` instead of (rank, world) - several
+    ranks may then hold the same slice."""
     world = get_model_parallel_world_size()
-    if world == 1:
+    index = get_model_parallel_rank()
+    if partition is not None:
+        index, world = partition
+    if world == 1 and partition is None:
         init_method(weight)
         return weight if return_master_weight else None
     master = torch.empty(out_features, in_features, dtype=weight.dtype, device="cpu")
     init_method(master)
     block = divide_and_check_no_remainder(per_partition_size, stride)
     pieces = torch.split(master, block, dim=partition_dim)
-    mine = pieces[get_model_parallel_rank()::world]
+    mine = pieces[index::world]
     with torch.no_grad():
         weight.copy_(torch.cat(mine, dim=partition_dim))
     return master if return_master_weight else None
@@ -96,14 +102,22 @@ class ColumnParallelLinear(torch.nn.Module):
     def __init__(self, in_features: int, out_features: int, bias: bool = True,
                  input_is_parallel: bool = False, gather_output: bool = False,
                  init_method: InitFn = init.xavier_normal_, stride: int = 1,
-                 keep_master_weight_for_test: bool = False, activation: Optional[str] = None) -> None:
+                 keep_master_weight_for_test: bool = False, activation: Optional[str] = None,
+                 partition: Optional[tuple] = None) -> None:
+        """`partition = (index, count)`: this rank holds output slice `index` of `count` (count smaller
+        than the group: consecutive ranks hold the same slice and compute the same output).  Used
+        where a projection must be replicated over part of the group - the shared q/k projection when
+        one attention head is split over several ranks.  Forward only: in training the gradient of a
+        replicated slice would have to be summed over its replicas, which this layer does not do."""
         super().__init__()
         self.in_features = in_features
         self.out_features = out_features
         self.input_is_parallel = input_is_parallel
         self.gather_output = gather_output
         self.activation = activation
-        world = get_model_parallel_world_size()
+        self.partition = partition
+        world = get_model_parallel_world_size() if partition is None else partition[1]
+        assert partition is None or not gather_output, "a replicated partition cannot be gathered"
         self.output_size_per_partition = divide_and_check_no_remainder(out_features, world)
         self.weight = Parameter(torch.empty(self.output_size_per_partition, in_features))
         self.has_bias = bias
@@ -113,7 +127,7 @@ class ColumnParallelLinear(torch.nn.Module):
             self.register_parameter("bias", None)
         self.master_weight = _initialize_affine_weight(
             self.weight, out_features, in_features, self.output_size_per_partition, 0,
-            init_method, stride=stride, return_master_weight=keep_master_weight_for_test)
+            init_method, stride=stride, return_master_weight=keep_master_weight_for_test, partition=partition)
 
     def get_master_weight(self) -> torch.Tensor:
         return gather_from_model_parallel_region(self.weight.data.t()).t()

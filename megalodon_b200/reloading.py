@@ -195,6 +195,52 @@ def reload_model(checkpoint_dir: str, init_distributed: bool = True,
     return model, tokenizer, reloaded
 
 
+# ---------------------------------------------------------------------------- re-slicing for tensor parallelism
+def shard_state_dict_for_model_parallel(state: Dict[str, torch.Tensor], num_heads: int, mp_rank: int,
+                                        mp_size: int) -> Dict[str, torch.Tensor]:
+    """Slice a full (model_parallel_size = 1) state dict down to what tensor-parallel rank `mp_rank` of
+    `mp_size` holds, following how each layer partitions itself:
+
+      output features (rows)   wv, wr, wh1, fc1, fc3 (+ biases), TimestepNorm weight / bias / priors,
+                               CEMA parameters, the layer scale `nffn.alpha`
+      input features (columns) wh2, fc2, the vocabulary projection, the embedding table
+      by head                  wz (+ bias) rows and gamma / beta columns; with more ranks than heads
+                               each head's slice is replicated on the mp_size / num_heads ranks that
+                               share the head
+      replicated               RMSNorm and LayerNorm weights (they act on gathered features), rope
+
+    The reference can only load a consolidated checkpoint at the tensor-parallel size it was written
+    with (reloading.py:117-122); this makes an mp = 1 file usable at any size, including sizes above
+    the number of heads."""
+    if mp_size == 1:
+        return dict(state)
+
+    def cut(t: torch.Tensor, dim: int, index: int = mp_rank, count: int = mp_size) -> torch.Tensor:
+        n = t.size(dim) // count
+        assert n * count == t.size(dim), (tuple(t.shape), dim, count)
+        return t.narrow(dim, index * n, n).contiguous()
+
+    head_split = max(1, mp_size // num_heads)
+    by_head = (mp_rank // head_split, num_heads) if mp_size > num_heads else (mp_rank, mp_size)
+    out: Dict[str, torch.Tensor] = {}
+    for key, t in state.items():
+        leaf = key.rsplit(".", 2)[-2:] if key.count(".") else [key]
+        mod, name = (leaf[0], leaf[1]) if len(leaf) == 2 else ("", leaf[0])
+        if mod in ("rmsnorm", "norm", "rope") or t.dim() == 0:
+            out[key] = t
+        elif mod == "wz":
+            out[key] = cut(t, 0, *by_head)
+        elif name in ("gamma", "beta") and mod == "mega":
+            out[key] = cut(t, 1, *by_head)
+        elif mod in ("wv", "wr", "wh1", "fc1", "fc3", "timenorm", "final_norm", "cema") or key.endswith("nffn.alpha"):
+            out[key] = cut(t, 0)
+        elif mod in ("wh2", "fc2", "output", "embed"):
+            out[key] = cut(t, 1) if t.dim() == 2 else t
+        else:
+            raise KeyError(f"no tensor-parallel slicing rule for {key!r} of shape {tuple(t.shape)}")
+    return out
+
+
 # ---------------------------------------------------------------------------- writing
 def _write_config(ckpt_dir: Path, model_cfg: ModelConf, tokenizer_cfg: Optional[TokenizerConf],
                   extra: Optional[Dict[str, Any]] = None) -> None:

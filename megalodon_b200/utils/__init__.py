@@ -154,7 +154,8 @@ def init_cache(bsz: int, model, compute_dtype: torch.dtype, truncate: bool = Fal
     for _ in range(model.num_layers):
         kv = None if truncate else (
             torch.empty((bsz, 0, model.local_heads, model.z_head_dim), dtype=compute_dtype, device=device),
-            torch.empty((bsz, 0, model.local_heads, model.v_head_dim), dtype=compute_dtype, device=device),
+            torch.empty((bsz, 0, model.local_heads, getattr(model, "local_v_head_dim", model.v_head_dim)),
+                        dtype=compute_dtype, device=device),
             0,
         )
         layers.append((kv, (None, None, None), None))
@@ -172,14 +173,39 @@ def reshard_cache(cache, mp_rank: int, mp_size: int):
         n = t.size(dim) // mp_size
         return t.narrow(dim, mp_rank * n, n).contiguous()
 
+    def kv_part(k, v):
+        """k [B, len, H, dk], v [B, len, H, dv].  Up to one rank per head the heads are split; beyond
+        that each head's value columns are split over mp_size / H ranks and its keys are replicated."""
+        heads = k.size(2)
+        if mp_size <= heads:
+            return part(k, 2), part(v, 2)
+        split = mp_size // heads
+        h, s = mp_rank // split, mp_rank % split
+        dv = v.size(3) // split
+        return k.narrow(2, h, 1).contiguous(), v.narrow(2, h, 1).narrow(3, s * dv, dv).contiguous()
+
     layers, out_norm = cache
     new_layers = []
     for kv, (count, mean, var), hx in layers:
         if kv is not None:
-            kv = (part(kv[0], 2), part(kv[1], 2), kv[2])
+            kv = kv_part(kv[0], kv[1]) + (kv[2],)
         new_layers.append((kv, (count, part(mean, 1), part(var, 1)), None if hx is None else part(hx, 1)))
     count, mean, var = out_norm
     return new_layers, (count, part(mean, 1), part(var, 1))
+
+
+def expand_cache(cache, batch: int):
+    """Repeat a batch-1 cache `batch` times (the same prompt decoded in `batch` streams)."""
+    def rep(t):
+        return t if t is None or not torch.is_tensor(t) or t.size(0) == batch else \
+            t.expand(batch, *t.shape[1:]).contiguous()
+
+    layers, out_norm = cache
+    new_layers = []
+    for kv, norm, hx in layers:
+        kv = None if kv is None else (rep(kv[0]), rep(kv[1]), kv[2])
+        new_layers.append((kv, tuple(rep(t) for t in norm), rep(hx)))
+    return new_layers, tuple(rep(t) for t in out_norm)
 
 
 def truncate_cache(cache, truncated_cache):

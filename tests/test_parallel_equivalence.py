@@ -210,12 +210,21 @@ def _cache_case(rank, world, mp):
     return cache
 
 
-def test_reshard_cache_matches_a_tensor_parallel_cache():
+def test_more_tensor_parallel_ranks_than_heads():
+    """4 ranks on a 2-head model: each head's value columns are split over two ranks, its shared q/k
+    projection is replicated on them.  Decoding must match the single-rank model."""
+    single = run_ranks(_decode_case, 1, 1)[0]
+    for got in run_ranks(_decode_case, 4, 4):
+        assert torch.allclose(got, single, atol=2e-4, rtol=2e-4), (got - single).abs().max()
+
+
+@pytest.mark.parametrize("mp", [2, 4])
+def test_reshard_cache_matches_a_tensor_parallel_cache(mp):
     from megalodon_b200.utils import reshard_cache
     full = run_ranks(_cache_case, 1, 1)[0]
-    per_rank = run_ranks(_cache_case, 2, 2)
+    per_rank = run_ranks(_cache_case, mp, mp)
     for r, (layers, out_norm) in enumerate(per_rank):
-        exp_layers, exp_out = reshard_cache(full, r, 2)
+        exp_layers, exp_out = reshard_cache(full, r, mp)
         for (kv, norm, hx), (ekv, enorm, ehx) in zip(layers, exp_layers):
             assert kv[2] == ekv[2]
             for a, b in list(zip(kv[:2], ekv[:2])) + list(zip(norm, enorm)):
@@ -223,3 +232,89 @@ def test_reshard_cache_matches_a_tensor_parallel_cache():
             assert torch.allclose(torch.view_as_real(hx), torch.view_as_real(ehx), atol=1e-4, rtol=1e-4)
         for a, b in zip(out_norm, exp_out):
             assert torch.allclose(a.float(), b.float(), atol=1e-4, rtol=1e-4)
+
+
+def _state_case(rank, world, mp):
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.utils import set_random_seed
+    if world > 1:
+        initialize_model_parallel(mp, 1)
+    set_random_seed(77)
+    model = build_model(_tiny_cfg(rescale_nffn=True), "fp32", False, False)
+    # make the zero-initialised parameters distinguishable
+    with torch.no_grad():
+        g = torch.Generator().manual_seed(5)
+        sd = model.state_dict()
+    return {k: v.clone() for k, v in sd.items()}
+
+
+@pytest.mark.parametrize("mp", [2, 4])
+def test_full_state_dict_slices_to_any_tensor_parallel_size(mp):
+    """`shard_state_dict_for_model_parallel` of the single-rank model equals, key by key, what a
+    model built on `mp` tensor-parallel ranks from the same seed holds (4 ranks on 2 heads included)."""
+    from megalodon_b200.reloading import shard_state_dict_for_model_parallel
+    full = run_ranks(_state_case, 1, 1)[0]
+    per_rank = run_ranks(_state_case, mp, mp)
+    for r, sd in enumerate(per_rank):
+        want = shard_state_dict_for_model_parallel(full, 2, r, mp)
+        assert set(want) == set(sd), set(want) ^ set(sd)
+        for k in sd:
+            assert want[k].shape == sd[k].shape, (k, want[k].shape, sd[k].shape)
+            assert torch.equal(want[k], sd[k]), k
+
+
+def _switch_case(rank, world):
+    """Chunk-parallel prefill on `world` ranks, then tensor-parallel decode on the same ranks with the
+    weights and the state handed over inside the process (what `infer_bench.py --phase both` does)."""
+    from megalodon_b200.decoding import DecodeSession
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.parallel import (destroy_model_parallel, get_model_parallel_rank,
+                                         initialize_model_parallel)
+    from megalodon_b200.reloading import shard_state_dict_for_model_parallel
+    from megalodon_b200.utils import expand_cache, init_cache, reshard_cache, set_random_seed
+    cfg = _tiny_cfg()
+    B, c = 1, cfg.chunk_size
+    prompt = torch.randint(0, cfg.vocab_size, (B, 4 * c), generator=torch.Generator().manual_seed(11))
+    outs = []
+    with torch.no_grad():
+        if world == 1:
+            set_random_seed(1234)
+            model = build_model(cfg, "fp32", False, False)
+            model.eval()
+            cache = init_cache(B, model._wrapped, torch.float32, device=torch.device("cpu"))
+            for s in range(0, 4 * c, 2 * c):
+                full, cache = model(prompt[:, s:s + 2 * c], cache=cache)
+            logits = full[:, -1]
+            decoder, state = model, cache
+        else:
+            initialize_model_parallel(1, world)
+            set_random_seed(1234)
+            model = build_model(cfg, "fp32", False, False, shard_over_chunk_group=True)
+            model.eval()
+            logits, cache = model(prompt, prefill=True)
+            full_sd = {k: v.clone() for k, v in model.gathered_state_dict().items()}
+            destroy_model_parallel()
+            initialize_model_parallel(world, 1)
+            set_random_seed(999)                               # the decoder's own initialisation must not matter
+            decoder = build_model(cfg, "fp32", False, False)
+            decoder.eval()
+            r = get_model_parallel_rank()
+            decoder.load_state_dict(shard_state_dict_for_model_parallel(full_sd, cfg.num_heads, r, world), strict=False)
+            state = reshard_cache(cache, r, world)
+        outs.append(logits.clone())
+        sess = DecodeSession(decoder, 2, torch.float32, use_graph=False)
+        sess.load_cache(expand_cache(state, 2))
+        tok = logits.argmax(-1).expand(2)
+        for _ in range(6):
+            lg = sess.step(tok)
+            outs.append(lg[:1].clone())
+            tok = lg.argmax(-1)
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_prefill_layout_hands_over_to_decode_layout(world):
+    single = run_ranks(_switch_case, 1)[0]
+    for got in run_ranks(_switch_case, world):
+        assert torch.allclose(got, single, atol=3e-4, rtol=3e-4), (got - single).abs().max()
