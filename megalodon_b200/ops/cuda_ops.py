@@ -603,7 +603,8 @@ class _Attention(torch.autograd.Function):
         B, L1, H, dk = q.shape
         L2, dv = k.shape[1], v.shape[-1]
         square = causal and L1 == L2
-        fused = drop_p == 0.0 and (square or not causal) and _FUSED_SOFTMAX[0]
+        # (key counts that are not a multiple of 8 leave the tensor-core path, see `gemm`)
+        fused = drop_p == 0.0 and (square or not causal) and _FUSED_SOFTMAX[0] and L2 % 8 == 0
         ld = -(-L2 // 128) * 128                     # padded row length of the score buffer
         P = torch.empty(B, H, L1, ld, dtype=q.dtype, device=q.device)
         out = torch.empty(B, L1, H, dv, dtype=q.dtype, device=q.device)
