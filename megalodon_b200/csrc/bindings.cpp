@@ -475,23 +475,38 @@ OptTensor gemv_small_m(const Tensor& x, const Tensor& w, const OptTensor& bias, 
 
 // ------------------------------------------------------------------ FFT long convolution
 // x [..., L] contiguous -> half spectrum [..., N2/2 + 1, 2] (fp32 pairs) of the zero-padded row
-Tensor rfft_rows(const Tensor& x, bool flip) {
+Tensor rfft_rows(const Tensor& x, bool flip, int64_t packed) {
   check_cuda_contig(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int L = x.size(-1);
-  TORCH_CHECK(mb::fftconv_supported(L), "rfft: length > 8192 is not supported by the native kernel");
+  TORCH_CHECK(mb::fftconv_supported(L), "rfft: length > 16384 is not supported by the native kernel");
   const long long rows = x.numel() / L;
   const int bins = (1 << mb::fftconv_logn(L)) / 2 + 1;
   auto shape = x.sizes().vec();
   shape.back() = bins;
   shape.push_back(2);
   Tensor out = torch::empty(shape, x.options().dtype(at::kFloat));
-  mb::rfft_rows(x.data_ptr(), out.data_ptr<float>(), rows, L, flip, dtype_code(x), stream());
+  mb::rfft_rows(x.data_ptr(), out.data_ptr<float>(), rows, L, flip, dtype_code(x), stream(), (int)packed);
+  return out;
+}
+
+// spec [..., N2/2 + 1, 2] fp32 -> first L samples of the inverse real transform, [..., L] fp32
+Tensor irfft_rows(const Tensor& spec, int64_t L, int64_t packed) {
+  check_cuda_contig(spec, "spec");
+  c10::cuda::CUDAGuard guard(spec.device());
+  TORCH_CHECK(mb::fftconv_supported((int)L) && spec.scalar_type() == at::kFloat && spec.dim() >= 2 && spec.size(-1) == 2);
+  const int bins = (1 << mb::fftconv_logn((int)L)) / 2 + 1;
+  TORCH_CHECK(spec.size(-2) == bins, "spectrum must have N2/2 + 1 bins for this length");
+  auto shape = spec.sizes().vec();
+  shape.pop_back();
+  shape.back() = L;
+  Tensor out = torch::empty(shape, spec.options());
+  mb::irfft_rows(spec.data_ptr<float>(), out.data_ptr<float>(), out.numel() / L, (int)L, stream(), (int)packed);
   return out;
 }
 
 // x [B, D, L], kf [D, N2/2 + 1, 2] -> y [B, D, L] = irfft(rfft(x) * kf (or conj kf))[:L]
-Tensor fftconv_apply(const Tensor& x, const Tensor& kf, bool conj_k) {
+Tensor fftconv_apply(const Tensor& x, const Tensor& kf, bool conj_k, int64_t packed) {
   check_cuda_contig(x, "x");
   check_cuda_contig(kf, "kf");
   c10::cuda::CUDAGuard guard(x.device());
@@ -500,7 +515,7 @@ Tensor fftconv_apply(const Tensor& x, const Tensor& kf, bool conj_k) {
   TORCH_CHECK(mb::fftconv_supported(L) && kf.scalar_type() == at::kFloat && kf.numel() == (long long)D * bins * 2);
   Tensor y = torch::empty_like(x);
   mb::fftconv_rows(x.data_ptr(), kf.data_ptr<float>(), y.data_ptr(), x.numel() / L, L, D, conj_k, dtype_code(x),
-                   stream());
+                   stream(), (int)packed);
   return y;
 }
 
@@ -510,7 +525,7 @@ Tensor fftconv_dk(const Tensor& dy, const Tensor& x) {
   check_cuda_contig(x, "x");
   c10::cuda::CUDAGuard guard(x.device());
   const int L = x.size(-1), D = x.size(-2);
-  TORCH_CHECK(mb::fftconv_supported(L) && dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type());
+  TORCH_CHECK(mb::fftconv_logn(L) <= 14 && dy.sizes() == x.sizes() && dy.scalar_type() == x.scalar_type());
   const int bins = (1 << mb::fftconv_logn(L)) / 2 + 1;
   Tensor acc = torch::zeros({D, bins, 2}, x.options().dtype(at::kFloat));
   Tensor dk = torch::empty({D, L}, x.options().dtype(at::kFloat));
@@ -836,8 +851,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
     return mb::gemm_gather_supported((int)M, (int)N, (int)K, (int)world);
   });
   m.def("gemv_small_m", checked(&gemv_small_m));
-  m.def("rfft_rows", checked(&rfft_rows));
-  m.def("fftconv_apply", checked(&fftconv_apply));
+  m.def("rfft_rows", checked(&rfft_rows), py::arg("x"), py::arg("flip"), py::arg("packed") = -1);
+  m.def("irfft_rows", checked(&irfft_rows), py::arg("spec"), py::arg("L"), py::arg("packed") = -1);
+  m.def("fftconv_apply", checked(&fftconv_apply), py::arg("x"), py::arg("kf"), py::arg("conj_k"), py::arg("packed") = -1);
   m.def("fftconv_dk", checked(&fftconv_dk));
   m.def("reduce_slots", checked(&reduce_slots));
   m.def("reduce_scatter_sumsq", checked(&reduce_scatter_sumsq), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),

@@ -118,10 +118,14 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
                       const GemmGatherSpec* gather = nullptr, const GemmSoftmaxSpec* softmax = nullptr);
 // ---- FFT long convolution (fftconv_kernels.cu); spectra are [rows, N2/2 + 1] complex, N2 = 1 << fftconv_logn(L)
 int fftconv_logn(int L);
-bool fftconv_supported(int L);          // L <= 8192
-void rfft_rows(const void* x, float* out_spec, long long rows, int L, bool flip, int dtype, cudaStream_t st);
+bool fftconv_supported(int L);          // L <= 16384
+// `packed`: -1 choose (packed half-size transform above 8192 samples), 0 plain, 1 packed
+void rfft_rows(const void* x, float* out_spec, long long rows, int L, bool flip, int dtype, cudaStream_t st,
+               int packed = -1);
+void irfft_rows(const float* spec, float* out, long long rows, int L, cudaStream_t st, int packed = -1);
 void fftconv_rows(const void* x, const float* kf, void* y, long long rows, int L, int D, bool conj_k, int dtype,
-                  cudaStream_t st);
+                  cudaStream_t st, int packed = -1);
+// the gradient w.r.t. the kernel in one pass; rows of at most 8192 samples (longer: rfft_rows + irfft_rows)
 void fftconv_dk(const void* dy, const void* x, float* acc_spec, float* dk, long long rows, int L, int D, int dtype,
                 cudaStream_t st);
 // y = act(alpha x w^T + bias) for M <= 16 rows of x (gemv_kernels.cu); false if the shapes do not qualify

@@ -543,13 +543,23 @@ class _FFTConv(torch.autograd.Function):
             _bump()
             dx = _C().fftconv_apply(dyc, kf, True)
         if ctx.needs_input_grad[1]:
-            _bump(2)
-            dk = _C().fftconv_dk(dyc, xc).to(ctx.k_dtype)
+            L = xc.shape[-1]
+            if L <= 8192:
+                _bump(2)
+                dk = _C().fftconv_dk(dyc, xc).to(ctx.k_dtype)
+            else:
+                # rows too long for one full-size transform in shared memory: two packed transforms per
+                # row, the product summed over the batch, one packed inverse per feature
+                _bump(3)
+                gy = torch.view_as_complex(_C().rfft_rows(dyc, False))
+                xs = torch.view_as_complex(_C().rfft_rows(xc, False))
+                acc = torch.view_as_real((gy * xs.conj()).sum(0)).contiguous()
+                dk = _C().irfft_rows(acc, L).to(ctx.k_dtype)
         return dx, dk
 
 
 def _fft_native_ok(x, L) -> bool:
-    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and 1 <= L <= 8192
+    return x.is_cuda and x.dtype in (torch.float32, torch.bfloat16, torch.float16) and 1 <= L <= 16384
 
 
 def fftconv(x, k):

@@ -493,7 +493,7 @@ def test_small_m_linear(M, N, K, act):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("B,D,L", [(2, 8, 37), (1, 16, 300), (2, 4, 4096)])
+@pytest.mark.parametrize("B,D,L", [(2, 8, 37), (1, 16, 300), (2, 4, 4096), (2, 4, 8192), (1, 4, 12000), (2, 3, 16384)])
 def test_fftconv_native(dtype, B, D, L):
     """Shared-memory FFT convolution (forward and both gradients) and rfft against torch.fft."""
     from megalodon_b200 import ops
@@ -518,6 +518,36 @@ def test_fftconv_native(dtype, B, D, L):
         f0 = torch.view_as_real(ops.rfft(x, flip))
         f1 = torch.view_as_real(reference.rfft(x, flip))
         _close(f0, f1, 5e-3 * max(1.0, f1.abs().max().item()), 2e-3, f"rfft flip={flip}")
+
+
+@pytest.mark.parametrize("L", [33, 500, 4096])
+def test_packed_real_transforms_match_the_plain_ones(L):
+    """The half-size (packed) transforms that rows above 8192 samples need, forced on short rows and
+    compared with the full-size kernels and with torch.fft."""
+    from megalodon_b200.ops._ext import require
+    ext = require()
+    torch.manual_seed(18)
+    dev = _dev()
+    x = torch.randn(3, 5, L, device=dev)
+    k = torch.randn(5, L, device=dev) * torch.exp(-torch.arange(L, device=dev) / 40.0)
+    for flip in (False, True):
+        plain = ext.rfft_rows(x, flip, 0)
+        packed = ext.rfft_rows(x, flip, 1)
+        scale = plain.abs().max().item()
+        assert (plain - packed).abs().max().item() < 2e-5 * scale * math.log2(L + 2)
+    kf = ext.rfft_rows(k, False, 0)
+    n2 = 2 * (kf.shape[-2] - 1)
+    want = torch.fft.irfft(torch.fft.rfft(x, n=n2) * torch.fft.rfft(k, n=n2), n=n2)[..., :L]
+    for conj in (False, True):
+        y0 = ext.fftconv_apply(x, kf, conj, 0)
+        y1 = ext.fftconv_apply(x, kf, conj, 1)
+        assert (y0 - y1).abs().max().item() < 1e-4 * max(1.0, y0.abs().max().item())
+        if not conj:
+            assert (y1 - want).abs().max().item() < 1e-3 * max(1.0, want.abs().max().item())
+    spec = ext.rfft_rows(x, False, 0)
+    back0 = ext.irfft_rows(spec, L, 0)
+    back1 = ext.irfft_rows(spec, L, 1)
+    assert (back0 - x).abs().max().item() < 1e-4 and (back1 - x).abs().max().item() < 1e-4
 
 
 def test_reduce_scatter_adamw_kernel_two_local_ranks():
