@@ -820,9 +820,11 @@ auto checked(R (*fn)(A...)) {
 }
 
 void register_cpu_ops(pybind11::module& m);      // cpu_ops.cpp
+void register_cpu_bwd_ops(pybind11::module& m);  // cpu_ops_bwd.cpp
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_cpu_ops(m);
+  register_cpu_bwd_ops(m);
   m.def("rms_norm_fwd", checked(&rms_norm_fwd));
   m.def("rms_norm_bwd", checked(&rms_norm_bwd));
   m.def("layer_norm_fwd", checked(&layer_norm_fwd));

@@ -12,7 +12,7 @@ CSRC = os.path.join("megalodon_b200", "csrc")
 
 
 def sources():
-    out = [os.path.join(CSRC, "bindings.cpp"), os.path.join(CSRC, "cpu_ops.cpp")]
+    out = [os.path.join(CSRC, "bindings.cpp"), os.path.join(CSRC, "cpu_ops.cpp"), os.path.join(CSRC, "cpu_ops_bwd.cpp")]
     for name in sorted(os.listdir(os.path.join(ROOT, CSRC))):
         if name.endswith(".cu"):
             out.append(os.path.join(CSRC, name))

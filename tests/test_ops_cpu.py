@@ -95,3 +95,98 @@ def test_cpu_ema_parameters_and_hidden_forward(with_h):
     if b0 is not None:
         assert torch.allclose(b0, b1, atol=1e-5, rtol=1e-5)
     assert torch.allclose(torch.view_as_real(h0), torch.view_as_real(h1), atol=1e-5, rtol=1e-5)
+
+
+# ---------------------------------------------------------------------------- C++ backward passes
+def _c():
+    return _ext.require()
+
+
+@needs_ext
+@pytest.mark.parametrize("B,L,H,G,masked", [(2, 70, 64, 8, True), (1, 5, 32, 32, False), (3, 33, 48, 4, False)])
+def test_cpu_timestep_norm_backward(B, L, H, G, masked):
+    torch.manual_seed(3)
+    x = torch.randn(B, L, H)
+    cnt = torch.randint(0, 5, (B,))
+    cnt[0] = 0
+    pm, pv = torch.randn(B, G) * 0.1, torch.rand(B, G) + 0.5
+    gm, bt = torch.randn(H) * 0.1, torch.randn(H) * 0.1
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool)
+        mask[-1, L - 7:] = True
+        mask[0, 2] = True
+    gy, gmean, gvar = torch.randn(B, L, H), torch.randn(B, G), torch.randn(B, G)
+    leaves = [t.clone().requires_grad_() for t in (x, pm, pv, gm, bt)]
+    y, _, m, v = reference.timestep_norm(leaves[0], cnt, leaves[1], leaves[2], leaves[3], leaves[4], mask, G, 1e-5, 1.0)
+    ((y * gy).sum() + (m * gmean).sum() + (v * gvar).sum()).backward()
+    got = _c().cpu_timestep_norm_bwd(gy, gmean, gvar, x, cnt, pm, pv, gm, 1.0, mask, G, 1e-5)
+    for name, a, b in zip(["dx", "dprev_mean", "dprev_var", "dgamma", "dbeta"], got, [t.grad for t in leaves]):
+        assert torch.allclose(a.double(), b.double(), atol=2e-4, rtol=2e-4), (name, (a - b).abs().max())
+
+
+@needs_ext
+@pytest.mark.parametrize("G,length_last,masked", [(0, False, True), (0, True, False), (4, False, False), (8, True, True)])
+def test_cpu_sequence_norm_backward(G, length_last, masked):
+    torch.manual_seed(4)
+    B, L, H = 3, 41, 32
+    x = torch.randn(B, L, H) * 2 + 0.5
+    if length_last:
+        x = x.transpose(1, 2).contiguous()
+    gm, bt = torch.randn(H) * 0.3 + 1, torch.randn(H) * 0.3
+    mask = None
+    if masked:
+        mask = torch.zeros(B, L, dtype=torch.bool)
+        mask[1, L - 9:] = True
+    gy = torch.randn_like(x)
+    leaves = [t.clone().requires_grad_() for t in (x, gm, bt)]
+    y = reference.sequence_norm(leaves[0], leaves[1], leaves[2], mask, G or None, 1e-5, length_last)
+    (y * gy).sum().backward()
+    got = _c().cpu_sequence_norm_bwd(gy, x, gm, mask, G, 1e-5, length_last)
+    for name, a, b in zip(["dx", "dgamma", "dbeta"], got, [t.grad for t in leaves]):
+        assert torch.allclose(a.double(), b.double(), atol=2e-4, rtol=2e-4), (name, (a - b).abs().max())
+
+
+def _ema_coeffs(D, N):
+    alpha, delta = torch.rand(D, N) * 0.5 + 0.1, torch.rand(D, N) * 0.5 + 0.1
+    q = torch.polar(1 - alpha * delta, torch.rand(D, N) * 3)
+    gamma = torch.view_as_complex(torch.randn(D, N, 2)) * 0.25
+    return alpha, q, gamma
+
+
+@needs_ext
+@pytest.mark.parametrize("with_h", [True, False])
+def test_cpu_ema_parameters_backward(with_h):
+    torch.manual_seed(5)
+    B, D, N, L = 2, 6, 4, 29
+    p, q, gamma = _ema_coeffs(D, N)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2)) if with_h else None
+    dk, db = torch.randn(D, L), torch.randn(B, D, L)
+    leaves = [t.clone().requires_grad_() for t in (p, q, gamma)] + ([hx.clone().requires_grad_()] if with_h else [])
+    k, b = reference.ema_parameters(leaves[0], leaves[1], leaves[2], leaves[3] if with_h else None, L)
+    loss = (k * dk).sum() + ((b * db).sum() if with_h else 0.0)
+    loss.backward()
+    got = _c().cpu_ema_parameters_bwd(dk, db if with_h else None, p, q, gamma, hx)
+    for name, a, b_ in zip(["dp", "dq", "dgamma", "dh"], got, [t.grad for t in leaves]):
+        a2 = torch.view_as_real(a) if a.is_complex() else a
+        b2 = torch.view_as_real(b_) if b_.is_complex() else b_
+        assert torch.allclose(a2.double(), b2.double(), atol=2e-4, rtol=2e-4), (name, (a2 - b2).abs().max())
+
+
+@needs_ext
+@pytest.mark.parametrize("with_h", [True, False])
+def test_cpu_ema_hidden_backward(with_h):
+    torch.manual_seed(6)
+    B, D, N, L = 2, 5, 4, 23
+    p, q, _ = _ema_coeffs(D, N)
+    x = torch.randn(B, D, L)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2)) if with_h else None
+    g = torch.view_as_complex(torch.randn(B, D, N, 2))
+    leaves = [t.clone().requires_grad_() for t in (x, p, q)] + ([hx.clone().requires_grad_()] if with_h else [])
+    h = reference.ema_hidden(leaves[0], leaves[1], leaves[2], leaves[3] if with_h else None)
+    h.backward(g)
+    got = _c().cpu_ema_hidden_bwd(g, x, p, q, hx)
+    for name, a, b_ in zip(["dx", "dp", "dq", "dh"], got, [t.grad for t in leaves]):
+        a2 = torch.view_as_real(a) if a.is_complex() else a
+        b2 = torch.view_as_real(b_) if b_.is_complex() else b_
+        assert torch.allclose(a2.double(), b2.double(), atol=2e-4, rtol=2e-4), (name, (a2 - b2).abs().max())
