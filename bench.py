@@ -53,6 +53,10 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="override depth (debugging only; marks the run invalid)")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_1cta", "cublas"])
     ap.add_argument("--no-ckpt", action="store_true")
+    ap.add_argument("--composition", default="fused", choices=["fused", "library"],
+                    help="library: the same model and step as a composition of library calls inside this framework "
+                         "(cuBLAS products, materialised matmul + softmax attention, NCCL hand-off / all-gather / "
+                         "reduce-scatter) - a context number for the fused paths, NOT the reference")
     ap.add_argument("--step-timeout-s", type=float, default=150.0,
                     help="a rank whose host makes no step progress for this long dumps its Python stacks and the "
                          "device's abort record to stderr and exits non-zero (the launcher then stops the others)")
@@ -215,10 +219,15 @@ def main():
         initialize_model_parallel(1, world)
     if args.gemm:
         cuda_ops.set_gemm_backend(args.gemm)
+    library = args.composition == "library"
+    if library:
+        cuda_ops.set_gemm_backend("cublas")
 
     cfg = dataclasses.replace(ModelStore[args.model])
     if args.layers is not None:
         cfg.num_layers = args.layers
+    if library:
+        cfg.efficient_attn = None             # matmul + softmax with the scores written out
     local_len = args.seq_len // world
     chunks_local = local_len // cfg.chunk_size
     # One GPU holds the whole 32K sequence only with layer checkpointing.  Activations cost about 1 GB
@@ -236,12 +245,17 @@ def main():
         # peaks at 139 GB allocated (148 GB reserved).  Ten checkpointed layers (170 GB reserved) ran into
         # allocator retries and was slower.
         cfg.ckpt_layers = 16
+    if library and cfg.layerwise_ckpt and args.ckpt_layers is None:
+        # the materialised fp32 scores add about 3 GB per un-checkpointed layer and 32K tokens
+        cfg.ckpt_layers = 32 if chunks_local == 8 else 24
     set_random_seed(1234)
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)
     model._wrapped.seq_microbatch_chunks = 1
     model.defer_grad_clip = True      # clipping coefficient is applied inside the fused AdamW kernel
-    if world > 1:
+    if world > 1 and library:
+        mailbox, abort_record = None, None    # NCCL send / recv, all-gather and reduce-scatter
+    elif world > 1:
         # CEMA / TimestepNorm state goes from rank to rank through peer memory, not NCCL send/recv
         from megalodon_b200.parallel.symm import enable_peer_transport
         from megalodon_b200.parallel.symm import AbortRecord
@@ -276,7 +290,7 @@ def main():
     def check_peers():
         # a bounded device-side wait that ran out shows up here instead of slowing every later step
         cuda_ops.check_kernel_errors()
-        if world > 1:
+        if abort_record is not None:
             abort_record.check()
 
     def peers_ok_so_far():
@@ -398,13 +412,14 @@ def main():
             "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": dev_ms / args.steps, "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "impl": "ours",
+            "impl": "ours" if not library else "library-composition (cuBLAS + NCCL + materialised attention in this framework; not the reference)",
             "config": {
                 "model": f"{args.model} (L{cfg.num_layers} D{cfg.model_dim} H{cfg.num_heads} z{cfg.z_dim} "
                          f"v{cfg.value_dim} ffn{cfg.ffn_hidden_dim} swiglu N{cfg.cema_ndim} chunk{cfg.chunk_size} "
                          f"V{cfg.vocab_size}), {n_params / 1e9:.2f}B params",
                 "global_batch": 1, "seq_len": args.seq_len,
-                "parallelism": f"cp{world}" + ("+zero3_over_cp+p2p_handoff" if world > 1 else ""),
+                "parallelism": f"cp{world}" + (("+zero3_over_cp+nccl" if library else "+zero3_over_cp+p2p_handoff+gathering_gemm")
+                                               if world > 1 else ""),
                 "activation_checkpointing": (False if not cfg.layerwise_ckpt else
                                              ("all layers" if cfg.ckpt_layers is None else f"first {cfg.ckpt_layers} layers")),
                 "optimizer": "AdamW fp32 master+moments, clip 1.0",
