@@ -687,15 +687,15 @@ void p2p_send(const Tensor& src, int64_t remote_dst, int64_t nbytes, int64_t rem
 }
 
 void p2p_recv(Tensor& dst, int64_t local_slot, int64_t nbytes, int64_t local_flag, int64_t seq, int64_t remote_ack,
-              Tensor& counter, int64_t timeout_ns, Tensor& abort, int64_t rank, int64_t dir) {
+              Tensor& counter, int64_t timeout_ns, Tensor& abort, int64_t rank, int64_t dir, bool poison) {
   check_cuda_contig(dst, "dst");
   c10::cuda::CUDAGuard guard(dst.device());
   TORCH_CHECK(nbytes % 16 == 0 && nbytes <= (int64_t)(dst.numel() * dst.element_size()));
   TORCH_CHECK(reinterpret_cast<uintptr_t>(dst.data_ptr()) % 16 == 0 && local_slot % 16 == 0);
-  mb::p2p_recv(dst.data_ptr(), reinterpret_cast<const void*>(local_slot), nbytes,
+  mb::p2p_recv(dst.data_ptr(), reinterpret_cast<void*>(local_slot), nbytes,
                reinterpret_cast<const unsigned int*>(local_flag), (unsigned int)seq,
                reinterpret_cast<unsigned int*>(remote_ack), reinterpret_cast<unsigned int*>(counter.data_ptr<int>()),
-               (unsigned long long)timeout_ns, abort_ptr(abort), (int)rank, (int)dir, stream());
+               (unsigned long long)timeout_ns, abort_ptr(abort), (int)rank, (int)dir, poison, stream());
 }
 
 // pads: int64 device tensor with the address of every rank's signal pad
@@ -738,7 +738,7 @@ const long long* table_ptr(const OptTensor& table, int* npieces) {
 
 // full (natural order) <- piece r of every parameter from peer_shards[r], for every rank r
 void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, int64_t listed_numel,
-                 const OptTensor& abort) {
+                 const OptTensor& abort, int64_t shard_numel) {
   check_cuda_contig(full, "full");
   check_cuda_contig(peer_shards, "peer_shards");
   c10::cuda::CUDAGuard guard(full.device());
@@ -749,7 +749,7 @@ void gather_pull(Tensor& full, const Tensor& peer_shards, const Tensor& table, i
   const int64_t listed = listed_numel;          // world * sum of the listed pieces, known to the caller
   mb::gather_pull(full.data_ptr(), reinterpret_cast<const void* const*>(peer_shards.data_ptr<int64_t>()),
                   (int)peer_shards.numel(), tab, npieces, listed, (int)full.element_size(), opt_abort(abort),
-                  stream());
+                  shard_numel, full.numel(), stream());
 }
 
 void reduce_scatter_sumsq(const Tensor& bufs, int64_t rank, int64_t in_dtype, double scale, Tensor& out,
@@ -862,7 +862,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("scale"), py::arg("out"), py::arg("sumsq"), py::arg("accumulate"), py::arg("abort") = py::none(),
         py::arg("table") = py::none());
   m.def("gather_pull", checked(&gather_pull), py::arg("full"), py::arg("peer_shards"), py::arg("table"),
-        py::arg("listed_numel"), py::arg("abort") = py::none());
+        py::arg("listed_numel"), py::arg("abort") = py::none(), py::arg("shard_numel") = 0);
   m.def("reduce_scatter_adamw", checked(&reduce_scatter_adamw), py::arg("bufs"), py::arg("rank"), py::arg("in_dtype"),
         py::arg("scale"), py::arg("p"), py::arg("m"), py::arg("v"), py::arg("low"), py::arg("sumsq"), py::arg("lr"),
         py::arg("beta1"), py::arg("beta2"), py::arg("eps"), py::arg("wd"), py::arg("step"),
@@ -876,7 +876,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_softmax_bwd", checked(&attn_softmax_bwd));
   m.def("attn_bwd_prep", checked(&attn_bwd_prep));
   m.def("p2p_send", checked(&p2p_send));
-  m.def("p2p_recv", checked(&p2p_recv));
+  m.def("p2p_recv", checked(&p2p_recv), py::arg("dst"), py::arg("local_slot"), py::arg("nbytes"), py::arg("local_flag"),
+        py::arg("seq"), py::arg("remote_ack"), py::arg("counter"), py::arg("timeout_ns"), py::arg("abort"),
+        py::arg("rank"), py::arg("dir"), py::arg("poison") = false);
   m.def("peer_barrier", checked(&peer_barrier));
   m.def("gemm_set_cta_pairs", [](bool on) { mb::gemm_set_cta_pairs(on); });
   m.def("gemm_pair_max_active_clusters", []() { return mb::gemm_pair_max_active_clusters(); });

@@ -65,6 +65,7 @@ constexpr unsigned int kPoison = 0xffffffffu;     // flag value meaning "the wri
 // [7] 1 when the cause was a peer's poison rather than a timeout, [8..9] address of the pinned host mirror.
 constexpr int kAbortWords = 16;
 enum WaitKind : int { kWaitSendAck = 1, kWaitRecv = 2, kWaitBarrier = 3, kWaitStaged = 4 };
+constexpr int kCodeBadIndex = 30;     // a table-driven kernel computed an index outside its buffer
 enum WaitResult : int { kWaitOk = 0, kWaitTimedOut = 1, kWaitAborted = 2, kWaitPoisoned = 3 };
 
 __device__ __forceinline__ int ld_volatile(const int* p) { return *reinterpret_cast<const volatile int*>(p); }
@@ -108,6 +109,18 @@ __device__ __forceinline__ void record_abort(int* abort, WaitResult res, int kin
     __threadfence_system();
     h[0] = 10 + kind;
   }
+}
+
+// Index check of the table-driven kernels (a wrong piece table must not become a fault on a peer GPU):
+// returns true if [idx, idx + n) lies inside [0, limit); otherwise records the index once and the caller
+// skips the access.  `limit` <= 0 disables the check.
+__device__ __forceinline__ bool index_ok(long long idx, long long n, long long limit, int* abort, int where) {
+  if (limit <= 0 || (idx >= 0 && idx + n <= limit)) return true;
+  if (abort != nullptr && atomicCAS(abort, 0, kCodeBadIndex) == 0) {
+    abort[1] = where; abort[2] = (int)(idx >> 32); abort[3] = (int)(limit & 0x7fffffff); abort[4] = (int)(idx & 0xffffffff);
+    abort[5] = -1; abort[6] = 0; abort[7] = 0;
+  }
+  return false;
 }
 
 // True (for every thread of the CTA alike) when the device's abort record is set: data kernels then
@@ -163,10 +176,14 @@ __global__ void p2p_send_kernel(const uint4* __restrict__ src, uint4* __restrict
   if (flagger) st_release_sys(remote_flag, any_failed ? kPoison : seq);     // a poisoned flag releases the receiver
 }
 
-__global__ void p2p_recv_kernel(uint4* __restrict__ dst, const uint4* __restrict__ local_slot, long long n16,
+// `poison`: after a word has been copied out, the slot word is overwritten with kSlotPoison (a quiet NaN
+// in fp32, bf16 and fp16) before the acknowledgement goes out.  A receiver that ever reads a slot the
+// sender has not refilled then sees NaNs instead of the plausible values of an older message.
+constexpr unsigned int kSlotPoison = 0x7fc07fc0u;
+__global__ void p2p_recv_kernel(uint4* __restrict__ dst, uint4* __restrict__ local_slot, long long n16,
                                 const unsigned int* local_flag, unsigned int seq, unsigned int* remote_ack,
                                 unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
-                                int dir) {
+                                int dir, int poison) {
   __shared__ int ok;
   if (threadIdx.x == 0) {
     WaitResult res = ld_volatile(abort) != 0 ? kWaitAborted : kWaitOk;
@@ -177,9 +194,12 @@ __global__ void p2p_recv_kernel(uint4* __restrict__ dst, const uint4* __restrict
   }
   __syncthreads();
   if (ok) {
+    const uint4 bad = make_uint4(kSlotPoison, kSlotPoison, kSlotPoison, kSlotPoison);
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n16;
-         i += (long long)gridDim.x * blockDim.x)
+         i += (long long)gridDim.x * blockDim.x) {
       dst[i] = local_slot[i];
+      if (poison) local_slot[i] = bad;
+    }
   }
   bool any_failed;
   const bool acker = last_block_done(counter, !ok, &any_failed);
@@ -354,6 +374,7 @@ __global__ void reduce_scatter_sumsq_kernel(const T* const* __restrict__ bufs, i
   for (long long v = tid; v < nvec; v += stride) {
     uint4 raw[kMaxWorld];
     const long long at = table != nullptr ? shard_to_natural(&pm, npieces, v * kPer) : v * kPer;
+    if (table != nullptr && !index_ok(at, kPer, (long long)world * shard_n, const_cast<int*>(abort), 3)) continue;
 #pragma unroll
     for (int p = 0; p < kMaxWorld; ++p)
       if (p < world) raw[p] = __ldcv(reinterpret_cast<const uint4*>(src[p] + at));
@@ -431,6 +452,7 @@ __global__ void reduce_scatter_adamw_kernel(const T* const* __restrict__ bufs, i
   for (long long i = tid; i < nvec; i += stride) {
     uint4 raw[kMaxWorld];
     const long long at = table != nullptr ? shard_to_natural(&pm, npieces, i * 8) : i * 8;
+    if (table != nullptr && !index_ok(at, 8, (long long)world * shard_n, const_cast<int*>(abort), 4)) continue;
 #pragma unroll
     for (int q = 0; q < kMaxWorld; ++q)
       if (q < world) raw[q] = __ldcv(reinterpret_cast<const uint4*>(src[q] + at));
@@ -475,7 +497,8 @@ struct NaturalMap {
   long long off[kMaxPieces], piece[kMaxPieces], soff[kMaxPieces];
 };
 __global__ void gather_pull_kernel(uint4* __restrict__ full, const uint4* const* __restrict__ peer_shards, int world,
-                                   const long long* __restrict__ table, int npieces, int per, const int* abort) {
+                                   const long long* __restrict__ table, int npieces, int per, const int* abort,
+                                   long long shard_numel, long long full_numel) {
   __shared__ NaturalMap nm;
   __shared__ long long total;
   if (block_sees_abort(abort)) return;
@@ -509,8 +532,11 @@ __global__ void gather_pull_kernel(uint4* __restrict__ full, const uint4* const*
         const long long rel = n - (nm.cum_end[lo] - (long long)world * nm.piece[lo]);
         const long long r = rel / nm.piece[lo];
         const long long j = rel - r * nm.piece[lo];
-        v[u] = __ldcv(peer_shards[r] + (nm.soff[lo] + j) / per);
-        dst[u] = (nm.off[lo] + rel) / per;
+        if (index_ok(nm.soff[lo] + j, per, shard_numel, const_cast<int*>(abort), 1) &&
+            index_ok(nm.off[lo] + rel, per, full_numel, const_cast<int*>(abort), 2)) {
+          v[u] = __ldcv(peer_shards[r] + (nm.soff[lo] + j) / per);
+          dst[u] = (nm.off[lo] + rel) / per;
+        }
       }
     }
 #pragma unroll
@@ -596,14 +622,15 @@ bool reduce_scatter_adamw(const void* const* bufs, int rank, int world, long lon
 int piece_table_limit() { return kMaxPieces; }
 
 void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
-                 long long listed_numel, int esize, const int* abort, cudaStream_t st) {
+                 long long listed_numel, int esize, const int* abort, long long shard_numel, long long full_numel,
+                 cudaStream_t st) {
   if (listed_numel == 0 || npieces == 0 || npieces > kMaxPieces) return;
   const int per = 16 / esize;
   const long long nwords = listed_numel / per;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(nwords, 256 * 4), 148LL * 4));
   prefer_max_shared(gather_pull_kernel);
   gather_pull_kernel<<<grid, 256, 0, st>>>((uint4*)full, (const uint4* const*)peer_shards, world, table, npieces, per,
-                                           abort);
+                                           abort, shard_numel, full_numel);
 }
 
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
@@ -616,14 +643,14 @@ void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int*
                                         need_ack, counter, timeout_ns, abort, rank, dir);
 }
 
-void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
+void p2p_recv(void* dst, void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
               unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
-              int dir, cudaStream_t st) {
+              int dir, bool poison, cudaStream_t st) {
   const long long n16 = nbytes / 16;
   const int grid = (int)std::max<long long>(1, std::min<long long>(div_up(n16, 256), 16));
   prefer_max_shared(p2p_recv_kernel);
-  p2p_recv_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (const uint4*)local_slot, n16, local_flag, seq, remote_ack,
-                                        counter, timeout_ns, abort, rank, dir);
+  p2p_recv_kernel<<<grid, 256, 0, st>>>((uint4*)dst, (uint4*)local_slot, n16, local_flag, seq, remote_ack,
+                                        counter, timeout_ns, abort, rank, dir, poison ? 1 : 0);
 }
 
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,

@@ -176,9 +176,10 @@ constexpr int kCommAbortWords = 16;
 void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int* remote_flag, unsigned int seq,
               const unsigned int* local_ack, unsigned int need_ack, unsigned int* counter,
               unsigned long long timeout_ns, int* abort, int rank, int dir, cudaStream_t st);
-void p2p_recv(void* dst, const void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
+// `poison`: overwrite the slot with NaN patterns once it has been read (debug aid, see comm_kernels.cu)
+void p2p_recv(void* dst, void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
               unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
-              int dir, cudaStream_t st);
+              int dir, bool poison, cudaStream_t st);
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
                   int* abort, int tag, cudaStream_t st);
 // out[i] (+)= scale * sum_p bufs[p][rank * shard_n + i]; out dtype = in dtype or fp32; sumsq += |out|^2
@@ -191,9 +192,12 @@ void reduce_scatter_sumsq(const void* const* bufs, int rank, int world, long lon
 int piece_table_limit();
 // Parameter all-gather by pull: full (natural order) <- piece r of every parameter listed in `table` from
 // rank r's shard (peer_shards[r], possibly peer memory), for all r.  `listed_numel` = world * sum of the
-// listed pieces (only sizes the grid).  Element size `esize` bytes (2 or 4).
+// listed pieces (only sizes the grid).  Element size `esize` bytes (2 or 4).  Every computed index is checked
+// against `shard_numel` / `full_numel` (elements; <= 0 disables): a bad one is recorded in `abort` (code 30)
+// and skipped, never dereferenced.
 void gather_pull(void* full, const void* const* peer_shards, int world, const long long* table, int npieces,
-                 long long listed_numel, int esize, const int* abort, cudaStream_t st);
+                 long long listed_numel, int esize, const int* abort, long long shard_numel, long long full_numel,
+                 cudaStream_t st);
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,
                      int dtype, const int* abort, cudaStream_t st);
 

@@ -51,6 +51,8 @@ class PeerTimeout(RuntimeError):
 
 
 POISON = 0xFFFFFFFF          # flag value written by a kernel that gave up
+_BAD_INDEX_WHERE = {1: "gather: shard index", 2: "gather: natural index", 3: "reduce-scatter: natural index",
+                    4: "reduce-scatter + AdamW: natural index"}
 _WAIT_KINDS = {1: "send (waiting for the receiver to acknowledge the slot)", 2: "receive (waiting for the message)",
                3: "flag barrier", 4: "staged-buffer wait"}
 _DIRS = {0: "forward", 1: "backward"}
@@ -59,6 +61,10 @@ _DIRS = {0: "forward", 1: "backward"}
 def describe_abort(words) -> str:
     """Readable form of an abort record (sequence of >= 8 ints, word 0 = code)."""
     code, kind, where, want, seen, rank, tag, poisoned = (int(w) for w in list(words)[:8])
+    if code == 30:
+        idx = (where << 32) | (seen & 0xFFFFFFFF)
+        return (f"{_BAD_INDEX_WHERE.get(kind, 'kernel')} {idx} outside a buffer of {want} elements: "
+                f"the access was skipped (wrong piece table?) (code 30)")
     want &= 0xFFFFFFFF
     seen &= 0xFFFFFFFF
     what = _WAIT_KINDS.get(kind, f"wait of kind {kind}")
@@ -221,6 +227,11 @@ class PeerMailbox:
         self.send_seq = [0, 0]
         self.recv_seq = [0, 0]
         self._is_host = isinstance(region, HostRegion)
+        # Debug aid (MEGALODON_B200_POISON_SLOTS=1): a slot is overwritten with NaN patterns once it has
+        # been read, so reading a slot that was not refilled shows up as NaNs downstream instead of the
+        # plausible values of an older message ("poison, then verify" with `verify_received`).
+        import os
+        self.poison_slots = os.environ.get("MEGALODON_B200_POISON_SLOTS", "0") == "1"
         if not self._is_host:
             dev = region.device
             self._counters = torch.zeros(4, dtype=torch.int32, device=dev)
@@ -284,10 +295,16 @@ class PeerMailbox:
             require().p2p_recv(dst, self.region.peer_ptr(me, self._slot_off(d, slot)), padded,
                                self.region.peer_ptr(me, self._flag_off(d, slot)), seq,
                                self.region.peer_ptr(peer, self._ack_off(d, slot)), self._counters[2 + d:3 + d],
-                               self.timeout_ns, self._abort.dev, self.region.rank, d)
+                               self.timeout_ns, self._abort.dev, self.region.rank, d, self.poison_slots)
             if dst.data_ptr() != buf.data_ptr():
                 buf.view(-1).view(torch.uint8).copy_(dst.view(torch.uint8)[:nbytes])
         return buf
+
+    @staticmethod
+    def verify_received(buf: torch.Tensor) -> None:
+        """With slot poisoning on: a received tensor must not contain poison (synchronises)."""
+        if buf.is_floating_point() and bool(torch.isnan(buf).any()):
+            raise RuntimeError("received message contains poisoned words: the slot was read before it was refilled")
 
     def check(self) -> None:
         """Raise `PeerTimeout` if a kernel on this device gave up waiting (synchronises the device)."""
@@ -604,13 +621,14 @@ class SymmetricParamGather:
             table = unit.piece_table(full.device)
             listed = unit._numel_padded
         if listed:
-            require().gather_pull(full, self._peer_ptrs[id(unit)], table, listed, self._abort.dev)
+            require().gather_pull(full, self._peer_ptrs[id(unit)], table, listed, self._abort.dev, unit._shard_numel)
 
     def pull_one(self, unit, info, full: torch.Tensor) -> None:
         """Gather a single parameter (a matrix whose first use was not a gathering GEMM)."""
         from ..ops._ext import require
         table = unit.piece_table(full.device, [info], key=("one", info.name))
-        require().gather_pull(full, self._peer_ptrs[id(unit)], table, self.world * info.piece, self._abort.dev)
+        require().gather_pull(full, self._peer_ptrs[id(unit)], table, self.world * info.piece, self._abort.dev,
+                              unit._shard_numel)
         unit._fused_pending.discard(info.name)
 
     def check(self) -> None:

@@ -870,3 +870,32 @@ def _rel_close(got, want, K, what, extra=0.0):
     scale = want.abs().max().item()
     err = (got - want).abs().max().item()
     assert err <= 2 ** -7 * scale + extra + 1e-6, f"{what}: max error {err:.4g} against magnitude {scale:.4g}"
+
+
+def test_table_driven_kernels_skip_and_record_a_bad_index():
+    """A piece table that points outside the buffers must not become an out-of-bounds access: the kernel
+    checks every index it computes, records the first bad one and skips the access."""
+    from megalodon_b200.ops._ext import require
+    from megalodon_b200.parallel.symm import describe_abort
+    ext = require()
+    dev = _dev()
+    world = 2
+    rows, total = _pieces(world, [4096, 1024])
+    S = total // world
+    shards = [torch.ones(S, device=dev, dtype=torch.bfloat16) for _ in range(world)]
+    ptrs = torch.tensor([t.data_ptr() for t in shards], dtype=torch.int64, device=dev)
+    full = torch.zeros(total, device=dev, dtype=torch.bfloat16)
+    abort = torch.zeros(16, dtype=torch.int32, device=dev)
+    bad = [list(r) for r in rows]
+    bad[1][2] = total + 4096                      # natural offset of the second parameter far outside `full`
+    ext.gather_pull(full, ptrs, torch.tensor(bad, dtype=torch.int64, device=dev), total, abort, S)
+    torch.cuda.synchronize()
+    words = abort.tolist()
+    assert words[0] == 30, words
+    assert "natural index" in describe_abort(words) and "skipped" in describe_abort(words)
+    assert bool((full[:rows[0][1] * world] == 1).all())          # the good parameter was still gathered
+    # a healthy table leaves the record alone
+    abort.zero_()
+    ext.gather_pull(full, ptrs, torch.tensor(rows, dtype=torch.int64, device=dev), total, abort, S)
+    torch.cuda.synchronize()
+    assert abort[0].item() == 0 and bool((full == 1).all())

@@ -116,6 +116,7 @@ def _line_case(rank, world):
     region = SymmetricRegion(PeerMailbox.bytes_needed(slot, n_slots), None, dev)
     box = PeerMailbox(region, rank - 1 if rank > 0 else None, rank + 1 if rank + 1 < world else None, slot,
                       n_slots=n_slots, timeout_s=timeout_s)
+    box.poison_slots = True              # every slot is overwritten with NaNs once read: a stale read would show
     ok = True
 
     def forward(k, withhold=False):
