@@ -11,7 +11,12 @@ For each forward projection of the 7B block (weight [N, K] row-sharded over the 
     pull, then gemm      stand-alone pull kernel over peer memory, then the plain GEMM
     NCCL, then gemm      all_gather_into_tensor, then the plain GEMM (what the reference's FSDP does)
 
-and the fused kernel's roofline fraction is printed: the target time is the slower of FLOPs over the
+    python benchmarks/gather_gemm_bench.py --local 8 [--only wv] [--iters 3]
+
+runs the fused kernel alone on ONE GPU with the 8 "ranks" as local buffers (no link traffic): the form a
+profiler can capture (one process, one kernel, a few launches).
+
+The fused kernel's roofline fraction is printed: the target time is the slower of FLOPs over the
 measured cuBLAS throughput and remote bytes over the measured per-direction link bandwidth (770 GB/s).
 The weight is re-sharded between iterations only logically: every iteration pulls the same shards again,
 so the remote bytes are real each time; the operands of one projection (weight + activations + output)
@@ -32,11 +37,57 @@ SHAPES = [("wz", 1024, 4096), ("wv", 8192, 4096), ("wr", 8192, 4096), ("wh1", 40
 LINK_GBS = 770.0
 
 
+def local_mode(args):
+    import torch
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.ops._ext import require
+    ext = require()
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    world, M = args.local, args.tokens
+    out = []
+    for name, N, K in SHAPES:
+        if (args.only and name != args.only) or not ext.gemm_gather_supported(M, N, K, world):
+            continue
+        w = (torch.randn(N, K, device=dev) / K ** 0.5).bfloat16()
+        blocks = [w[r * (N // world):(r + 1) * (N // world)].clone() for r in range(world)]
+        x = torch.randn(M, K, device=dev).bfloat16()
+        full = torch.empty(N, K, device=dev, dtype=torch.bfloat16)
+        ptrs = [b.data_ptr() for b in blocks]
+
+        def run():
+            return cuda_ops.gemm(x, full, b_gather=(ptrs, 1))[0]
+        for _ in range(2):
+            run()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.iters):
+            y = run()
+        e1.record()
+        torch.cuda.synchronize()
+        plain0, plain1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        plain0.record()
+        for _ in range(args.iters):
+            ref = cuda_ops.gemm(x, w)[0]
+        plain1.record()
+        torch.cuda.synchronize()
+        out.append({"weight": name, "N": N, "K": K, "fused_local_ms": round(e0.elapsed_time(e1) / args.iters, 4),
+                    "gemm_only_ms": round(plain0.elapsed_time(plain1) / args.iters, 4),
+                    "max_abs_diff": (y.float() - ref.float()).abs().max().item()})
+    cuda_ops.check_kernel_errors()
+    print(json.dumps({"bench": "gather_gemm_local", "ranks_emulated": world, "tokens": M, "rows": out}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--local", type=int, default=0, help="emulate this many ranks with local buffers on one GPU")
+    ap.add_argument("--only", default=None, help="one projection by name (wz, wv, wr, wh1, wh2, fc1, fc2)")
     args = ap.parse_args()
+    if args.local:
+        return local_mode(args)
     import torch
     import torch.distributed as dist
     from megalodon_b200.ops import cuda_ops
