@@ -420,6 +420,13 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
   }
   // softmax fused into the epilogue (attention products): fp32 row vectors [batch, M]
   mb::GemmSoftmaxSpec sm;
+  bool with_addend = false;
+  if (epi_kind == 0 && aux.has_value()) {
+    TORCH_CHECK(aux->is_cuda() && aux->scalar_type() == C.scalar_type() && aux->sizes() == C.sizes() &&
+                aux->strides() == C.strides(), "the addend must have the dtype and layout of the output");
+    sm.aux = aux->data_ptr();
+    with_addend = true;
+  }
   if (epi_kind != 0) {
     auto rowvec = [&](const OptTensor& t, const char* what) -> float* {
       TORCH_CHECK(t.has_value() && t->is_cuda() && t->scalar_type() == at::kFloat && t->is_contiguous() &&
@@ -446,7 +453,7 @@ std::tuple<Tensor, OptTensor, int64_t> gemm(const Tensor& A, const Tensor& B, co
                                        (int)out_dtype_code, err.data_ptr<int>(), sms, stream(),
                                        (a_parts > 1 || c_part_ptrs.size() > 1) ? &peers : nullptr,
                                        accumulate && out.has_value(), gather.world > 0 ? &gather : nullptr,
-                                       sm.kind != 0 ? &sm : nullptr);
+                                       (sm.kind != 0 || with_addend) ? &sm : nullptr);
   // the launcher's status goes back to Python, which raises on a non-zero code
   return {C, pre, (int64_t)rc};
 }

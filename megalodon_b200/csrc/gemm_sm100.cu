@@ -467,6 +467,7 @@ gemm_tcgen05_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_cons
           } else {
             const long long off = (long long)tc.bz * p.c_batch_stride + (long long)row * p.ldc + col0;
             if (p.accumulate) add_row32<OutT>(C + off, v, nvalid);
+            if (p.aux != nullptr) add_row32<OutT>(reinterpret_cast<const OutT*>(p.aux) + off, v, nvalid);   // + addend
             if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
             if (p.act == 1) {
 #pragma unroll
@@ -801,6 +802,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
           } else {
             const long long off = (long long)bz * p.c_batch_stride + (long long)row * p.ldc + col0;
             if (p.accumulate) add_row32<OutT>(C + off, v, nvalid);
+            if (p.aux != nullptr) add_row32<OutT>(reinterpret_cast<const OutT*>(p.aux) + off, v, nvalid);   // + addend
             if (P != nullptr) store_row32<OutT>(P + off, v, nvalid);
             if (p.act == 1) {
 #pragma unroll
@@ -956,6 +958,10 @@ int gemm_bf16_tcgen05(const void* A, const void* B, void* C, void* preact, const
   p.err = err; p.ldc = ldc; p.mode = mode; p.alpha = alpha; p.batch = batch; p.c_batch_stride = c_bs;
   p.a_parts = 1; p.a_part_k = K; p.a_first = 0; p.c_nparts = 1; p.c_part_cols = N;
   p.accumulate = accumulate ? 1 : 0;
+  if (softmax != nullptr && softmax->kind == 0 && softmax->aux != nullptr) {
+    if (peers != nullptr && peers->c_nparts > 1) return -10;
+    p.aux = softmax->aux;              // standard epilogue with an addend of C's layout
+  }
   if (softmax != nullptr && softmax->kind != 0) {
     if (softmax->kind < 1 || softmax->kind > 4 || bias != nullptr || act != 0 || preact != nullptr || accumulate ||
         peers != nullptr)

@@ -100,6 +100,7 @@ struct GemmGatherSpec {
 //   kind 2: C = exp(alpha acc - row_in[i]), row_out[i] += sum_j C[i, j]                        (Q K^T, pass 2)
 //   kind 3: C = alpha acc / row_in[i]                                                         (P V)
 //   kind 4: C = aux / row_in[i] * (alpha acc - row_in2[i]); aux laid out like C, may be C      (dO V^T -> dS)
+//   kind 0 with aux: the standard epilogue plus an addend, C = act(alpha acc + bias + aux)     (residual adds)
 struct GemmSoftmaxSpec {
   int kind = 0;
   const float* row_in = nullptr;

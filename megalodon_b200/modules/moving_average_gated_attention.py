@@ -272,9 +272,14 @@ class MovingAverageGatedAttention(nn.Module):
         attn, cache_attn = self.inner_attention(q, k, v, mask, freqs_cis, cache_attn)
         attn = ops.memory_efficient_dropout(attn * r, self.hidden_dropout, self.training)
 
-        h = self.wh1(mx) + self.wh2(attn)
-        h = ops.memory_efficient_dropout(h, self.dropout, self.training)
-        out = h + residual
+        if get_model_parallel_world_size() == 1 and not (self.training and self.dropout > 0.0):
+            # both additions ride in the epilogues of the two projections
+            h = ops.linear_add(mx, self.wh1.weight, self.wh1.bias, residual)
+            out = ops.linear_add(attn, self.wh2.weight, None, h)
+        else:
+            h = self.wh1(mx) + self.wh2(attn)
+            h = ops.memory_efficient_dropout(h, self.dropout, self.training)
+            out = h + residual
         if cache is not None:
             return out, (cache_attn, cache_norm, hx)
         return out, new_carry

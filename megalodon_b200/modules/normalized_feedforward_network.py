@@ -8,6 +8,7 @@ import torch
 from torch import nn
 
 from .. import ops
+from ..parallel.initialize import get_model_parallel_world_size
 from ..parallel.model_parallel import (
     ColumnParallelLinear,
     RowParallelLinear,
@@ -56,6 +57,9 @@ class NormalizedFeedForwardNetwork(nn.Module):
         else:
             hidden = self.fc1(x)
         hidden = ops.memory_efficient_dropout(hidden, self.hidden_dropout, self.training)
+        if (self.alpha is None and get_model_parallel_world_size() == 1
+                and not (self.training and self.dropout > 0.0)):
+            return ops.linear_add(hidden, self.fc2.weight, None, residual)     # residual add in the GEMM epilogue
         x = self.fc2(hidden)
         x = ops.memory_efficient_dropout(x, self.dropout, self.training)
         return self.rescale(x) + residual

@@ -45,6 +45,13 @@ def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: Optional[str] 
     return reference.linear(x, w, b, act)
 
 
+def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Tensor:
+    """x @ w^T + b + addend (on the GPU the addition rides in the GEMM epilogue)."""
+    if native_for(x):
+        return _cuda().linear_add(x, w, b, addend)
+    return reference.linear(x, w, b, None) + addend
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     if native_for(a):
         return _cuda().swiglu(a, b)

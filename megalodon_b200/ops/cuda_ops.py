@@ -101,7 +101,7 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
                                  a_part_ptrs=list(a_part_ptrs or []), a_first=a_first,
                                  c_part_ptrs=list(c_part_ptrs or []),
                                  b_gather_ptrs=list(b_gather[0]) if b_gather else [],
-                                 b_gather_rank=int(b_gather[1]) if b_gather else 0)
+                                 b_gather_rank=int(b_gather[1]) if b_gather else 0, **(softmax or {}))
         if rc != 0:
             raise RuntimeError(f"tcgen05 GEMM launch failed with code {rc}")
         return res, pre
@@ -141,6 +141,67 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
     return res, pre
 
 
+def _gemm_gathering(x2: Tensor, w: Tensor, b, act, **kw):
+    """`gemm(x2, w, ...)` for a linear layer's forward.  A sharded weight seen for the first time since the
+    last optimiser step (`_gather_spec` pending) is gathered by this GEMM itself where the kernel can,
+    by a stand-alone pull otherwise."""
+    spec = getattr(w, "_gather_spec", None)
+    if spec is not None and spec.pending:
+        if (_GEMM_BACKEND[0] == "tcgen05" and w.is_contiguous() and _tma_ok(x2)
+                and _C().gemm_gather_supported(x2.shape[0], w.shape[0], w.shape[1], len(spec.sources()[0]))):
+            out = gemm(x2, w, b, act, b_gather=spec.sources(), **kw)
+            spec.done()
+            return out
+        spec.pull_now()
+    return gemm(x2, w, b, act, **kw)
+
+
+class _LinearAdd(torch.autograd.Function):
+    """y = x w^T + b + addend, the addition done in the GEMM epilogue (residual adds and the sum of two
+    projections cost no kernel of their own).  Gradients as for `_Linear`; the addend's is dy itself."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, addend):
+        x2 = x.reshape(-1, x.shape[-1])
+        a2 = addend.reshape(-1, addend.shape[-1])
+        if not a2.is_contiguous():
+            a2 = a2.contiguous()
+        y, _ = _gemm_gathering(x2, w, b, None, softmax=dict(aux=a2), out=torch.empty_like(a2))
+        ctx.save_for_backward(x2, w)
+        ctx.wgrad_sink = getattr(w, "_wgrad_sink", None)
+        ctx.has_bias = b is not None
+        ctx.x_shape = x.shape
+        ctx.bias_dtype = b.dtype if b is not None else None
+        return y.view(addend.shape)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        g = dy.reshape(-1, dy.shape[-1]).contiguous()
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx, _ = gemm(g, w, None, None, b_mn=True)
+            dx = dx.view(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            sink = ctx.wgrad_sink
+            target = sink() if sink is not None else None
+            if target is not None and target.dtype == g.dtype:
+                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=True)
+            else:
+                dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = g.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+        return dx, dw, db, (dy if ctx.needs_input_grad[3] else None)
+
+
+def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Tensor:
+    """x w^T + b + addend; `addend` has the shape of the result."""
+    if (x.dtype == torch.float32 or _GEMM_BACKEND[0] != "tcgen05" or addend.dtype != x.dtype
+            or w.shape[0] % 8 != 0 or not _tma_ok(x.reshape(-1, x.shape[-1]))):
+        return linear(x, w, b) + addend
+    return _LinearAdd.apply(x, w, b, addend)
+
+
 def ensure_gathered(w: Tensor) -> Tensor:
     """A weight whose all-gather was left to its first consuming GEMM (`_gather_spec`) but is about to
     be read by something else: gather it now."""
@@ -155,18 +216,7 @@ class _Linear(torch.autograd.Function):
     def forward(ctx, x, w, b, act):
         x2 = x.reshape(-1, x.shape[-1])
         need_pre = act is not None and any(ctx.needs_input_grad[:3])
-        spec = getattr(w, "_gather_spec", None)
-        if spec is not None and spec.pending:
-            # first use of a sharded weight since the last optimiser step: this GEMM gathers it
-            if (_GEMM_BACKEND[0] == "tcgen05" and w.is_contiguous() and _tma_ok(x2)
-                    and _C().gemm_gather_supported(x2.shape[0], w.shape[0], w.shape[1], len(spec.sources()[0]))):
-                y, pre = gemm(x2, w, b, act, want_preact=need_pre, b_gather=spec.sources())
-                spec.done()
-            else:
-                spec.pull_now()
-                y, pre = gemm(x2, w, b, act, want_preact=need_pre)
-        else:
-            y, pre = gemm(x2, w, b, act, want_preact=need_pre)
+        y, pre = _gemm_gathering(x2, w, b, act, want_preact=need_pre)
         ctx.save_for_backward(x2, w, pre if pre is not None else torch.empty(0, device=x.device))
         ctx.wgrad_sink = getattr(w, "_wgrad_sink", None)
         ctx.has_bias = b is not None

@@ -899,3 +899,27 @@ def test_table_driven_kernels_skip_and_record_a_bad_index():
     ext.gather_pull(full, ptrs, torch.tensor(rows, dtype=torch.int64, device=dev), total, abort, S)
     torch.cuda.synchronize()
     assert abort[0].item() == 0 and bool((full == 1).all())
+
+
+def test_linear_add_epilogue():
+    """x w^T + b + addend with the addition in the GEMM epilogue, values and all four gradients."""
+    from megalodon_b200 import ops
+    torch.manual_seed(24)
+    dev = _dev()
+    x = torch.randn(2, 300, 256, device=dev).bfloat16()
+    w = (torch.randn(384, 256, device=dev) * 0.05).bfloat16()
+    b = torch.randn(384, device=dev).bfloat16()
+    r = torch.randn(2, 300, 384, device=dev).bfloat16()
+    g = torch.randn(2, 300, 384, device=dev).bfloat16()
+    for bias in (b, None):
+        a = [t.clone().requires_grad_() for t in (x, w, r)] + ([bias.clone().requires_grad_()] if bias is not None else [None])
+        f = [t.float().clone().requires_grad_() for t in (x, w, r)] + ([bias.float().clone().requires_grad_()] if bias is not None else [None])
+        y0 = ops.linear_add(a[0], a[1], a[3], a[2])
+        y0.backward(g)
+        y1 = torch.nn.functional.linear(f[0], f[1], f[3]) + f[2]
+        y1.backward(g.float())
+        _close(y0, y1, 5e-2, 3e-2, "linear_add")
+        for n, p, q in zip(["dx", "dw", "dr", "db"], a, f):
+            if p is not None:
+                rel = (p.grad.float() - q.grad).norm() / (q.grad.norm() + 1e-6)
+                assert rel < 2e-2, (n, rel)
