@@ -273,6 +273,47 @@ Tensor rotary(const Tensor& x, const Tensor& freqs, bool conj) {
   return out;
 }
 
+// z [..., S] (16-bit, S = H * Dh), gamma / beta [2, S] (fp32 or z's dtype), freqs [P, Dh/2, 2] fp32 -> (q, k) like z
+std::tuple<Tensor, Tensor> qk_rotary_fwd(const Tensor& z, const Tensor& gamma, const Tensor& beta, const Tensor& freqs,
+                                         int64_t Dh) {
+  check_cuda_contig(z, "z");
+  check_cuda_contig(gamma, "gamma");
+  check_cuda_contig(beta, "beta");
+  check_cuda_contig(freqs, "freqs");
+  c10::cuda::CUDAGuard guard(z.device());
+  const int S = z.size(-1), P = freqs.size(0);
+  TORCH_CHECK(z.scalar_type() == at::kBFloat16 || z.scalar_type() == at::kHalf, "16-bit activations only");
+  TORCH_CHECK(S % 8 == 0 && S <= 8192 && S % Dh == 0 && Dh % 2 == 0 && freqs.scalar_type() == at::kFloat &&
+              freqs.size(1) == Dh / 2 && gamma.numel() == 2 * S && beta.numel() == 2 * S);
+  TORCH_CHECK(gamma.scalar_type() == beta.scalar_type() &&
+              (gamma.scalar_type() == at::kFloat || gamma.scalar_type() == z.scalar_type()));
+  Tensor q = torch::empty_like(z), k = torch::empty_like(z);
+  mb::qk_rotary_fwd(z.data_ptr(), gamma.data_ptr(), beta.data_ptr(), freqs.data_ptr<float>(), q.data_ptr(), k.data_ptr(),
+                    z.numel() / S, S, (int)Dh, P, dtype_code(z), dtype_code(gamma), stream());
+  return {q, k};
+}
+
+// -> (dz like z, dgamma [2, S] fp32, dbeta [2, S] fp32)
+std::tuple<Tensor, Tensor, Tensor> qk_rotary_bwd(const Tensor& dq, const Tensor& dk, const Tensor& z, const Tensor& gamma,
+                                                 const Tensor& freqs, int64_t Dh) {
+  check_cuda_contig(dq, "dq");
+  check_cuda_contig(dk, "dk");
+  check_cuda_contig(z, "z");
+  check_cuda_contig(gamma, "gamma");
+  c10::cuda::CUDAGuard guard(z.device());
+  const int S = z.size(-1), P = freqs.size(0);
+  const long long rows = z.numel() / S;
+  TORCH_CHECK(dq.sizes() == z.sizes() && dk.sizes() == z.sizes() && dq.scalar_type() == z.scalar_type() &&
+              dk.scalar_type() == z.scalar_type() && S % 8 == 0 && S <= 8192);
+  Tensor dz = torch::empty_like(z);
+  const int ctas = mb::qk_rotary_bwd_ctas(rows);
+  Tensor partial = torch::empty({ctas, 4, S}, z.options().dtype(at::kFloat));
+  mb::qk_rotary_bwd(dq.data_ptr(), dk.data_ptr(), z.data_ptr(), gamma.data_ptr(), freqs.data_ptr<float>(), dz.data_ptr(),
+                    partial.data_ptr<float>(), rows, S, (int)Dh, P, dtype_code(z), dtype_code(gamma), stream());
+  Tensor sums = partial.sum(0);                       // [4, S]
+  return {dz, sums.narrow(0, 0, 2), sums.narrow(0, 2, 2)};
+}
+
 std::tuple<Tensor, Tensor> cross_entropy_fwd(const Tensor& logits, const Tensor& target, int64_t ignore_index) {
   check_cuda_contig(logits, "logits");
   check_cuda_contig(target, "target");
@@ -843,6 +884,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("swiglu_fwd", checked(&swiglu_fwd));
   m.def("swiglu_bwd", checked(&swiglu_bwd));
   m.def("rotary", checked(&rotary));
+  m.def("qk_rotary_fwd", checked(&qk_rotary_fwd));
+  m.def("qk_rotary_bwd", checked(&qk_rotary_bwd));
   m.def("cross_entropy_fwd", checked(&cross_entropy_fwd));
   m.def("cross_entropy_bwd", checked(&cross_entropy_bwd));
   m.def("adamw_step", checked(&adamw_step));

@@ -69,6 +69,91 @@ __global__ void rotary_kernel(const T* __restrict__ x, const float2* __restrict_
   }
 }
 
+// Shared q / k of the MEGA attention from the normalised z, in one pass:
+//   q = rot(z * (gamma_q + 1) / sqrt(Dh) + beta_q),  k = rot(z * (gamma_k + 1) / sqrt(Dh) + beta_k)
+// z, q, k [rows, S] with S = H * Dh, gamma / beta [2, S] (row 0 for q, row 1 for k), rot = the rotary
+// rotation of pairs (2j, 2j + 1) by freqs[row % P, j % (Dh / 2)].  One thread per 4 pairs (16-byte accesses).
+template <typename T, typename W>
+__global__ void qk_rotary_fwd_kernel(const T* __restrict__ z, const W* __restrict__ gamma, const W* __restrict__ beta,
+                                     const float2* __restrict__ freqs, T* __restrict__ q, T* __restrict__ k,
+                                     long long rows, int S, int Dh, int P, float inv_sqrt) {
+  const int per_row = S / 8;
+  const long long total = rows * per_row;
+  const int half = Dh / 2;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    const long long row = i / per_row;
+    const int c0 = (int)(i - row * per_row) * 8;
+    const int pos = (int)(row % P);
+    float zv[8], qv[8], kv[8];
+    load8(z + row * S + c0, zv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int c = c0 + 2 * j;
+      const float2 f = freqs[(long long)pos * half + ((c % Dh) >> 1)];
+      const float a0 = zv[2 * j] * (to_f(gamma[c]) + 1.f) * inv_sqrt + to_f(beta[c]);
+      const float a1 = zv[2 * j + 1] * (to_f(gamma[c + 1]) + 1.f) * inv_sqrt + to_f(beta[c + 1]);
+      const float b0 = zv[2 * j] * (to_f(gamma[S + c]) + 1.f) * inv_sqrt + to_f(beta[S + c]);
+      const float b1 = zv[2 * j + 1] * (to_f(gamma[S + c + 1]) + 1.f) * inv_sqrt + to_f(beta[S + c + 1]);
+      qv[2 * j] = a0 * f.x - a1 * f.y; qv[2 * j + 1] = a0 * f.y + a1 * f.x;
+      kv[2 * j] = b0 * f.x - b1 * f.y; kv[2 * j + 1] = b0 * f.y + b1 * f.x;
+    }
+    store8(q + row * S + c0, qv);
+    store8(k + row * S + c0, kv);
+  }
+}
+
+// Backward of the above.  CTA = S / 8 threads (thread t owns columns [8t, 8t + 8)) walking a slab of rows:
+// dz per element, and per CTA one partial row of d gamma_q, d gamma_k, d beta_q, d beta_k
+// (partial [gridDim.x, 4, S] fp32, summed over CTAs afterwards).
+template <typename T, typename W>
+__global__ void qk_rotary_bwd_kernel(const T* __restrict__ dq, const T* __restrict__ dk, const T* __restrict__ z,
+                                     const W* __restrict__ gamma, const float2* __restrict__ freqs,
+                                     T* __restrict__ dz, float* __restrict__ partial, long long rows, int S, int Dh,
+                                     int P, float inv_sqrt) {
+  const int c0 = threadIdx.x * 8;
+  if (c0 >= S) return;
+  const int half = Dh / 2;
+  const long long slab = (rows + gridDim.x - 1) / gridDim.x;
+  const long long r0 = (long long)blockIdx.x * slab, r1 = min(rows, r0 + slab);
+  float sq[8], sk[8], gq[8], gk[8], bq[8], bk[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    sq[j] = (to_f(gamma[c0 + j]) + 1.f) * inv_sqrt;
+    sk[j] = (to_f(gamma[S + c0 + j]) + 1.f) * inv_sqrt;
+    gq[j] = gk[j] = bq[j] = bk[j] = 0.f;
+  }
+  for (long long row = r0; row < r1; ++row) {
+    const int pos = (int)(row % P);
+    float a[8], b[8], zv[8], o[8];
+    load8(dq + row * S + c0, a);
+    load8(dk + row * S + c0, b);
+    load8(z + row * S + c0, zv);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = freqs[(long long)pos * half + (((c0 + 2 * j) % Dh) >> 1)];
+      // inverse rotation of the incoming gradients
+      const float a0 = a[2 * j] * f.x + a[2 * j + 1] * f.y, a1 = -a[2 * j] * f.y + a[2 * j + 1] * f.x;
+      const float b0 = b[2 * j] * f.x + b[2 * j + 1] * f.y, b1 = -b[2 * j] * f.y + b[2 * j + 1] * f.x;
+      o[2 * j] = a0 * sq[2 * j] + b0 * sk[2 * j];
+      o[2 * j + 1] = a1 * sq[2 * j + 1] + b1 * sk[2 * j + 1];
+      gq[2 * j] = fmaf(a0, zv[2 * j], gq[2 * j]);         gq[2 * j + 1] = fmaf(a1, zv[2 * j + 1], gq[2 * j + 1]);
+      gk[2 * j] = fmaf(b0, zv[2 * j], gk[2 * j]);         gk[2 * j + 1] = fmaf(b1, zv[2 * j + 1], gk[2 * j + 1]);
+      bq[2 * j] += a0; bq[2 * j + 1] += a1;
+      bk[2 * j] += b0; bk[2 * j + 1] += b1;
+    }
+    store8(dz + row * S + c0, o);
+  }
+  float* pr = partial + (long long)blockIdx.x * 4 * S;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    pr[c0 + j] = gq[j] * inv_sqrt;
+    pr[S + c0 + j] = gk[j] * inv_sqrt;
+    pr[2 * S + c0 + j] = bq[j];
+    pr[3 * S + c0 + j] = bk[j];
+  }
+}
+
 // one CTA per row
 template <typename T>
 __global__ void ce_fwd_kernel(const T* __restrict__ logits, const long long* __restrict__ target,
@@ -241,6 +326,41 @@ void rotary_apply(const void* x, const float* freqs, void* out, long long rows, 
   const long long n = rows * H * (Dh / 2);
   MB_DISPATCH_DTYPE(dtype, (rotary_kernel<scalar_t><<<ew_grid(n), 256, 0, st>>>(
                                (const scalar_t*)x, (const float2*)freqs, (scalar_t*)out, rows, L, H, Dh, conj)));
+}
+
+// gamma / beta are fp32 or of the activation dtype (w_dtype)
+void qk_rotary_fwd(const void* z, const void* gamma, const void* beta, const float* freqs, void* q, void* k,
+                   long long rows, int S, int Dh, int P, int dtype, int w_dtype, cudaStream_t st) {
+  if (rows == 0) return;
+  const long long n = rows * (S / 8);
+  const float inv = 1.f / sqrtf((float)Dh);
+  MB_DISPATCH_16BIT(dtype, {
+    if (w_dtype == kF32)
+      qk_rotary_fwd_kernel<scalar_t, float><<<ew_grid(n), 256, 0, st>>>((const scalar_t*)z, (const float*)gamma,
+          (const float*)beta, (const float2*)freqs, (scalar_t*)q, (scalar_t*)k, rows, S, Dh, P, inv);
+    else
+      qk_rotary_fwd_kernel<scalar_t, scalar_t><<<ew_grid(n), 256, 0, st>>>((const scalar_t*)z, (const scalar_t*)gamma,
+          (const scalar_t*)beta, (const float2*)freqs, (scalar_t*)q, (scalar_t*)k, rows, S, Dh, P, inv);
+  });
+}
+
+int qk_rotary_bwd_ctas(long long rows) { return (int)std::max<long long>(1, std::min<long long>(rows / 8, 148LL * 4)); }
+
+// partial: [qk_rotary_bwd_ctas(rows), 4, S] fp32 (rows of d gamma_q, d gamma_k, d beta_q, d beta_k per CTA)
+void qk_rotary_bwd(const void* dq, const void* dk, const void* z, const void* gamma, const float* freqs, void* dz,
+                   float* partial, long long rows, int S, int Dh, int P, int dtype, int w_dtype, cudaStream_t st) {
+  if (rows == 0) return;
+  const float inv = 1.f / sqrtf((float)Dh);
+  const int grid = qk_rotary_bwd_ctas(rows);
+  const int threads = ((S / 8 + 31) / 32) * 32;
+  MB_DISPATCH_16BIT(dtype, {
+    if (w_dtype == kF32)
+      qk_rotary_bwd_kernel<scalar_t, float><<<grid, threads, 0, st>>>((const scalar_t*)dq, (const scalar_t*)dk,
+          (const scalar_t*)z, (const float*)gamma, (const float2*)freqs, (scalar_t*)dz, partial, rows, S, Dh, P, inv);
+    else
+      qk_rotary_bwd_kernel<scalar_t, scalar_t><<<grid, threads, 0, st>>>((const scalar_t*)dq, (const scalar_t*)dk,
+          (const scalar_t*)z, (const scalar_t*)gamma, (const float2*)freqs, (scalar_t*)dz, partial, rows, S, Dh, P, inv);
+  });
 }
 
 void cross_entropy_fwd(const void* logits, const long long* target, float* loss, float* lse, long long rows,

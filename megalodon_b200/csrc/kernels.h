@@ -53,6 +53,13 @@ void swiglu_bwd(const void* g, const void* a, const void* b, void* da, void* db,
                 cudaStream_t st);
 void rotary_apply(const void* x, const float* freqs, void* out, long long rows, int L, int H, int Dh,
                   bool conj, int dtype, cudaStream_t st);
+// q, k = rotary(z * (gamma + 1) / sqrt(Dh) + beta) for the two rows of gamma / beta [2, S]; z [rows, S], S = H * Dh a
+// multiple of 8 (and at most 8192), position of a row = row % P, freqs [P, Dh / 2] (cos, sin); 16-bit activations
+void qk_rotary_fwd(const void* z, const void* gamma, const void* beta, const float* freqs, void* q, void* k,
+                   long long rows, int S, int Dh, int P, int dtype, int w_dtype, cudaStream_t st);
+int qk_rotary_bwd_ctas(long long rows);
+void qk_rotary_bwd(const void* dq, const void* dk, const void* z, const void* gamma, const float* freqs, void* dz,
+                   float* partial, long long rows, int S, int Dh, int P, int dtype, int w_dtype, cudaStream_t st);
 void cross_entropy_fwd(const void* logits, const long long* target, float* loss, float* lse, long long rows,
                        int V, long long ignore_index, int dtype, cudaStream_t st);
 void cross_entropy_bwd(const void* logits, const long long* target, const float* lse, const float* dloss,

@@ -70,7 +70,8 @@ class _InnerAttention(nn.Module):
         xq = xq.view(bs, slen, self.n_heads, self.z_head_dim)
         xk = xk.view(bs, slen, self.n_heads, self.z_head_dim)
         xv = xv.view(bs, slen, self.n_heads, self.v_head_dim)
-        if slen <= c:
+        # freqs_cis None: the caller already rotated q and k (fused with their affine map)
+        if slen <= c and freqs_cis is not None:
             xq, xk = apply_rotary_emb(xq, xk, freqs_cis, backward=False)
 
         if cache is not None and isinstance(cache[2], torch.Tensor):
@@ -92,7 +93,7 @@ class _InnerAttention(nn.Module):
         if c < clen:
             xk = xk.reshape(bs * (clen // c), c, self.n_heads, self.z_head_dim)
             xv = xv.reshape(bs * (clen // c), c, self.n_heads, self.v_head_dim)
-        if slen > c:
+        if slen > c and freqs_cis is not None:
             xq, xk = apply_rotary_emb(xq, xk, freqs_cis, backward=False)
 
         if self.efficient_attn is None:
@@ -262,14 +263,13 @@ class MovingAverageGatedAttention(nn.Module):
 
         z = self.wz(mx).view(bsz, seq_len, self.local_heads, self.z_head_dim)
         z = self.znorm(z).view(bsz, seq_len, -1)
-        scale = (self.gamma + 1.0) / math.sqrt(self.z_head_dim)
-        qk = z.unsqueeze(2) * scale.to(z.dtype) + self.beta.to(z.dtype)
-        q, k = torch.unbind(qk, dim=2)
+        # q, k = rotary(z (gamma + 1) / sqrt(d) + beta): one kernel; positions are those of the chunk
+        q, k = ops.qk_rotary(z, self.gamma, self.beta, freqs_cis, self.z_head_dim)
 
         v = self.wv(out_tsn)          # SiLU fused
         r = self.wr(mx)               # SiLU fused
 
-        attn, cache_attn = self.inner_attention(q, k, v, mask, freqs_cis, cache_attn)
+        attn, cache_attn = self.inner_attention(q, k, v, mask, None, cache_attn)
         attn = ops.memory_efficient_dropout(attn * r, self.hidden_dropout, self.training)
 
         if get_model_parallel_world_size() == 1 and not (self.training and self.dropout > 0.0):

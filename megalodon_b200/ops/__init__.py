@@ -52,6 +52,23 @@ def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Ten
     return reference.linear(x, w, b, None) + addend
 
 
+def qk_rotary(z: Tensor, gamma: Tensor, beta: Tensor, freqs_cis: Tensor, head_dim: int):
+    """Shared q / k of the MEGA attention: (z (gamma + 1) / sqrt(head_dim) + beta) for the two rows of
+    gamma / beta [2, S], then the rotary rotation; z [B, L, S], position of (b, l) = (b L + l) % len(freqs_cis)."""
+    if native_for(z) and z.dtype in (torch.bfloat16, torch.float16) and z.shape[-1] % 8 == 0 and z.shape[-1] <= 8192:
+        return _cuda().qk_rotary(z, gamma, beta, freqs_cis, head_dim)
+    import math
+    B, L, S = z.shape
+    scale = (gamma + 1.0) / math.sqrt(head_dim)
+    qk = z.unsqueeze(2) * scale.to(z.dtype) + beta.to(z.dtype)
+    q, k = torch.unbind(qk, dim=2)
+    P = freqs_cis.shape[0]
+    shape = (B * L // P, P, S // head_dim, head_dim)
+    q = rotary(q.reshape(shape), freqs_cis).reshape(B, L, S)
+    k = rotary(k.reshape(shape), freqs_cis).reshape(B, L, S)
+    return q, k
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     if native_for(a):
         return _cuda().swiglu(a, b)

@@ -796,6 +796,37 @@ class _Rotary(torch.autograd.Function):
         return _C().rotary(g.contiguous(), freqs, not ctx.conj), None, None
 
 
+class _QKRotary(torch.autograd.Function):
+    """q, k = rotary(z (gamma + 1) / sqrt(d) + beta) for the two rows of gamma / beta, one kernel each way
+    (replaces two broadcast multiply-adds, two strided copies and two rotary launches, and in backward
+    their gradients and four column reductions)."""
+
+    @staticmethod
+    def forward(ctx, z, gamma, beta, freqs, head_dim):
+        zc = z.contiguous()
+        gc, bc = gamma.contiguous(), beta.contiguous()
+        _bump()
+        q, k = _C().qk_rotary_fwd(zc, gc, bc, freqs, head_dim)
+        ctx.save_for_backward(zc, gc, freqs)
+        ctx.meta = (head_dim, gamma.dtype, beta.dtype)
+        return q, k
+
+    @staticmethod
+    def backward(ctx, dq, dk):
+        zc, gc, freqs = ctx.saved_tensors
+        head_dim, gdt, bdt = ctx.meta
+        _bump(2)
+        dz, dgamma, dbeta = _C().qk_rotary_bwd(dq.contiguous(), dk.contiguous(), zc, gc, freqs, head_dim)
+        return dz, dgamma.to(gdt), dbeta.to(bdt), None, None
+
+
+def qk_rotary(z, gamma, beta, freqs_cis, head_dim: int):
+    """z [B, L, S] normalised per head; gamma, beta [2, S]; freqs_cis [P, head_dim / 2] complex with the
+    position of (b, l) being (b L + l) % P.  Returns rotated q, k [B, L, S]."""
+    freqs = torch.view_as_real(freqs_cis.to(torch.complex64).contiguous())
+    return _QKRotary.apply(z, gamma, beta, freqs, int(head_dim))
+
+
 def rotary(x, freqs_cis, conj=False):
     freqs = torch.view_as_real(freqs_cis.to(torch.complex64).contiguous())
     return _Rotary.apply(x, freqs, conj)

@@ -923,3 +923,31 @@ def test_linear_add_epilogue():
             if p is not None:
                 rel = (p.grad.float() - q.grad).norm() / (q.grad.norm() + 1e-6)
                 assert rel < 2e-2, (n, rel)
+
+
+@pytest.mark.parametrize("B,L,H,dh,P,wdtype", [(2, 256, 2, 64, 256, torch.bfloat16), (1, 1024, 4, 256, 512, torch.float32),
+                                              (3, 1, 4, 32, 1, torch.bfloat16), (2, 40, 1, 16, 40, torch.float32)])
+def test_fused_qk_affine_rotary(B, L, H, dh, P, wdtype):
+    """q, k = rotary(z (gamma + 1) / sqrt(d) + beta) in one kernel against the composition of the separate
+    operators in fp32, with the gradients w.r.t. z, gamma and beta."""
+    from megalodon_b200 import ops
+    torch.manual_seed(25)
+    dev = _dev()
+    S = H * dh
+    z = torch.randn(B, L, S, device=dev).bfloat16()
+    gamma = (torch.randn(2, S, device=dev) * 0.2).to(wdtype)
+    beta = (torch.randn(2, S, device=dev) * 0.2).to(wdtype)
+    ang = torch.outer(torch.arange(P, device=dev, dtype=torch.float32) + 3, torch.rand(dh // 2, device=dev))
+    freqs = torch.polar(torch.ones_like(ang), ang)
+    gq, gk = torch.randn(B, L, S, device=dev).bfloat16(), torch.randn(B, L, S, device=dev).bfloat16()
+    a = [t.clone().requires_grad_() for t in (z, gamma, beta)]
+    q0, k0 = ops.qk_rotary(a[0], a[1], a[2], freqs, dh)
+    (q0.float() * gq.float()).sum().add((k0.float() * gk.float()).sum()).backward()
+    f = [t.float().clone().requires_grad_() for t in (z, gamma, beta)]
+    q1, k1 = ops.qk_rotary(f[0], f[1], f[2], freqs, dh)            # fp32 input takes the composed path
+    (q1 * gq.float()).sum().add((k1 * gk.float()).sum()).backward()
+    _close(q0, q1, 3e-2, 2e-2, "q")
+    _close(k0, k1, 3e-2, 2e-2, "k")
+    for n, p, r in zip(["dz", "dgamma", "dbeta"], a, f):
+        rel = (p.grad.float() - r.grad).norm() / (r.grad.norm() + 1e-6)
+        assert rel < 2e-2, (n, rel.item())
