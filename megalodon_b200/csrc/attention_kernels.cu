@@ -268,7 +268,70 @@ __global__ void attn_bwd_prep_kernel(const T* __restrict__ dout, const T* __rest
   if (lane == 0) delta[vidx] = acc;
 }
 
+// One decode step of the chunk attention against fixed-size key / value buffers, reading only the filled
+// slots.  q [B, H, dk], k_buf [B, H, C, dk], v_buf [B, H, C, dv], pos: device scalar, index of the newest key
+// (keys 0 .. pos are valid).  out [B, H, dv] = softmax(scale q k^T) v.  Grid (B * H, dv / 256), 256 threads:
+// every CTA computes the pos + 1 scores (warps stride over the keys, lanes over dk), normalises them in
+// shared memory, and accumulates its 256 value columns.  Nothing depends on host-side lengths, so the
+// launch can sit in a CUDA graph.
+template <typename T>
+__global__ void decode_attention_kernel(const T* __restrict__ q, const T* __restrict__ kb, const T* __restrict__ vb,
+                                        const long long* __restrict__ pos, T* __restrict__ out, int C, int dk,
+                                        int dv, float scale) {
+  extern __shared__ float sc[];                 // C scores
+  __shared__ float red[32];
+  const int bh = blockIdx.x;
+  const int n = min((int)pos[0] + 1, C);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nwarps = blockDim.x >> 5;
+  const T* qr = q + (long long)bh * dk;
+  const T* kr = kb + (long long)bh * C * dk;
+  for (int j = warp; j < n; j += nwarps) {
+    float acc = 0.f;
+    for (int c = lane * 8; c < dk; c += 256) {
+      float a[8], b[8];
+      load8(qr + c, a);
+      load8(kr + (long long)j * dk + c, b);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fmaf(a[i], b[i], acc);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) sc[j] = acc * scale;
+  }
+  __syncthreads();
+  float m = -INFINITY;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) m = fmaxf(m, sc[j]);
+  m = block_max(m, red);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < n; j += blockDim.x) {
+    const float e = __expf(sc[j] - m);
+    sc[j] = e;
+    sum += e;
+  }
+  sum = block_sum(sum, red);
+  __syncthreads();
+  const int col = blockIdx.y * blockDim.x + threadIdx.x;
+  if (col >= dv) return;
+  const T* vr = vb + (long long)bh * C * dv + col;
+  float acc = 0.f;
+  for (int j = 0; j < n; ++j) acc = fmaf(sc[j], to_f(vr[(long long)j * dv]), acc);
+  out[(long long)bh * dv + col] = from_f<T>(acc / sum);
+}
+
 }  // namespace
+
+void decode_attention(const void* q, const void* kb, const void* vb, const long long* pos, void* out, int BH, int C,
+                      int dk, int dv, float scale, int dtype, cudaStream_t st) {
+  if (BH == 0) return;
+  dim3 grid(BH, div_up(dv, 256));
+  const size_t smem = sizeof(float) * C;
+  MB_DISPATCH_16BIT(dtype, {
+    if (smem > 48 * 1024)
+      cudaFuncSetAttribute(decode_attention_kernel<scalar_t>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    decode_attention_kernel<scalar_t><<<grid, 256, smem, st>>>((const scalar_t*)q, (const scalar_t*)kb, (const scalar_t*)vb,
+                                                                pos, (scalar_t*)out, C, dk, dv, scale);
+  });
+}
 
 void attn_bwd_prep(const void* dout, const void* out, const float* rowsum, void* dos, float* delta, int B, int L,
                    int H, int dv, int dtype, cudaStream_t st) {

@@ -606,6 +606,24 @@ void attn_softmax_bwd(const Tensor& p, Tensor& dp, int64_t L1, int64_t L2, bool 
                        stream());
 }
 
+// q [B, H, dk], k_buf [B, H, C, dk], v_buf [B, H, C, dv] (16-bit, contiguous), pos int64 device tensor [1] -> [B, H, dv]
+Tensor decode_attention(const Tensor& q, const Tensor& k_buf, const Tensor& v_buf, const Tensor& pos, double scale) {
+  check_cuda_contig(q, "q");
+  check_cuda_contig(k_buf, "k_buf");
+  check_cuda_contig(v_buf, "v_buf");
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(q.dim() == 3 && k_buf.dim() == 4 && v_buf.dim() == 4 && pos.is_cuda() && pos.scalar_type() == at::kLong);
+  TORCH_CHECK(q.scalar_type() == at::kBFloat16 || q.scalar_type() == at::kHalf);
+  TORCH_CHECK(k_buf.scalar_type() == q.scalar_type() && v_buf.scalar_type() == q.scalar_type());
+  const int B = q.size(0), H = q.size(1), dk = q.size(2), C = k_buf.size(2), dv = v_buf.size(3);
+  TORCH_CHECK(k_buf.size(0) == B && k_buf.size(1) == H && k_buf.size(3) == dk && v_buf.size(2) == C && dk % 8 == 0);
+  TORCH_CHECK(C * 4 <= 200 * 1024, "key buffer too long for the score array in shared memory");
+  Tensor out = torch::empty({B, H, dv}, q.options());
+  mb::decode_attention(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), pos.data_ptr<int64_t>(), out.data_ptr(), B * H,
+                       C, dk, dv, (float)scale, dtype_code(q), stream());
+  return out;
+}
+
 // dout, out [B, L, H, dv] (16-bit), rowsum [B, H, L] fp32 -> (dout / rowsum, delta [B, H, L] = dout . out)
 std::tuple<Tensor, Tensor> attn_bwd_prep(const Tensor& dout, const Tensor& out, const Tensor& rowsum) {
   check_cuda_contig(dout, "dout");
@@ -925,6 +943,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("attn_softmax_fwd", checked(&attn_softmax_fwd));
   m.def("attn_softmax_bwd", checked(&attn_softmax_bwd));
   m.def("attn_bwd_prep", checked(&attn_bwd_prep));
+  m.def("decode_attention", checked(&decode_attention));
   m.def("p2p_send", checked(&p2p_send));
   m.def("p2p_recv", checked(&p2p_recv), py::arg("dst"), py::arg("local_slot"), py::arg("nbytes"), py::arg("local_flag"),
         py::arg("seq"), py::arg("remote_ack"), py::arg("counter"), py::arg("timeout_ns"), py::arg("abort"),

@@ -157,6 +157,10 @@ void attn_softmax_fwd(void* s_inout, float* lse, long long rows, int L1, int L2,
                       cudaStream_t st);
 void attn_softmax_bwd(const void* p, void* dp_inout, long long rows, int L1, int L2, long long ld, bool causal,
                       int dtype, cudaStream_t st);
+// one decode step against fixed key / value buffers [BH, C, dk] / [BH, C, dv], keys 0 .. *pos valid (device scalar);
+// dk a multiple of 8, 16-bit types; out [BH, dv]
+void decode_attention(const void* q, const void* kb, const void* vb, const long long* pos, void* out, int BH, int C,
+                      int dk, int dv, float scale, int dtype, cudaStream_t st);
 // delta[b, h, l] = dO . O and dO' = dO / rowsum[b, h, l] over rows of dv values (dv a multiple of 8, 16-bit types)
 void attn_bwd_prep(const void* dout, const void* out, const float* rowsum, void* dos, float* delta, int B, int L,
                    int H, int dv, int dtype, cudaStream_t st);

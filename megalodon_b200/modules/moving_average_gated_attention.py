@@ -121,6 +121,10 @@ class _InnerAttention(nn.Module):
         assert slen == 1, "the static cache takes one token per step"
         k_buf.index_copy_(2, pos, xk.transpose(1, 2).to(k_buf.dtype))
         v_buf.index_copy_(2, pos, xv.transpose(1, 2).to(v_buf.dtype))
+        if ops.decode_attention_native(xq, k_buf):
+            # one kernel that attends over the filled slots only (keys 0 .. pos)
+            out = ops.decode_attention(xq[:, 0], k_buf, v_buf, pos, 1.0)                 # [B, H, dv]
+            return out.reshape(bs, 1, -1), cache
         scores = torch.matmul(xq.transpose(1, 2), k_buf.transpose(2, 3)).float()         # [B, H, 1, chunk]
         hidden = torch.arange(k_buf.size(2), device=pos.device) > pos
         probs = torch.softmax(scores.masked_fill(hidden, float("-inf")), dim=-1).to(xq.dtype)

@@ -69,6 +69,22 @@ def qk_rotary(z: Tensor, gamma: Tensor, beta: Tensor, freqs_cis: Tensor, head_di
     return q, k
 
 
+def decode_attention_native(q: Tensor, k_buf: Tensor) -> bool:
+    return (native_for(q) and q.dtype in (torch.bfloat16, torch.float16) and k_buf.dtype == q.dtype
+            and q.shape[-1] % 8 == 0 and k_buf.is_contiguous() and k_buf.shape[2] * 4 <= 200 * 1024)
+
+
+def decode_attention(q: Tensor, k_buf: Tensor, v_buf: Tensor, pos: Tensor, scale: float) -> Tensor:
+    """One decode step against fixed buffers: q [B, H, dk], k_buf [B, H, C, dk], v_buf [B, H, C, dv], `pos` a
+    device index tensor [1]; keys 0 .. pos take part.  Returns [B, H, dv]."""
+    if decode_attention_native(q, k_buf):
+        return _cuda().decode_attention(q, k_buf, v_buf, pos, scale)
+    scores = torch.einsum("bhd,bhcd->bhc", q.float(), k_buf.float()) * scale
+    hidden = torch.arange(k_buf.size(2), device=pos.device) > pos
+    probs = torch.softmax(scores.masked_fill(hidden, float("-inf")), dim=-1)
+    return torch.einsum("bhc,bhcd->bhd", probs, v_buf.float()).to(q.dtype)
+
+
 def swiglu(a: Tensor, b: Tensor) -> Tensor:
     if native_for(a):
         return _cuda().swiglu(a, b)

@@ -735,6 +735,11 @@ class _Attention(torch.autograd.Function):
         return dq, dk_, dv_, None, None, None
 
 
+def decode_attention(q, k_buf, v_buf, pos, scale):
+    _bump()
+    return _C().decode_attention(q.contiguous(), k_buf, v_buf.contiguous(), pos, float(scale))
+
+
 _FUSED_SOFTMAX = [True]
 
 

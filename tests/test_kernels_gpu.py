@@ -951,3 +951,24 @@ def test_fused_qk_affine_rotary(B, L, H, dh, P, wdtype):
     for n, p, r in zip(["dz", "dgamma", "dbeta"], a, f):
         rel = (p.grad.float() - r.grad).norm() / (r.grad.norm() + 1e-6)
         assert rel < 2e-2, (n, rel.item())
+
+
+@pytest.mark.parametrize("B,H,C,dk,dv,pos", [(1, 4, 4096, 256, 2048, 0), (4, 4, 4096, 256, 2048, 1234),
+                                             (16, 2, 512, 64, 192, 511), (2, 1, 100, 32, 40, 57)])
+def test_decode_attention_reads_only_the_filled_slots(B, H, C, dk, dv, pos):
+    """The decode-step attention kernel against fp32 PyTorch; slots beyond `pos` hold NaNs, which a kernel
+    that touched them would propagate."""
+    from megalodon_b200 import ops
+    torch.manual_seed(26)
+    dev = _dev()
+    q = (torch.randn(B, H, dk, device=dev) * 0.3).bfloat16()
+    kb = (torch.randn(B, H, C, dk, device=dev) * 0.3).bfloat16()
+    vb = torch.randn(B, H, C, dv, device=dev).bfloat16()
+    kb[:, :, pos + 1:] = float("nan")
+    vb[:, :, pos + 1:] = float("nan")
+    p = torch.tensor([pos], device=dev, dtype=torch.int64)
+    out = ops.decode_attention(q, kb, vb, p, 0.9)
+    s = torch.einsum("bhd,bhcd->bhc", q.float(), kb[:, :, :pos + 1].float()) * 0.9
+    ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(s, -1), vb[:, :, :pos + 1].float())
+    assert torch.isfinite(out.float()).all()
+    _close(out, ref, 2e-2, 2e-2, "decode attention")
