@@ -619,7 +619,8 @@ Tensor decode_attention(const Tensor& q, const Tensor& k_buf, const Tensor& v_bu
   TORCH_CHECK(k_buf.size(0) == B && k_buf.size(1) == H && k_buf.size(3) == dk && v_buf.size(2) == C && dk % 8 == 0);
   TORCH_CHECK(C * 4 <= 200 * 1024, "key buffer too long for the score array in shared memory");
   Tensor out = torch::empty({B, H, dv}, q.options());
-  mb::decode_attention(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(), pos.data_ptr<int64_t>(), out.data_ptr(), B * H,
+  mb::decode_attention(q.data_ptr(), k_buf.data_ptr(), v_buf.data_ptr(),
+                       reinterpret_cast<const long long*>(pos.data_ptr<int64_t>()), out.data_ptr(), B * H,
                        C, dk, dv, (float)scale, dtype_code(q), stream());
   return out;
 }
