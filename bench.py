@@ -29,6 +29,8 @@ import time
 # before CUDA initialises: peer-waiting kernels must never be held up by a lazy kernel load
 os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
 os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")    # one hardware queue per stream in use
+# growable segments: the step allocates 154 GB of 180; fixed-size segments left 17 GB reserved but unusable
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:

@@ -27,6 +27,8 @@ import sys
 
 os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
 os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")    # one hardware queue per stream in use
+# growable segments: the step allocates 154 GB of 180; fixed-size segments left 17 GB reserved but unusable
+os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 sys.path.insert(0, ROOT)
 
