@@ -196,8 +196,10 @@ class _LinearAdd(torch.autograd.Function):
 
 def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Tensor:
     """x w^T + b + addend; `addend` has the shape of the result."""
+    rows = x.numel() // x.shape[-1]
     if (x.dtype == torch.float32 or _GEMM_BACKEND[0] != "tcgen05" or addend.dtype != x.dtype
-            or w.shape[0] % 8 != 0 or not _tma_ok(x.reshape(-1, x.shape[-1]))):
+            or w.shape[0] % 8 != 0 or rows <= 16 or not _tma_ok(x.reshape(-1, x.shape[-1]))):
+        # (a few rows - decoding - stay on the weight-streaming kernel behind `linear`)
         return linear(x, w, b) + addend
     return _LinearAdd.apply(x, w, b, addend)
 
