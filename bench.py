@@ -59,6 +59,11 @@ def parse():
                     help="library: the same model and step as a composition of library calls inside this framework "
                          "(cuBLAS products, materialised matmul + softmax attention, NCCL hand-off / all-gather / "
                          "reduce-scatter) - a context number for the fused paths, NOT the reference")
+    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: 'peer' moves the chunk hand-off, the parameter gathers and the gradient "
+                         "reduce-scatter through peer memory with this package's kernels; 'nccl' keeps every fused "
+                         "compute kernel but moves those three through NCCL.  A 'peer' run whose bounded peer wait "
+                         "or step watchdog fires restarts itself ONCE with 'nccl' and says so in its result line")
     ap.add_argument("--step-timeout-s", type=float, default=150.0,
                     help="a rank whose host makes no step progress for this long dumps its Python stacks and the "
                          "device's abort record to stderr and exits non-zero (the launcher then stops the others)")
@@ -71,8 +76,9 @@ class StepWatchdog:
     device's abort record (set by the first kernel whose bounded wait on a peer ran out).  Either one
     ends the process with a report instead of leaving N GPUs waiting for the collective timeout."""
 
-    def __init__(self, rank: int, timeout_s: float, abort_record=None):
+    def __init__(self, rank: int, timeout_s: float, abort_record=None, restart_argv=None):
         self.rank, self.timeout_s, self.abort = rank, timeout_s, abort_record
+        self.restart_argv = restart_argv      # set: a failure restarts this rank with the NCCL transport
         self.last = time.time()
         self.where = "start"
         self._stop = False
@@ -87,6 +93,20 @@ class StepWatchdog:
     def stop(self) -> None:
         self._stop = True
 
+    def _leave(self, code: int, why: str) -> None:
+        """End this rank: with a restart command line, replace the process by one that uses the NCCL
+        transport (every rank's watchdog sees the same stalled step and does the same; they meet again at
+        a new rendezvous port, since the first store still holds the keys of the first process group);
+        without one, exit non-zero so that the launcher stops the other ranks."""
+        if self.restart_argv is None:
+            os._exit(code)
+        env = dict(os.environ)
+        env["MEGALODON_B200_BENCH_RESTARTED"] = f"{why} (rank {self.rank}, after '{self.where}')"[:300]
+        env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 1)
+        env["TORCHELASTIC_USE_AGENT_STORE"] = "False"
+        print(f"[rank {self.rank}] restarting with --transport nccl: {why}", file=sys.stderr, flush=True)
+        os.execve(sys.executable, [sys.executable] + self.restart_argv, env)
+
     def _run(self):
         import faulthandler
         tripped_at = None
@@ -99,12 +119,12 @@ class StepWatchdog:
                     print(f"[rank {self.rank}] peer wait failed after '{self.where}': "
                           f"{describe_abort(self.abort.host.tolist())}", file=sys.stderr, flush=True)
                 elif time.time() - tripped_at > 20.0:      # the main thread had its chance to raise
-                    os._exit(4)
+                    self._leave(4, "a bounded wait on a peer ran out")
             if time.time() - self.last > self.timeout_s:
                 print(f"[rank {self.rank}] no progress for {self.timeout_s:.0f} s after '{self.where}'; stacks:",
                       file=sys.stderr, flush=True)
                 faulthandler.dump_traceback(file=sys.stderr, all_threads=True)
-                os._exit(3)
+                self._leave(3, f"no step progress for {self.timeout_s:.0f} s")
 
 
 class ClockSampler:
@@ -192,11 +212,25 @@ def step_roofline(cfg, seq_len: int, world: int, ms_per_step: float) -> dict:
             "peaks": pk["source"]}
 
 
+_WATCHDOG = []       # the running benchmark's watchdog, for the handler of an exception that escapes run()
+
+
 def main():
     args = parse()
     if args.impl == "reference":
         reference_arm(args)
         return
+    try:
+        run(args)
+    except Exception as e:  # noqa: BLE001 - a peer-transport run gets its one restart on NCCL, whatever failed
+        if not _WATCHDOG or _WATCHDOG[0].restart_argv is None:
+            raise
+        import traceback
+        traceback.print_exc()
+        _WATCHDOG[0]._leave(5, f"{type(e).__name__}: {e}"[:200])
+
+
+def run(args):
 
     import torch
     import torch.distributed as dist
@@ -255,7 +289,9 @@ def main():
                         shard_over_chunk_group=True)
     model._wrapped.seq_microbatch_chunks = 1
     model.defer_grad_clip = True      # clipping coefficient is applied inside the fused AdamW kernel
-    if world > 1 and library:
+    restarted = os.environ.get("MEGALODON_B200_BENCH_RESTARTED")
+    peer = world > 1 and not library and args.transport == "peer" and not restarted
+    if world > 1 and not peer:
         mailbox, abort_record = None, None    # NCCL send / recv, all-gather and reduce-scatter
     elif world > 1:
         # CEMA / TimestepNorm state goes from rank to rank through peer memory, not NCCL send/recv
@@ -266,7 +302,11 @@ def main():
         abort_record = AbortRecord.get(torch.device("cuda", local_rank))
     else:
         abort_record = None
-    dog = StepWatchdog(rank, args.step_timeout_s, abort_record)
+    restart_argv = None
+    if peer:
+        restart_argv = [os.path.abspath(__file__)] + [a for a in sys.argv[1:]] + ["--transport", "nccl"]
+    dog = StepWatchdog(rank, args.step_timeout_s, abort_record, restart_argv)
+    _WATCHDOG.append(dog)
     opt, sched = build_optimizer(model, OptimConf(lr=1e-4, warmup=10, clip=1.0), 1000, "bf16")
     data = SyntheticTokens(cfg.vocab_size, 1, args.seq_len, seed=0)
     n_params = sum(p.numel() for p in model.parameters()) * (world if world > 1 else 1)
@@ -289,17 +329,25 @@ def main():
             dist.barrier()
         torch.cuda.synchronize()
 
+    def peer_failure(e):
+        # every rank's record is poisoned by the first failure, so every rank comes through here
+        print(f"[rank {rank}] {e}", file=sys.stderr, flush=True)
+        dog._leave(4, "a bounded wait on a peer ran out")
+
     def check_peers():
         # a bounded device-side wait that ran out shows up here instead of slowing every later step
         cuda_ops.check_kernel_errors()
         if abort_record is not None:
-            abort_record.check()
+            try:
+                abort_record.check()
+            except Exception as e:  # noqa: BLE001 - PeerTimeout: every rank restarts on the NCCL transport
+                peer_failure(e)
 
     def peers_ok_so_far():
         # host-only look at the pinned mirror of the abort record: costs nothing inside a timed region
         if abort_record is not None and abort_record.tripped():
             torch.cuda.synchronize()
-            abort_record.check()
+            check_peers()
 
     for i in range(args.warmup):
         x, y = next(data)
@@ -307,6 +355,10 @@ def main():
         torch.cuda.synchronize()
         check_peers()
         dog.progress(f"warm-up step {i} done, loss {last:.4f}")
+        if peer and os.environ.get("MEGALODON_B200_BENCH_FAIL_AT") == f"{rank}:{i}":
+            # failure drill, made on the host between two steps (nothing of this rank in flight): this rank
+            # raises, the others find out when their next bounded peer wait runs out
+            raise RuntimeError(f"injected host failure on rank {rank} after warm-up step {i}")
 
     sampler = ClockSampler(local_rank)
     sampler.start()
@@ -420,7 +472,7 @@ def main():
                          f"v{cfg.value_dim} ffn{cfg.ffn_hidden_dim} swiglu N{cfg.cema_ndim} chunk{cfg.chunk_size} "
                          f"V{cfg.vocab_size}), {n_params / 1e9:.2f}B params",
                 "global_batch": 1, "seq_len": args.seq_len,
-                "parallelism": f"cp{world}" + (("+zero3_over_cp+nccl" if library else "+zero3_over_cp+p2p_handoff+gathering_gemm")
+                "parallelism": f"cp{world}" + (("+zero3_over_cp+p2p_handoff+gathering_gemm" if peer else "+zero3_over_cp+nccl")
                                                if world > 1 else ""),
                 "activation_checkpointing": (False if not cfg.layerwise_ckpt else
                                              ("all layers" if cfg.ckpt_layers is None else f"first {cfg.ckpt_layers} layers")),
@@ -443,6 +495,9 @@ def main():
             out["roofline"] = step_roofline(cfg, args.seq_len, world, dev_ms / args.steps)
         except Exception as e:  # noqa: BLE001 - never lose the result line over the derived figures
             out["roofline"] = {"error": repr(e)[:200]}
+        if restarted:
+            out["config"]["transport_fallback"] = ("the peer-memory transport failed and the run restarted itself "
+                                                   "with NCCL for hand-off, gathers and reduce-scatter: " + restarted)
         if args.layers is not None:
             out["invalid"] = "reduced depth (debug run)"
         print(json.dumps(out))

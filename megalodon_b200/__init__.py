@@ -18,5 +18,10 @@ _os.environ.setdefault("CUDA_MODULE_LOADING", "EAGER")
 # gradient reduction, one internal stream per NCCL communicator); 32 gives each its own.  Also read
 # when CUDA initialises.
 _os.environ.setdefault("CUDA_DEVICE_MAX_CONNECTIONS", "32")
+# The kernels of this package reach peer memory with plain loads and stores only (no `multimem`), so the
+# symmetric-memory allocator is asked not to bind its buffers to an NVLink multicast object: a rank that
+# leaves (a failed step, the benchmark's restart on another transport) while its memory is bound to one
+# can raise NVLink faults on the GPUs of the ranks that stay.
+_os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
 
 __version__ = "0.1.0"

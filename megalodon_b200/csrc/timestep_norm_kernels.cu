@@ -172,6 +172,116 @@ __global__ void tsn_seg_apply_kernel(const float* __restrict__ gu, const float* 
   }
 }
 
+// ---- the same scan as ONE kernel when a sequence's segments fit one CTA (L <= 16384): a CTA owns GT
+// groups of one batch row, thread (segment, group) keeps its kSegLen samples in registers, the exclusive
+// prefix over segments runs in shared memory (log2(nseg) doubling steps), and the running statistics are
+// written from the registers.  Three dependent launches and the round trip of the segment sums through
+// global memory become one launch.
+constexpr int kScanMaxThreads = 512;   // 128 registers per thread: the segment's samples stay in registers
+
+template <typename T>
+__global__ void __launch_bounds__(kScanMaxThreads)
+tsn_scan_fused_kernel(const float* __restrict__ gu, const float* __restrict__ gv, const bool* __restrict__ mask,
+                      const long long* __restrict__ prev_count, const T* __restrict__ prev_mean,
+                      const T* __restrict__ prev_var, long long* __restrict__ count_out, T* __restrict__ mean_out,
+                      T* __restrict__ var_out, float* __restrict__ cummean, float* __restrict__ cumrstd, int L, int G,
+                      int nseg, int GT, float eps) {
+  __shared__ double sh[3][kScanMaxThreads];
+  const int tid = threadIdx.x;
+  const int gl = tid % GT, sgi = tid / GT;
+  const int g = blockIdx.x * GT + gl, b = blockIdx.y;
+  const bool live = g < G;
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
+  const long long off = (long long)b * L * G + (live ? g : 0);
+  const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
+  float us[kSegLen], vs[kSegLen];
+  unsigned valid = 0;   // bit j: step t0 + j exists and is not padded
+  double n = 0, a = 0, c = 0;
+#pragma unroll
+  for (int j = 0; j < kSegLen; ++j) {
+    const int t = t0 + j;
+    const bool in = live && t < t1;
+    us[j] = in ? gu[off + (long long)t * G] : 0.f;
+    vs[j] = in ? gv[off + (long long)t * G] : 0.f;
+    if (in && !(mb_ && mb_[t])) valid |= 1u << j;
+  }
+#pragma unroll
+  for (int j = 0; j < kSegLen; ++j)
+    if (valid >> j & 1u) {
+      const double u = us[j], v = vs[j];
+      n += 1.0;
+      a += u;
+      c += v + u * u;
+    }
+  sh[0][tid] = n;
+  sh[1][tid] = a;
+  sh[2][tid] = c;
+  __syncthreads();
+  for (int step = 1; step < nseg; step <<= 1) {   // inclusive prefix over segments, per group
+    double tn = 0, ta = 0, tc = 0;
+    if (sgi >= step) {
+      tn = sh[0][tid - step * GT];
+      ta = sh[1][tid - step * GT];
+      tc = sh[2][tid - step * GT];
+    }
+    __syncthreads();
+    if (sgi >= step) {
+      sh[0][tid] += tn;
+      sh[1][tid] += ta;
+      sh[2][tid] += tc;
+    }
+    __syncthreads();
+  }
+  if (!live) return;
+  const double n0 = (double)prev_count[b];
+  const double u0 = to_f(prev_mean[b * G + g]), v0 = to_f(prev_var[b * G + g]);
+  double cn = n0, s1 = n0 * u0, s2 = n0 * (v0 + u0 * u0);
+  if (sgi == nseg - 1) {   // the sequence's final statistics
+    const double fn = cn + sh[0][tid], f1 = s1 + sh[1][tid], f2 = s2 + sh[2][tid];
+    double mean = u0, var = v0;
+    if (fn > 0.5) {
+      mean = f1 / fn;
+      var = fmax(f2 / fn - mean * mean, 0.0);
+    }
+    mean_out[b * G + g] = from_f<T>((float)mean);
+    var_out[b * G + g] = from_f<T>((float)var);
+    if (g == 0) count_out[b] = (long long)(fn + 0.5);
+  }
+  if (sgi > 0) {
+    cn += sh[0][tid - GT];
+    s1 += sh[1][tid - GT];
+    s2 += sh[2][tid - GT];
+  }
+  double mean = u0, var = v0;
+  if (cn > 0.5) {
+    mean = s1 / cn;
+    var = fmax(s2 / cn - mean * mean, 0.0);
+  }
+#pragma unroll
+  for (int j = 0; j < kSegLen; ++j) {
+    const int t = t0 + j;
+    if (t >= t1) break;
+    if (valid >> j & 1u) {
+      const double u = us[j], v = vs[j];
+      cn += 1.0;
+      s1 += u;
+      s2 += v + u * u;
+      mean = s1 / cn;
+      var = fmax(s2 / cn - mean * mean, 0.0);
+    }
+    cummean[off + (long long)t * G] = (float)mean;
+    cumrstd[off + (long long)t * G] = (float)(1.0 / sqrt(var + (double)eps));
+  }
+}
+
+// groups per CTA of the fused scans: as many as keep the CTA near 512 threads (0: the sequence is too long)
+inline int tsn_fused_groups(int nseg) {
+  if (nseg > kScanMaxThreads) return 0;
+  int gt = 1;
+  while (gt * 2 * nseg <= kScanMaxThreads && gt < 32) gt *= 2;
+  return gt;
+}
+
 template <typename T, typename W>
 __global__ void tsn_apply_kernel(const T* __restrict__ x, const float* __restrict__ cummean,
                                  const float* __restrict__ cumrstd, const W* __restrict__ gamma,
@@ -341,6 +451,90 @@ __global__ void tsn_bwd_seg_apply_kernel(StepIn in, const bool* __restrict__ mas
   const double pm = to_f(prev_mean[b * G + g]);
   const long long off = (long long)b * L * G + g;
   double u = maps[i], v = maps[total + i];
+  for (int t = t1 - 1; t >= t0; --t) {
+    const long long e = off + (long long)t * G;
+    if (mb_ && mb_[t]) {
+      dux[e] = 0.f;
+      dvx[e] = 0.f;
+      continue;
+    }
+    const double md = count_at(cumvalid, first, b, L, t);
+    const double c1 = (md - 1.0) / md, c2 = 1.0 / md;
+    const double prev_u = t == 0 ? pm : (double)in.cummean[e - G];
+    const double delta = (double)in.ux[e] - prev_u;
+    const double r = in.cumrstd[e];
+    const double du = u - r * (double)in.db[e];
+    const double dv = v - 0.5 * r * r * r * (double)in.ds[e];
+    dux[e] = (float)(c2 * du + 2.0 * c1 * c2 * dv * delta);
+    dvx[e] = (float)(c2 * dv);
+    u = c1 * du - 2.0 * c1 * c2 * dv * delta;
+    v = c1 * dv;
+  }
+}
+
+// The backward scan as ONE kernel under the same condition as the forward one: thread (segment, group)
+// composes its segment's map, the suffix composition over segments runs in shared memory (the maps do not
+// commute: the later segment's map is applied first), and the segment is replayed from its incoming state.
+template <typename T>
+__global__ void __launch_bounds__(kScanMaxThreads)
+tsn_bwd_scan_fused_kernel(StepIn in, const bool* __restrict__ mask, const int* __restrict__ cumvalid,
+                          const long long* __restrict__ count_final, const T* __restrict__ prev_mean,
+                          const T* __restrict__ dmean_out, const T* __restrict__ dvar_out,
+                          T* __restrict__ dprev_mean, T* __restrict__ dprev_var, float* __restrict__ dux,
+                          float* __restrict__ dvx, int L, int G, int nseg, int GT) {
+  __shared__ double sh[4][kScanMaxThreads];
+  const int tid = threadIdx.x;
+  const int gl = tid % GT, sgi = tid / GT;
+  const int g = blockIdx.x * GT + gl, b = blockIdx.y;
+  const bool live = g < G;
+  const int t0 = sgi * kSegLen, t1 = min(L, t0 + kSegLen);
+  const bool* mb_ = mask ? mask + (long long)b * L : nullptr;
+  const long long first = count_final[b] - (cumvalid ? cumvalid[(long long)b * L + L - 1] : L);
+  const double pm = live ? (double)to_f(prev_mean[b * G + g]) : 0.0;
+  const long long off = (long long)b * L * G + (live ? g : 0);
+  Affine seg = affine_identity();
+  if (live)
+    for (int t = t1 - 1; t >= t0; --t) {
+      if (mb_ && mb_[t]) continue;
+      seg = affine_compose(tsn_step_map(in, off + (long long)t * G, G, t, pm, count_at(cumvalid, first, b, L, t)), seg);
+    }
+  // position j = nseg - 1 - sgi counts the segments in the order the backward pass meets them
+  const int j = nseg - 1 - sgi;
+  const int slot = j * GT + gl;
+  sh[0][slot] = seg.a;
+  sh[1][slot] = seg.b;
+  sh[2][slot] = seg.o1;
+  sh[3][slot] = seg.o2;
+  __syncthreads();
+  for (int step = 1; step < nseg; step <<= 1) {   // inclusive: P[j] = M_j o M_{j-1} o ... o M_0
+    Affine early = affine_identity(), late = affine_identity();
+    if (j >= step) {
+      const int e = slot - step * GT;
+      early = {sh[0][e], sh[1][e], sh[2][e], sh[3][e]};
+      late = {sh[0][slot], sh[1][slot], sh[2][slot], sh[3][slot]};
+    }
+    __syncthreads();
+    if (j >= step) {
+      const Affine r = affine_compose(late, early);
+      sh[0][slot] = r.a;
+      sh[1][slot] = r.b;
+      sh[2][slot] = r.o1;
+      sh[3][slot] = r.o2;
+    }
+    __syncthreads();
+  }
+  if (!live) return;
+  const double iu = to_f(dmean_out[b * G + g]), iv = to_f(dvar_out[b * G + g]);
+  if (sgi == 0) {   // every segment applied: the gradient of the carried statistics
+    dprev_mean[b * G + g] = from_f<T>((float)(sh[0][slot] * iu + sh[1][slot] * iv + sh[2][slot]));
+    dprev_var[b * G + g] = from_f<T>((float)(sh[0][slot] * iv + sh[3][slot]));
+  }
+  double u = iu, v = iv;
+  if (j > 0) {
+    const int e = slot - GT;
+    u = sh[0][e] * iu + sh[1][e] * iv + sh[2][e];
+    v = sh[0][e] * iv + sh[3][e];
+  }
   for (int t = t1 - 1; t >= t0; --t) {
     const long long e = off + (long long)t * G;
     if (mb_ && mb_[t]) {
@@ -646,6 +840,12 @@ void timestep_norm_fwd(const void* x, const long long* prev_count, const void* p
     }
     const int nseg = tsn_num_segments(L);
     const long long nsg = (long long)B * nseg * G;
+    const int gt = tsn_fused_groups(nseg);
+    if (gt > 0 && B <= 65535) {
+      tsn_scan_fused_kernel<T><<<dim3(div_up(G, gt), B), gt * nseg, 0, st>>>(
+          gu, gv, mask, prev_count, (const T*)prev_mean, (const T*)prev_var, count_out, (T*)mean_out, (T*)var_out,
+          cummean, cumrstd, L, G, nseg, gt, eps);
+    } else {
     tsn_seg_sums_kernel<<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, B, L, G, nseg);
     tsn_seg_prefix_kernel<T><<<div_up((long long)B * G, 128), 128, 0, st>>>(
         seg_scratch, prev_count, (const T*)prev_mean, (const T*)prev_var, count_out, (T*)mean_out, (T*)var_out,
@@ -653,6 +853,7 @@ void timestep_norm_fwd(const void* x, const long long* prev_count, const void* p
     tsn_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(gu, gv, mask, seg_scratch, (const T*)prev_mean,
                                                             (const T*)prev_var, cummean, cumrstd, B, L, G, nseg,
                                                             eps);
+    }
     if (vec) {
       const int grid = (int)std::min<long long>(div_up(rows * (H / 8), 256), 148LL * 16);
       tsn_apply_vec_kernel<T, W><<<grid, 256, 0, st>>>((const T*)x, cummean, cumrstd, (const W*)gamma,
@@ -693,12 +894,19 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
     if (mask != nullptr) tsn_cumvalid_kernel<<<div_up(B, 32), 32, 0, st>>>(mask, cumvalid, B, L);
     const int* cv = mask != nullptr ? cumvalid : nullptr;
     const StepIn in{ux, ds, db, cummean, cumrstd};
+    const int gt = tsn_fused_groups(nseg);
+    if (gt > 0 && B <= 65535) {
+      tsn_bwd_scan_fused_kernel<T><<<dim3(div_up(G, gt), B), gt * nseg, 0, st>>>(
+          in, mask, cv, count_final, (const T*)prev_mean, (const T*)dmean_out, (const T*)dvar_out, (T*)dprev_mean,
+          (T*)dprev_var, dux, dvx, L, G, nseg, gt);
+    } else {
     tsn_bwd_seg_maps_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
                                                                seg_scratch, B, L, G, nseg);
     tsn_bwd_seg_prefix_kernel<T><<<div_up((long long)B * G, 128), 128, 0, st>>>(
         seg_scratch, (const T*)dmean_out, (const T*)dvar_out, (T*)dprev_mean, (T*)dprev_var, B, G, nseg);
     tsn_bwd_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
                                                                 seg_scratch, dux, dvx, B, L, G, nseg);
+    }
     const int grid = (int)std::min<long long>(rows, vec ? 148LL * 2 : 148LL * 4);
     if (vec) {
       const int hv = H / 8;

@@ -27,6 +27,7 @@ def _C():
 # ----------------------------------------------------------------------------- GEMM / linear
 _GEMM_ERR = {}
 _GEMM_BACKEND = [os.environ.get("MEGALODON_B200_GEMM", "tcgen05")]
+_GEMV_MAX_ROWS = 4          # up to this many rows a product runs on the weight-streaming CUDA-core kernel
 _launches = [0]          # kernels launched by this framework (bench bookkeeping)
 
 
@@ -125,9 +126,11 @@ def gemm(a: Tensor, b: Tensor, bias: Optional[Tensor] = None, act: Optional[str]
                 out.copy_(res)
             res = out
         return res.to(out_dtype), (pre.to(out_dtype) if want_preact else None)
-    if (a.dim() == 2 and a.shape[0] <= 16 and not a_mn and not b_mn and mode == 0 and out is None
+    if (a.dim() == 2 and a.shape[0] <= _GEMV_MAX_ROWS and not a_mn and not b_mn and mode == 0 and out is None
             and not want_preact and not accumulate and not softmax):
-        # a few rows (decoding): one pass over the weights on the CUDA cores beats a 128-row MMA tile
+        # a few rows (decoding): one pass over the weights on the CUDA cores beats a 128-row MMA tile; its
+        # time grows with the rows (7B decode: 6.3 / 12.7 / 42 ms per token at 1 / 4 / 16 rows), the MMA
+        # tile's does not, and from about five rows the tile wins
         _bump()
         res = _C().gemv_small_m(a, b, bias, 1 if act == "silu" else 0, _DT[out_dtype], alpha)
         if res is not None:
@@ -198,7 +201,7 @@ def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Ten
     """x w^T + b + addend; `addend` has the shape of the result."""
     rows = x.numel() // x.shape[-1]
     if (x.dtype == torch.float32 or _GEMM_BACKEND[0] != "tcgen05" or addend.dtype != x.dtype
-            or w.shape[0] % 8 != 0 or rows <= 16 or not _tma_ok(x.reshape(-1, x.shape[-1]))):
+            or w.shape[0] % 8 != 0 or rows <= _GEMV_MAX_ROWS or not _tma_ok(x.reshape(-1, x.shape[-1]))):
         # (a few rows - decoding - stay on the weight-streaming kernel behind `linear`)
         return linear(x, w, b) + addend
     return _LinearAdd.apply(x, w, b, addend)

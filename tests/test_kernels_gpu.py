@@ -58,7 +58,8 @@ def test_rms_and_layer_norm(dtype, D):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("B,L,H,G,masked", [(2, 70, 64, 8, True), (1, 1, 128, 32, False),
-                                            (2, 1030, 256, 4, False), (1, 300, 96, 96, True)])
+                                            (2, 1030, 256, 4, False), (1, 300, 96, 96, True),
+                                            (1, 16500, 32, 4, True)])   # the last: longer than the one-CTA scan covers
 def test_timestep_norm(dtype, B, L, H, G, masked):
     from megalodon_b200 import ops
     from megalodon_b200.ops import reference

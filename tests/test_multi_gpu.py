@@ -442,3 +442,29 @@ def test_fsdp_reduce_scatter_fused_with_adamw_matches_separate_kernels():
             assert abs(l0 - l1) < 5e-2, (c0, c1)
         assert c1[-1] < c1[0], c1                       # it actually trains
         assert (s0 - s1).abs().max().item() < 2e-2, (s0 - s1).abs().max().item()
+
+
+def test_benchmark_restarts_on_nccl_after_a_host_made_rank_failure():
+    """Rank 1 of a two-GPU benchmark run raises on the host between two warm-up steps (nothing of it in
+    flight).  Rank 0's next bounded peer wait runs out, both ranks restart themselves with the NCCL
+    transport, meet at the new rendezvous port and finish; the result line says what happened."""
+    _need_gpus(2)
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0", MEGALODON_B200_BENCH_FAIL_AT="1:0",
+               MEGALODON_B200_PEER_TIMEOUT_S="2")
+    for k in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "MEGALODON_B200_BENCH_RESTARTED"):
+        env.pop(k, None)
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), os.path.join(root, "bench.py"), "--gpus", "2", "--steps", "2",
+           "--warmup", "3", "--layers", "2", "--seq-len", "16384", "--step-timeout-s", "60"]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-3000:]
+    line = [l for l in res.stdout.splitlines() if l.startswith("{")][-1]
+    out = json.loads(line)
+    assert "transport_fallback" in out["config"], out["config"]
+    assert "nccl" in out["config"]["parallelism"]
+    assert out["value"] > 0 and out["config"]["final_loss"] == out["config"]["final_loss"]
+    assert "restarting with --transport nccl" in res.stderr
