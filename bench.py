@@ -182,14 +182,20 @@ def reference_arm(args):
     why = ("reference not installable offline: `pip install --no-index` of the unmodified source fails "
            "(csrc/ops/attention_kernel.cu uses at::Context::alertCuBLASConfigNotDeterministic, removed from "
            "torch 2.11) and its model imports fairscale + apex, which are not in the wheelhouse")
-    ref_dir = os.path.join(ROOT, "baseline", "_ref", "megalodon")
-    if os.path.isdir(ref_dir):
+    ref_root = os.path.join(ROOT, "baseline", "_ref")
+    if os.path.isdir(os.path.join(ref_root, "megalodon")):
+        # an install exists: drive it through the reference's own API (baseline/reference_driver.py)
         try:
-            sys.path.insert(0, os.path.join(ROOT, "baseline", "_ref"))
-            import megalodon.model.mega  # noqa: F401
-            why = "reference imports but no driver for it is wired up"
+            sys.path.insert(0, os.path.join(ROOT, "baseline"))
+            import reference_driver
+            out = reference_driver.run(args, ref_root)
+            if out is not None:
+                out["metric"] = METRIC
+                out["vs_baseline"] = None
+                print(json.dumps(out))
+            return
         except Exception as e:  # noqa: BLE001
-            why = f"reference import fails: {type(e).__name__}: {e}"[:300]
+            why = f"reference installed but does not run: {type(e).__name__}: {e}"[:300]
     if int(os.environ.get("RANK", "0")) == 0:          # one line per job, also when launched as N ranks
         print(json.dumps({"impl": "reference", "unavailable": why}))
 
