@@ -105,6 +105,17 @@ class StepWatchdog:
         env["MASTER_PORT"] = str(int(env.get("MASTER_PORT", "29500")) + 1)
         env["TORCHELASTIC_USE_AGENT_STORE"] = "False"
         print(f"[rank {self.rank}] restarting with --transport nccl: {why}", file=sys.stderr, flush=True)
+        sys.stdout.flush()
+        # every descriptor but the standard three is marked close-on-exec (the driver's device files among
+        # them), so that this process' device memory is released when its successor takes over; marking,
+        # not closing, because the other threads of this process run until the exec
+        import fcntl
+        for name in os.listdir("/proc/self/fd"):
+            try:
+                if int(name) > 2:
+                    fcntl.fcntl(int(name), fcntl.F_SETFD, fcntl.FD_CLOEXEC)
+            except (OSError, ValueError):
+                pass
         os.execve(sys.executable, [sys.executable] + self.restart_argv, env)
 
     def _run(self):

@@ -74,8 +74,11 @@ std::tuple<Tensor, OptTensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, co
     dw = torch::zeros({D}, x.options().dtype(at::kFloat));
     wc = weight_code(x, *w);
   }
+  Tensor ws;     // partial column sums of the wide-row kernel (caching allocator: no device call)
+  if (w.has_value() && D > 1024) ws = torch::empty({(long long)mb::kColsumRows * D}, x.options().dtype(at::kFloat));
   mb::rms_norm_bwd(dy.data_ptr(), x.data_ptr(), opt_ptr(w), (float)w_off, rstd.data_ptr<float>(), dx.data_ptr(),
-                   dw.has_value() ? dw->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream());
+                   dw.has_value() ? dw->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream(),
+                   ws.defined() ? ws.data_ptr<float>() : nullptr);
   return {dx, dw};
 }
 
@@ -112,9 +115,12 @@ std::tuple<Tensor, OptTensor, OptTensor> layer_norm_bwd(const Tensor& dy, const 
     db = torch::zeros({D}, x.options().dtype(at::kFloat));
     wc = weight_code(x, *w);
   }
+  Tensor ws;
+  if (w.has_value() && D > 1024) ws = torch::empty({2LL * mb::kColsumRows * D}, x.options().dtype(at::kFloat));
   mb::layer_norm_bwd(dy.data_ptr(), x.data_ptr(), opt_ptr(w), (float)w_off, mean.data_ptr<float>(),
                      rstd.data_ptr<float>(), dx.data_ptr(), dw.has_value() ? dw->data_ptr<float>() : nullptr,
-                     db.has_value() ? db->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream());
+                     db.has_value() ? db->data_ptr<float>() : nullptr, M, D, dtype_code(x), wc, stream(),
+                     ws.defined() ? ws.data_ptr<float>() : nullptr);
   return {dx, dw, db};
 }
 
@@ -178,13 +184,14 @@ std::vector<Tensor> timestep_norm_bwd(const Tensor& dy, const Tensor& dmean, con
   const long long n = (long long)B * L * G;
   Tensor seg = torch::empty({4LL * B * mb::tsn_num_segments(L) * G}, x.options().dtype(at::kDouble));
   Tensor cumvalid = torch::empty({mask.has_value() ? (long long)B * L : 0}, x.options().dtype(at::kInt));
+  Tensor ws = torch::empty({2LL * mb::kColsumRows * H}, f32);    // partial sums of dgamma | dbeta per CTA
   mb::timestep_norm_bwd(dy.data_ptr(), dmean.data_ptr(), dvar.data_ptr(), x.data_ptr(), prev_mean.data_ptr(),
                         (const long long*)count.data_ptr<int64_t>(), cummean.data_ptr<float>(),
                         cumrstd.data_ptr<float>(), gamma.data_ptr(), (float)gamma_off,
                         mask.has_value() ? mask->data_ptr<bool>() : nullptr, dx.data_ptr(), dpm.data_ptr(),
                         dpv.data_ptr(), dgamma.data_ptr<float>(), dbeta.data_ptr<float>(), sp, sp + n, sp + 2 * n,
                         sp + 3 * n, sp + 4 * n, seg.data_ptr<double>(), cumvalid.data_ptr<int>(), B, L, H, (int)G,
-                        dtype_code(x), weight_code(x, gamma), stream());
+                        dtype_code(x), weight_code(x, gamma), stream(), ws.data_ptr<float>());
   return {dx, dpm, dpv, dgamma, dbeta};
 }
 

@@ -9,13 +9,20 @@ namespace mb {
 // ---- row-wise norms (norm_kernels.cu); weight dtype is fp32 or the activation dtype
 void rms_norm_fwd(const void* x, const void* w, float w_off, void* y, float* rstd, long long M, int D,
                   float eps, int x_dtype, int w_dtype, cudaStream_t st);
+// `colsum_ws`: kColsumRows * D floats (2 * kColsumRows * D for LayerNorm and TimestepNorm) or null.  With
+// it, every CTA of the wide-row kernels stores its partial column sums (the weight / bias gradients) as one
+// plain row and `colsum_finish` adds the rows up; without it the partial sums go out as atomics.  Either
+// way the sums are ADDED to dw / db.
+constexpr int kColsumRows = 296;
+void colsum_finish(const float* ws, int rows, int D, float* out0, float* out1, cudaStream_t st);
 void rms_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* rstd, void* dx,
-                  float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st);
+                  float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st,
+                  float* colsum_ws = nullptr);
 void layer_norm_fwd(const void* x, const void* w, const void* b, float w_off, void* y, float* mean,
                     float* rstd, long long M, int D, float eps, int x_dtype, int w_dtype, cudaStream_t st);
 void layer_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* mean,
                     const float* rstd, void* dx, float* dw, float* db, long long M, int D, int x_dtype,
-                    int w_dtype, cudaStream_t st);
+                    int w_dtype, cudaStream_t st, float* colsum_ws = nullptr);
 
 // ---- TimestepNorm (timestep_norm_kernels.cu)
 void timestep_norm_fwd(const void* x, const long long* prev_count, const void* prev_mean,
@@ -31,7 +38,8 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
                        const float* cumrstd, const void* gamma, float gamma_offset, const bool* mask,
                        void* dx, void* dprev_mean, void* dprev_var, float* dgamma, float* dbeta,
                        float* ux, float* ds, float* db, float* dux, float* dvx, double* seg_scratch,
-                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st);
+                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st,
+                       float* colsum_ws = nullptr);
 
 // ---- CEMA (cema_kernels.cu); complex tensors are interleaved (re, im) fp32
 constexpr int kCemaSegLen = 128;

@@ -231,7 +231,7 @@ __global__ void norm_bwd_vec_kernel(const T* __restrict__ dy, const T* __restric
                                     const W* __restrict__ weight, float weight_offset,
                                     const float* __restrict__ mean_in, const float* __restrict__ rstd_in,
                                     T* __restrict__ dx, float* __restrict__ dweight, float* __restrict__ dbias,
-                                    long long M, int D) {
+                                    long long M, int D, float* __restrict__ colsum_ws) {
   __shared__ float scratch[32];
   const int rows_per_cta = blockDim.x / ROW_THREADS;
   const int sub = threadIdx.x / ROW_THREADS;
@@ -296,7 +296,19 @@ __global__ void norm_bwd_vec_kernel(const T* __restrict__ dy, const T* __restric
       }
     }
   }
-  if (dweight != nullptr) {
+  if (dweight != nullptr && colsum_ws != nullptr) {
+    // one row of partial sums per CTA (one row per CTA iteration on this path: ROW_THREADS == blockDim.x)
+    constexpr int kSets = LAYER ? 2 : 1;
+    float* mine = colsum_ws + (long long)blockIdx.x * kSets * D;
+#pragma unroll
+    for (int i = 0; i < kVecVPT; ++i) {
+      const int g = t + i * ROW_THREADS;
+      if (g < nvec) {
+        store8(mine + 8 * g, acc_w[i]);
+        if (LAYER) store8(mine + D + 8 * g, acc_b[i]);
+      }
+    }
+  } else if (dweight != nullptr) {
 #pragma unroll
     for (int i = 0; i < kVecVPT; ++i) {
       const int g = t + i * ROW_THREADS;
@@ -308,6 +320,36 @@ __global__ void norm_bwd_vec_kernel(const T* __restrict__ dy, const T* __restric
         }
       }
     }
+  }
+}
+
+// out0[j] += sum over rows of ws[row][0][j] (and out1 from ws[row][1][j] when given): a warp owns 32
+// adjacent columns (128-byte reads), the 8 warps of a CTA take every 8th row and meet in shared memory.
+__global__ void colsum_finish_kernel(const float* __restrict__ ws, int rows, int D, float* __restrict__ out0,
+                                     float* __restrict__ out1) {
+  __shared__ float part[2][8][32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j = blockIdx.x * 32 + lane;
+  const int sets = out1 != nullptr ? 2 : 1;
+  float s0 = 0.f, s1 = 0.f;
+  if (j < D) {
+#pragma unroll 4
+    for (int r = warp; r < rows; r += 8) {
+      s0 += ws[((long long)r * sets) * D + j];
+      if (out1 != nullptr) s1 += ws[((long long)r * sets + 1) * D + j];
+    }
+  }
+  part[0][warp][lane] = s0;
+  part[1][warp][lane] = s1;
+  __syncthreads();
+  if (warp == 0 && j < D) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) {
+      s0 += part[0][w][lane];
+      s1 += part[1][w][lane];
+    }
+    out0[j] += s0;
+    if (out1 != nullptr) out1[j] += s1;
   }
 }
 
@@ -357,19 +399,22 @@ void launch_fwd(const void* x, const void* w, const void* b, float off, void* y,
 
 template <typename T, typename W, bool LAYER>
 void launch_bwd(const void* dy, const void* x, const void* w, float off, const float* mean,
-                const float* rstd, void* dx, float* dw, float* db, long long M, int D, cudaStream_t st) {
+                const float* rstd, void* dx, float* dw, float* db, long long M, int D, cudaStream_t st,
+                float* ws) {
   if (D <= 1024 && vec_ok(D, 32, {dy, x, w, dx})) {
     const int threads = 128, rows = threads / 32;
     const int grid = (int)std::min<long long>((M + rows - 1) / rows, 148LL * 4);
     VPT_SWITCH(D, 32, (norm_bwd_vec_kernel<T, W, LAYER, 32, VPT><<<grid, threads, 0, st>>>(
-                           (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D)));
+                           (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D, nullptr)));
     return;
   }
   if (D > 1024 && vec_ok(D, 256, {dy, x, w, dx})) {
-    // one resident wave: the per-CTA column sums end in D atomics each, and those dominate beyond that
-    const int grid = (int)std::min<long long>(M, 148LL * 2);
+    // one resident wave (the accumulators of the column sums cap the kernel at two CTAs per SM)
+    const int grid = (int)std::min<long long>(M, (long long)kColsumRows);
+    float* use_ws = (dw != nullptr && (!LAYER || db != nullptr)) ? ws : nullptr;
     VPT_SWITCH(D, 256, (norm_bwd_vec_kernel<T, W, LAYER, 256, VPT><<<grid, 256, 0, st>>>(
-                            (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D)));
+                            (const T*)dy, (const T*)x, (const W*)w, off, mean, rstd, (T*)dx, dw, db, M, D, use_ws)));
+    if (use_ws != nullptr) colsum_finish(use_ws, grid, D, dw, LAYER ? db : nullptr, st);
     return;
   }
   if (D <= 1024) {
@@ -405,10 +450,14 @@ void rms_norm_fwd(const void* x, const void* w, float w_off, void* y, float* rst
   NORM_DISPATCH(x_dtype, w_dtype, (launch_fwd<T, W, false>(x, w, nullptr, w_off, y, nullptr, rstd, M, D, eps, st)));
 }
 
+void colsum_finish(const float* ws, int rows, int D, float* out0, float* out1, cudaStream_t st) {
+  colsum_finish_kernel<<<(D + 31) / 32, 256, 0, st>>>(ws, rows, D, out0, out1);
+}
+
 void rms_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* rstd, void* dx,
-                  float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st) {
+                  float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st, float* colsum_ws) {
   NORM_DISPATCH(x_dtype, w_dtype,
-                (launch_bwd<T, W, false>(dy, x, w, w_off, nullptr, rstd, dx, dw, nullptr, M, D, st)));
+                (launch_bwd<T, W, false>(dy, x, w, w_off, nullptr, rstd, dx, dw, nullptr, M, D, st, colsum_ws)));
 }
 
 void layer_norm_fwd(const void* x, const void* w, const void* b, float w_off, void* y, float* mean,
@@ -418,9 +467,9 @@ void layer_norm_fwd(const void* x, const void* w, const void* b, float w_off, vo
 
 void layer_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* mean,
                     const float* rstd, void* dx, float* dw, float* db, long long M, int D, int x_dtype,
-                    int w_dtype, cudaStream_t st) {
+                    int w_dtype, cudaStream_t st, float* colsum_ws) {
   NORM_DISPATCH(x_dtype, w_dtype,
-                (launch_bwd<T, W, true>(dy, x, w, w_off, mean, rstd, dx, dw, db, M, D, st)));
+                (launch_bwd<T, W, true>(dy, x, w, w_off, mean, rstd, dx, dw, db, M, D, st, colsum_ws)));
 }
 
 }  // namespace mb

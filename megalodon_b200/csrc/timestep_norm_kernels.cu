@@ -710,7 +710,7 @@ __global__ void tsn_bwd_apply_vec_kernel(const T* __restrict__ dy, const T* __re
                                          const float* __restrict__ dvx, const W* __restrict__ gamma,
                                          float gamma_offset, const bool* __restrict__ mask, T* __restrict__ dx,
                                          float* __restrict__ dgamma, float* __restrict__ dbeta, long long rows,
-                                         int H, int G) {
+                                         int H, int G, float* __restrict__ colsum_ws) {
   const int Dg = H / G;
   const int hv = H / 8;
   const float inv_d = 1.f / Dg;
@@ -753,6 +753,18 @@ __global__ void tsn_bwd_apply_vec_kernel(const T* __restrict__ dy, const T* __re
       }
       store8(dx + e, o);
     }
+  }
+  if (colsum_ws != nullptr) {   // one row of partial sums per CTA: [dgamma | dbeta]
+    float* mine = colsum_ws + (long long)blockIdx.x * 2 * H;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * kBwdThreads;
+      if (c < hv) {
+        store8(mine + c * 8, acc_g[i]);
+        store8(mine + H + c * 8, acc_b[i]);
+      }
+    }
+    return;
   }
 #pragma unroll
   for (int i = 0; i < VPT; ++i) {
@@ -871,7 +883,8 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
                        const float* cumrstd, const void* gamma, float gamma_offset, const bool* mask,
                        void* dx, void* dprev_mean, void* dprev_var, float* dgamma, float* dbeta,
                        float* ux, float* ds, float* db, float* dux, float* dvx, double* seg_scratch,
-                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st) {
+                       int* cumvalid, int B, int L, int H, int G, int x_dtype, int w_dtype, cudaStream_t st,
+                       float* colsum_ws) {
   const long long rows = (long long)B * L;
   const int lpg = pick_lpg(H / G);
   TSN_DISPATCH(x_dtype, w_dtype, {
@@ -907,21 +920,22 @@ void timestep_norm_bwd(const void* dy, const void* dmean_out, const void* dvar_o
     tsn_bwd_seg_apply_kernel<T><<<div_up(nsg, 256), 256, 0, st>>>(in, mask, cv, count_final, (const T*)prev_mean,
                                                                 seg_scratch, dux, dvx, B, L, G, nseg);
     }
-    const int grid = (int)std::min<long long>(rows, vec ? 148LL * 2 : 148LL * 4);
+    const int grid = (int)std::min<long long>(rows, vec ? (long long)kColsumRows : 148LL * 4);
     if (vec) {
       const int hv = H / 8;
       if (hv <= kBwdThreads)
         tsn_bwd_apply_vec_kernel<T, W, 1><<<grid, kBwdThreads, 0, st>>>(
             (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
-            dgamma, dbeta, rows, H, G);
+            dgamma, dbeta, rows, H, G, colsum_ws);
       else if (hv <= 2 * kBwdThreads)
         tsn_bwd_apply_vec_kernel<T, W, 2><<<grid, kBwdThreads, 0, st>>>(
             (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
-            dgamma, dbeta, rows, H, G);
+            dgamma, dbeta, rows, H, G, colsum_ws);
       else
         tsn_bwd_apply_vec_kernel<T, W, 4><<<grid, kBwdThreads, 0, st>>>(
             (const T*)dy, (const T*)x, cummean, cumrstd, ux, dux, dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,
-            dgamma, dbeta, rows, H, G);
+            dgamma, dbeta, rows, H, G, colsum_ws);
+      if (colsum_ws != nullptr) colsum_finish(colsum_ws, grid, H, dgamma, dbeta, st);
     } else
     tsn_bwd_apply_kernel<T, W><<<grid, kBwdThreads, 0, st>>>((const T*)dy, (const T*)x, cummean, cumrstd, ux, dux,
                                                      dvx, (const W*)gamma, gamma_offset, mask, (T*)dx,

@@ -973,3 +973,29 @@ def test_decode_attention_reads_only_the_filled_slots(B, H, C, dk, dv, pos):
     ref = torch.einsum("bhc,bhcd->bhd", torch.softmax(s, -1), vb[:, :, :pos + 1].float())
     assert torch.isfinite(out.float()).all()
     _close(out, ref, 2e-2, 2e-2, "decode attention")
+
+
+@pytest.mark.parametrize("kind", ["rms", "layer"])
+def test_norm_backward_weight_gradients_with_more_rows_than_ctas(kind):
+    """2048 rows of 4096: every CTA of the backward kernel walks several rows and leaves one row of partial
+    column sums in the workspace, which the finishing kernel adds up."""
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import reference
+    torch.manual_seed(5)
+    dev = _dev()
+    x = torch.randn(1, 2048, 4096, device=dev).bfloat16()
+    w = (torch.randn(4096, device=dev) * 0.1).bfloat16()
+    b = (torch.randn(4096, device=dev) * 0.1).bfloat16()
+    g = torch.randn_like(x)
+    got = []
+    for mod, dt in ((ops, torch.bfloat16), (reference, torch.float32)):
+        xs, ws, bs = (t.to(dt).clone().requires_grad_() for t in (x, w, b))
+        y = mod.rms_norm(xs, ws, 1e-5, 1.0) if kind == "rms" else mod.layer_norm(xs, ws, bs, 1e-5, 1.0)
+        y.backward(g.to(dt))
+        got.append((xs.grad, ws.grad, bs.grad))
+    for name, a, r in zip(("dx", "dw", "db"), got[0], got[1]):
+        if a is None:
+            assert name == "db" and kind == "rms"
+            continue
+        rel = (a.float() - r).norm() / r.norm()
+        assert rel < 2e-2, f"{kind} {name}: relative error {rel:.4f}"
