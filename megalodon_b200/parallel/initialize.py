@@ -112,7 +112,18 @@ def initialize_model_parallel(
             if k == my_mp:
                 topo.shard_group, topo.shard_ranks = g, ranks
     elif cp > 1:
-        topo.shard_group, topo.shard_ranks = topo.cp_group, topo.cp_ranks
+        # The same ranks as the chunk group, but a communicator of its own.  The chunk group carries the
+        # rank-to-rank hand-off of the CEMA / TimestepNorm state, which the ranks of a line issue at
+        # different points of their programs (one sends where its neighbour receives); parameter gathers
+        # and gradient reduce-scatters issued into the SAME communicator are ordered against those
+        # transfers in issue order, and two neighbours that interleave them differently wait for each
+        # other for ever (rank r: reduce-scatter, then send; rank r-1: receive, then reduce-scatter).
+        for i in range(dp):
+            for k in range(mp):
+                ranks = grid[i, :, k].tolist()
+                g = dist.new_group(ranks, backend=ddp_backend, **tkw)
+                if (i, k) == (my_dp, my_mp):
+                    topo.shard_group, topo.shard_ranks = g, ranks
     else:
         topo.shard_group, topo.shard_ranks = topo.dp_group, topo.dp_ranks
     topo.ready = True
