@@ -187,9 +187,9 @@ class _LinearAdd(torch.autograd.Function):
             dx = dx.view(ctx.x_shape)
         if ctx.needs_input_grad[1]:
             sink = ctx.wgrad_sink
-            target = sink() if sink is not None else None
-            if target is not None and target.dtype == g.dtype:
-                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=True)
+            if sink is not None and w.dtype == g.dtype:
+                target, add = sink()
+                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=add)
             else:
                 dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
@@ -245,9 +245,9 @@ class _Linear(torch.autograd.Function):
             # unit's flat gradient: the weight gradient is accumulated there by the GEMM epilogue and
             # nothing is handed to autograd (no per-parameter tensor, no concatenation, no add).
             sink = ctx.wgrad_sink
-            target = sink() if sink is not None else None
-            if target is not None and target.dtype == g.dtype:
-                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=True)
+            if sink is not None and w.dtype == g.dtype:
+                target, add = sink()        # first product of the iteration writes, later ones accumulate
+                gemm(g, x2, None, None, a_mn=True, b_mn=True, out=target, accumulate=add)
             else:
                 dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)   # [M, N]^T x [M, K] -> [N, K]
         if ctx.has_bias and ctx.needs_input_grad[2]:

@@ -471,30 +471,73 @@ class FullyShardedDataParallel(nn.Module):
         fused = {i.name for i in getattr(self, "_fused_infos", ())}
         for info, v in zip(self._infos, views):
             if direct and len(info.shape) == 2:
-                v._wgrad_sink = functools.partial(self._grad_view, info)
+                v._wgrad_sink = _WgradSink(self, info)
             if info.name in fused:
                 v._gather_spec = _GatherSpec(self, info)
             for mod, pname, _ in info.owners:
                 mod.__dict__[pname] = v
 
     def _grad_buffer(self) -> torch.Tensor:
-        """Flat gradient of this iteration in compute dtype, zero-filled on first use."""
+        """Flat gradient of this iteration in compute dtype.  Nothing is zero-filled up front: the first
+        contribution to a parameter's range is written (the weight-gradient GEMM runs without its
+        accumulating epilogue, other gradients are copied), later ones are added, and what received
+        nothing is zeroed when the unit's gradients leave (`_zero_unwritten`).  Only the gaps between
+        parameters and the padding at the end are cleared here."""
         if self._flat_grad is None:
-            self._flat_grad = torch.zeros(self._numel_padded, dtype=self._full.dtype, device=self._full.device)
+            self._flat_grad = torch.empty(self._numel_padded, dtype=self._full.dtype, device=self._full.device)
+            self._grad_unwritten = {id(info) for info in self._infos}
+            for a, b in self._grad_gaps():
+                self._flat_grad[a:b].zero_()
         return self._flat_grad
+
+    def _grad_gaps(self):
+        gaps = getattr(self, "_grad_gap_list", None)
+        if gaps is None:
+            gaps, pos = [], 0
+            for info in sorted(self._infos, key=lambda i: i.offset):
+                if info.offset > pos:
+                    gaps.append((pos, info.offset))
+                pos = max(pos, info.offset + info.numel)
+            if pos < self._numel_padded:
+                gaps.append((pos, self._numel_padded))
+            self._grad_gap_list = gaps
+        return gaps
 
     def _grad_view(self, info: "_ParamInfo") -> torch.Tensor:
         return self._grad_buffer()[info.offset:info.offset + info.numel].view(info.shape)
+
+    def _claim_first_write(self, info: "_ParamInfo") -> bool:
+        """True once per parameter and iteration: the caller must overwrite the range, not add to it."""
+        self._grad_buffer()
+        if id(info) in self._grad_unwritten:
+            self._grad_unwritten.discard(id(info))
+            return True
+        return False
+
+    def _zero_unwritten(self) -> None:
+        buf = self._grad_buffer()
+        for info in self._infos:
+            if id(info) in self._grad_unwritten:
+                buf[info.offset:info.offset + info.numel].zero_()
+        self._grad_unwritten = set()
 
     def _collect_grads(self, grads) -> None:
         """Backward of `_FlatViews`: add the gradients autograd produced (everything except weights
         whose GEMM already accumulated into the buffer), then see whether the unit is complete."""
         buf = self._grad_buffer()
-        dsts, srcs = [], []
+        dsts, srcs, cdst, csrc = [], [], [], []
         for info, g in zip(self._infos, grads):
             if g is not None:
-                dsts.append(buf[info.offset:info.offset + info.numel])
-                srcs.append(g.reshape(-1) if g.dtype == buf.dtype else g.reshape(-1).to(buf.dtype))
+                dst = buf[info.offset:info.offset + info.numel]
+                src = g.reshape(-1) if g.dtype == buf.dtype else g.reshape(-1).to(buf.dtype)
+                if self._claim_first_write(info):
+                    cdst.append(dst)
+                    csrc.append(src)
+                else:
+                    dsts.append(dst)
+                    srcs.append(src)
+        if cdst:
+            torch._foreach_copy_(cdst, csrc)
         if dsts:
             torch._foreach_add_(dsts, srcs)      # a couple of multi-tensor launches instead of one per parameter
         self._post_backward()
@@ -563,6 +606,7 @@ class FullyShardedDataParallel(nn.Module):
         expected = self._calls if isinstance(self._wrapped, CheckpointWrapper) else 1
         if self._fires < expected and not force:
             return None          # keep accumulating in the flat gradient buffer
+        self._zero_unwritten()
         flat_grad = self._grad_buffer()
         self._flat_grad = None
         self._full_leaf = None
@@ -939,6 +983,21 @@ class FullyShardedDataParallel(nn.Module):
                 f"mixed_precision={self.mixed_precision}, compute_dtype={self.compute_dtype}, "
                 f"fp32_reduce_scatter={self.fp32_reduce_scatter}, "
                 f"reshard_after_forward={self.reshard_after_forward}")
+
+
+class _WgradSink:
+    """Carried by a 2-D weight view: where its gradient goes.  Calling it returns the matching view of the
+    unit's flat gradient and whether the product has to be ADDED to what is there (False the first time in
+    an iteration: the range is still uninitialised memory and the GEMM writes it)."""
+
+    __slots__ = ("unit", "info")
+
+    def __init__(self, unit, info):
+        self.unit, self.info = unit, info
+
+    def __call__(self):
+        first = self.unit._claim_first_write(self.info)
+        return self.unit._grad_view(self.info), not first
 
 
 class _GatherSpec:
