@@ -45,7 +45,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--ckpt-layers", type=int, default=None,
-                    help="checkpoint only the first K layers (default: 28 at N=1, 16 at N=2, none from N=4)")
+                    help="checkpoint only the first K layers (default: 27 at N=1, 8 at N=2, none from N=4)")
     ap.add_argument("--kernel-profile", default=None,
                     help="after the timed regions, run one more step under torch.profiler and write a per-kernel "
                          "summary to this path (rank number appended); never part of a reported number")
@@ -239,9 +239,9 @@ def main():
         return
     try:
         run(args)
-    except Exception as e:  # noqa: BLE001 - a peer-transport run gets its one restart on NCCL, whatever failed
-        if not _WATCHDOG or _WATCHDOG[0].restart_argv is None:
-            raise
+    except Exception as e:  # noqa: BLE001 - a peer-transport run gets its one restart on NCCL
+        if not _WATCHDOG or _WATCHDOG[0].restart_argv is None or "OutOfMemory" in type(e).__name__:
+            raise               # (running out of memory has nothing to do with the transport)
         import traceback
         traceback.print_exc()
         _WATCHDOG[0]._leave(5, f"{type(e).__name__}: {e}"[:200])
@@ -290,14 +290,16 @@ def run(args):
     if args.ckpt_layers is not None:
         cfg.ckpt_layers = args.ckpt_layers
     elif chunks_local == 8:
-        # N = 1: 138 GB of optimiser state; four un-checkpointed layers bring the peak to 154 GB allocated
-        # (170 GB reserved) and save their recomputation
-        cfg.ckpt_layers = 28
+        # N = 1: 138 GB of optimiser state and 7.6 GB of activations per un-checkpointed layer; measured peaks
+        # with growable segments: 28 checkpointed layers 153.6 GB, 26 168.8 GB, 25 176.4 GB (of 178.4)
+        cfg.ckpt_layers = 27
     elif chunks_local == 4:
-        # N = 2: state 86 GB + about 3 GB of activations per un-checkpointed layer; 16 of 32 checkpointed
-        # peaks at 139 GB allocated (148 GB reserved).  Ten checkpointed layers (170 GB reserved) ran into
-        # allocator retries and was slower.
-        cfg.ckpt_layers = 16
+        # N = 2: state 86 GB + 2.7 GB of activations per un-checkpointed layer.  Measured with growable
+        # segments and the parameter gathers in peer memory: 16 checkpointed layers 130.6 GB and 1410 ms,
+        # 8 layers 161.0 GB and 1292 ms, 4 layers out of memory.  The NCCL transport holds 9 GB more
+        # (gather and reduce-scatter staging), so a restarted run goes back to 16.
+        cfg.ckpt_layers = 8 if (args.transport == "peer" and not os.environ.get("MEGALODON_B200_BENCH_RESTARTED")
+                                and not library) else 16
     if library and cfg.layerwise_ckpt and args.ckpt_layers is None:
         # the materialised fp32 scores add about 3 GB per un-checkpointed layer and 32K tokens
         cfg.ckpt_layers = 32 if chunks_local == 8 else 24
