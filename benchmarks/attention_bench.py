@@ -21,6 +21,7 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--only", default=None, help="substring of the product names to run (for a profiler capture)")
     args = ap.parse_args()
     import torch
     from megalodon_b200.ops import cuda_ops
@@ -36,7 +37,9 @@ def main():
     do = torch.randn(B, L, H, dv, device=dev).bfloat16()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
 
-    def timed(fn):
+    def timed(fn, name=None):
+        if args.only and (name is None or args.only not in name):
+            return None
         for _ in range(3):
             fn()
         tot = 0.0
@@ -62,31 +65,33 @@ def main():
     rows = []
 
     def row(name, ms, flops):
+        if ms is None:
+            return
         rows.append({"product": name, "ms": round(ms, 4), "gflop": round(flops / 1e9, 1),
                      "tflops": round(flops / ms / 1e9, 1), "fraction_of_sustained_cublas": round(flops / (ms / 1e3) / peak, 3)})
 
-    row("Q K^T pass 1 (row maxima only)", timed(lambda: cuda_ops.gemm(qb, kb, out=Pb, mode=1, alpha=1.0, softmax=dict(epi_kind=1, row_out=rmax[0]))), f_qk)
-    row("Q K^T pass 2 (exp, row sums, P written)", timed(lambda: cuda_ops.gemm(qb, kb, out=Pb, mode=1, alpha=1.0, softmax=dict(epi_kind=2, row_in=rmax[0], row_out=rsum[0]))), f_qk)
-    row("P V (scaled by 1 / row sum)", timed(lambda: cuda_ops.gemm(Pb, vb, b_mn=True, out=ob, mode=2, softmax=dict(epi_kind=3, row_in=rsum[0]))), f_pv)
+    row("Q K^T pass 1 (row maxima only)", timed(lambda: cuda_ops.gemm(qb, kb, out=Pb, mode=1, alpha=1.0, softmax=dict(epi_kind=1, row_out=rmax[0])), "Q K^T pass 1 (row maxima only)"), f_qk)
+    row("Q K^T pass 2 (exp, row sums, P written)", timed(lambda: cuda_ops.gemm(qb, kb, out=Pb, mode=1, alpha=1.0, softmax=dict(epi_kind=2, row_in=rmax[0], row_out=rsum[0])), "Q K^T pass 2 (exp, row sums, P written)"), f_qk)
+    row("P V (scaled by 1 / row sum)", timed(lambda: cuda_ops.gemm(Pb, vb, b_mn=True, out=ob, mode=2, softmax=dict(epi_kind=3, row_in=rsum[0])), "P V (scaled by 1 / row sum)"), f_pv)
     dos, delta = cuda_ops._C().attn_bwd_prep(do, out, rsum)
-    row("attn_bwd_prep (delta, dO / row sum)", timed(lambda: cuda_ops._C().attn_bwd_prep(do, out, rsum)), 0.0)
+    row("attn_bwd_prep (delta, dO / row sum)", timed(lambda: cuda_ops._C().attn_bwd_prep(do, out, rsum), "attn_bwd_prep (delta, dO / row sum)"), 0.0)
     dvb = hv(torch.empty_like(v), 0)
     dqb = hv(torch.empty_like(q), 0)
     dkb = hv(torch.empty_like(k), 0)
-    row("dV = P^T dO'", timed(lambda: cuda_ops.gemm(Pb, hv(dos, 0), a_mn=True, b_mn=True, out=dvb, mode=3)), f_pv)
+    row("dV = P^T dO'", timed(lambda: cuda_ops.gemm(Pb, hv(dos, 0), a_mn=True, b_mn=True, out=dvb, mode=3), "dV = P^T dO'"), f_pv)
     P2 = P.clone()
-    row("dS from dO V^T (epilogue over P)", timed(lambda: cuda_ops.gemm(dob, vb, out=P2[0], mode=1, softmax=dict(epi_kind=4, row_in=rsum[0], row_in2=delta[0], aux=P2[0]))), f_pv)
-    row("dQ = dS K", timed(lambda: cuda_ops.gemm(Pb, kb, b_mn=True, out=dqb, mode=2, alpha=1.0)), f_qk)
-    row("dK = dS^T Q", timed(lambda: cuda_ops.gemm(Pb, qb, a_mn=True, b_mn=True, out=dkb, mode=3, alpha=1.0)), f_qk)
+    row("dS from dO V^T (epilogue over P)", timed(lambda: cuda_ops.gemm(dob, vb, out=P2[0], mode=1, softmax=dict(epi_kind=4, row_in=rsum[0], row_in2=delta[0], aux=P2[0])), "dS from dO V^T (epilogue over P)"), f_pv)
+    row("dQ = dS K", timed(lambda: cuda_ops.gemm(Pb, kb, b_mn=True, out=dqb, mode=2, alpha=1.0), "dQ = dS K"), f_qk)
+    row("dK = dS^T Q", timed(lambda: cuda_ops.gemm(Pb, qb, a_mn=True, b_mn=True, out=dkb, mode=3, alpha=1.0), "dK = dS^T Q"), f_qk)
 
     qr, kr, vr = (t.clone().requires_grad_() for t in (q, k, v))
-    row("forward (op)", timed(lambda: cuda_ops.attention(qr, kr, vr, 1.0, 0.0, True, True)), 2 * f_qk + f_pv)
+    row("forward (op)", timed(lambda: cuda_ops.attention(qr, kr, vr, 1.0, 0.0, True, True), "forward (op)"), 2 * f_qk + f_pv)
 
     def fwd_bwd():
         o = cuda_ops.attention(qr, kr, vr, 1.0, 0.0, True, True)
         o.backward(do)
         qr.grad = kr.grad = vr.grad = None
-    row("forward + backward (op)", timed(fwd_bwd), 4 * f_qk + 3 * f_pv)
+    row("forward + backward (op)", timed(fwd_bwd, "forward + backward (op)"), 4 * f_qk + 3 * f_pv)
     cuda_ops.check_kernel_errors()
     print(json.dumps({"bench": "attention", "tokens": L, "heads": H, "d_qk": dk, "d_v": dv, "dtype": "bf16",
                       "peak_tflops_sustained": peak / 1e12, "rows": rows}))

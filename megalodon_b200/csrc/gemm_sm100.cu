@@ -509,7 +509,10 @@ struct PairSmem {
   static constexpr int b_bytes = (kPairBN / 2) * BK * 2;      // this CTA's 128 rows of B
   static constexpr int stage_bytes = a_bytes + b_bytes;       // 32 KiB
   static constexpr int bar_offset = kPairStages * stage_bytes;
-  static constexpr int total = bar_offset + 256 + 1024;
+  // one staging buffer per epilogue warp: 32 rows x 128 bytes (64 columns of a 16-bit output)
+  static constexpr int epi_stage_bytes = 32 * 128;
+  static constexpr int epi_offset = bar_offset + 256;
+  static constexpr int total = epi_offset + kEpiWarps * epi_stage_bytes + 1024;
 };
 
 __device__ __forceinline__ bool pair_tile_skipped(const GemmParams& p, int m0, int n0) {
@@ -526,10 +529,50 @@ __device__ __forceinline__ void pair_k_range(const GemmParams& p, int m0, int nu
 constexpr int kGatherWarps = 4;                 // copy warps of the gathering variant
 constexpr int kGatherUnitBytes = 8192;          // one claim: 32 lanes x 16 loads of 16 bytes
 
+// Tiles of one batch element that the kernel computes: with mode 1 (causal scores) only those on or below
+// the diagonal.
+__device__ __forceinline__ int pair_tiles_per_batch(const GemmParams& p, int num_m, int num_n) {
+  if (p.mode != 1) return num_m * num_n;
+  int t = 0;
+  for (int mt = 0; mt < num_m; ++mt) t += min(mt + 1, num_n);
+  return t;
+}
+
 // Tile -> (m0, n0, batch).  With a gathered B the n-tiles are walked starting at this rank's own rows,
-// whose chunks are copied first.
+// whose chunks are copied first.  The causal modes hand every CTA pair tiles `pair, pair + P, ...` of an
+// ORDER chosen for balance: mode 1 numbers only the tiles it computes (the plain order left a pair with up
+// to 10 of them against a mean of 7.4); modes 2 and 3, whose k loop grows with the distance from the
+// diagonal, order all tiles of all batch elements from the longest k loop to the shortest and deal them
+// out in alternating direction (the plain order: 0.84 of the mean on the busiest pair, this one 0.97).
 __device__ __forceinline__ void pair_tile_coords(const GemmParams& p, int tile, int num_m, int num_n,
-                                                 int tiles_per_batch, int& m0, int& n0, int& bz) {
+                                                 int tiles_per_batch, int num_pairs, int& m0, int& n0, int& bz) {
+  if (p.mode >= 1 && p.mode <= 3 && p.g_world == 0) {
+    const int num_tiles = tiles_per_batch * p.batch;
+    const int round = tile / num_pairs;
+    int pos = tile - round * num_pairs;
+    if (round & 1) pos = min(num_pairs, num_tiles - round * num_pairs) - 1 - pos;
+    const int i = round * num_pairs + pos;
+    int mt, nt;
+    if (p.mode == 1) {
+      bz = i / tiles_per_batch;
+      int t = i - bz * tiles_per_batch;
+      mt = 0;
+      while (t >= min(mt + 1, num_n)) {
+        t -= min(mt + 1, num_n);
+        ++mt;
+      }
+      nt = t;
+    } else {
+      const int per_m = num_n * p.batch;
+      const int q = i / per_m, rem = i - q * per_m;
+      mt = p.mode == 2 ? num_m - 1 - q : q;       // longest k loop first
+      bz = rem / num_n;
+      nt = rem - bz * num_n;
+    }
+    m0 = mt * kPairBM;
+    n0 = nt * kPairBN;
+    return;
+  }
   bz = tile / tiles_per_batch;
   const int t = tile - bz * tiles_per_batch;
   int nt = t / num_m;
@@ -600,6 +643,138 @@ __device__ __forceinline__ void gather_copy_warp(const GemmParams& p, int lane) 
   }
 }
 
+// ---- staged epilogue of the pair kernel (16-bit outputs).  A thread owns one row of the accumulator, so
+// writing its 32 columns straight to global memory makes every warp store touch 32 different lines, 16
+// bytes each: the load/store unit, not DRAM, bounds products with short k loops (attention scores: 77 %
+// of the L1 data path busy, tensor pipe 12 %).  Instead the warp collects 64 columns (128 bytes per row)
+// in shared memory and moves them with 8 instructions that each cover 4 whole rows; inputs of the
+// epilogue (the accumulated C, an addend, the stored probabilities of the dS epilogue) come in the same
+// way.  Pieces of 16 bytes are XOR-swizzled by the row, which makes both directions conflict-free.
+__device__ __forceinline__ uint32_t epi_stage_addr(uint32_t base, int row, int piece) {
+  return base + row * 128 + ((piece ^ (row & 7)) << 4);
+}
+__device__ __forceinline__ void lds128(uint32_t addr, uint4& v) {
+  asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+}
+__device__ __forceinline__ void sts128(uint32_t addr, const uint4& v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+template <typename OutT>
+__device__ __forceinline__ uint32_t pack2(float a, float b);
+template <>
+__device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 t = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 t = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&t);
+}
+template <>
+__device__ __forceinline__ uint32_t pack2<float>(float a, float) { return __float_as_uint(a); }   // never used
+template <typename OutT>
+__device__ __forceinline__ void unpack2(uint32_t w, float& a, float& b);
+template <>
+__device__ __forceinline__ void unpack2<__nv_bfloat16>(uint32_t w, float& a, float& b) {
+  a = __uint_as_float(w << 16);
+  b = __uint_as_float(w & 0xffff0000u);
+}
+template <>
+__device__ __forceinline__ void unpack2<__half>(uint32_t w, float& a, float& b) {
+  const __half2 t = *reinterpret_cast<__half2*>(&w);
+  a = __low2float(t);
+  b = __high2float(t);
+}
+template <>
+__device__ __forceinline__ void unpack2<float>(uint32_t w, float& a, float& b) { a = b = __uint_as_float(w); }
+// global [32 rows x 64 columns] <-> the warp's staging buffer; rows >= rows_valid are skipped
+template <typename OutT>
+__device__ __forceinline__ void epi_stage_in(uint32_t stg, const OutT* src, long long ld, int rows_valid, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r = 4 * j + (lane >> 3), q = lane & 7;
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + (long long)r * ld + q * 8);
+    sts128(epi_stage_addr(stg, r, q), v);
+  }
+}
+template <typename OutT>
+__device__ __forceinline__ void epi_stage_out(uint32_t stg, OutT* dst, long long ld, int rows_valid, int lane) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int r = 4 * j + (lane >> 3), q = lane & 7;
+    uint4 v;
+    lds128(epi_stage_addr(stg, r, q), v);
+    if (r < rows_valid) *reinterpret_cast<uint4*>(dst + (long long)r * ld + q * 8) = v;
+  }
+}
+// the thread's own row: 32 columns (half h of the 64) as floats
+template <typename OutT>
+__device__ __forceinline__ void epi_stage_get(uint32_t stg, int lane, int h, float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w;
+    lds128(epi_stage_addr(stg, lane, h * 4 + i), w);
+    unpack2<OutT>(w.x, v[8 * i + 0], v[8 * i + 1]);
+    unpack2<OutT>(w.y, v[8 * i + 2], v[8 * i + 3]);
+    unpack2<OutT>(w.z, v[8 * i + 4], v[8 * i + 5]);
+    unpack2<OutT>(w.w, v[8 * i + 6], v[8 * i + 7]);
+  }
+}
+template <typename OutT>
+__device__ __forceinline__ void epi_stage_put(uint32_t stg, int lane, int h, const float (&v)[32]) {
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 w;
+    w.x = pack2<OutT>(v[8 * i + 0], v[8 * i + 1]);
+    w.y = pack2<OutT>(v[8 * i + 2], v[8 * i + 3]);
+    w.z = pack2<OutT>(v[8 * i + 4], v[8 * i + 5]);
+    w.w = pack2<OutT>(v[8 * i + 6], v[8 * i + 7]);
+    sts128(epi_stage_addr(stg, lane, h * 4 + i), w);
+  }
+}
+// Per-row constants of the fused epilogues, folded so that an element costs one FMA plus the operation
+// itself: exp(alpha s - m) = 2^(s * alpha log2e - m log2e); dS = p~ (s * alpha / l - delta / l).
+struct EpiFold {
+  float k1, k2;
+};
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// 32 columns of the thread's row: raw accumulator `r` -> values to store in `v`.  MASKED: the tile touches
+// the diagonal and columns beyond `last` give zero (and take no part in maxima / sums); tiles below the
+// diagonal skip the comparison.  The row sum of kEpiExp adds the values before they are rounded to the
+// output type.
+template <typename OutT, bool MASKED>
+__device__ __forceinline__ void epi_compute(const GemmParams& p, const uint32_t (&r)[32], const float (&pt)[32],
+                                            float (&v)[32], int last, int col0, const EpiFold& f, EpiRow& er) {
+  if (p.epi == kEpiRowMax) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i)
+      if (!MASKED || col0 + i <= last) er.acc = fmaxf(er.acc, __uint_as_float(r[i]));     // raw: scaled by alpha at the end
+  } else if (p.epi == kEpiExp) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      float e = ex2_approx(fmaf(__uint_as_float(r[i]), f.k1, -f.k2));
+      if (MASKED && col0 + i > last) e = 0.f;
+      er.acc += e;
+      v[i] = e;
+    }
+  } else if (p.epi == kEpiRowScale) {
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * f.k1;
+  } else {   // kEpiDS
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float d = pt[i] * fmaf(__uint_as_float(r[i]), f.k1, -f.k2);
+      v[i] = (MASKED && col0 + i > last) ? 0.f : d;
+    }
+  }
+}
+
 template <bool A_MN, bool B_MN, typename OutT, bool GATHER = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kGemmThreads + (GATHER ? kGatherWarps * 32 : 0), 1)
 gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -621,7 +796,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
   const int num_pairs = gridDim.x >> 1;
   const int num_m = (p.M + kPairBM - 1) / kPairBM;
   const int num_n = (p.N + kPairBN - 1) / kPairBN;
-  const int tiles_per_batch = num_m * num_n;
+  const int tiles_per_batch = pair_tiles_per_batch(p, num_m, num_n);
   const int num_tiles = tiles_per_batch * p.batch;
   const int num_k = (p.K + BK - 1) / BK;
   constexpr uint32_t kTmemCols = 2 * kPairBN;       // two accumulators of 256 columns
@@ -659,7 +834,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m0, n0, bz;
-        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
+        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, num_pairs, m0, n0, bz);
         if (pair_tile_skipped(p, m0, n0)) continue;
         const int my_m = m0 + (int)rank * BM;
         const int my_n = n0 + (int)rank * (kPairBN / 2);
@@ -709,7 +884,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         int m0, n0, bz;
-        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
+        pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, num_pairs, m0, n0, bz);
         if (pair_tile_skipped(p, m0, n0)) continue;
         int kb0, kb1;
         pair_k_range(p, m0, num_k, kb0, kb1);
@@ -749,6 +924,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
     const int quarter = warp & 3;
+    const uint32_t stage_buf = smem_u32(smem + L::epi_offset + quarter * L::epi_stage_bytes);
     int acc = 0;
     uint32_t acc_phase = 0;
     bool ok = true;
@@ -756,7 +932,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
     OutT* P = reinterpret_cast<OutT*>(p.preact);
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       int m0, n0, bz;
-      pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, m0, n0, bz);
+      pair_tile_coords(p, tile, num_m, num_n, tiles_per_batch, num_pairs, m0, n0, bz);
       if (pair_tile_skipped(p, m0, n0)) continue;
       if (!wait_or_abort(tmem_full + acc, acc_phase, abort_flag)) { ok = false; break; }
       tcgen05_fence_after();
@@ -765,13 +941,13 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
       const long long ridx = (long long)bz * p.M + row;
       EpiRow er;
       if (p.epi != kEpiStd) epi_row_begin(p, ridx, row < p.M, er);
-#pragma unroll 1
-      for (int c = 0; c < kPairBN / 32; ++c) {
+      // chunk c (32 columns) written straight from the registers: partial groups, fp32 outputs, split C
+      auto direct_chunk = [&](int c) {
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
         const int col0 = n0 + c * 32;
-        if (col0 >= p.N) continue;            // warp-uniform
+        if (col0 >= p.N) return;              // warp-uniform
         float v[32];
 #pragma unroll
         for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]) * p.alpha;
@@ -780,7 +956,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
           if (row < p.M)
             epi_chunk<OutT>(p, v, row, col0, nvalid, (long long)bz * p.c_batch_stride + (long long)row * p.ldc + col0,
                             C, er);
-          continue;
+          return;
         }
         if (p.bias != nullptr) {
 #pragma unroll
@@ -810,6 +986,87 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ TmapArray tmaps_a, const __grid
             }
             store_row32<OutT>(C + off, v, nvalid);
           }
+        }
+            };
+      const int row_base = m0 + (int)rank * BM + quarter * 32;
+      const int rows_valid = p.M - row_base;
+      const bool std_in = p.epi == kEpiStd && (p.accumulate || p.aux != nullptr);
+      // groups of 64 columns: both 32-column reads of tensor memory are issued before the wait, the
+      // results pass through the warp's staging buffer and leave as whole 128-byte row segments
+      const bool can_group = sizeof(OutT) == 2 && P == nullptr && p.c_nparts <= 1 &&
+                             !(p.epi == kEpiStd && p.accumulate && p.aux != nullptr) &&
+                             ((p.ldc | p.c_batch_stride) & 7) == 0 &&
+                             ((reinterpret_cast<uintptr_t>(C) | reinterpret_cast<uintptr_t>(p.aux)) & 15) == 0 &&
+                             n0 + kPairBN <= p.N && !(p.epi == kEpiRowMax && p.alpha < 0.f);
+      // (the gathering variant, whose 320 threads leave fewer registers each, keeps the direct form: a
+      // register spilled between an asynchronous tensor-memory read and its wait would be read too early)
+      if (GATHER || !can_group) {
+#pragma unroll 1
+        for (int c = 0; c < kPairBN / 32; ++c) direct_chunk(c);
+      } else if constexpr (!GATHER) {
+        const bool need_in = p.epi == kEpiDS || std_in;
+        const OutT* src = (p.epi == kEpiDS || !p.accumulate) ? reinterpret_cast<const OutT*>(p.aux) : C;
+        const long long off_row0 = (long long)bz * p.c_batch_stride + (long long)row_base * p.ldc + n0;
+        const int last = p.mode == 1 ? row + p.causal_off : 0x7fffffff;
+        // does any row of this warp end inside the tile?  (warp-uniform)
+        const bool masked = p.mode == 1 && n0 + kPairBN - 1 > row_base + p.causal_off;
+        EpiFold fold{p.alpha, 0.f};
+        if (p.epi == kEpiExp) fold = {p.alpha * 1.4426950408889634f, er.a * 1.4426950408889634f};
+        else if (p.epi == kEpiRowScale) fold = {p.alpha * er.a, 0.f};
+        else if (p.epi == kEpiDS) fold = {p.alpha * er.a, er.a * er.b};
+#pragma unroll 1
+        for (int g = 0; g < kPairBN / 64; ++g) {
+          const int colg = n0 + g * 64;
+          const long long off0 = off_row0 + g * 64;
+          uint32_t ra[32], rb[32];
+          tmem_ld_32x32(t_row + g * 64, ra);
+          tmem_ld_32x32(t_row + g * 64 + 32, rb);
+          if (need_in) epi_stage_in<OutT>(stage_buf, src + off0, p.ldc, rows_valid, lane);
+          tmem_ld_wait();
+          if (need_in) __syncwarp();
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const int col0 = colg + h * 32;
+            const uint32_t (&rr)[32] = h == 0 ? ra : rb;
+            float v[32], pt[32];
+            if (need_in) epi_stage_get<OutT>(stage_buf, lane, h, pt);
+            if (p.epi != kEpiStd) {
+              if (masked) epi_compute<OutT, true>(p, rr, pt, v, last, col0, fold, er);
+              else epi_compute<OutT, false>(p, rr, pt, v, last, col0, fold, er);
+              if (p.epi == kEpiRowMax) continue;
+            } else {
+#pragma unroll
+              for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(rr[i]) * p.alpha;
+              if (p.bias != nullptr) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                  float bv;
+                  if (p.bias_dtype == kF32) bv = reinterpret_cast<const float*>(p.bias)[col0 + i];
+                  else if (p.bias_dtype == kBF16) bv = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p.bias)[col0 + i]);
+                  else bv = __half2float(reinterpret_cast<const __half*>(p.bias)[col0 + i]);
+                  v[i] += bv;
+                }
+              }
+              if (need_in) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] += pt[i];
+              }
+              if (p.act == 1) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = silu_f(v[i]);
+              }
+            }
+            epi_stage_put<OutT>(stage_buf, lane, h, v);
+          }
+          if (p.epi != kEpiRowMax) {
+            __syncwarp();
+            epi_stage_out<OutT>(stage_buf, C + off0, p.ldc, rows_valid, lane);
+            __syncwarp();
+          }
+        }
+        if (p.epi == kEpiRowMax) {
+          // the maximum was taken over raw accumulators: alpha >= 0 on this path, so it scales through
+          er.acc = er.acc > -INFINITY ? er.acc * p.alpha : er.acc;
         }
       }
       if (p.epi != kEpiStd) epi_row_end(p, ridx, row < p.M, er);
