@@ -55,6 +55,8 @@ def parse():
     ap.add_argument("--layers", type=int, default=None, help="override depth (debugging only; marks the run invalid)")
     ap.add_argument("--gemm", default=None, choices=[None, "tcgen05", "tcgen05_1cta", "cublas"])
     ap.add_argument("--no-ckpt", action="store_true")
+    ap.add_argument("--recompute-scores", action="store_true",
+                    help="attention keeps row maxima instead of probabilities for backward (memory for time)")
     ap.add_argument("--composition", default="fused", choices=["fused", "library"],
                     help="library: the same model and step as a composition of library calls inside this framework "
                          "(cuBLAS products, materialised matmul + softmax attention, NCCL hand-off / all-gather / "
@@ -303,6 +305,10 @@ def run(args):
     if library and cfg.layerwise_ckpt and args.ckpt_layers is None:
         # the materialised fp32 scores add about 3 GB per un-checkpointed layer and 32K tokens
         cfg.ckpt_layers = 32 if chunks_local == 8 else 24
+    if args.recompute_scores:
+        # keeping the row maxima instead of the attention probabilities frees 0.54 GB per un-checkpointed
+        # layer and 16K tokens; the extra score pass costs 54 us per layer and chunk in backward
+        cuda_ops.set_attention_recompute_scores(True)
     set_random_seed(1234)
     model = build_model(cfg, "bf16", fp32_reduce_scatter=False, reshard_after_forward=False,
                         shard_over_chunk_group=True)

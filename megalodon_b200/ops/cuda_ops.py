@@ -684,7 +684,14 @@ class _Attention(torch.autograd.Function):
                      softmax=dict(epi_kind=2, row_in=rmax[b], row_out=rsum[b]))
                 gemm(Pb, _heads_view(v, b), b_mn=True, out=_heads_view(out, b), mode=mode_o,
                      softmax=dict(epi_kind=3, row_in=rsum[b]))
-            ctx.save_for_backward(q, k, v, P, rsum, out)
+            if _RECOMPUTE_SCORES[0]:
+                # keep the row maxima (16 KB per head) instead of the 32 MB of P~ per head: backward runs
+                # the second score pass again
+                ctx.save_for_backward(q, k, v, rmax, rsum, out)
+                ctx.scores_kept = False
+            else:
+                ctx.save_for_backward(q, k, v, P, rsum, out)
+                ctx.scores_kept = True
         else:
             seed = offset = 0
             if drop_p > 0.0:
@@ -704,6 +711,14 @@ class _Attention(torch.autograd.Function):
         scale, causal, square, L2, fused = ctx.meta
         if fused:
             q, k, v, P, rsum, out = ctx.saved_tensors
+            if not ctx.scores_kept:
+                rmax, (Bq, Lq, Hq, _) = P, q.shape
+                ld = -(-L2 // 128) * 128
+                P = torch.empty(Bq, Hq, Lq, ld, dtype=q.dtype, device=q.device)
+                scratch = torch.empty_like(rsum)
+                for b in range(Bq):
+                    gemm(_heads_view(q, b), _heads_view(k, b), out=P[b][:, :, :L2], mode=1 if square else 0,
+                         alpha=scale, softmax=dict(epi_kind=2, row_in=rmax[b], row_out=scratch[b]))
         else:
             q, k, v, P = ctx.saved_tensors
         dout = dout.contiguous()
@@ -746,6 +761,14 @@ def decode_attention(q, k_buf, v_buf, pos, scale):
 
 
 _FUSED_SOFTMAX = [True]
+_RECOMPUTE_SCORES = [False]
+
+
+def set_attention_recompute_scores(on: bool) -> None:
+    """Fused-softmax attention keeps the un-normalised probabilities for backward (default) or only the
+    row maxima and recomputes the probabilities there (one more pass of the Q K^T product per backward;
+    128 MB less kept per layer and 4096-token chunk of the 7B model)."""
+    _RECOMPUTE_SCORES[0] = bool(on)
 
 
 def set_fused_attention_softmax(on: bool) -> None:

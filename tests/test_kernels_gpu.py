@@ -999,3 +999,26 @@ def test_norm_backward_weight_gradients_with_more_rows_than_ctas(kind):
             continue
         rel = (a.float() - r).norm() / r.norm()
         assert rel < 2e-2, f"{kind} {name}: relative error {rel:.4f}"
+
+
+def test_attention_backward_with_recomputed_probabilities_matches_kept_ones():
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(11)
+    dev = _dev()
+    B, L, H, dk, dv = 2, 512, 2, 64, 256
+    q = (torch.randn(B, L, H, dk, device=dev) / dk ** 0.5).bfloat16()
+    k = torch.randn(B, L, H, dk, device=dev).bfloat16()
+    v = torch.randn(B, L, H, dv, device=dev).bfloat16()
+    g = torch.randn(B, L, H, dv, device=dev).bfloat16()
+    res = []
+    try:
+        for recompute in (False, True):
+            cuda_ops.set_attention_recompute_scores(recompute)
+            leaves = [t.clone().requires_grad_() for t in (q, k, v)]
+            out = cuda_ops.attention(leaves[0], leaves[1], leaves[2], 1.0, 0.0, True, True)
+            out.backward(g)
+            res.append([out] + [t.grad for t in leaves])
+    finally:
+        cuda_ops.set_attention_recompute_scores(False)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), res[0], res[1]):
+        assert torch.equal(a, b), f"{name} differs: {(a.float() - b.float()).abs().max().item()}"
