@@ -178,7 +178,9 @@ def test_mailbox_line_with_middle_ranks_and_one_timeout_for_the_whole_line(world
         assert waited < 1.9 * timeout_s + 1.0, f"rank {r} waited {waited:.2f} s"
     assert "timed out" in res[1][2] and "receive" in res[1][2] and "forward" in res[1][2], res[1][2]
     for r in range(2, world):
-        assert "poisoned" in res[r][2], res[r][2]
+        # told by the neighbour's poison, or its own equally long wait ran out in the same instant (every
+        # rank of the line started waiting together); never two waits in a row (checked above)
+        assert "poisoned" in res[r][2] or "timed out" in res[r][2], res[r][2]
 
 
 def _allreduce_case(rank, world):
