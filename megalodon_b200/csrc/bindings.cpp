@@ -781,6 +781,32 @@ void peer_barrier(const Tensor& pads, int64_t rank, int64_t epoch, int64_t timeo
                    (unsigned int)epoch, (unsigned long long)timeout_ns, abort_ptr(abort), (int)tag, stream());
 }
 
+// Sum over the group (gather = false) or concatenation along the last dimension (gather = true) of a
+// small contiguous 16-bit tensor; `counter` (int32[1]) is the device-side epoch.  Captures in a CUDA graph.
+Tensor small_collective(const Tensor& x, const Tensor& bufs, const Tensor& pads, Tensor& counter, int64_t rank,
+                        int64_t slot_bytes, bool gather, int64_t timeout_ns, Tensor& abort) {
+  check_cuda_contig(x, "x");
+  c10::cuda::CUDAGuard guard(x.device());
+  const int64_t world = bufs.numel();
+  const int64_t nbytes = x.numel() * x.element_size();
+  TORCH_CHECK(x.element_size() == 2 && nbytes % 16 == 0 && nbytes <= slot_bytes && slot_bytes % 16 == 0,
+              "small_collective: 16-bit tensor of a multiple of 16 bytes, at most one slot");
+  TORCH_CHECK(bufs.scalar_type() == at::kLong && pads.scalar_type() == at::kLong && pads.numel() == world && world <= 32);
+  TORCH_CHECK(counter.is_cuda() && counter.scalar_type() == at::kInt);
+  const int64_t last = x.size(-1);
+  const int64_t rows = x.numel() / last;
+  if (gather) TORCH_CHECK((last * 2) % 16 == 0, "small_collective: rows of a multiple of 16 bytes");
+  std::vector<int64_t> shape(x.sizes().begin(), x.sizes().end());
+  if (gather) shape.back() = last * world;
+  Tensor out = torch::empty(shape, x.options());
+  mb::small_collective(x.data_ptr(), out.data_ptr(), reinterpret_cast<void* const*>(bufs.data_ptr<int64_t>()),
+                       reinterpret_cast<unsigned int* const*>(pads.data_ptr<int64_t>()),
+                       reinterpret_cast<unsigned int*>(counter.data_ptr<int>()), (int)rank, (int)world, nbytes,
+                       slot_bytes, (int)rows, gather, dtype_code(x), (unsigned long long)timeout_ns, abort_ptr(abort),
+                       stream());
+  return out;
+}
+
 // bufs: int64 device tensor with the address of every rank's copy of the buffer (same byte offset everywhere)
 const int* opt_abort(const OptTensor& abort) {
   if (!abort.has_value()) return nullptr;
@@ -957,6 +983,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("seq"), py::arg("remote_ack"), py::arg("counter"), py::arg("timeout_ns"), py::arg("abort"),
         py::arg("rank"), py::arg("dir"), py::arg("poison") = false);
   m.def("peer_barrier", checked(&peer_barrier));
+  m.def("small_collective", checked(&small_collective));
   m.def("gemm_set_cta_pairs", [](bool on) { mb::gemm_set_cta_pairs(on); });
   m.def("gemm_pair_max_active_clusters", []() { return mb::gemm_pair_max_active_clusters(); });
   m.def("allreduce_sumsq", checked(&allreduce_sumsq), py::arg("bufs"), py::arg("rank"), py::arg("nbytes"),

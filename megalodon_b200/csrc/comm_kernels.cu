@@ -261,6 +261,78 @@ struct Vec8<__half> {
   }
 };
 
+// ---- small all-reduce / all-gather of a decode step (a few rows of activations) in ONE kernel that can
+// be captured in a CUDA graph: the epoch is not a launch argument but a counter in device memory that the
+// kernel itself advances, so a replayed graph keeps the flag protocol intact.  Every rank stores its
+// vector into slot [rank] of every peer's buffer (two buffers, alternating with the epoch: a rank can be
+// at most one collective ahead of the slowest, because it needs that rank's flag of the current one),
+// raises flag [rank] on every peer, waits for all flags of its own pad, then sums (or concatenates) the
+// `world` slots of its own buffer in rank order - the same order on every rank, so all ranks hold
+// identical results.  One CTA; n16 = number of 16-byte words of the vector.
+//   bufs[p]  : rank p's buffer, 2 * world * slot16 words      pads[p] : rank p's flags, `world` uint32
+template <typename T, bool GATHER>
+__global__ void small_collective_kernel(const uint4* __restrict__ x, uint4* __restrict__ out,
+                                        uint4* const* __restrict__ bufs, unsigned int* const* __restrict__ pads,
+                                        unsigned int* __restrict__ counter, int rank, int world, int n16,
+                                        int slot16, int rows, unsigned long long timeout_ns, int* abort) {
+  __shared__ unsigned int s_epoch;
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) {
+    s_epoch = *counter + 1;
+    s_fail = ld_volatile(abort) != 0 ? 1 : 0;
+  }
+  __syncthreads();
+  const unsigned int epoch = s_epoch;
+  const long long half = (long long)(epoch & 1u) * world * slot16;
+  if (!s_fail) {
+    for (int p = 0; p < world; ++p) {
+      uint4* dst = bufs[p] + half + (long long)rank * slot16;
+      for (int i = threadIdx.x; i < n16; i += blockDim.x) dst[i] = x[i];
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    const int p = threadIdx.x;
+    WaitResult res = s_fail ? kWaitAborted : kWaitOk;
+    unsigned int seen = 0;
+    if (p < world && !s_fail) {
+      st_release_sys(pads[p] + rank, epoch);
+      res = wait_flag_ge(pads[rank] + p, epoch, timeout_ns, abort, &seen);
+    }
+    record_abort(abort, res, kWaitBarrier, p, epoch, seen, rank, 0x5c);
+    if (__any_sync(0xffffffffu, res != kWaitOk)) {
+      if (p < world) st_release_sys(pads[p] + rank, kPoison);
+      if (p == 0) s_fail = 1;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) *counter = epoch;
+  if (s_fail) return;
+  const uint4* mine = bufs[rank] + half;
+  if (GATHER) {
+    // slot r holds [rows, n16 / rows] words; the result is [rows, world * n16 / rows]
+    const int w = n16 / rows;
+    for (int i = threadIdx.x; i < n16 * world; i += blockDim.x) {
+      const int row = i / (w * world), c = i - row * (w * world);
+      const int r = c / w, j = c - r * w;
+      out[i] = mine[(long long)r * slot16 + row * w + j];
+    }
+  } else {
+    for (int i = threadIdx.x; i < n16; i += blockDim.x) {
+      float acc[8];
+      Vec8<T>::unpack(mine[i], acc);
+      for (int r = 1; r < world; ++r) {
+        float f[8];
+        Vec8<T>::unpack(mine[(long long)r * slot16 + i], f);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] += f[k];
+      }
+      out[i] = Vec8<T>::pack(acc);
+    }
+  }
+}
+
 // 16-bit element types: 8 elements per 16-byte word.  bufs[p] = address of rank p's copy.
 // Rank r owns words [r * slice16, (r + 1) * slice16) of the n16-word buffer.
 template <typename T>
@@ -657,6 +729,26 @@ void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int e
                   int* abort, int tag, cudaStream_t st) {
   prefer_max_shared(peer_barrier_kernel);
   peer_barrier_kernel<<<1, 32, 0, st>>>(pads, rank, world, epoch, timeout_ns, abort, tag);
+}
+
+void small_collective(const void* x, void* out, void* const* bufs, unsigned int* const* pads, unsigned int* counter,
+                      int rank, int world, long long nbytes, long long slot_bytes, int rows, bool gather, int dtype,
+                      unsigned long long timeout_ns, int* abort, cudaStream_t st) {
+  const int n16 = (int)(nbytes / 16), slot16 = (int)(slot_bytes / 16);
+  const int threads = 1024;
+  if (gather) {
+    prefer_max_shared(small_collective_kernel<__nv_bfloat16, true>);
+    small_collective_kernel<__nv_bfloat16, true><<<1, threads, 0, st>>>(
+        (const uint4*)x, (uint4*)out, (uint4* const*)bufs, pads, counter, rank, world, n16, slot16, rows, timeout_ns, abort);
+  } else if (dtype == kBF16) {
+    prefer_max_shared(small_collective_kernel<__nv_bfloat16, false>);
+    small_collective_kernel<__nv_bfloat16, false><<<1, threads, 0, st>>>(
+        (const uint4*)x, (uint4*)out, (uint4* const*)bufs, pads, counter, rank, world, n16, slot16, rows, timeout_ns, abort);
+  } else {
+    prefer_max_shared(small_collective_kernel<__half, false>);
+    small_collective_kernel<__half, false><<<1, threads, 0, st>>>(
+        (const uint4*)x, (uint4*)out, (uint4* const*)bufs, pads, counter, rank, world, n16, slot16, rows, timeout_ns, abort);
+  }
 }
 
 void allreduce_sumsq(void* const* bufs, int rank, int world, long long nbytes, float scale, double* sumsq,

@@ -200,6 +200,11 @@ void p2p_send(const void* src, void* remote_dst, long long nbytes, unsigned int*
 void p2p_recv(void* dst, void* local_slot, long long nbytes, const unsigned int* local_flag, unsigned int seq,
               unsigned int* remote_ack, unsigned int* counter, unsigned long long timeout_ns, int* abort, int rank,
               int dir, bool poison, cudaStream_t st);
+// all-reduce (sum) or all-gather along the last dimension of a small 16-bit vector in one kernel whose
+// epoch lives in device memory (`counter`), so that it can be captured in a CUDA graph; see the kernel
+void small_collective(const void* x, void* out, void* const* bufs, unsigned int* const* pads, unsigned int* counter,
+                      int rank, int world, long long nbytes, long long slot_bytes, int rows, bool gather, int dtype,
+                      unsigned long long timeout_ns, int* abort, cudaStream_t st);
 void peer_barrier(unsigned int* const* pads, int rank, int world, unsigned int epoch, unsigned long long timeout_ns,
                   int* abort, int tag, cudaStream_t st);
 // out[i] (+)= scale * sum_p bufs[p][rank * shard_n + i]; out dtype = in dtype or fp32; sumsq += |out|^2

@@ -42,11 +42,20 @@ class DecodeSession:
         self.B = batch_size
         self.dtype = dtype
         self.device = next(model.parameters()).device
-        # graph capture is the default on one GPU; with tensor-parallel ranks the eager fixed-shape
-        # step is used unless asked for (a captured step with NCCL collectives did not complete here)
-        multi = torch.distributed.is_available() and torch.distributed.is_initialized() and \
-            torch.distributed.get_world_size() > 1
-        self.use_graph = (self.device.type == "cuda" and not multi) if use_graph is None else use_graph
+        # Graph capture is the default on a GPU.  With tensor-parallel ranks the collectives of the step
+        # (all-reduce after the row-parallel projections, gathers of feature-sharded activations and of
+        # the logits) go through `SmallCollective`: one peer-memory kernel each, whose epoch lives in
+        # device memory, so the captured step replays correctly (NCCL inside the capture did not complete).
+        self._small = None
+        from .parallel.initialize import (get_model_parallel_group, get_model_parallel_world_size,
+                                          model_parallel_is_initialized)
+        mp = get_model_parallel_world_size() if model_parallel_is_initialized() else 1
+        if mp > 1 and self.device.type == "cuda" and use_graph is not False:
+            from .parallel.model_parallel import mappings
+            from .parallel.symm import SmallCollective
+            self._small = SmallCollective(get_model_parallel_group(), self.device, max_bytes=2 << 20)
+            mappings.use_small_collective(self._small)
+        self.use_graph = (self.device.type == "cuda") if use_graph is None else use_graph
         c = m.chunk_size
         first = _unwrap(m.layers[0]).mega
         H, dk, dv = first.local_heads, first.z_head_dim, first.local_v_head_dim
@@ -144,8 +153,15 @@ class DecodeSession:
             dist_on = torch.distributed.is_available() and torch.distributed.is_initialized()
             mode = {"capture_error_mode": "thread_local"} if dist_on else {}
             try:
-                with torch.cuda.graph(graph, **mode):
-                    captured = self._step_body()
+                if self._small is not None:
+                    from .parallel.model_parallel import mappings
+                    mappings.small_collective_strict(True)
+                try:
+                    with torch.cuda.graph(graph, **mode):
+                        captured = self._step_body()
+                finally:
+                    if self._small is not None:
+                        mappings.small_collective_strict(False)
             except Exception as e:  # noqa: BLE001 - an op that cannot be captured: stay on the eager step
                 import logging
                 logging.getLogger().warning(f"decode step could not be captured in a CUDA graph ({e}); "

@@ -34,10 +34,41 @@ def _dim(x: torch.Tensor, dim: Optional[int]) -> int:
     return x.dim() - 1 if dim is None else dim % x.dim()
 
 
+# Set by a decode session on tensor-parallel ranks (`use_small_collective`): small inference-time
+# activations then go through one peer-memory kernel per collective, which a CUDA graph can hold.
+_SMALL = [None]
+
+
+def use_small_collective(obj) -> None:
+    """`obj`: a `parallel.symm.SmallCollective` over the model-parallel group, or None to go back to NCCL."""
+    _SMALL[0] = obj
+
+
+_STRICT = [False]
+
+
+def small_collective_strict(on: bool) -> None:
+    """While on (a decode step being captured in a CUDA graph), a collective that the small-collective
+    kernel cannot take raises instead of falling back to NCCL, which must not run inside the capture."""
+    _STRICT[0] = bool(on)
+
+
+def _small_for(x: torch.Tensor):
+    sc = _SMALL[0]
+    ok = sc is not None and not torch.is_grad_enabled() and sc.fits(x)
+    if _STRICT[0] and not ok:
+        raise RuntimeError(f"collective on a {tuple(x.shape)} {x.dtype} tensor cannot go through the "
+                           "graph-capturable kernel")
+    return sc if ok else None
+
+
 def _all_reduce(x: torch.Tensor) -> torch.Tensor:
     if get_model_parallel_world_size() == 1:
         return x
     x = x.contiguous()
+    sc = _small_for(x)
+    if sc is not None:
+        return sc.all_reduce(x)
     dist.all_reduce(x, group=get_model_parallel_group())
     return x
 
@@ -59,6 +90,10 @@ def _gather(x: torch.Tensor, dim: Optional[int]) -> torch.Tensor:
         return x
     d = _dim(x, dim)
     x = x.contiguous()
+    if d == x.dim() - 1:
+        sc = _small_for(x)
+        if sc is not None:
+            return sc.all_gather_last_dim(x)
     out = torch.empty((world,) + tuple(x.shape), dtype=x.dtype, device=x.device)
     all_gather_flat(out, x, get_model_parallel_group())
     # [W, ..., n_d, ...] -> [..., W * n_d, ...]

@@ -452,6 +452,48 @@ class SymmetricAllReduce:
         _reset_pads(self, self.region, self.pad_off)
 
 
+class SmallCollective:
+    """All-reduce and last-dimension all-gather of small 16-bit tensors (the activations of a decode step)
+    over peer memory, one kernel each, with the epoch kept in device memory: the calls carry no
+    per-launch sequence number, so a step that contains them can be captured in a CUDA graph and replayed.
+    Every rank must issue the same sequence of calls.  Results are bitwise identical on all ranks (the
+    slots are summed in rank order)."""
+
+    def __init__(self, group: Optional[dist.ProcessGroup], device: torch.device, max_bytes: int = 1 << 18,
+                 timeout_s: float = 10.0):
+        self.slot_bytes = _round_up(max_bytes, 256)
+        world = dist.get_world_size(group)
+        self.buf_bytes = 2 * world * self.slot_bytes
+        self.region = SymmetricRegion(self.buf_bytes + _round_up(4 * world, 256), group, device)
+        self.rank, self.world = self.region.rank, world
+        self.timeout_ns = int(timeout_s * 1e9)
+        self._abort = AbortRecord.get(self.region.device)
+        self._bufs = self.region.ptr_table_at(0).contiguous()
+        self._pads = self.region.ptr_table_at(self.buf_bytes).contiguous()
+        self._counter = torch.zeros(1, dtype=torch.int32, device=self.region.device)
+        torch.cuda.synchronize(self.region.device)
+        dist.barrier(group=self.region.group)          # every pad is zero before the first flag arrives
+
+    def fits(self, x: torch.Tensor) -> bool:
+        nbytes = x.numel() * x.element_size()
+        return (x.is_cuda and x.dtype in (torch.bfloat16, torch.float16) and 0 < nbytes <= self.slot_bytes
+                and nbytes % 16 == 0 and (x.shape[-1] * 2) % 16 == 0)
+
+    def _call(self, x: torch.Tensor, gather: bool) -> torch.Tensor:
+        from ..ops._ext import require
+        return require().small_collective(x.contiguous(), self._bufs, self._pads, self._counter, self.rank,
+                                          self.slot_bytes, gather, self.timeout_ns, self._abort.dev)
+
+    def all_reduce(self, x: torch.Tensor) -> torch.Tensor:
+        return self._call(x, False)
+
+    def all_gather_last_dim(self, x: torch.Tensor) -> torch.Tensor:
+        return self._call(x, True)
+
+    def check(self) -> None:
+        self._abort.check()
+
+
 class SymmetricReduceScatter:
     """Gradient reduce-scatter of an FSDP unit by pulling from peer memory, fused with the averaging
     scale, the cast to the shard dtype and the squared-norm partial sum used for clipping.  Two staging

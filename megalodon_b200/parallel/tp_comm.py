@@ -177,7 +177,9 @@ class LinearRS(torch.autograd.Function):
 
 def usable(x: torch.Tensor) -> bool:
     ws = workspace()
-    return (ws is not None and x.is_cuda and x.dtype == ws.dtype
+    # (a decode step's few rows take the plain layers: their collectives then go through the
+    # graph-capturable small-collective kernel, and a 128-row tile would be nearly empty)
+    return (ws is not None and x.is_cuda and x.dtype == ws.dtype and x.numel() // max(x.shape[-1], 1) > 16
             and x.numel() // x.shape[-1] * max(x.shape[-1], 1) <= ws.max_elems * ws.world)
 
 

@@ -470,3 +470,97 @@ def test_benchmark_restarts_on_nccl_after_a_host_made_rank_failure():
     assert "nccl" in out["config"]["parallelism"]
     assert out["value"] > 0 and out["config"]["final_loss"] == out["config"]["final_loss"]
     assert "restarting with --transport nccl" in res.stderr
+
+
+def _small_collective_case(rank, world):
+    import torch.distributed as dist
+    from megalodon_b200.parallel.symm import SmallCollective
+    dev = torch.device("cuda", rank)
+    sc = SmallCollective(None, dev, max_bytes=1 << 18, timeout_s=5.0)
+    ok = True
+    g = torch.Generator(device=dev).manual_seed(100 + rank)
+    # eager: sums and gathers of several shapes, against NCCL
+    for shape in [(1, 1, 4096), (4, 1, 512), (16, 1, 2048), (3, 1, 8)]:
+        x = torch.randn(shape, device=dev, generator=g).bfloat16()
+        ref = x.float().clone()
+        dist.all_reduce(ref)
+        got = sc.all_reduce(x)
+        ok = ok and torch.allclose(got.float(), ref, atol=0.06, rtol=0.02)
+        parts = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(parts, x)
+        ok = ok and torch.equal(sc.all_gather_last_dim(x), torch.cat(parts, dim=-1))
+    # every rank holds the same bits
+    x = torch.randn(8, 1, 1024, device=dev, generator=g).bfloat16()
+    mine = sc.all_reduce(x)
+    parts = [torch.empty_like(mine) for _ in range(world)]
+    dist.all_gather(parts, mine)
+    ok = ok and all(torch.equal(p, mine) for p in parts)
+    # captured: three collectives per replay, inputs rewritten between replays
+    a = torch.zeros(4, 1, 1024, device=dev, dtype=torch.bfloat16)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+        s1 = sc.all_reduce(a)
+        s2 = sc.all_gather_last_dim(s1 * 0.5)
+        s3 = sc.all_reduce(s2[..., :512].contiguous())
+    for it in range(6):
+        a.copy_(torch.full_like(a, float(rank + 1 + it)))
+        graph.replay()
+        torch.cuda.synchronize()
+        total = sum(r + 1 + it for r in range(world))
+        ok = ok and bool((s1.float() == total).all()) and bool((s2.float() == 0.5 * total).all())
+        ok = ok and bool((s3.float() == 0.5 * total * world).all())
+    # eager calls after the replays continue the same epoch sequence
+    got = sc.all_reduce(torch.ones(2, 1, 64, device=dev, dtype=torch.bfloat16))
+    ok = ok and bool((got.float() == world).all())
+    torch.cuda.synchronize()
+    sc.check()
+    return ok
+
+
+@pytest.mark.parametrize("world", WORLDS)
+def test_small_collectives_eager_and_graph_replayed(world):
+    _need_gpus(world)
+    assert all(_run(_small_collective_case, world))
+
+
+def _tp_graph_decode_case(rank, world):
+    from megalodon_b200.config import ModelConf
+    from megalodon_b200.decoding import DecodeSession
+    from megalodon_b200.models.mega import build_model
+    from megalodon_b200.ops import cuda_ops
+    from megalodon_b200.parallel import initialize_model_parallel
+    from megalodon_b200.utils import init_cache, set_random_seed
+    initialize_model_parallel(world, 1)
+    cfg = ModelConf(num_layers=2, model_dim=256, num_heads=2, z_dim=128, value_dim=512, ffn_hidden_dim=512,
+                    cema_ndim=16, chunk_size=128, vocab_size=512, swiglu=True, norm_num_groups=16,
+                    efficient_attn="fused")
+    set_random_seed(0)
+    model = build_model(cfg, "bf16", False, False)
+    model.eval()
+    inner = model._wrapped
+    B = 2
+    prompt = torch.randint(0, 512, (B, 128 + 120), generator=torch.Generator().manual_seed(1)).cuda()
+    with torch.no_grad():
+        cache = init_cache(B, inner, torch.bfloat16, device=prompt.device)
+        _, cache = model(prompt[:, :128], cache=cache)
+        logits, cache = model(prompt[:, 128:], cache=cache)
+        sess = DecodeSession(model, B, torch.bfloat16)
+        sess.load_cache(cache)
+        tok = logits[:, -1].argmax(-1)
+        worst = 0.0
+        for _ in range(14):                       # crosses the chunk boundary at 128
+            ref, cache = model(tok.view(B, 1), cache=cache)
+            got = sess.step(tok)
+            worst = max(worst, (ref[:, -1] - got).abs().max().item())
+            tok = ref[:, -1].argmax(-1)
+        torch.cuda.synchronize()
+        cuda_ops.check_kernel_errors()
+    return worst, sess._graph is not None
+
+
+def test_tensor_parallel_decode_replays_from_a_cuda_graph():
+    _need_gpus(2)
+    for worst, captured in _run(_tp_graph_decode_case):
+        assert captured, "the tensor-parallel step was not captured"
+        assert worst < 0.2, worst
