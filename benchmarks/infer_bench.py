@@ -45,6 +45,9 @@ def main():
     ap.add_argument("--kernel-profile", default=None,
                     help="decode: also run one eager fixed-shape step per batch size under torch.profiler and write "
                          "the per-kernel summary to this path (never part of a reported number)")
+    ap.add_argument("--stall-dump-s", type=float, default=240.0,
+                    help="a phase that makes no progress for this long dumps every thread's Python stack to stderr "
+                         "and ends the process (0: off)")
     ap.add_argument("--eager", action="store_true", help="decode through the regular cache path instead of the "
                                                          "graph-replayed fixed-shape session")
     args = ap.parse_args()
@@ -203,8 +206,11 @@ def main():
             inner = inner._wrapped
         c = cfg.chunk_size
         results = {}
+        import faulthandler
         with torch.inference_mode():
             for B in [int(b) for b in args.batches.split(",")]:
+                if args.stall_dump_s > 0:
+                    faulthandler.dump_traceback_later(args.stall_dump_s, exit=True)     # re-armed per batch size
                 g = torch.Generator().manual_seed(B)
                 prompt = torch.randint(0, cfg.vocab_size, (B, c + 17), generator=g).cuda()
                 cache = init_cache(B, inner, torch.bfloat16, device=prompt.device)
@@ -234,6 +240,8 @@ def main():
                 e1.record()
                 barrier()
                 results[B] = maxed(e0.elapsed_time(e1) / args.gen_len)
+                faulthandler.cancel_dump_traceback_later()
+                print(f"[rank {rank}] batch {B}: {results[B]:.2f} ms/token", file=sys.stderr, flush=True)
                 if args.kernel_profile and rank == 0:
                     import collections
                     from torch.profiler import ProfilerActivity, profile
