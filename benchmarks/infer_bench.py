@@ -242,6 +242,8 @@ def main():
                 results[B] = maxed(e0.elapsed_time(e1) / args.gen_len)
                 faulthandler.cancel_dump_traceback_later()
                 print(f"[rank {rank}] batch {B}: {results[B]:.2f} ms/token", file=sys.stderr, flush=True)
+                if not args.eager and not args.kernel_profile:
+                    del sess, step
                 if args.kernel_profile and rank == 0:
                     import collections
                     from torch.profiler import ProfilerActivity, profile
@@ -275,8 +277,19 @@ def main():
                 out["invalid"] = "reduced depth (debug run)"
             print(json.dumps(out))
     if world > 1:
+        import faulthandler
+        import gc
+        # sessions (captured graphs, peer-memory regions of their collectives) go before the process group
+        from megalodon_b200.parallel.model_parallel import mappings
+        mappings.use_small_collective(None)
+        sess = None  # noqa: F841
+        gc.collect()
+        torch.cuda.synchronize()
+        if args.stall_dump_s > 0:
+            faulthandler.dump_traceback_later(min(args.stall_dump_s, 90.0), exit=True)
         dist.barrier()
         dist.destroy_process_group()
+        faulthandler.cancel_dump_traceback_later()
 
 
 if __name__ == "__main__":
