@@ -82,6 +82,21 @@ std::tuple<Tensor, OptTensor> rms_norm_bwd(const Tensor& dy, const Tensor& x, co
   return {dx, dw};
 }
 
+// fp32 column sums of a 16-bit matrix [M, N] (the bias gradient of a linear layer)
+Tensor colsum(const Tensor& g) {
+  check_cuda_contig(g, "g");
+  TORCH_CHECK(g.dim() == 2, "colsum: a matrix");
+  c10::cuda::CUDAGuard guard(g.device());
+  const int N = g.size(1);
+  const long long M = g.size(0);
+  Tensor out = torch::zeros({N}, g.options().dtype(at::kFloat));
+  Tensor ws = torch::empty({(long long)mb::kColsumRows * N}, g.options().dtype(at::kFloat));
+  const bool done = g.element_size() == 2 &&
+                    mb::colsum_16bit(g.data_ptr(), M, N, ws.data_ptr<float>(), out.data_ptr<float>(), dtype_code(g), stream());
+  if (!done) return g.sum(0, /*keepdim=*/false, at::kFloat);
+  return out;
+}
+
 std::tuple<Tensor, Tensor, Tensor> layer_norm_fwd(const Tensor& x, const OptTensor& w, const OptTensor& b,
                                                   double w_off, double eps) {
   check_cuda_contig(x, "x");
@@ -927,6 +942,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   register_cpu_bwd_ops(m);
   m.def("rms_norm_fwd", checked(&rms_norm_fwd));
   m.def("rms_norm_bwd", checked(&rms_norm_bwd));
+  m.def("colsum", checked(&colsum));
   m.def("layer_norm_fwd", checked(&layer_norm_fwd));
   m.def("layer_norm_bwd", checked(&layer_norm_bwd));
   m.def("timestep_norm_fwd", checked(&timestep_norm_fwd));

@@ -15,6 +15,8 @@ void rms_norm_fwd(const void* x, const void* w, float w_off, void* y, float* rst
 // way the sums are ADDED to dw / db.
 constexpr int kColsumRows = 296;
 void colsum_finish(const float* ws, int rows, int D, float* out0, float* out1, cudaStream_t st);
+// out[j] += sum over rows of a row-major 16-bit matrix [M, N] (bias gradients); false: shape not covered
+bool colsum_16bit(const void* g, long long M, int N, float* ws, float* out, int dtype, cudaStream_t st);
 void rms_norm_bwd(const void* dy, const void* x, const void* w, float w_off, const float* rstd, void* dx,
                   float* dw, long long M, int D, int x_dtype, int w_dtype, cudaStream_t st,
                   float* colsum_ws = nullptr);

@@ -450,6 +450,56 @@ void rms_norm_fwd(const void* x, const void* w, float w_off, void* y, float* rst
   NORM_DISPATCH(x_dtype, w_dtype, (launch_fwd<T, W, false>(x, w, nullptr, w_off, y, nullptr, rstd, M, D, eps, st)));
 }
 
+// Column sums of a row-major 16-bit matrix (the bias gradient of a linear layer): every CTA walks a strip
+// of rows with 8-column vectors per thread and leaves one row of partial sums; `colsum_finish` adds them.
+template <typename T, int VPT>
+__global__ void colsum_partial_kernel(const T* __restrict__ g, long long M, int N, float* __restrict__ ws) {
+  const int nvec = N / 8;
+  float acc[VPT][8];
+#pragma unroll
+  for (int i = 0; i < VPT; ++i)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
+  for (long long row = blockIdx.x; row < M; row += gridDim.x) {
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+      const int c = threadIdx.x + i * 256;
+      if (c < nvec) {
+        float v[8];
+        load8(g + row * N + c * 8, v);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] += v[j];
+      }
+    }
+  }
+  float* mine = ws + (long long)blockIdx.x * N;
+#pragma unroll
+  for (int i = 0; i < VPT; ++i) {
+    const int c = threadIdx.x + i * 256;
+    if (c < nvec) store8(mine + c * 8, acc[i]);
+  }
+}
+
+// out[j] += sum_m g[m, j]; needs N % 8 == 0, N <= 8192, g 16-byte aligned; ws: kColsumRows * N floats.
+// Returns false (nothing launched) when the shape is not covered.
+bool colsum_16bit(const void* g, long long M, int N, float* ws, float* out, int dtype, cudaStream_t st) {
+  if (N % 8 != 0 || N > 8192 || (reinterpret_cast<uintptr_t>(g) & 15) != 0 || (dtype != kBF16 && dtype != kF16))
+    return false;
+  const int grid = (int)std::min<long long>(M, (long long)kColsumRows);
+  const int vpt = (N / 8 + 255) / 256;
+#define MB_COLSUM(TT)                                                                                   \
+  do {                                                                                                  \
+    if (vpt <= 1) colsum_partial_kernel<TT, 1><<<grid, 256, 0, st>>>((const TT*)g, M, N, ws);           \
+    else if (vpt <= 2) colsum_partial_kernel<TT, 2><<<grid, 256, 0, st>>>((const TT*)g, M, N, ws);      \
+    else colsum_partial_kernel<TT, 4><<<grid, 256, 0, st>>>((const TT*)g, M, N, ws);                    \
+  } while (0)
+  if (dtype == kBF16) MB_COLSUM(__nv_bfloat16);
+  else MB_COLSUM(__half);
+#undef MB_COLSUM
+  colsum_finish_kernel<<<(N + 31) / 32, 256, 0, st>>>(ws, grid, N, out, nullptr);
+  return true;
+}
+
 void colsum_finish(const float* ws, int rows, int D, float* out0, float* out1, cudaStream_t st) {
   colsum_finish_kernel<<<(D + 31) / 32, 256, 0, st>>>(ws, rows, D, out0, out1);
 }

@@ -193,8 +193,16 @@ class _LinearAdd(torch.autograd.Function):
             else:
                 dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = g.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+            db = _bias_grad(g).to(ctx.bias_dtype)
         return dx, dw, db, (dy if ctx.needs_input_grad[3] else None)
+
+
+def _bias_grad(g: Tensor) -> Tensor:
+    """fp32 column sums of the output gradient [rows, features]."""
+    if g.is_cuda and g.dtype in (torch.bfloat16, torch.float16) and g.dim() == 2 and g.is_contiguous():
+        _bump()
+        return _C().colsum(g)
+    return g.sum(0, dtype=torch.float32)
 
 
 def linear_add(x: Tensor, w: Tensor, b: Optional[Tensor], addend: Tensor) -> Tensor:
@@ -251,7 +259,7 @@ class _Linear(torch.autograd.Function):
             else:
                 dw, _ = gemm(g, x2, None, None, a_mn=True, b_mn=True)   # [M, N]^T x [M, K] -> [N, K]
         if ctx.has_bias and ctx.needs_input_grad[2]:
-            db = g.sum(0, dtype=torch.float32).to(ctx.bias_dtype)
+            db = _bias_grad(g).to(ctx.bias_dtype)
         return dx, dw, db, None
 
 

@@ -1022,3 +1022,17 @@ def test_attention_backward_with_recomputed_probabilities_matches_kept_ones():
         cuda_ops.set_attention_recompute_scores(False)
     for name, a, b in zip(("out", "dq", "dk", "dv"), res[0], res[1]):
         assert torch.equal(a, b), f"{name} differs: {(a.float() - b.float()).abs().max().item()}"
+
+
+@pytest.mark.parametrize("M,N", [(4096, 8192), (300, 1024), (37, 264), (5, 16384)])
+def test_bias_gradient_column_sums(M, N):
+    """The bias gradient of the linear layers: fp32 column sums of a bf16 matrix through per-CTA partial rows
+    (the last shape is wider than the kernel covers and takes the library reduction)."""
+    from megalodon_b200.ops import cuda_ops
+    torch.manual_seed(2)
+    g = torch.randn(M, N, device=_dev()).bfloat16()
+    got = cuda_ops._bias_grad(g)
+    ref = g.double().sum(0)
+    assert got.dtype == torch.float32 and got.shape == (N,)
+    err = (got.double() - ref).abs().max().item()
+    assert err < 1e-3 * max(1.0, M ** 0.5), err
