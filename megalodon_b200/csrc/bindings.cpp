@@ -271,6 +271,16 @@ Tensor swiglu_fwd(const Tensor& a, const Tensor& b) {
   return out;
 }
 
+Tensor silu_bwd(const Tensor& g, const Tensor& a) {
+  check_cuda_contig(g, "g");
+  check_cuda_contig(a, "a");
+  TORCH_CHECK(g.numel() == a.numel() && g.scalar_type() == a.scalar_type(), "silu_bwd: g and a must match");
+  c10::cuda::CUDAGuard guard(a.device());
+  Tensor da = torch::empty_like(a);
+  mb::silu_bwd(g.data_ptr(), a.data_ptr(), da.data_ptr(), a.numel(), dtype_code(a), stream());
+  return da;
+}
+
 std::tuple<Tensor, Tensor> swiglu_bwd(const Tensor& g, const Tensor& a, const Tensor& b) {
   check_cuda_contig(g, "g");
   c10::cuda::CUDAGuard guard(a.device());
@@ -951,6 +961,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("cema_bwd", checked(&cema_bwd));
   m.def("swiglu_fwd", checked(&swiglu_fwd));
   m.def("swiglu_bwd", checked(&swiglu_bwd));
+  m.def("silu_bwd", checked(&silu_bwd));
   m.def("rotary", checked(&rotary));
   m.def("qk_rotary_fwd", checked(&qk_rotary_fwd));
   m.def("qk_rotary_bwd", checked(&qk_rotary_bwd));

@@ -49,6 +49,23 @@ __global__ void swiglu_bwd_kernel(const T* __restrict__ g, const T* __restrict__
   }
 }
 
+// da = g * silu'(a): the backward of a SiLU fused into a GEMM epilogue (two reads, one write)
+template <typename T>
+__global__ void silu_bwd_kernel(const T* __restrict__ g, const T* __restrict__ a, T* __restrict__ da, long long n,
+                                long long n8) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = tid; i < n8; i += stride) {
+    float gv[8], av[8], oa[8];
+    load8(g + 8 * i, gv);
+    load8(a + 8 * i, av);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oa[j] = gv[j] * silu_grad_f(av[j]);
+    store8(da + 8 * i, oa);
+  }
+  for (long long i = 8 * n8 + tid; i < n; i += stride) da[i] = from_f<T>(to_f(g[i]) * silu_grad_f(to_f(a[i])));
+}
+
 // x [rows, H, Dh]; position of a row is row % L; freqs [L, Dh/2] (cos, sin)
 template <typename T>
 __global__ void rotary_kernel(const T* __restrict__ x, const float2* __restrict__ freqs, T* __restrict__ out,
@@ -310,6 +327,13 @@ void swiglu_fwd(const void* a, const void* b, void* out, long long n, int dtype,
   const long long n8 = (aligned32(a) && aligned32(b) && aligned32(out)) ? n / 8 : 0;
   MB_DISPATCH_DTYPE(dtype, (swiglu_fwd_kernel<scalar_t><<<ew_grid(std::max(n8, n - 8 * n8)), 256, 0, st>>>(
                                (const scalar_t*)a, (const scalar_t*)b, (scalar_t*)out, n, n8)));
+}
+
+void silu_bwd(const void* g, const void* a, void* da, long long n, int dtype, cudaStream_t st) {
+  if (n == 0) return;
+  const long long n8 = (aligned32(g) && aligned32(a) && aligned32(da)) ? n / 8 : 0;
+  MB_DISPATCH_DTYPE(dtype, (silu_bwd_kernel<scalar_t><<<ew_grid(std::max(n8, n - 8 * n8)), 256, 0, st>>>(
+                               (const scalar_t*)g, (const scalar_t*)a, (scalar_t*)da, n, n8)));
 }
 
 void swiglu_bwd(const void* g, const void* a, const void* b, void* da, void* db, long long n, int dtype,

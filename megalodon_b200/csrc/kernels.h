@@ -59,6 +59,7 @@ void cema_bwd(const void* dy, const void* x, const float* p, const float* q, con
 
 // ---- element-wise (elementwise_kernels.cu)
 void swiglu_fwd(const void* a, const void* b, void* out, long long n, int dtype, cudaStream_t st);
+void silu_bwd(const void* g, const void* a, void* da, long long n, int dtype, cudaStream_t st);
 void swiglu_bwd(const void* g, const void* a, const void* b, void* da, void* db, long long n, int dtype,
                 cudaStream_t st);
 void rotary_apply(const void* x, const float* freqs, void* out, long long rows, int L, int H, int Dh,

@@ -270,22 +270,9 @@ def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: Optional[str] 
 
 
 def silu_bwd(g: Tensor, pre: Tensor) -> Tensor:
-    """g * silu'(pre) through the SwiGLU-backward kernel (b = 1 gives da = g silu'(a))."""
+    """g * silu'(pre): two reads and one write."""
     _bump()
-    ones = _ones_like_cache(pre)
-    da, _ = _C().swiglu_bwd(g.contiguous(), pre.contiguous(), ones)
-    return da
-
-
-_ONES = {}
-
-
-def _ones_like_cache(t: Tensor) -> Tensor:
-    key = (t.device, t.dtype, t.numel())
-    if key not in _ONES:
-        _ONES.clear()
-        _ONES[key] = torch.ones(t.numel(), dtype=t.dtype, device=t.device)
-    return _ONES[key].view(t.shape)
+    return _C().silu_bwd(g.contiguous(), pre.contiguous())
 
 
 class _SwiGLU(torch.autograd.Function):
