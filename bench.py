@@ -151,6 +151,7 @@ class ClockSampler:
         self.index = index
         self.rows = []
         self.proc = None
+        self.since = 0.0
 
     def start(self):
         try:
@@ -163,7 +164,15 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            if time.time() >= self.since:
+                self.rows.append([c.strip() for c in line.split(",")])
+
+    def count_from_now(self):
+        """Drop what was sampled so far: the sampler is started during the warm-up (the start of the
+        `nvidia-smi` process and its first driver queries stay out of the timed steps) and only samples
+        taken inside the timed regions are reported."""
+        self.since = time.time()
+        self.rows.clear()
 
     def stop(self):
         if self.proc is not None:
@@ -374,24 +383,43 @@ def run(args):
             torch.cuda.synchronize()
             check_peers()
 
+    # The last two warm-up steps are enqueued back to back like the steps of the first timed region (no
+    # host synchronisation between them): with side streams (N > 1) the caching allocator only reaches its
+    # steady state once the host runs ahead of the device - blocks released on another stream are not yet
+    # reusable - and that one-time growth (0.1 - 0.5 s) belongs to the warm-up, not to a timed step.
+    synced = max(1, args.warmup - 2)
+    tail = None
+    sampler = ClockSampler(local_rank)
     for i in range(args.warmup):
         x, y = next(data)
-        last = step(x, y, True)
-        torch.cuda.synchronize()
-        check_peers()
-        dog.progress(f"warm-up step {i} done, loss {last:.4f}")
-        if peer and os.environ.get("MEGALODON_B200_BENCH_FAIL_AT") == f"{rank}:{i}":
-            # failure drill, made on the host between two steps (nothing of this rank in flight): this rank
-            # raises, the others find out when their next bounded peer wait runs out
-            raise RuntimeError(f"injected host failure on rank {rank} after warm-up step {i}")
+        if i == args.warmup - 1:
+            sampler.start()
+        if i < synced:
+            last = step(x, y, True)
+            torch.cuda.synchronize()
+            check_peers()
+            dog.progress(f"warm-up step {i} done, loss {last:.4f}")
+            if peer and os.environ.get("MEGALODON_B200_BENCH_FAIL_AT") == f"{rank}:{i}":
+                # failure drill, made on the host between two steps (nothing of this rank in flight): this
+                # rank raises, the others find out when their next bounded peer wait runs out
+                raise RuntimeError(f"injected host failure on rank {rank} after warm-up step {i}")
+        else:
+            tail = step(x.cuda(), y.cuda(), False)
+            dog.progress(f"warm-up step {i} enqueued")
+    torch.cuda.synchronize()
+    check_peers()
+    if tail is not None:
+        last = tail.item()
+        dog.progress(f"warm-up done, loss {last:.4f}")
 
-    sampler = ClockSampler(local_rank)
-    sampler.start()
+    if sampler.proc is None:
+        sampler.start()
 
     # ---- region 1: batch resident on the device
     x, y = next(data)
     xd, yd = x.cuda(), y.cuda()
     barrier()
+    sampler.count_from_now()
     launches0 = cuda_ops.count_launches()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     marks = []           # per step: events at the phase boundaries (recording an event costs no device time)
