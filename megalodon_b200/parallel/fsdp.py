@@ -484,11 +484,22 @@ class FullyShardedDataParallel(nn.Module):
         nothing is zeroed when the unit's gradients leave (`_zero_unwritten`).  Only the gaps between
         parameters and the padding at the end are cleared here."""
         if self._flat_grad is None:
-            self._flat_grad = torch.empty(self._numel_padded, dtype=self._full.dtype, device=self._full.device)
+            arena = getattr(self, "_grad_arena", None)
+            if arena is not None and self.flat_param._grad_shard is None and self.flat_param.grad is None:
+                # peer-mapped home of this unit's gradient (chunk-group all-reduce in place); a second
+                # backward before the optimiser step finds the first gradient still there and takes
+                # ordinary memory instead
+                region, off, nbytes = arena
+                self._flat_grad = region.view(off, nbytes, self._full.dtype)[:self._numel_padded]
+            else:
+                self._flat_grad = torch.empty(self._numel_padded, dtype=self._full.dtype, device=self._full.device)
             self._grad_unwritten = {id(info) for info in self._infos}
             for a, b in self._grad_gaps():
                 self._flat_grad[a:b].zero_()
         return self._flat_grad
+
+    def _full_dtype_size(self) -> int:
+        return torch.empty(0, dtype=self.compute_dtype if self.mixed_precision else torch.float32).element_size()
 
     def _grad_gaps(self):
         gaps = getattr(self, "_grad_gap_list", None)
@@ -744,7 +755,20 @@ class FullyShardedDataParallel(nn.Module):
         if fused is not None:
             # one pass over peer memory: sum over the chunk group + this rank's share of |g|^2
             acc = torch.zeros((), dtype=torch.float64, device=self.compute_device)
-            fused.all_reduce_(self._grad_tensors(), sumsq=acc)
+            rest = []
+            for u in self._units():
+                p = u.flat_param
+                g, arena = p._grad_shard, getattr(u, "_grad_arena", None)
+                if g is not None and arena is not None and g.data_ptr() == arena[0].local.data_ptr() + arena[1]:
+                    # the gradient already lives in peer-mapped memory: reduced where it is (the slot's
+                    # padding beyond the unit was zeroed when the region was made and nothing writes it)
+                    fused.all_reduce_arena_(arena[1], arena[2], g.dtype, sumsq=acc)
+                elif g is not None:
+                    rest.append(g)
+                if p.grad is not None:
+                    rest.append(p.grad)
+            if rest:
+                fused.all_reduce_(rest, sumsq=acc)
             self._fused_sumsq = acc
             self._fused_sumsq_kind = "allreduce"
             return

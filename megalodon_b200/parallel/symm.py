@@ -444,6 +444,27 @@ class SymmetricAllReduce:
                 self._barrier()                      # every rank has pushed its reduced slice
                 part.copy_(stage[:part.numel()])
 
+    # ---- gradients that already live in peer-mapped memory (no copy-in / copy-out)
+    def attach_arena(self, arena: SymmetricRegion) -> None:
+        """`arena`: a region in which the caller keeps its gradient buffers at the same offsets on every
+        rank; `all_reduce_arena_` then reduces them where they are."""
+        self.arena = arena
+
+    @torch.no_grad()
+    def all_reduce_arena_(self, offset: int, nbytes: int, dtype: torch.dtype,
+                          sumsq: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+        """Sum bytes [offset, offset + nbytes) of the arena over the group in place (every rank reduces one
+        slice from all peers and pushes the result to all of them), with this rank's share of the squared
+        norm added to `sumsq`.  `nbytes` must be a multiple of 16 * world.  Two barriers, no copies."""
+        from ..ops._ext import require
+        from ..ops.cuda_ops import _DT
+        assert nbytes % (16 * self.region.world) == 0 and offset % 16 == 0
+        self.arena.check_range(offset, nbytes, align=16)
+        bufs = self.arena.ptr_table_at(offset, nbytes)
+        self._barrier()                      # every rank's backward has written this range
+        require().allreduce_sumsq(bufs, self.region.rank, nbytes, scale, sumsq, _DT[dtype], self._abort.dev)
+        self._barrier()                      # every rank has pushed its reduced slice
+
     def check(self) -> None:
         self._abort.check()
 
@@ -751,6 +772,21 @@ def enable_peer_transport(model, max_batch: int, *, n_slots: int = 8, allreduce_
         ar_region = SymmetricRegion(SymmetricAllReduce.bytes_needed(bucket, cp), group, device)
         reducer = SymmetricAllReduce(ar_region, bucket, timeout_s=timeout_s)
         model._symm_allreduce = reducer
+        if (getattr(model, "world_size", 1) == 1 and hasattr(model, "_units")
+                and getattr(model, "mixed_precision", False)
+                and os.environ.get("MEGALODON_B200_GRAD_ARENA", "1") == "1"):
+            # no data parallelism inside the chunk group: the flat gradient of every unit IS what gets
+            # all-reduced, so it is kept in peer-mapped memory and reduced where it is
+            model._lazy_init()
+            units = list(model._units())
+            step = 16 * cp
+            sizes = [_round_up(u._numel_padded * u._full_dtype_size(), max(256, step)) for u in units]
+            arena = SymmetricRegion(sum(sizes), group, device)
+            off = 0
+            for u, nb in zip(units, sizes):
+                u._grad_arena = (arena, off, nb)
+                off += nb
+            reducer.attach_arena(arena)
     return mailbox, reducer
 
 
