@@ -57,3 +57,44 @@ def test_chunk_group_sum_invalidates_the_norm_of_the_reduce_scatter():
     with mock.patch.object(dist, "all_reduce", lambda t, group=None, op=None: t.mul_(2.0)):
         unit.grad_all_reduce()
     assert unit._fused_sumsq is None
+
+
+def test_flat_gradient_is_not_zero_filled_but_unused_parameters_and_gaps_end_up_zero():
+    """The flat gradient buffer starts as uninitialised memory: the first contribution to a parameter is
+    written, later ones are added, a parameter that received nothing and the gaps / padding between
+    parameters are cleared before the gradients leave the unit."""
+    from megalodon_b200.parallel.fsdp import FullyShardedDataParallel
+
+    class Two(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.used = nn.Linear(40, 24)
+            self.unused = nn.Linear(24, 7)          # 7 * 24 + 7 elements: leaves an odd-sized tail
+
+        def forward(self, x):
+            return self.used(x) + self.used(x * 0.5)        # the weight is used twice: write, then add
+
+    torch.manual_seed(0)
+    mod = Two()
+    ref = Two()
+    ref.load_state_dict(mod.state_dict())
+    unit = FullyShardedDataParallel(mod, mixed_precision=False, materialize_fp32_grads=False)
+    x = torch.randn(8, 40)
+    for _ in range(2):                                       # two iterations: the bookkeeping resets
+        unit.zero_grad()
+        unit(x).pow(2).sum().backward()
+        unit.finish_backward()
+        ref.zero_grad()
+        ref(x).pow(2).sum().backward()
+        shard = unit.flat_param._grad_shard
+        assert torch.isfinite(shard).all()
+        covered = torch.zeros(shard.numel(), dtype=torch.bool)
+        for info in unit._infos:
+            got = shard[info.offset:info.offset + info.numel].view(info.shape)
+            covered[info.offset:info.offset + info.numel] = True
+            want = dict(ref.named_parameters())[info.name].grad
+            if want is None:
+                assert bool((got == 0).all()), info.name
+            else:
+                assert torch.allclose(got, want, atol=1e-5, rtol=1e-5), info.name
+        assert bool((shard[~covered] == 0).all())
