@@ -37,6 +37,21 @@ def _cpu_native_ok(x: Tensor, *others) -> bool:
     return True
 
 
+def _cpu_native_autograd_ok(x: Tensor, *others) -> bool:
+    """fp32 host tensors that take part in autograd: forward and backward both run in C++
+    (`ops/cpu_native.py`).  MEGALODON_B200_CPU_NATIVE_AUTOGRAD=0 keeps the PyTorch statements."""
+    import os
+    if x.is_cuda or x.dtype != torch.float32 or not have_ext():
+        return False
+    if os.environ.get("MEGALODON_B200_CPU_NATIVE_AUTOGRAD", "1") != "1":
+        return False
+    for t in others:
+        if t is not None and torch.is_tensor(t) and (t.is_cuda or t.dtype not in (torch.float32, torch.complex64)):
+            return False
+    return torch.is_grad_enabled() and any(t is not None and torch.is_tensor(t) and t.requires_grad
+                                           for t in (x,) + others)
+
+
 # ------------------------------------------------------------------ GEMM-shaped
 def linear(x: Tensor, w: Tensor, b: Optional[Tensor] = None, act: Optional[str] = None) -> Tensor:
     """y = act(x @ w^T + b); `act` is None or "silu"."""
@@ -116,6 +131,10 @@ def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask=
         G = x.shape[-1] if num_groups is None else num_groups
         return require_ext().cpu_timestep_norm_fwd(x, prev_count, prev_mean, prev_var, gamma, float(gamma_offset),
                                                    beta, padding_mask, G, float(eps))
+    if _cpu_native_autograd_ok(x, prev_mean, prev_var, gamma, beta) and prev_count is not None:
+        from . import cpu_native
+        return cpu_native.timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, padding_mask,
+                                        x.shape[-1] if num_groups is None else num_groups, eps, gamma_offset)
     return reference.timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta,
                                    padding_mask, num_groups, eps, gamma_offset)
 
@@ -127,6 +146,9 @@ def sequence_norm(x, gamma, beta, padding_mask=None, num_groups=None, eps: float
     if _cpu_native_ok(x, gamma, beta):
         return require_ext().cpu_sequence_norm_fwd(x, gamma, beta, padding_mask, int(num_groups or 0), float(eps),
                                                    bool(length_last))
+    if _cpu_native_autograd_ok(x, gamma, beta):
+        from . import cpu_native
+        return cpu_native.sequence_norm(x, gamma, beta, padding_mask, int(num_groups or 0), eps, length_last)
     return reference.sequence_norm(x, gamma, beta, padding_mask, num_groups, eps, length_last)
 
 
@@ -138,6 +160,9 @@ def ema_parameters(p, q, gamma, hx, length: int):
             t is not None and t.requires_grad for t in (p, q, gamma, hx)))):
         k, b = require_ext().cpu_ema_parameters_fwd(p, q, gamma, hx, int(length))
         return k, b
+    if _cpu_native_autograd_ok(p, q, gamma, hx):
+        from . import cpu_native
+        return cpu_native.ema_parameters(p, q, gamma, hx, length)
     return reference.ema_parameters(p, q, gamma, hx, length)
 
 
@@ -146,6 +171,9 @@ def ema_hidden(x, p, q, hx):
         return _cuda().ema_hidden(x, p, q, hx)
     if _cpu_native_ok(x, p, q, hx):
         return require_ext().cpu_ema_hidden_fwd(x, p, q, hx)
+    if _cpu_native_autograd_ok(x, p, q, hx):
+        from . import cpu_native
+        return cpu_native.ema_hidden(x, p, q, hx)
     return reference.ema_hidden(x, p, q, hx)
 
 

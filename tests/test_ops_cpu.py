@@ -190,3 +190,53 @@ def test_cpu_ema_hidden_backward(with_h):
         a2 = torch.view_as_real(a) if a.is_complex() else a
         b2 = torch.view_as_real(b_) if b_.is_complex() else b_
         assert torch.allclose(a2.double(), b2.double(), atol=2e-4, rtol=2e-4), (name, (a2 - b2).abs().max())
+
+
+# ---------------------------------------------------------------------------- autograd over the C++ host code
+@needs_ext
+def test_cpu_autograd_runs_native_forward_and_backward():
+    """fp32 host tensors with gradients go through `ops/cpu_native.py` (C++ forward and backward); values
+    and gradients equal autograd through the PyTorch statements of `ops/reference.py`."""
+    from megalodon_b200 import ops
+    from megalodon_b200.ops import cpu_native
+
+    def close(a, b, what):
+        a2 = torch.view_as_real(a) if a.is_complex() else a
+        b2 = torch.view_as_real(b) if b.is_complex() else b
+        assert torch.allclose(a2.double(), b2.double(), atol=3e-4, rtol=3e-4), (what, (a2 - b2).abs().max())
+
+    torch.manual_seed(7)
+    B, L, H, G = 2, 37, 32, 8
+    x = torch.randn(B, L, H)
+    cnt = torch.tensor([0, 3])
+    pm, pv = torch.randn(B, G) * 0.1, torch.rand(B, G) + 0.5
+    gm, bt = torch.randn(H) * 0.1, torch.randn(H) * 0.1
+    mask = torch.zeros(B, L, dtype=torch.bool)
+    mask[1, 30:] = True
+    gy, gmean, gvar = torch.randn(B, L, H), torch.randn(B, G), torch.randn(B, G)
+    res = []
+    for fn in (reference.timestep_norm, ops.timestep_norm):
+        lv = [t.clone().requires_grad_() for t in (x, pm, pv, gm, bt)]
+        y, c, m, v = fn(lv[0], cnt, lv[1], lv[2], lv[3], lv[4], mask, G, 1e-5, 1.0)
+        ((y * gy).sum() + (m * gmean).sum() + (v * gvar).sum()).backward()
+        res.append([y, m, v] + [t.grad for t in lv])
+    assert res[1][0].grad_fn is not None and "TimestepNorm" in type(res[1][0].grad_fn).__name__
+    for i, (a, b) in enumerate(zip(*res)):
+        close(a, b, f"timestep_norm {i}")
+
+    D, N, Lk = 6, 4, 29
+    p, q, gamma = _ema_coeffs(D, N)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2))
+    dk, db = torch.randn(D, Lk), torch.randn(B, D, Lk)
+    xx, g = torch.randn(B, D, Lk), torch.view_as_complex(torch.randn(B, D, N, 2))
+    res = []
+    for mod in (reference, ops):
+        lv = [t.clone().requires_grad_() for t in (p, q, gamma, hx, xx)]
+        k, b = mod.ema_parameters(lv[0], lv[1], lv[2], lv[3], Lk)
+        h = mod.ema_hidden(lv[4], lv[0], lv[1], lv[3])
+        ((k * dk).sum() + (b * db).sum()).backward(retain_graph=True)
+        h.backward(g)
+        res.append([k, b, h] + [t.grad for t in lv])
+    for i, (a, b_) in enumerate(zip(*res)):
+        close(a, b_, f"ema {i}")
+    assert cpu_native is not None
