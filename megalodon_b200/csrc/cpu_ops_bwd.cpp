@@ -308,9 +308,94 @@ std::tuple<Tensor, Tensor, Tensor, c10::optional<Tensor>> ema_hidden_bwd(const T
   return {dx.to(at::kFloat), dp_b.sum(0).to(at::kFloat), dq_b.sum(0).to(at::kComplexFloat), dh_o};
 }
 
+// Backward of the fused complex-EMA layer (cpu_ops.cpp: cema_fwd): h_t = q h_{t-1} + p x_t,
+// y_t = Re(sum_n gamma_n h_t,n) + omega x_t, last state h_L returned.  dy [B, L, D]; dh_last [B, D, N] complex
+// or undefined; x [B, L, D] fp32; p [D, N]; q, gamma [D, N] complex64; omega [D]; hx [B, D, N] or undefined.
+// Gradients of complex tensors are d/dRe + i d/dIm, as autograd hands them around.  The adjoint of the state
+// obeys lambda_t = conj(gamma) dy_t + conj(q) lambda_{t+1} (lambda_L also takes dh_last), and
+//   dx_t = sum_n p_n Re(lambda_t,n) + omega dy_t      dp_n = sum_t x_t Re(lambda_t,n)
+//   dq_n = sum_t lambda_t,n conj(h_{t-1},n)           dgamma_n = sum_t dy_t conj(h_t,n)
+//   domega = sum_t dy_t x_t                           dhx_n = conj(q_n) lambda_1,n
+// The states of one (batch, feature) row are kept from a forward sweep (L * N complex doubles).
+// Returns (dx, dp, dq, dgamma, domega, dhx or undefined).
+std::tuple<Tensor, Tensor, Tensor, Tensor, Tensor, c10::optional<Tensor>> cema_bwd(
+    const Tensor& dy, const c10::optional<Tensor>& dh_last, const Tensor& x, const Tensor& p, const Tensor& q,
+    const Tensor& gamma, const Tensor& omega, const c10::optional<Tensor>& hx) {
+  TORCH_CHECK(!x.is_cuda() && x.dim() == 3 && x.scalar_type() == at::kFloat, "x must be a CPU fp32 [B, L, D] tensor");
+  const Tensor xc = x.contiguous(), dyc = dy.to(at::kFloat).contiguous();
+  const int64_t B = x.size(0), L = x.size(1), D = x.size(2);
+  const Tensor pc = p.reshape({D, -1}).to(at::kDouble).contiguous();
+  const int64_t N = pc.size(1);
+  const Tensor qc = q.reshape({D, N}).to(at::kComplexDouble).contiguous();
+  const Tensor gc = gamma.reshape({D, N}).to(at::kComplexDouble).contiguous();
+  const Tensor oc = omega.reshape({D}).to(at::kDouble).contiguous();
+  Tensor hc, gl;
+  if (hx.has_value()) hc = hx->to(at::kComplexDouble).contiguous();
+  if (dh_last.has_value()) gl = dh_last->to(at::kComplexDouble).contiguous();
+  Tensor dx = torch::empty({B, L, D}, xc.options());
+  Tensor dp = torch::zeros({D, N}, pc.options());
+  Tensor dq = torch::zeros({D, N}, qc.options());
+  Tensor dg = torch::zeros({D, N}, qc.options());
+  Tensor dom = torch::zeros({D}, oc.options());
+  Tensor dhx;
+  if (hc.defined()) dhx = torch::empty({B, D, N}, qc.options());
+  const float* xp = xc.data_ptr<float>();
+  const float* dyp = dyc.data_ptr<float>();
+  float* dxp = dx.data_ptr<float>();
+  const double* pp = pc.data_ptr<double>();
+  const auto* qp = reinterpret_cast<const cdouble*>(qc.data_ptr<c10::complex<double>>());
+  const auto* gp = reinterpret_cast<const cdouble*>(gc.data_ptr<c10::complex<double>>());
+  const double* op = oc.data_ptr<double>();
+  const cdouble* hp = hc.defined() ? reinterpret_cast<const cdouble*>(hc.data_ptr<c10::complex<double>>()) : nullptr;
+  const cdouble* glp = gl.defined() ? reinterpret_cast<const cdouble*>(gl.data_ptr<c10::complex<double>>()) : nullptr;
+  double* dpp = dp.data_ptr<double>();
+  auto* dqp = reinterpret_cast<cdouble*>(dq.data_ptr<c10::complex<double>>());
+  auto* dgp = reinterpret_cast<cdouble*>(dg.data_ptr<c10::complex<double>>());
+  double* domp = dom.data_ptr<double>();
+  cdouble* dhp = dhx.defined() ? reinterpret_cast<cdouble*>(dhx.data_ptr<c10::complex<double>>()) : nullptr;
+  // one feature per task: its parameter gradients are summed over the batch without races
+  at::parallel_for(0, D, 1, [&](int64_t lo, int64_t hi) {
+    std::vector<cdouble> hist((L + 1) * N), lam(N);
+    for (int64_t d = lo; d < hi; ++d) {
+      for (int64_t b = 0; b < B; ++b) {
+        const int64_t bd = b * D + d;
+        for (int64_t n = 0; n < N; ++n) hist[n] = hp != nullptr ? hp[bd * N + n] : cdouble(0.0, 0.0);
+        for (int64_t t = 0; t < L; ++t) {
+          const double xv = xp[(b * L + t) * D + d];
+          for (int64_t n = 0; n < N; ++n)
+            hist[(t + 1) * N + n] = qp[d * N + n] * hist[t * N + n] + pp[d * N + n] * xv;
+        }
+        for (int64_t n = 0; n < N; ++n) lam[n] = glp != nullptr ? glp[bd * N + n] : cdouble(0.0, 0.0);
+        for (int64_t t = L - 1; t >= 0; --t) {
+          const double g = dyp[(b * L + t) * D + d];
+          const double xv = xp[(b * L + t) * D + d];
+          double acc = op[d] * g;
+          for (int64_t n = 0; n < N; ++n) {
+            const int64_t i = d * N + n;
+            lam[n] += std::conj(gp[i]) * g;                       // lambda_{t+1}: adjoint of h_{t+1} (1-based)
+            acc += pp[i] * lam[n].real();
+            dpp[i] += xv * lam[n].real();
+            dqp[i] += lam[n] * std::conj(hist[t * N + n]);
+            dgp[i] += g * std::conj(hist[(t + 1) * N + n]);
+            lam[n] = std::conj(qp[i]) * lam[n];                   // carried to the previous step
+          }
+          dxp[(b * L + t) * D + d] = (float)acc;
+          domp[d] += g * xv;
+        }
+        if (dhp != nullptr)
+          for (int64_t n = 0; n < N; ++n) dhp[bd * N + n] = lam[n];
+      }
+    }
+  });
+  c10::optional<Tensor> dhx_o;
+  if (dhx.defined()) dhx_o = dhx.to(at::kComplexFloat);
+  return {dx, dp.to(at::kFloat), dq.to(at::kComplexFloat), dg.to(at::kComplexFloat), dom.to(at::kFloat), dhx_o};
+}
+
 }  // namespace mb_cpu
 
 void register_cpu_bwd_ops(pybind11::module& m) {
+  m.def("cpu_cema_bwd", &mb_cpu::cema_bwd);
   m.def("cpu_timestep_norm_bwd", &mb_cpu::timestep_norm_bwd);
   m.def("cpu_sequence_norm_bwd", &mb_cpu::sequence_norm_bwd);
   m.def("cpu_ema_parameters_bwd", &mb_cpu::ema_parameters_bwd);

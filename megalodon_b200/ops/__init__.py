@@ -196,6 +196,9 @@ def cema(x, p, q, gamma, omega, hx, compute_last_state: bool):
     if _cpu_native_ok(x, p, q, gamma, omega, hx):
         y, h = require_ext().cpu_cema_fwd(x, p, q, gamma, omega, hx)
         return y, (h if compute_last_state else None)
+    if _cpu_native_autograd_ok(x, p, q, gamma, omega, hx):
+        from . import cpu_native
+        return cpu_native.cema(x, p, q, gamma, omega, hx, compute_last_state)
     return reference.cema(x, p, q, gamma, omega, hx, compute_last_state)
 
 

@@ -105,6 +105,33 @@ class _EmaHidden(torch.autograd.Function):
         return dx, dp, dq, (dh if ctx.has_h else None)
 
 
+class _Cema(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, p, q, gamma, omega, hx):
+        x, p, q, gamma, omega, hx = (_c(t) for t in (x, p, q, gamma, omega, hx))
+        y, h = _require().cpu_cema_fwd(x, p, q, gamma, omega, hx)
+        ctx.save_for_backward(x, p, q, gamma, omega, *(() if hx is None else (hx,)))
+        ctx.has_h = hx is not None
+        ctx.shapes = (p.shape, q.shape, gamma.shape, omega.shape)
+        return y, h
+
+    @staticmethod
+    def backward(ctx, dy, dh):
+        saved = ctx.saved_tensors
+        x, p, q, gamma, omega = saved[:5]
+        hx = saved[5] if ctx.has_h else None
+        dy = torch.zeros_like(x) if dy is None else dy.contiguous()
+        dx, dp, dq, dg, dom, dhx = _require().cpu_cema_bwd(dy, None if dh is None else dh.contiguous(), x, p, q,
+                                                          gamma, omega, hx)
+        ps, qs, gs, os_ = ctx.shapes
+        return dx, dp.reshape(ps), dq.reshape(qs), dg.reshape(gs), dom.reshape(os_), (dhx if ctx.has_h else None)
+
+
+def cema(x, p, q, gamma, omega, hx, compute_last_state: bool):
+    y, h = _Cema.apply(x, p, q, gamma, omega, hx)
+    return y, (h if compute_last_state else None)
+
+
 def timestep_norm(x, prev_count, prev_mean, prev_var, gamma, beta, mask, groups, eps, gamma_offset):
     return _TimestepNorm.apply(x, prev_count, prev_mean, prev_var, gamma, beta, mask, groups, eps, gamma_offset)
 

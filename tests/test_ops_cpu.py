@@ -240,3 +240,35 @@ def test_cpu_autograd_runs_native_forward_and_backward():
     for i, (a, b_) in enumerate(zip(*res)):
         close(a, b_, f"ema {i}")
     assert cpu_native is not None
+
+
+@needs_ext
+@pytest.mark.parametrize("with_h", [True, False])
+def test_cpu_cema_layer_native_autograd(with_h):
+    """The fused complex-EMA layer on the host: C++ forward and backward against autograd through the
+    explicit recurrence of `reference.cema_scan` (values, every gradient, the last state and its gradient)."""
+    from megalodon_b200 import ops
+    torch.manual_seed(8)
+    B, L, D, N = 2, 45, 6, 4
+    p, q, gamma = _ema_coeffs(D, N)
+    p, q, gamma = p.view(D, N, 1), q.view(D, N, 1), gamma.view(D, N, 1)
+    omega = torch.randn(D, 1)
+    x = torch.randn(B, L, D)
+    hx = torch.view_as_complex(torch.randn(B, D, N, 2)) if with_h else None
+    gy, gh = torch.randn(B, L, D), torch.view_as_complex(torch.randn(B, D, N, 2))
+    res = []
+    for native in (False, True):
+        lv = [t.clone().requires_grad_() for t in (x, p, q, gamma, omega)] + ([hx.clone().requires_grad_()] if with_h else [])
+        h0 = lv[5] if with_h else None
+        if native:
+            y, h = ops.cema(lv[0], lv[1], lv[2], lv[3], lv[4], h0, True)
+            assert "Cema" in type(y.grad_fn).__name__
+        else:
+            y, h = reference.cema_scan(lv[0], lv[1], lv[2], lv[3], lv[4], h0)
+        ((y * gy).sum() + (torch.view_as_real(h) * torch.view_as_real(gh)).sum()).backward()
+        res.append([y, h] + [t.grad for t in lv])
+    names = ["y", "h", "dx", "dp", "dq", "dgamma", "domega", "dhx"]
+    for name, a, b in zip(names, *res):
+        a2 = torch.view_as_real(a) if a.is_complex() else a
+        b2 = torch.view_as_real(b) if b.is_complex() else b
+        assert torch.allclose(a2.double(), b2.double(), atol=3e-4, rtol=3e-4), (name, (a2 - b2).abs().max())
