@@ -98,6 +98,20 @@ def main() -> None:
     if cfg.extra.peer_transport and torch.cuda.is_available() and cfg.chunk_parallel_size > 1:
         from megalodon_b200.parallel.symm import enable_peer_transport
         enable_peer_transport(model, max_batch=cfg.batch_size)
+    elif (cfg.extra.peer_transport and torch.cuda.is_available() and get_data_parallel_world_size() > 1
+          and cfg.dtype != "fp32"):
+        # plain data parallelism: gradient reduce-scatter and parameter gathers through peer memory
+        from megalodon_b200.parallel.symm import enable_peer_gather, enable_peer_reduce_scatter
+        enable_peer_reduce_scatter(model)
+        enable_peer_gather(model)
+    if (cfg.extra.peer_transport and torch.cuda.is_available() and cfg.model_parallel_size > 1
+            and cfg.dtype != "fp32"):
+        # collectives of the tensor-parallel projections inside their GEMMs
+        from megalodon_b200.parallel.tp_comm import enable_tp_fused
+        local_len = cfg.seq_len // max(1, cfg.chunk_parallel_size)
+        if cfg.extra.seq_microbatch_chunks:
+            local_len = min(local_len, cfg.model.chunk_size * cfg.extra.seq_microbatch_chunks)
+        enable_tp_fused(model, max_tokens=cfg.batch_size * local_len)
     logger.info(model)
     optimizer, scheduler = build_optimizer(model, cfg.optim, cfg.steps, cfg.dtype)
     step = 0
