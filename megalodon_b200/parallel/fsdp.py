@@ -60,7 +60,6 @@ from collections import OrderedDict
 from enum import Enum, auto
 from typing import Any, Dict, Iterator, List, Optional, Tuple, Union
 
-import functools
 
 import torch
 import torch.distributed as dist
